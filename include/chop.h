@@ -1,0 +1,114 @@
+/* chop.h - C ABI of libchop_b200.so: plane-sweep cost volume (+ gradient) and manifold 3-D
+ * convolution for NVIDIA B200 (sm_100a).
+ *
+ * The entry points sit exactly where the reference project's TensorFlow OpKernels call their
+ * device functors: the caller (an OpKernel, a torch wrapper, a cgo/ctypes stub ...) validates
+ * nothing, owns every buffer, and passes raw DEVICE pointers plus a CUDA stream.  The library
+ *   - allocates nothing and keeps no global state (unless an entry point says otherwise),
+ *   - enqueues all work on the given stream and never synchronises,
+ *   - returns 0 on success, a negative chop_status for an invalid argument detected on the host
+ *     before any launch, or a positive cudaError_t value if a launch failed,
+ *   - never aborts and never throws across the boundary; it is re-entrant and thread-safe.
+ * There is no CPU fallback: without a CUDA device every compute entry point fails.
+ *
+ * Tensor layouts are the reference's (row-major, channels last):
+ *   ref [B,H,W,C]   src [B,N,Hs,Ws,C]   Rs [B,N,3,3]   Ts [B,N,3]
+ *   CostVolume   : base_plane [B,H,W,1], offsets [B,D]   -> cost [B,H,W,D,C], mask [B,H,W,D,1|C]
+ *   CostVolumeV2 : depth_grid [B,H,W,D]                  -> cost [B,H,W,D,G], mask [B,H,W,D,1|G]
+ *   CostAggregate: base_plane, offsets                   -> cost [B,H,W,D],   mask [B,H,W,D]
+ * (mask is int32; its last dimension is 1 for MEAN and C|G for MIN).
+ */
+#ifndef CHOP_H_
+#define CHOP_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum chop_status {
+  CHOP_OK = 0,
+  CHOP_ERR_NULL = -1,         /* a required pointer is NULL */
+  CHOP_ERR_SHAPE = -2,        /* a dimension is < 1, inconsistent, or too large for 32-bit texel indices */
+  CHOP_ERR_ATTR = -3,         /* unknown kind / dtype / reduce method, groups does not divide C ... */
+  CHOP_ERR_UNSUPPORTED = -4,  /* valid for the reference but not implemented here */
+  CHOP_ERR_ALIGN = -5,        /* a pointer is not aligned for the element type */
+  CHOP_ERR_WORKSPACE = -6,    /* workspace missing or too small */
+  CHOP_ERR_RANGE = -7         /* depth range outside [0, D] */
+} chop_status;
+
+typedef enum chop_dtype {
+  CHOP_F32 = 0,  /* everything float32 (reference dtype) */
+  CHOP_F64 = 1,  /* everything float64 (reference dtype) */
+  CHOP_BF16 = 2  /* ref/src (cost volume) or images/filters (conv) in bfloat16; depths, cameras,
+                    cost, upstream gradients and all gradient outputs float32 (superset of the
+                    reference, which accepts float32/float64 only) */
+} chop_dtype;
+
+typedef enum chop_kind {
+  CHOP_COST_VOLUME = 1,    /* op CostVolume / CostVolumeGrad */
+  CHOP_COST_VOLUME_V2 = 2, /* op CostVolumeV2 / CostVolumeGradV2 */
+  CHOP_COST_AGGREGATE = 3  /* op CostAggregate / CostAggregateGrad */
+} chop_kind;
+
+typedef enum chop_reduce { CHOP_REDUCE_MEAN = 0, CHOP_REDUCE_MIN = 1 } chop_reduce;
+
+/* flags */
+#define CHOP_FLAG_STRICT 1u     /* forward: every floating operation is the single correctly rounded IEEE
+                                   operation of the reference source, in source order (no fused
+                                   multiply-add), so cost is reproducible bit for bit.  MIN always runs
+                                   this way because its arg-indices must be exact. */
+#define CHOP_FLAG_ACCUMULATE 2u /* backward: add into ref_grad/src_grad/base_plane_grad instead of
+                                   zero-filling them first (used when a batch item is split by depth
+                                   range over several calls). */
+
+/* Describes one cost-volume call.  Replaces the scalar argument list of the reference functors
+ * CostVolumeFunctor / CostVolumeGradFunctor (custom_helper_op/cc/kernels/cost_volume.h:37-132) and
+ * their v2 / aggregate twins (cost_volume_v2.h, cost_aggregate.h). */
+typedef struct chop_cv_desc {
+  int32_t kind;        /* chop_kind */
+  int32_t dtype;       /* chop_dtype */
+  int32_t reduce;      /* chop_reduce; attr reduce_method */
+  int32_t half_centor; /* attr half_centor (pixel centres at +0.5) */
+  int32_t groups;      /* attr groups (CostVolumeV2 only; must divide C) */
+  uint32_t flags;
+  int64_t B, H, W, C;  /* ref image */
+  int64_t D;           /* depth hypotheses = extent of every D-indexed tensor passed in */
+  int64_t N, Hs, Ws;   /* source views */
+  int64_t d_begin;     /* process depth planes [d_begin, d_end) only; d_end == 0 means D.  Planes */
+  int64_t d_end;       /* outside the range are neither read nor written.                         */
+} chop_cv_desc;
+
+/* Forward.  Replaces CostVolumeFunctor<GPUDevice,T,half_centor>::operator()
+ * (custom_helper_op/cc/kernels/cost_volume_kernels_gpu.cu.cc:289-335), CostVolumeV2Functor
+ * (cost_volume_kernels_gpu_v2.cu.cc:296-342) and CostAggregateFunctor.
+ * depth = base_plane (kinds 1,3) or depth_grid (kind 2); offsets is NULL for kind 2. */
+int chop_cost_volume_fwd(const chop_cv_desc *desc, const void *ref, const void *src, const void *depth,
+                         const void *offsets, const void *Rs, const void *Ts, void *cost, int32_t *mask,
+                         void *stream);
+
+/* Gradient.  Replaces CostVolumeGradFunctor::operator() including its zero fill of the outputs
+ * (cost_volume_kernels_gpu.cu.cc:590-655; v2 :614-679).  depth_grad has the shape of `depth`.
+ * There is no gradient for offsets, Rs, Ts (custom_helper_op/python/ops/custom_helper_ops.py:61). */
+int chop_cost_volume_bwd(const chop_cv_desc *desc, const void *ref, const void *src, const void *depth,
+                         const void *offsets, const void *Rs, const void *Ts, const void *cost_grad,
+                         const int32_t *mask, void *ref_grad, void *src_grad, void *depth_grad,
+                         void *stream);
+
+/* Text for a status returned by any entry point (negative: chop_status, positive: CUDA). */
+const char *chop_status_string(int status);
+
+/* Library version as major*10000 + minor*100 + patch. */
+int chop_version(void);
+
+/* Tuning knobs for experiments: "fwd_chunk", "bwd_chunk" (depth planes per warp work item, 0 =
+ * heuristic), "bwd_views" (source views per backward pass, 0 = heuristic).  Returns CHOP_ERR_ATTR
+ * for an unknown name.  Process-wide; not part of the reference surface. */
+int chop_set_tuning(const char *name, int value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CHOP_H_ */
