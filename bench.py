@@ -1,0 +1,403 @@
+#!/usr/bin/env python3
+"""Benchmark of the plane-sweep cost-volume hot path: forward + backward, voxel*views per second.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One step = one forward (CostVolume) plus one backward (CostVolumeGrad) over one batch of synthetic
+input.  A unit of work is one (b,h,w,d) voxel x one source view; units per step = B*H*W*D*N.
+At N GPUs every rank processes its own batch item of the workload (batch sharding, no collective
+in the data path): weak scaling.  `--shard depth` instead splits ONE item's depth range over the
+ranks and all-reduces the partial gradients (strong scaling; exercises the NCCL exchange).
+
+The line printed by rank 0 carries
+  value        device-timed throughput with inputs resident in HBM (CUDA events, max over ranks)
+  e2e          the same work through the public op functions from pinned HOST buffers, with every
+               host<->device copy inside the timed region
+  roofline     the dominant kernel against the measured HBM copy bandwidth
+  cpu_baseline the reference's kernel source compiled for the host cores (a bounded sample)
+`--impl reference` times only that CPU implementation (all host threads) and prints the same line.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+METRIC = "cost_volume_fwd_bwd_voxel_views_per_s"
+UNIT = "voxel*views/s"
+
+
+# ------------------------------------------------------------------------------------------------
+# workload description and algorithmic traffic
+# ------------------------------------------------------------------------------------------------
+def workload_dims(name):
+    from custom_helper_op_b200 import synth
+    c = dict(synth.CONFIGS[name])
+    return dict(kind=c["kind"], B=c["B"], N=c["V"] - 1, C=c["C"], H=c["H"], W=c["W"], D=c["D"],
+                G=c.get("groups", 1))
+
+
+def algorithmic_bytes(w, feat_bytes=4):
+    """Compulsory HBM traffic of one forward and one backward call: every tensor touched once,
+    gathers and atomics assumed to be served by L2."""
+    B, N, C, H, W, D = w["B"], w["N"], w["C"], w["H"], w["W"], w["D"]
+    Vx = B * H * W * D
+    Co = C if w["kind"] == 1 else w["G"]
+    F = (1 + N) * B * H * W * C * feat_bytes
+    P = 4 * (B * H * W + B * D) if w["kind"] == 1 else 4 * Vx
+    fwd = F + P + 4 * Vx * Co + 4 * Vx
+    bwd = 4 * Vx * Co + 4 * Vx + F + P + 4 * (1 + N) * B * H * W * C + (4 * B * H * W if w["kind"] == 1 else 4 * Vx)
+    return fwd, bwd
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.samples = []
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                 "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), line.strip()))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self, t0, t1):
+        rows = []
+        for ts, line in self.samples:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                rows.append((ts, float(parts[0]), float(parts[1]), parts[3:7]))
+            except ValueError:
+                continue
+        inside = [r for r in rows if t0 <= r[0] <= t1]
+        window = "timed_region"
+        if len(inside) < 3:
+            inside, window = rows, "timed_region_plus_probe_loop"
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "window": "unavailable"}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in inside for n, v in zip(names, r[3]) if v.lower().startswith("active")})
+        return {"sm_mhz": float(np.median([r[1] for r in inside])), "sm_max_mhz": inside[0][2], "reasons": reasons,
+                "samples": len(inside), "window": window}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU reference (the reference's kernel bodies compiled for the host, or the C restatement)
+# ------------------------------------------------------------------------------------------------
+def cpu_reference_run(workload, budget_s, steps=1, warmup=0):
+    """Time forward+backward on the host cores over a band of image rows sized to `budget_s` per
+    step.  Returns (units_per_s, info)."""
+    import oracle
+    from custom_helper_op_b200 import synth
+    impl, kind = ("ref", "reference") if oracle.have_ref() else ("port", "port")
+    w = synth.make(workload, with_grad=False)
+    dims = workload_dims(workload)
+    cores = oracle.max_threads()
+    H, W, D, N, B = dims["H"], dims["W"], dims["D"], dims["N"], dims["B"]
+
+    def run(rows, reps):
+        ref = np.ascontiguousarray(w["ref"][:1, :rows])
+        base = np.ascontiguousarray(w["base_plane"][:1, :rows])
+        src, offs, Rs, Ts = w["src"][:1], w["offsets"][:1], w["Rs"][:1], w["Ts"][:1]
+        cg = np.random.default_rng(1).standard_normal((1, rows, W, D, dims["C"])).astype(np.float32)
+        best = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            cost, mask = oracle.cost_fwd(1, ref, src, base, offs, Rs, Ts, impl=impl, nthreads=cores)
+            oracle.cost_bwd(1, ref, src, base, offs, Rs, Ts, cg, mask, impl=impl, nthreads=cores)
+            best.append(time.perf_counter() - t0)
+        return best
+
+    # calibrate on a thin band, then size the sample
+    probe_rows = max(2, H // 32)
+    t_probe = min(run(probe_rows, 2))
+    rows = int(min(H, max(probe_rows, probe_rows * budget_s / max(t_probe, 1e-6))))
+    for _ in range(warmup):
+        run(rows, 1)
+    times = run(rows, max(1, steps))
+    units = rows * W * D * N  # one batch item
+    t = float(np.median(times))
+    info = {"kind": kind, "cores": cores,
+            "sample": "rows 0..%d of %d of one batch item (all %d depth planes, %d source views), median of %d" %
+                      (rows, H, D, N, len(times)),
+            "ms_per_step": t * 1e3, "units_per_step": units}
+    return units / t, info
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------
+def gpu_main(args):
+    import torch
+    import torch.distributed as dist
+
+    from custom_helper_op_b200 import synth
+    from custom_helper_op_b200.python.ops import custom_helper_ops as ops
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus != world and world > 1:
+        raise SystemExit("--gpus %d does not match WORLD_SIZE %d" % (args.gpus, world))
+    if args.gpus > 1 and world == 1:
+        raise SystemExit("launch N>1 with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    dims = workload_dims(args.workload)
+    if dims["kind"] != 1:
+        raise SystemExit("bench.py times the CostVolume (v1) workloads; %s is a parity-test case" % args.workload)
+    B, N, C, H, W, D = dims["B"], dims["N"], dims["C"], dims["H"], dims["W"], dims["D"]
+
+    # synthetic inputs: rank r takes batch item r of a global batch of `world` items
+    wl = synth.make(args.workload, with_grad=False)
+    rng = np.random.default_rng(synth.CONFIG_SEEDS[args.workload] + 1000 * rank)
+    if world > 1:
+        wl["ref"] = rng.standard_normal(wl["ref"].shape).astype(np.float32)
+        wl["src"] = rng.standard_normal(wl["src"].shape).astype(np.float32)
+    host = {k: torch.from_numpy(np.ascontiguousarray(v)).pin_memory() for k, v in wl.items()}
+    t = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+    d_lo, d_hi = 0, D
+    if args.shard == "depth" and world > 1:
+        per = (D + world - 1) // world
+        d_lo, d_hi = min(D, rank * per), min(D, (rank + 1) * per)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234 + rank)
+    cost_grad = torch.randn((B, H, W, D, C), device=dev, generator=gen)
+    cost = torch.empty((B, H, W, D, C), device=dev)
+    mask = torch.empty((B, H, W, D, 1), dtype=torch.int32, device=dev)
+    grads = (torch.empty((B, H, W, C), device=dev), torch.empty((B, N, H, W, C), device=dev),
+             torch.empty((B, H, W, 1), device=dev))
+    packed = None
+    if args.shard == "depth" and world > 1:
+        n_el = sum(g.numel() for g in grads)
+        packed = torch.empty(n_el, device=dev)
+        views, o = [], 0
+        for g in grads:
+            views.append(packed[o:o + g.numel()].view(g.shape))
+            o += g.numel()
+        grads = tuple(views)
+    drange = None if (d_lo, d_hi) == (0, D) else (d_lo, d_hi)
+
+    def fwd():
+        ops.cost_forward(1, t["ref"], t["src"], t["base_plane"], t["offsets"], t["Rs"], t["Ts"], d_range=drange,
+                         out=(cost, mask))
+
+    if drange is None:
+        # full-range call: the library zero-fills the gradient outputs itself
+        def bwd():
+            return ops.cost_backward(1, t["ref"], t["src"], t["base_plane"], t["offsets"], t["Rs"], t["Ts"],
+                                     cost_grad, mask)
+    else:
+        # depth shard: partial gradients into one packed buffer, summed over the ranks by NCCL
+        def bwd():
+            packed.zero_()
+            ops.cost_backward(1, t["ref"], t["src"], t["base_plane"], t["offsets"], t["Rs"], t["Ts"], cost_grad, mask,
+                              d_range=drange, accumulate_into=grads)
+            dist.all_reduce(packed)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        fwd()
+        bwd()
+    barrier()
+
+    K = args.steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    t_wall0 = time.time()
+    for i in range(K):
+        ev[i][0].record()
+        fwd()
+        ev[i][1].record()
+        bwd()
+        ev[i][2].record()
+    barrier()
+    t_wall1 = time.time()
+    total_ms = ev[0][0].elapsed_time(ev[K - 1][2])
+    fwd_ms = float(np.mean([e[0].elapsed_time(e[1]) for e in ev]))
+    bwd_ms = float(np.mean([e[1].elapsed_time(e[2]) for e in ev]))
+    if world > 1:
+        tt = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        total_ms = float(tt.item())
+    ms_per_step = total_ms / K
+    units_rank = B * H * W * (d_hi - d_lo) * N
+    units_total = units_rank * world if args.shard == "batch" else B * H * W * D * N
+    value = units_total / (ms_per_step * 1e-3)
+
+    # a short probe loop after the timed region so the clock sampler sees load even for small K
+    if rank == 0 and (t_wall1 - t_wall0) < 1.0:
+        t_end = time.time() + 1.0
+        while time.time() < t_end:
+            for _ in range(50):
+                fwd()
+                bwd()
+            torch.cuda.synchronize()
+    if rank == 0:
+        sampler.stop()
+
+    # ---- end to end through the public op functions with host buffers (rank-local, N-way total) ----
+    e2e = None
+    if args.shard == "batch":
+        h_cg = torch.empty(cost_grad.shape, dtype=torch.float32).pin_memory()
+        h_cg.copy_(cost_grad)
+        h_out = dict(cost=torch.empty(cost.shape).pin_memory(), mask=torch.empty(mask.shape, dtype=torch.int32).pin_memory(),
+                     rg=torch.empty(grads[0].shape).pin_memory(), sg=torch.empty(grads[1].shape).pin_memory(),
+                     dg=torch.empty(grads[2].shape).pin_memory())
+        h2d = sum(v.numel() * v.element_size() for v in host.values()) + h_cg.numel() * 4
+        d2h = sum(v.numel() * v.element_size() for v in h_out.values())
+
+        def e2e_step():
+            d = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+            cg = h_cg.to(dev, non_blocking=True)
+            c, m = ops.cost_forward(1, d["ref"], d["src"], d["base_plane"], d["offsets"], d["Rs"], d["Ts"])
+            rg, sg, dg = ops.cost_backward(1, d["ref"], d["src"], d["base_plane"], d["offsets"], d["Rs"], d["Ts"], cg, m)
+            h_out["cost"].copy_(c, non_blocking=True)
+            h_out["mask"].copy_(m, non_blocking=True)
+            h_out["rg"].copy_(rg, non_blocking=True)
+            h_out["sg"].copy_(sg, non_blocking=True)
+            h_out["dg"].copy_(dg, non_blocking=True)
+            torch.cuda.synchronize()
+
+        ke = max(3, min(K, 20))
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(ke):
+            e2e_step()
+        barrier()
+        dt = (time.perf_counter() - t0) / ke
+        if world > 1:
+            tt = torch.tensor([dt], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            dt = float(tt.item())
+        e2e = {"value": units_rank * world / dt, "unit": UNIT, "h2d_bytes_per_step": int(h2d),
+               "d2h_bytes_per_step": int(d2h), "ms_per_step": dt * 1e3, "steps": ke}
+
+    if rank == 0:
+        fwd_b, bwd_b = algorithmic_bytes(dict(dims, D=(d_hi - d_lo)))
+        peak, peak_kind = measured_peak()
+        dom = ("cv_bwd_kernel", bwd_b, bwd_ms) if bwd_ms >= fwd_ms else ("cv_fwd_kernel", fwd_b, fwd_ms)
+        ach = dom[1] / (dom[2] * 1e-3) / 1e9
+        roof = {"bound": "hbm", "kernel": dom[0], "achieved": ach, "peak": peak, "peak_source": peak_kind,
+                "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                "fwd": {"ms": fwd_ms, "algorithmic_bytes": fwd_b, "gbs": fwd_b / (fwd_ms * 1e-3) / 1e9},
+                "bwd": {"ms": bwd_ms, "algorithmic_bytes": bwd_b, "gbs": bwd_b / (bwd_ms * 1e-3) / 1e9,
+                        "note": "includes the three zero-fill memsets of the gradient outputs"},
+                "fwd_plus_bwd_frac": (fwd_b + bwd_b) / (ms_per_step * 1e-3) / 1e9 / peak}
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            v, info = cpu_reference_run(args.workload, budget_s=6.0, steps=3)
+            cpu = {"value": v, "unit": UNIT, "cores": info["cores"], "kind": info["kind"], "sample": info["sample"]}
+        out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K,
+               "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+               "scaling": "weak" if args.shard == "batch" else "strong", "vs_baseline": None, "dtype": "f32",
+               "data": "synthetic",
+               "config": {"workload": "%s: CostVolume fwd+bwd fp32, B=%d per GPU, V=%d, C=%d, %dx%d, D=%d, MEAN" %
+                                      (args.workload, B, N + 1, C, H, W, D),
+                          "shard": args.shard, "l2": "inputs_exceed_l2 (cost and cost_grad are %d MB each, L2 is 126 MB)" %
+                                                     (B * H * W * D * C * 4 // 2**20)},
+               "clocks": sampler.summary(t_wall0, t_wall1), "e2e": e2e, "gpu_launches": 2 * K,
+               "roofline": roof, "cpu_baseline": cpu}
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def reference_main(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    dims = workload_dims(args.workload)
+    K = args.steps
+    budget = max(0.02, min(10.0, 150.0 / max(1, K + args.warmup)))
+    v, info = cpu_reference_run(args.workload, budget_s=budget, steps=K, warmup=args.warmup)
+    out = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": world, "steps": K,
+           "warmup": args.warmup, "ms_per_step": info["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+           "config": {"workload": "%s: CostVolume fwd+bwd fp32, V=%d, C=%d, %dx%d, D=%d, MEAN" %
+                                  (args.workload, dims["N"] + 1, dims["C"], dims["H"], dims["W"], dims["D"]),
+                      "note": "the reference registers GPU kernels only; this is its kernel source compiled for the "
+                              "host and swept over all host threads"},
+           "cpu_baseline": {"value": v, "unit": UNIT, "cores": info["cores"], "kind": info["kind"],
+                            "sample": info["sample"]},
+           "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+           "gpu_launches": 0}
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c1_mvsnet")
+    ap.add_argument("--shard", default="batch", choices=["batch", "depth"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_main(args)
+    else:
+        gpu_main(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,7 @@
+"""B200-native drop-in for the cost-volume path of custom_helper_op: the same op functions as the
+reference package exports (custom_helper_op/__init__.py:20-31), backed by hand-written sm_100a CUDA
+kernels behind a C ABI (include/chop.h)."""
+from custom_helper_op_b200.python.ops.custom_helper_ops import (cost_aggregate, cost_volume,  # noqa: F401
+                                                                 cost_volume_v2)
+
+__all__ = ["cost_volume", "cost_volume_v2", "cost_aggregate"]

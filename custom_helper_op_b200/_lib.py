@@ -1,0 +1,67 @@
+"""ctypes binding of libchop_b200.so - the same C ABI a TensorFlow OpKernel, a cgo stub or any other
+host would bind (include/chop.h).  There is no fallback: if the library is missing or a call fails,
+the caller gets an exception."""
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libchop_b200.so")
+
+F32, F64, BF16 = 0, 1, 2
+KIND_V1, KIND_V2, KIND_AGG = 1, 2, 3
+REDUCE_MEAN, REDUCE_MIN = 0, 1
+FLAG_STRICT, FLAG_ACCUMULATE = 1, 2
+
+
+class CvDesc(ctypes.Structure):
+    """struct chop_cv_desc (include/chop.h)."""
+    _fields_ = [("kind", ctypes.c_int32), ("dtype", ctypes.c_int32), ("reduce", ctypes.c_int32),
+                ("half_centor", ctypes.c_int32), ("groups", ctypes.c_int32), ("flags", ctypes.c_uint32),
+                ("B", ctypes.c_int64), ("H", ctypes.c_int64), ("W", ctypes.c_int64), ("C", ctypes.c_int64),
+                ("D", ctypes.c_int64), ("N", ctypes.c_int64), ("Hs", ctypes.c_int64), ("Ws", ctypes.c_int64),
+                ("d_begin", ctypes.c_int64), ("d_end", ctypes.c_int64)]
+
+
+class ChopError(RuntimeError):
+    def __init__(self, status, what):
+        self.status = status
+        super().__init__("%s failed with status %d: %s" % (what, status, status_string(status)))
+
+
+_lib = None
+
+
+def lib():
+    """Load the shared library once.  Raises if it has not been built (python -m
+    custom_helper_op_b200.build) - there is deliberately no CPU or PyTorch fallback."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError("libchop_b200.so not found at %s; build it with "
+                              "`python -m custom_helper_op_b200.build`" % LIB_PATH)
+        L = ctypes.CDLL(LIB_PATH)
+        vp = ctypes.c_void_p
+        L.chop_cost_volume_fwd.restype = ctypes.c_int
+        L.chop_cost_volume_fwd.argtypes = [ctypes.POINTER(CvDesc)] + [vp] * 9
+        L.chop_cost_volume_bwd.restype = ctypes.c_int
+        L.chop_cost_volume_bwd.argtypes = [ctypes.POINTER(CvDesc)] + [vp] * 12
+        L.chop_status_string.restype = ctypes.c_char_p
+        L.chop_status_string.argtypes = [ctypes.c_int]
+        L.chop_version.restype = ctypes.c_int
+        L.chop_set_tuning.restype = ctypes.c_int
+        L.chop_set_tuning.argtypes = [ctypes.c_char_p, ctypes.c_int]
+        _lib = L
+    return _lib
+
+
+def status_string(status):
+    return lib().chop_status_string(int(status)).decode()
+
+
+def check(status, what):
+    if status != 0:
+        raise ChopError(status, what)
+
+
+def set_tuning(name, value):
+    check(lib().chop_set_tuning(name.encode(), int(value)), "chop_set_tuning")

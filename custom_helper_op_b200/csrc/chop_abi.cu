@@ -1,0 +1,299 @@
+// extern "C" surface of libchop_b200.so for the cost-volume ops: argument validation (what the
+// reference's OpKernel::Compute checks with OP_REQUIRES, custom_helper_op/cc/kernels/
+// cost_volume_kernels.cc:91-106), launch planning, the zero fill of the gradient outputs, dispatch.
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstring>
+
+#include "../../include/chop.h"
+#include "cv_entry.h"
+#include "cv_launch.cuh"
+
+namespace {
+
+using chop::CvArgs;
+using chop::CvPlan;
+
+std::atomic<int> g_fwd_chunk{0}, g_bwd_chunk{0}, g_bwd_views{0};
+
+inline int pow2ceil_log2(int x) {
+  int l = 0;
+  while ((1 << l) < x) ++l;
+  return l;
+}
+inline bool is_pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+struct Typed {
+  size_t feat_size;  // bytes per ref/src element
+  size_t real_size;  // bytes per depth/camera/cost element
+};
+
+int typed_of(int dtype, Typed* t) {
+  switch (dtype) {
+    case CHOP_F32: *t = {4, 4}; return 0;
+    case CHOP_F64: *t = {8, 8}; return 0;
+    case CHOP_BF16: *t = {2, 4}; return 0;
+    default: return CHOP_ERR_ATTR;
+  }
+}
+
+// Shape / attribute checks shared by forward and backward.  Fills the narrowed CvArgs dims.
+int validate(const chop_cv_desc* d, CvArgs* a, Typed* ty) {
+  if (!d) return CHOP_ERR_NULL;
+  if (d->kind < CHOP_COST_VOLUME || d->kind > CHOP_COST_AGGREGATE) return CHOP_ERR_ATTR;
+  if (d->reduce != CHOP_REDUCE_MEAN && d->reduce != CHOP_REDUCE_MIN) return CHOP_ERR_ATTR;
+  if (int e = typed_of(d->dtype, ty)) return e;
+  const int64_t dims[] = {d->B, d->H, d->W, d->C, d->D, d->N, d->Hs, d->Ws};
+  for (int64_t v : dims)
+    if (v < 1 || v > INT32_MAX) return CHOP_ERR_SHAPE;
+  // the reference's host op requires source and reference images of one size
+  // (cost_volume_kernels.cc:93-95)
+  if (d->Hs != d->H || d->Ws != d->W) return CHOP_ERR_SHAPE;
+  if (d->Hs < 2 || d->Ws < 2) return CHOP_ERR_SHAPE;
+  int G = 1;
+  if (d->kind == CHOP_COST_VOLUME_V2) {
+    if (d->groups < 1 || d->C % d->groups != 0) return CHOP_ERR_ATTR;  // cost_volume_kernels_v2.cc:107-108
+    G = d->groups;
+  }
+  // texel and pixel indices are 32-bit inside the kernels; voxel and element offsets are 64-bit
+  if (d->B * d->N * d->Hs * d->Ws > INT32_MAX) return CHOP_ERR_SHAPE;
+  if (d->B * d->H * d->W > INT32_MAX) return CHOP_ERR_SHAPE;
+  if (d->B * d->D > INT32_MAX) return CHOP_ERR_SHAPE;
+  const int64_t d_end = d->d_end == 0 ? d->D : d->d_end;
+  if (d->d_begin < 0 || d_end > d->D || d->d_begin > d_end) return CHOP_ERR_RANGE;
+  a->B = (int)d->B; a->H = (int)d->H; a->W = (int)d->W; a->C = (int)d->C; a->D = (int)d->D;
+  a->N = (int)d->N; a->Hs = (int)d->Hs; a->Ws = (int)d->Ws; a->G = G;
+  a->d_begin = (int)d->d_begin;
+  a->d_end = (int)d_end;
+  a->half_centor = d->half_centor ? 1 : 0;
+  a->npix = d->B * d->H * d->W;
+  return 0;
+}
+
+// Channel slice per lane and lanes per pixel.
+int plan_lanes(const chop_cv_desc* d, const CvArgs& a, int* cpl, int* lgl) {
+  int c = 1;
+  if (d->dtype == CHOP_F32 && a.C % 4 == 0) c = 4;
+  if (d->dtype == CHOP_F64 && a.C % 2 == 0) c = 2;
+  if (d->dtype == CHOP_BF16 && a.C % 8 == 0) c = 8;
+  const int lanes = (a.C + c - 1) / c;
+  if (lanes > 32) return CHOP_ERR_UNSUPPORTED;
+  *cpl = c;
+  *lgl = pow2ceil_log2(lanes);
+  return 0;
+}
+
+void plan_chunks(CvArgs* a, int LG, int wanted_warps, int min_chunk, int forced) {
+  const int G = 32 / LG;
+  a->npb = (int)((a->npix + G - 1) / G);
+  const int drange = a->d_end - a->d_begin;
+  int chunk;
+  if (forced > 0) {
+    chunk = forced;
+  } else {
+    if (min_chunk < LG) min_chunk = LG;
+    int by_depth = (drange + min_chunk - 1) / min_chunk;
+    int by_warps = (wanted_warps + a->npb - 1) / a->npb;
+    int nchunks = by_depth < by_warps ? by_depth : by_warps;
+    if (nchunks < 1) nchunks = 1;
+    chunk = (drange + nchunks - 1) / nchunks;
+  }
+  chunk = (chunk + LG - 1) / LG * LG;
+  if (chunk < LG) chunk = LG;
+  a->chunk = chunk;
+  a->nchunks = (drange + chunk - 1) / chunk;
+}
+
+int pick_warps(size_t smem_per_warp) {
+  int w = 8;
+  while (w > 1 && smem_per_warp * w > 200 * 1024) w >>= 1;
+  return smem_per_warp * w > 200 * 1024 ? 0 : w;
+}
+
+int dispatch_fwd(int dtype, const CvArgs& a, const CvPlan& p, cudaStream_t st) {
+  switch (dtype) {
+    case CHOP_F32: return chop::cv_fwd_f32(a, p, st);
+    case CHOP_F64: return chop::cv_fwd_f64(a, p, st);
+    default: return chop::cv_fwd_bf16(a, p, st);
+  }
+}
+int dispatch_bwd(int dtype, const CvArgs& a, const CvPlan& p, cudaStream_t st) {
+  switch (dtype) {
+    case CHOP_F32: return chop::cv_bwd_f32(a, p, st);
+    case CHOP_F64: return chop::cv_bwd_f64(a, p, st);
+    default: return chop::cv_bwd_bf16(a, p, st);
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int chop_cost_volume_fwd(const chop_cv_desc* d, const void* ref, const void* src, const void* depth,
+                         const void* offsets, const void* Rs, const void* Ts, void* cost, int32_t* mask,
+                         void* stream) {
+  CvArgs a;
+  std::memset(&a, 0, sizeof(a));
+  Typed ty;
+  if (int e = validate(d, &a, &ty)) return e;
+  if (!ref || !src || !depth || !Rs || !Ts || !cost || !mask) return CHOP_ERR_NULL;
+  if (d->kind != CHOP_COST_VOLUME_V2 && !offsets) return CHOP_ERR_NULL;
+  if (a.d_begin == a.d_end) return CHOP_OK;
+  int cpl, lgl;
+  if (int e = plan_lanes(d, a, &cpl, &lgl)) return e;
+  const int mode = d->reduce == CHOP_REDUCE_MIN ? 2 : ((d->flags & CHOP_FLAG_STRICT) ? 1 : 0);
+
+  CvPlan p;
+  std::memset(&p, 0, sizeof(p));
+  p.kind = d->kind;
+  p.mode = mode;
+  // how lanes combine channels into groups (kinds 2 and 3)
+  p.fwd.group_mode = chop::GROUP_IN_LANE;
+  p.fwd.sub = 1;
+  p.fwd.run = 1;
+  if (d->kind != CHOP_COST_VOLUME) {
+    for (int attempt = 0; attempt < 2; ++attempt) {
+      const int LG = 1 << lgl;
+      const int sub = d->kind == CHOP_COST_VOLUME_V2 ? a.C / a.G : a.C;
+      p.fwd.sub = sub;
+      bool ok = true;
+      if (d->kind == CHOP_COST_VOLUME_V2 && cpl % sub == 0) {
+        p.fwd.group_mode = chop::GROUP_IN_LANE;
+      } else if (mode == 0 && d->kind == CHOP_COST_AGGREGATE) {
+        p.fwd.group_mode = chop::GROUP_XOR;
+        p.fwd.run = LG;
+      } else if (mode == 0 && sub % cpl == 0 && is_pow2(sub / cpl)) {
+        p.fwd.group_mode = chop::GROUP_XOR;
+        p.fwd.run = sub / cpl;
+      } else {
+        p.fwd.group_mode = chop::GROUP_SMEM;
+        const int ngroups = d->kind == CHOP_COST_VOLUME_V2 ? a.G : 1;
+        ok = ngroups <= LG;
+      }
+      if (ok) break;
+      if (attempt == 1 || cpl == 1) return CHOP_ERR_UNSUPPORTED;
+      // one channel per lane always has at least as many lanes as groups
+      cpl = 1;
+      if (a.C > 32) return CHOP_ERR_UNSUPPORTED;
+      lgl = pow2ceil_log2(a.C);
+    }
+  }
+  p.cpl = cpl;
+  a.lg_log2 = lgl;
+  const int LG = 1 << lgl;
+  if (!aligned(ref, cpl * ty.feat_size) || !aligned(src, cpl * ty.feat_size) || !aligned(depth, ty.real_size) ||
+      !aligned(cost, (d->kind == CHOP_COST_VOLUME ? cpl : 1) * ty.real_size) || !aligned(mask, 4))
+    return CHOP_ERR_ALIGN;
+  if (d->kind == CHOP_COST_VOLUME && d->reduce == CHOP_REDUCE_MIN && !aligned(mask, cpl * 4)) return CHOP_ERR_ALIGN;
+
+  plan_chunks(&a, LG, 148 * 64, 16, g_fwd_chunk.load());
+  p.fwd.smem_per_warp = ty.real_size == 8
+      ? chop::fwd_smem_per_warp<double>(a.N, 32 / LG, LG, cpl, p.fwd.group_mode == chop::GROUP_SMEM)
+      : chop::fwd_smem_per_warp<float>(a.N, 32 / LG, LG, cpl, p.fwd.group_mode == chop::GROUP_SMEM);
+  p.fwd.warps = pick_warps(p.fwd.smem_per_warp);
+  if (p.fwd.warps == 0) return CHOP_ERR_UNSUPPORTED;
+  const long long items = (long long)a.npb * a.nchunks;
+  const long long blocks = (items + p.fwd.warps - 1) / p.fwd.warps;
+  if (blocks > INT32_MAX) return CHOP_ERR_SHAPE;
+  p.blocks = (int)blocks;
+
+  a.ref = ref; a.src = src; a.depth = depth; a.offsets = offsets; a.Rs = Rs; a.Ts = Ts;
+  a.cost = cost; a.mask = mask;
+  return dispatch_fwd(d->dtype, a, p, static_cast<cudaStream_t>(stream));
+}
+
+int chop_cost_volume_bwd(const chop_cv_desc* d, const void* ref, const void* src, const void* depth,
+                         const void* offsets, const void* Rs, const void* Ts, const void* cost_grad,
+                         const int32_t* mask, void* ref_grad, void* src_grad, void* depth_grad, void* stream) {
+  CvArgs a;
+  std::memset(&a, 0, sizeof(a));
+  Typed ty;
+  if (int e = validate(d, &a, &ty)) return e;
+  if (!ref || !src || !depth || !Rs || !Ts || !cost_grad || !mask || !ref_grad || !src_grad || !depth_grad)
+    return CHOP_ERR_NULL;
+  if (d->kind != CHOP_COST_VOLUME_V2 && !offsets) return CHOP_ERR_NULL;
+  int cpl, lgl;
+  if (int e = plan_lanes(d, a, &cpl, &lgl)) return e;
+  a.lg_log2 = lgl;
+  const int LG = 1 << lgl;
+  if (!aligned(ref, cpl * ty.feat_size) || !aligned(src, cpl * ty.feat_size) || !aligned(depth, ty.real_size) ||
+      !aligned(cost_grad, (d->kind == CHOP_COST_VOLUME ? cpl : 1) * ty.real_size) || !aligned(mask, 4) ||
+      !aligned(ref_grad, cpl * ty.real_size) || !aligned(src_grad, cpl * ty.real_size) ||
+      !aligned(depth_grad, ty.real_size))
+    return CHOP_ERR_ALIGN;
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!(d->flags & CHOP_FLAG_ACCUMULATE)) {
+    // the reference launcher zero-fills the three outputs (cost_volume_kernels_gpu.cu.cc:637-642);
+    // the v2 depth gradient is a per-voxel store and needs no fill
+    cudaError_t e = cudaMemsetAsync(ref_grad, 0, (size_t)a.npix * a.C * ty.real_size, st);
+    if (e == cudaSuccess)
+      e = cudaMemsetAsync(src_grad, 0, (size_t)a.B * a.N * a.Hs * a.Ws * a.C * ty.real_size, st);
+    if (e == cudaSuccess && d->kind != CHOP_COST_VOLUME_V2)
+      e = cudaMemsetAsync(depth_grad, 0, (size_t)a.npix * ty.real_size, st);
+    if (e != cudaSuccess) return (int)e;
+  }
+  if (a.d_begin == a.d_end) return CHOP_OK;
+
+  CvPlan p;
+  std::memset(&p, 0, sizeof(p));
+  p.kind = d->kind;
+  p.cpl = cpl;
+  p.rmin = d->reduce == CHOP_REDUCE_MIN;
+  int nv = g_bwd_views.load();
+  if (nv <= 0) {
+    // accumulator registers grow with views per pass x channels per lane; keep the product modest
+    const int cap = cpl >= 8 ? 2 : 4;
+    const int passes = (a.N + cap - 1) / cap;
+    nv = (a.N + passes - 1) / passes;
+  }
+  if (nv > 4) nv = 4;
+  if (nv > a.N) nv = a.N;
+  if (p.rmin) nv = 2;
+  p.nv = nv;
+  p.bwd.sub = d->kind == CHOP_COST_VOLUME_V2 ? a.C / a.G : 1;
+  plan_chunks(&a, LG, 148 * 24, 32, g_bwd_chunk.load());
+  p.bwd.smem_per_warp = ty.real_size == 8 ? chop::bwd_smem_per_warp<double>(a.N, 32 / LG, nv)
+                                         : chop::bwd_smem_per_warp<float>(a.N, 32 / LG, nv);
+  p.bwd.warps = pick_warps(p.bwd.smem_per_warp);
+  if (p.bwd.warps == 0) return CHOP_ERR_UNSUPPORTED;
+  const long long items = (long long)a.npb * a.nchunks;
+  const long long blocks = (items + p.bwd.warps - 1) / p.bwd.warps;
+  if (blocks > INT32_MAX) return CHOP_ERR_SHAPE;
+  p.blocks = (int)blocks;
+
+  a.ref = ref; a.src = src; a.depth = depth; a.offsets = offsets; a.Rs = Rs; a.Ts = Ts;
+  a.cost_grad = cost_grad; a.mask = const_cast<int32_t*>(mask);
+  a.ref_grad = ref_grad; a.src_grad = src_grad; a.depth_grad = depth_grad;
+  return dispatch_bwd(d->dtype, a, p, st);
+}
+
+const char* chop_status_string(int status) {
+  switch (status) {
+    case CHOP_OK: return "ok";
+    case CHOP_ERR_NULL: return "a required pointer is NULL";
+    case CHOP_ERR_SHAPE: return "invalid or inconsistent shape";
+    case CHOP_ERR_ATTR: return "invalid attribute (kind, dtype, reduce_method or groups)";
+    case CHOP_ERR_UNSUPPORTED: return "configuration not supported by this build";
+    case CHOP_ERR_ALIGN: return "pointer not aligned for its element type";
+    case CHOP_ERR_WORKSPACE: return "workspace missing or too small";
+    case CHOP_ERR_RANGE: return "depth range outside [0, D]";
+    default: break;
+  }
+  if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
+  return "unknown status";
+}
+
+int chop_version(void) { return 100; }
+
+int chop_set_tuning(const char* name, int value) {
+  if (!name) return CHOP_ERR_NULL;
+  if (!std::strcmp(name, "fwd_chunk")) { g_fwd_chunk = value; return CHOP_OK; }
+  if (!std::strcmp(name, "bwd_chunk")) { g_bwd_chunk = value; return CHOP_OK; }
+  if (!std::strcmp(name, "bwd_views")) { g_bwd_views = value; return CHOP_OK; }
+  return CHOP_ERR_ATTR;
+}
+
+}  // extern "C"

@@ -1,0 +1,191 @@
+"""Python surface of the cost-volume ops, mirroring the reference wrapper
+custom_helper_op/python/ops/custom_helper_ops.py: same function names, positional order, defaults
+and return values (cost_volume :32-38, cost_volume_v2 :65-71, cost_aggregate), same gradient
+contract (gradients for the two feature inputs and the depth input, None for offsets/Rs/Ts,
+:41-61 and :74-94).
+
+The reference wrapper feeds TensorFlow tensors to a TensorFlow op library.  TensorFlow is not a
+dependency here: the functions take torch CUDA tensors and call the C ABI of libchop_b200.so on the
+current CUDA stream; torch only supplies device memory, streams and autograd plumbing.  Every call
+runs the CUDA kernels - a CPU tensor or a missing library raises.
+"""
+import ctypes
+
+import torch
+
+from custom_helper_op_b200 import _lib
+
+_DT = {torch.float32: _lib.F32, torch.float64: _lib.F64, torch.bfloat16: _lib.BF16}
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require(cond, msg):
+    # the reference reports these through OP_REQUIRES -> InvalidArgumentError
+    if not cond:
+        raise ValueError(msg)
+
+
+def _prep(ref_image, src_images, depth, offsets, Rs, Ts, kind):
+    _require(ref_image.is_cuda, "cost volume ops run on CUDA tensors only (no CPU kernel is registered)")
+    _require(ref_image.dtype in _DT, "dtype must be float32, float64 or bfloat16")
+    real = torch.float32 if ref_image.dtype == torch.bfloat16 else ref_image.dtype
+    dev = ref_image.device
+    cv = lambda t, dt: torch.as_tensor(t, device=dev).to(dt).contiguous()
+    ref_image = ref_image.contiguous()
+    src_images = cv(src_images, ref_image.dtype)
+    depth = cv(depth, real)
+    offsets = cv(offsets, real) if offsets is not None else None
+    Rs = cv(Rs, real)
+    Ts = cv(Ts, real)
+    _require(ref_image.dim() == 4, "ref image must have rank 4")
+    B, H, W, C = ref_image.shape
+    _require(src_images.dim() == 5 and src_images.shape[0] == B and tuple(src_images.shape[2:]) == (H, W, C),
+             "src_images must have rank 5, and must compate to ref_image")
+    N = src_images.shape[1]
+    if kind == _lib.KIND_V2:
+        _require(depth.dim() == 4 and tuple(depth.shape[:3]) == (B, H, W),
+                 "depth_grid must have rank 4, and must compate to ref_image")
+        D = depth.shape[3]
+    else:
+        _require(depth.dim() == 4 and tuple(depth.shape) == (B, H, W, 1),
+                 "base_plane must have rank 4, and must compate to ref_image")
+        _require(offsets.dim() == 2 and offsets.shape[0] == B,
+                 "offsets must have rank 2, and must compate to ref_image")
+        D = offsets.shape[1]
+    _require(tuple(Rs.shape) == (B, N, 3, 3), "Rs must have rank 4, and must compate to ref_image")
+    _require(tuple(Ts.shape) == (B, N, 3), "Ts must have rank 3, and must compate to ref_image")
+    return ref_image, src_images, depth, offsets, Rs, Ts, (B, H, W, C, D, N), real
+
+
+def _desc(kind, dtype, reduce_method, half_centor, groups, dims, flags=0, d_range=None):
+    _require(reduce_method in ("MEAN", "MIN"),
+             "Invalid reduce method %s. Supported types: MEAN, MIN" % reduce_method)
+    B, H, W, C, D, N = dims
+    d = _lib.CvDesc()
+    d.kind, d.dtype = kind, _DT[dtype]
+    d.reduce = _lib.REDUCE_MIN if reduce_method == "MIN" else _lib.REDUCE_MEAN
+    d.half_centor = int(bool(half_centor))
+    d.groups = int(groups or 1)
+    d.flags = flags
+    d.B, d.H, d.W, d.C, d.D, d.N, d.Hs, d.Ws = B, H, W, C, D, N, H, W
+    d.d_begin, d.d_end = d_range if d_range is not None else (0, 0)
+    return d
+
+
+def _out_channels(kind, C, groups):
+    return C if kind == _lib.KIND_V1 else (groups if kind == _lib.KIND_V2 else 1)
+
+
+def cost_forward(kind, ref_image, src_images, depth, offsets, Rs, Ts, reduce_method="MEAN", groups=None,
+                 half_centor=True, strict=False, d_range=None, out=None):
+    """Raw forward op (CostVolume / CostVolumeV2 / CostAggregate).  Returns (cost, cost_mask).
+    ``d_range=(d0,d1)`` computes only those depth planes (into ``out=(cost, mask)`` if given)."""
+    ref_image, src_images, depth, offsets, Rs, Ts, dims, real = _prep(ref_image, src_images, depth, offsets, Rs, Ts, kind)
+    B, H, W, C, D, N = dims
+    if kind == _lib.KIND_V2:
+        _require(groups is not None and groups >= 1 and C % groups == 0, "channels must be divisible by groups")
+    CO = _out_channels(kind, C, groups)
+    MC = CO if reduce_method == "MIN" else 1
+    if out is None:
+        alloc = torch.empty if d_range is None else torch.zeros
+        cost = alloc((B, H, W, D, CO), dtype=real, device=ref_image.device)
+        mask = alloc((B, H, W, D, MC), dtype=torch.int32, device=ref_image.device)
+    else:
+        cost, mask = out
+    d = _desc(kind, ref_image.dtype, reduce_method, half_centor, groups, dims,
+              _lib.FLAG_STRICT if strict else 0, d_range)
+    st = _lib.lib().chop_cost_volume_fwd(ctypes.byref(d), _ptr(ref_image), _ptr(src_images), _ptr(depth),
+                                         _ptr(offsets), _ptr(Rs), _ptr(Ts), _ptr(cost), _ptr(mask), _stream())
+    _lib.check(st, "chop_cost_volume_fwd")
+    if kind == _lib.KIND_AGG and out is None:
+        return cost.view(B, H, W, D), mask.view(B, H, W, D)
+    return cost, mask
+
+
+def cost_backward(kind, ref_image, src_images, depth, offsets, Rs, Ts, cost_grad, cost_mask,
+                  reduce_method="MEAN", groups=None, half_centor=True, d_range=None, accumulate_into=None):
+    """Raw gradient op (CostVolumeGrad / CostVolumeGradV2 / CostAggregateGrad).
+    Returns (ref_image_grad, src_images_grad, depth_grad)."""
+    ref_image, src_images, depth, offsets, Rs, Ts, dims, real = _prep(ref_image, src_images, depth, offsets, Rs, Ts, kind)
+    B, H, W, C, D, N = dims
+    CO = _out_channels(kind, C, groups)
+    MC = CO if reduce_method == "MIN" else 1
+    cost_grad = cost_grad.to(real).contiguous()
+    cost_mask = cost_mask.contiguous()
+    _require(cost_grad.numel() == B * H * W * D * CO, "cost_grad must have rank 5, and must compate to ref_image")
+    _require(cost_mask.dtype == torch.int32 and cost_mask.numel() == B * H * W * D * MC,
+             "cost_mask must be the int32 mask returned by the forward op")
+    flags = 0
+    if accumulate_into is None:
+        ref_grad = torch.empty((B, H, W, C), dtype=real, device=ref_image.device)
+        src_grad = torch.empty((B, N, H, W, C), dtype=real, device=ref_image.device)
+        depth_grad = torch.empty_like(depth) if d_range is None else torch.zeros_like(depth)
+    else:
+        ref_grad, src_grad, depth_grad = accumulate_into
+        flags |= _lib.FLAG_ACCUMULATE
+    d = _desc(kind, ref_image.dtype, reduce_method, half_centor, groups, dims, flags, d_range)
+    st = _lib.lib().chop_cost_volume_bwd(ctypes.byref(d), _ptr(ref_image), _ptr(src_images), _ptr(depth),
+                                         _ptr(offsets), _ptr(Rs), _ptr(Ts), _ptr(cost_grad), _ptr(cost_mask),
+                                         _ptr(ref_grad), _ptr(src_grad), _ptr(depth_grad), _stream())
+    _lib.check(st, "chop_cost_volume_bwd")
+    return ref_grad, src_grad, depth_grad
+
+
+class _CostFn(torch.autograd.Function):
+    """Glue between torch autograd and the two raw ops; the counterpart of the reference's
+    @tf.RegisterGradient functions."""
+
+    @staticmethod
+    def forward(ctx, kind, reduce_method, groups, half_centor, ref_image, src_images, depth, offsets, Rs, Ts):
+        cost, mask = cost_forward(kind, ref_image, src_images, depth, offsets, Rs, Ts, reduce_method, groups,
+                                  half_centor)
+        ctx.save_for_backward(ref_image, src_images, depth, offsets, Rs, Ts, mask)
+        ctx.conf = (kind, reduce_method, groups, half_centor)
+        ctx.feature_dtype = ref_image.dtype
+        ctx.mark_non_differentiable(mask)
+        return cost, mask
+
+    @staticmethod
+    def backward(ctx, grad_out, grad_mask):
+        ref_image, src_images, depth, offsets, Rs, Ts, mask = ctx.saved_tensors
+        kind, reduce_method, groups, half_centor = ctx.conf
+        rg, sg, dg = cost_backward(kind, ref_image, src_images, depth, offsets, Rs, Ts, grad_out, mask,
+                                   reduce_method, groups, half_centor)
+        rg = rg.to(ctx.feature_dtype)
+        sg = sg.to(ctx.feature_dtype)
+        return None, None, None, None, rg, sg, dg.view_as(depth), None, None, None
+
+
+def cost_volume(ref_image, src_images, base_plane, offsets, Rs, Ts, reduce_method="MEAN", half_centor=True,
+                name=None):
+    """cost [B,H,W,D,C], cost_mask [B,H,W,D,1|C] (reference: custom_helper_ops.py:32-38)."""
+    dev = ref_image.device
+    return _CostFn.apply(_lib.KIND_V1, reduce_method, None, half_centor, ref_image, src_images, base_plane,
+                         torch.as_tensor(offsets, device=dev), torch.as_tensor(Rs, device=dev),
+                         torch.as_tensor(Ts, device=dev))
+
+
+def cost_volume_v2(ref_image, src_images, depth_grid, Rs, Ts, reduce_method="MEAN", groups=None, half_centor=True,
+                   name=None):
+    """cost [B,H,W,D,G], cost_mask [B,H,W,D,1|G] (reference: custom_helper_ops.py:65-71)."""
+    dev = ref_image.device
+    return _CostFn.apply(_lib.KIND_V2, reduce_method, groups, half_centor, ref_image, src_images,
+                         torch.as_tensor(depth_grid, device=dev), None, torch.as_tensor(Rs, device=dev),
+                         torch.as_tensor(Ts, device=dev))
+
+
+def cost_aggregate(ref_image, src_images, base_plane, offsets, Rs, Ts, reduce_method="MEAN", half_centor=True,
+                   name=None):
+    """cost [B,H,W,D], cost_mask [B,H,W,D]: the channel-averaged form of cost_volume the reference's
+    CostMapLayer uses (custom_helper_ops.py cost_aggregate)."""
+    dev = ref_image.device
+    return _CostFn.apply(_lib.KIND_AGG, reduce_method, None, half_centor, ref_image, src_images, base_plane,
+                         torch.as_tensor(offsets, device=dev), torch.as_tensor(Rs, device=dev),
+                         torch.as_tensor(Ts, device=dev))

@@ -28,12 +28,18 @@
 extern "C" {
 #endif
 
+#if defined(__GNUC__)
+#define CHOP_API __attribute__((visibility("default")))
+#else
+#define CHOP_API
+#endif
+
 typedef enum chop_status {
   CHOP_OK = 0,
   CHOP_ERR_NULL = -1,         /* a required pointer is NULL */
   CHOP_ERR_SHAPE = -2,        /* a dimension is < 1, inconsistent, or too large for 32-bit texel indices */
   CHOP_ERR_ATTR = -3,         /* unknown kind / dtype / reduce method, groups does not divide C ... */
-  CHOP_ERR_UNSUPPORTED = -4,  /* valid for the reference but not implemented here (see DESIGN.md) */
+  CHOP_ERR_UNSUPPORTED = -4,  /* valid for the reference but not implemented here */
   CHOP_ERR_ALIGN = -5,        /* a pointer is not aligned for the element type */
   CHOP_ERR_WORKSPACE = -6,    /* workspace missing or too small */
   CHOP_ERR_RANGE = -7         /* depth range outside [0, D] */
@@ -85,28 +91,28 @@ typedef struct chop_cv_desc {
  * (custom_helper_op/cc/kernels/cost_volume_kernels_gpu.cu.cc:289-335), CostVolumeV2Functor
  * (cost_volume_kernels_gpu_v2.cu.cc:296-342) and CostAggregateFunctor.
  * depth = base_plane (kinds 1,3) or depth_grid (kind 2); offsets is NULL for kind 2. */
-int chop_cost_volume_fwd(const chop_cv_desc *desc, const void *ref, const void *src, const void *depth,
+CHOP_API int chop_cost_volume_fwd(const chop_cv_desc *desc, const void *ref, const void *src, const void *depth,
                          const void *offsets, const void *Rs, const void *Ts, void *cost, int32_t *mask,
                          void *stream);
 
 /* Gradient.  Replaces CostVolumeGradFunctor::operator() including its zero fill of the outputs
  * (cost_volume_kernels_gpu.cu.cc:590-655; v2 :614-679).  depth_grad has the shape of `depth`.
  * There is no gradient for offsets, Rs, Ts (custom_helper_op/python/ops/custom_helper_ops.py:61). */
-int chop_cost_volume_bwd(const chop_cv_desc *desc, const void *ref, const void *src, const void *depth,
+CHOP_API int chop_cost_volume_bwd(const chop_cv_desc *desc, const void *ref, const void *src, const void *depth,
                          const void *offsets, const void *Rs, const void *Ts, const void *cost_grad,
                          const int32_t *mask, void *ref_grad, void *src_grad, void *depth_grad,
                          void *stream);
 
 /* Text for a status returned by any entry point (negative: chop_status, positive: CUDA). */
-const char *chop_status_string(int status);
+CHOP_API const char *chop_status_string(int status);
 
 /* Library version as major*10000 + minor*100 + patch. */
-int chop_version(void);
+CHOP_API int chop_version(void);
 
 /* Tuning knobs for experiments: "fwd_chunk", "bwd_chunk" (depth planes per warp work item, 0 =
  * heuristic), "bwd_views" (source views per backward pass, 0 = heuristic).  Returns CHOP_ERR_ATTR
  * for an unknown name.  Process-wide; not part of the reference surface. */
-int chop_set_tuning(const char *name, int value);
+CHOP_API int chop_set_tuning(const char *name, int value);
 
 #ifdef __cplusplus
 }

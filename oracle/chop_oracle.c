@@ -53,10 +53,9 @@ int oracle_cost_bwd(int kind, int dtype, int reduce_min, int half_centor, const 
                     const void *offsets, const void *Rs, const void *Ts, const void *cost_grad,
                     const int32_t *mask, void *ref_grad, void *src_grad, void *depth_grad,
                     int nthreads) {
-  (void)nthreads; /* the restated gradient is serial so that its sums are reproducible */
   if (dtype == 0)
-    cost_bwd_f32(kind, reduce_min, half_centor, dims, groups, ref, src, depth, offsets, Rs, Ts, cost_grad, mask, ref_grad, src_grad, depth_grad);
+    cost_bwd_f32(kind, reduce_min, half_centor, dims, groups, ref, src, depth, offsets, Rs, Ts, cost_grad, mask, ref_grad, src_grad, depth_grad, nthreads);
   else
-    cost_bwd_f64(kind, reduce_min, half_centor, dims, groups, ref, src, depth, offsets, Rs, Ts, cost_grad, mask, ref_grad, src_grad, depth_grad);
+    cost_bwd_f64(kind, reduce_min, half_centor, dims, groups, ref, src, depth, offsets, Rs, Ts, cost_grad, mask, ref_grad, src_grad, depth_grad, nthreads);
   return 0;
 }

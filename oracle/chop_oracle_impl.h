@@ -138,10 +138,22 @@ static void FN(cost_fwd)(int kind, int reduce_min, int half_centor, const int64_
  * the reference launcher does (:637-642).  Sums are accumulated voxel by voxel in ascending
  * linear index with views and channels innermost - the order a single reference thread uses -
  * so that with nthreads <= 1 the result is reproducible bit for bit. */
+#ifndef SCATTER_ADD
+#define SCATTER_ADD(p, v)                 \
+  do {                                    \
+    if (par) {                            \
+      _Pragma("omp atomic") *(p) += (v);  \
+    } else {                              \
+      *(p) += (v);                        \
+    }                                     \
+  } while (0)
+#endif
+
 static void FN(cost_bwd)(int kind, int reduce_min, int half_centor, const int64_t *dims, int groups,
                          const REAL *ref, const REAL *src, const REAL *depth_in,
                          const REAL *offsets, const REAL *Rs, const REAL *Ts, const REAL *cost_grad,
-                         const int32_t *mask, REAL *ref_grad, REAL *src_grad, REAL *depth_grad) {
+                         const int32_t *mask, REAL *ref_grad, REAL *src_grad, REAL *depth_grad,
+                         int nthreads) {
   const int64_t B = dims[0], H = dims[1], W = dims[2], C = dims[3], D = dims[4], N = dims[5],
                 Hs = dims[6], Ws = dims[7];
   const int64_t CO = kind == 1 ? C : (kind == 2 ? groups : 1);
@@ -151,6 +163,10 @@ static void FN(cost_bwd)(int kind, int reduce_min, int half_centor, const int64_
   memset(ref_grad, 0, sizeof(REAL) * (size_t)(npix * C));
   memset(src_grad, 0, sizeof(REAL) * (size_t)(B * N * Hs * Ws * C));
   if (kind != 2) memset(depth_grad, 0, sizeof(REAL) * (size_t)npix);
+  /* nthreads > 1: pixels are spread over threads and the source-gradient scatter becomes an atomic
+   * update (what the reference does on the GPU); the sums then depend on the thread schedule. */
+  const int par = nthreads > 1;
+#pragma omp parallel for schedule(dynamic, 16) num_threads(par ? nthreads : 1) if (par)
   for (int64_t pix = 0; pix < npix; ++pix) {
     const int64_t b = pix / (H * W), h = (pix / W) % H, w = pix % W;
     REAL x = (REAL)w, y = (REAL)h;
@@ -196,10 +212,10 @@ static void FN(cost_bwd)(int kind, int reduce_min, int half_centor, const int64_
             else gsrc = reduce_min ? (REAL)2 * df * cg[k] : (REAL)2 * df * cg[k] / (REAL)mo[0];
             rg[c] += -gsrc;                                  /* :440 */
           }
-          g00[c] += gsrc * wt[0];
-          g01[c] += gsrc * wt[1];
-          g11[c] += gsrc * wt[2];
-          g10[c] += gsrc * wt[3];
+          SCATTER_ADD(&g00[c], gsrc * wt[0]);
+          SCATTER_ADD(&g01[c], gsrc * wt[1]);
+          SCATTER_ADD(&g11[c], gsrc * wt[2]);
+          SCATTER_ADD(&g10[c], gsrc * wt[3]);
           REAL t1 = t11[c] - t10[c] - t01[c] + t00[c];       /* :447 */
           hg += gsrc * (t1 * p.dw + t10[c] - t00[c]);
           wg += gsrc * (t1 * p.dh + t01[c] - t00[c]);

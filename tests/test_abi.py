@@ -1,0 +1,61 @@
+"""CPU tests of the C-ABI library: it loads, exports every symbol the header declares, and rejects
+bad arguments on the host before touching the GPU."""
+import ctypes
+import os
+import re
+
+from custom_helper_op_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    names = set()
+    for fn in os.listdir(os.path.join(ROOT, "include")):
+        if fn.endswith(".h"):
+            text = open(os.path.join(ROOT, "include", fn)).read()
+            names.update(re.findall(r"CHOP_API[^;(]*?\b(chop_\w+)\s*\(", text))
+    return sorted(names)
+
+
+def test_library_exports_every_declared_symbol():
+    L = _lib.lib()
+    syms = declared_symbols()
+    assert "chop_cost_volume_fwd" in syms and "chop_cost_volume_bwd" in syms
+    for s in syms:
+        assert hasattr(L, s), s
+    assert L.chop_version() >= 100
+
+
+def test_desc_layout_matches_header():
+    # 6 x int32 followed by 10 x int64
+    assert ctypes.sizeof(_lib.CvDesc) == 6 * 4 + 10 * 8
+
+
+def _desc(**kw):
+    d = _lib.CvDesc()
+    d.kind, d.dtype, d.reduce, d.half_centor, d.groups = 1, 0, 0, 1, 1
+    d.B, d.H, d.W, d.C, d.D, d.N, d.Hs, d.Ws = 1, 8, 8, 4, 4, 2, 8, 8
+    for k, v in kw.items():
+        setattr(d, k, v)
+    return d
+
+
+def _fwd(d, ptr=ctypes.c_void_p(256)):
+    return _lib.lib().chop_cost_volume_fwd(ctypes.byref(d), ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, None)
+
+
+def test_invalid_arguments_are_rejected_on_the_host():
+    assert _fwd(_desc(kind=9)) == -3
+    assert _fwd(_desc(dtype=7)) == -3
+    assert _fwd(_desc(reduce=5)) == -3
+    assert _fwd(_desc(B=0)) == -2
+    assert _fwd(_desc(Hs=9)) == -2                      # source and reference sizes must agree
+    assert _fwd(_desc(kind=2, groups=3)) == -3          # groups must divide C
+    assert _fwd(_desc(d_begin=3, d_end=9)) == -7
+    assert _fwd(_desc(), ptr=None) == -1
+    assert _fwd(_desc(C=33 * 4 + 4)) == -4              # more channels than 32 lanes x 4 can hold
+    assert _fwd(_desc(), ptr=ctypes.c_void_p(258)) == -5
+    assert _fwd(_desc(d_begin=2, d_end=2)) == 0         # empty depth range: nothing to do
+    assert b"NULL" in _lib.lib().chop_status_string(-1)
+    assert _lib.lib().chop_set_tuning(b"nope", 1) == -3

@@ -1,0 +1,203 @@
+"""Parity of the CUDA cost-volume kernels (called through the C ABI) with the CPU oracle.
+
+Tolerances (float32): validity mask and MIN arg-indices bit-exact; cost bit-exact in strict mode and
+within 1e-5 (scale-relative) in the default fused mode; gradients within 1e-4 (the sums are
+accumulated in a different order and through atomics).  float64: 1e-12 / 1e-10.
+"""
+import numpy as np
+import pytest
+import torch
+
+from custom_helper_op_b200 import _lib
+from custom_helper_op_b200.python.ops import custom_helper_ops as ops
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+TOL = {np.float32: (1e-5, 1e-4), np.float64: (1e-12, 1e-10)}
+
+
+def run_gpu(kind, c, reduce, groups, half_centor, cost_grad, strict=False, bf16=False, mask=None):
+    dev = "cuda:0"
+    tt = lambda a, feat=False: None if a is None else (
+        torch.from_numpy(a).to(dev).to(torch.bfloat16) if (feat and bf16) else torch.from_numpy(a).to(dev))
+    ref, src = tt(c["ref"], True), tt(c["src"], True)
+    depth, offs, Rs, Ts = tt(c["depth"]), tt(c["offsets"]), tt(c["Rs"]), tt(c["Ts"])
+    cost, m = ops.cost_forward(kind, ref, src, depth, offs, Rs, Ts, reduce, groups, half_centor, strict=strict)
+    use_mask = m if mask is None else torch.from_numpy(mask).to(dev)
+    rg, sg, dg = ops.cost_backward(kind, ref, src, depth, offs, Rs, Ts, tt(cost_grad), use_mask, reduce, groups,
+                                   half_centor)
+    torch.cuda.synchronize()
+    return dict(cost=cost.cpu().numpy(), mask=m.cpu().numpy(), ref_grad=rg.cpu().numpy(),
+                src_grad=sg.cpu().numpy(), depth_grad=dg.cpu().numpy())
+
+
+def check(got, want, dtype, exact_cost):
+    ftol, gtol = TOL[dtype]
+    assert helpers.bits_equal(got["mask"].reshape(want["mask"].shape), want["mask"]), "mask differs"
+    gc = got["cost"].reshape(want["cost"].shape)
+    if exact_cost:
+        assert helpers.bits_equal(gc, want["cost"]), "strict cost differs"
+    else:
+        assert helpers.rel_err(gc, want["cost"]) <= ftol
+    for k in ("ref_grad", "src_grad", "depth_grad"):
+        assert helpers.rel_err(got[k].reshape(want[k].shape), want[k]) <= gtol, k
+
+
+@pytest.mark.parametrize("name", helpers.golden_names())
+def test_golden_fixtures(name):
+    kind, reduce, groups, hc, ins, gold = helpers.load_golden(name)
+    dtype = ins["ref"].dtype.type
+    for strict in (False, True):
+        got = run_gpu(kind, ins, reduce, groups, hc, gold["cost_grad"], strict=strict)
+        check(got, gold, dtype, exact_cost=strict or reduce == "MIN")
+
+
+SHAPES = [  # B, N, H, W, C, D   (ragged: odd sizes, C not a multiple of the vector width, D < / > lanes)
+    (1, 1, 12, 16, 3, 5), (2, 2, 12, 18, 5, 10), (2, 3, 12, 16, 32, 6), (1, 2, 9, 11, 8, 33),
+    (1, 4, 7, 13, 16, 3), (1, 5, 10, 10, 4, 9), (1, 2, 6, 8, 64, 4), (1, 6, 8, 9, 12, 7),
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("reduce", ["MEAN", "MIN"])
+@pytest.mark.parametrize("camera", ["identity", "shift", "rot_z", "rot_y", "random"])
+def test_cost_volume_v1(shape, reduce, camera):
+    B, N, H, W, C, D = shape
+    c = helpers.make_case(1, 100 + C + D, B, N, H, W, C, D, camera, np.float32)
+    want = helpers.oracle_fwd_bwd(1, c, reduce, 1, True, np.float32)
+    for strict in (False, True):
+        got = run_gpu(1, c, reduce, 1, True, want["cost_grad"], strict=strict)
+        check(got, want, np.float32, exact_cost=strict or reduce == "MIN")
+
+
+@pytest.mark.parametrize("cgs", [(9, 3), (8, 8), (8, 2), (32, 8), (16, 1), (12, 3), (6, 2), (64, 8), (24, 2)])
+@pytest.mark.parametrize("reduce", ["MEAN", "MIN"])
+def test_cost_volume_v2(cgs, reduce):
+    C, G = cgs
+    c = helpers.make_case(2, 200 + C, 2, 3, 10, 14, C, 7, "random", np.float32)
+    want = helpers.oracle_fwd_bwd(2, c, reduce, G, True, np.float32)
+    for strict in (False, True):
+        got = run_gpu(2, c, reduce, G, True, want["cost_grad"], strict=strict)
+        check(got, want, np.float32, exact_cost=strict or reduce == "MIN")
+
+
+@pytest.mark.parametrize("C", [3, 8, 20, 32])
+@pytest.mark.parametrize("reduce", ["MEAN", "MIN"])
+def test_cost_aggregate(C, reduce):
+    c = helpers.make_case(3, 300 + C, 2, 3, 10, 14, C, 6, "random", np.float32)
+    want = helpers.oracle_fwd_bwd(3, c, reduce, 1, True, np.float32)
+    for strict in (False, True):
+        got = run_gpu(3, c, reduce, 1, True, want["cost_grad"], strict=strict)
+        check(got, want, np.float32, exact_cost=strict or reduce == "MIN")
+
+
+@pytest.mark.parametrize("kind", [1, 2, 3])
+@pytest.mark.parametrize("C", [5, 8])
+def test_float64(kind, C):
+    groups = {5: 1, 8: 4}[C] if kind == 2 else 1
+    c = helpers.make_case(kind, 400 + C, 1, 2, 10, 12, C, 6, "random", np.float64)
+    want = helpers.oracle_fwd_bwd(kind, c, "MEAN", groups, True, np.float64)
+    got = run_gpu(kind, c, "MEAN", groups, True, want["cost_grad"], strict=True)
+    check(got, want, np.float64, exact_cost=True)
+
+
+def test_no_half_centor():
+    c = helpers.make_case(1, 17, 1, 2, 10, 12, 8, 6, "random", np.float32)
+    want = helpers.oracle_fwd_bwd(1, c, "MEAN", 1, False, np.float32)
+    got = run_gpu(1, c, "MEAN", 1, False, want["cost_grad"], strict=True)
+    check(got, want, np.float32, exact_cost=True)
+
+
+@pytest.mark.parametrize("kind,C,G", [(1, 32, 1), (2, 32, 8), (2, 16, 8), (2, 8, 8)])
+def test_bfloat16_features(kind, C, G):
+    """bf16 features are an extension; the oracle is the float32 reference arithmetic on the
+    bf16-rounded features."""
+    c = helpers.make_case(kind, 500 + C, 1, 3, 10, 12, C, 6, "random", np.float32)
+    for k in ("ref", "src"):
+        c[k] = torch.from_numpy(c[k]).to(torch.bfloat16).to(torch.float32).numpy()
+    want = helpers.oracle_fwd_bwd(kind, c, "MEAN", G, True, np.float32)
+    got = run_gpu(kind, c, "MEAN", G, True, want["cost_grad"], strict=True, bf16=True)
+    check(got, want, np.float32, exact_cost=True)
+
+
+def test_depth_range_calls_compose():
+    """Splitting a batch item by depth range (how work is sharded across GPUs) reproduces the
+    single-call result: forward slices are disjoint, gradients add up."""
+    c = helpers.make_case(1, 23, 1, 2, 12, 16, 8, 20, "random", np.float32)
+    want = helpers.oracle_fwd_bwd(1, c, "MEAN", 1, True, np.float32)
+    dev = "cuda:0"
+    t = {k: (None if v is None else torch.from_numpy(v).to(dev)) for k, v in c.items()}
+    cg = torch.from_numpy(want["cost_grad"]).to(dev)
+    cost = torch.zeros(want["cost"].shape, device=dev)
+    mask = torch.zeros(want["mask"].shape, dtype=torch.int32, device=dev)
+    grads = None
+    for d0, d1 in ((0, 7), (7, 8), (8, 20)):
+        ops.cost_forward(1, t["ref"], t["src"], t["depth"], t["offsets"], t["Rs"], t["Ts"], strict=True,
+                         d_range=(d0, d1), out=(cost, mask))
+        if grads is None:
+            grads = ops.cost_backward(1, t["ref"], t["src"], t["depth"], t["offsets"], t["Rs"], t["Ts"], cg,
+                                      torch.from_numpy(want["mask"]).to(dev), d_range=(d0, d1))
+        else:
+            ops.cost_backward(1, t["ref"], t["src"], t["depth"], t["offsets"], t["Rs"], t["Ts"], cg,
+                              torch.from_numpy(want["mask"]).to(dev), d_range=(d0, d1), accumulate_into=grads)
+    got = dict(cost=cost.cpu().numpy(), mask=mask.cpu().numpy(), ref_grad=grads[0].cpu().numpy(),
+               src_grad=grads[1].cpu().numpy(), depth_grad=grads[2].cpu().numpy())
+    check(got, want, np.float32, exact_cost=True)
+
+
+@pytest.mark.parametrize("chunk", [8, 16, 64])
+@pytest.mark.parametrize("views", [1, 2, 3, 4])
+def test_tuning_knobs_do_not_change_results(chunk, views):
+    c = helpers.make_case(1, 29, 1, 5, 10, 12, 32, 40, "random", np.float32)
+    want = helpers.oracle_fwd_bwd(1, c, "MEAN", 1, True, np.float32)
+    try:
+        _lib.set_tuning("fwd_chunk", chunk)
+        _lib.set_tuning("bwd_chunk", chunk)
+        _lib.set_tuning("bwd_views", views)
+        got = run_gpu(1, c, "MEAN", 1, True, want["cost_grad"], strict=True)
+    finally:
+        for k in ("fwd_chunk", "bwd_chunk", "bwd_views"):
+            _lib.set_tuning(k, 0)
+    check(got, want, np.float32, exact_cost=True)
+
+
+def test_autograd_wrapper_matches_raw_ops():
+    c = helpers.make_case(1, 41, 1, 2, 10, 12, 8, 6, "random", np.float32)
+    want = helpers.oracle_fwd_bwd(1, c, "MEAN", 1, True, np.float32)
+    dev = "cuda:0"
+    ref = torch.from_numpy(c["ref"]).to(dev).requires_grad_()
+    src = torch.from_numpy(c["src"]).to(dev).requires_grad_()
+    base = torch.from_numpy(c["depth"]).to(dev).requires_grad_()
+    cost, mask = ops.cost_volume(ref, src, base, c["offsets"], c["Rs"], c["Ts"])
+    assert not mask.requires_grad
+    (cost * torch.from_numpy(want["cost_grad"]).to(dev)).sum().backward()
+    assert helpers.rel_err(ref.grad.cpu().numpy(), want["ref_grad"]) <= 1e-4
+    assert helpers.rel_err(src.grad.cpu().numpy(), want["src_grad"]) <= 1e-4
+    assert helpers.rel_err(base.grad.cpu().numpy(), want["depth_grad"]) <= 1e-4
+
+
+def test_errors_are_loud():
+    c = helpers.make_case(1, 43, 1, 2, 10, 12, 8, 6, "random", np.float32)
+    t = {k: torch.from_numpy(v) for k, v in c.items()}
+    with pytest.raises(ValueError):   # CPU tensors: there is no CPU kernel
+        ops.cost_volume(t["ref"], t["src"], t["depth"], t["offsets"], t["Rs"], t["Ts"])
+    g = {k: v.cuda() for k, v in t.items()}
+    with pytest.raises(ValueError):
+        ops.cost_volume(g["ref"], g["src"], g["depth"], g["offsets"], g["Rs"], g["Ts"], reduce_method="MAX")
+    with pytest.raises(ValueError):
+        ops.cost_volume(g["ref"], g["src"][:, :, :-1], g["depth"], g["offsets"], g["Rs"], g["Ts"])
+
+
+@pytest.mark.parametrize("name", ["c0_cpu", "c1_mvsnet"])
+def test_benchmark_configs_scaled(name):
+    """The benchmark workloads at reduced image size, against the oracle."""
+    from custom_helper_op_b200 import synth
+    w = synth.make(name, scale=0.25)
+    c = dict(ref=w["ref"], src=w["src"], depth=w["base_plane"], offsets=w["offsets"], Rs=w["Rs"], Ts=w["Ts"])
+    want = helpers.oracle_fwd_bwd(1, c, "MEAN", 1, True, np.float32, cost_grad=w["cost_grad"])
+    assert (want["mask"] > 0).mean() > 0.5
+    got = run_gpu(1, c, "MEAN", 1, True, w["cost_grad"], strict=True)
+    check(got, want, np.float32, exact_cost=True)
+    got = run_gpu(1, c, "MEAN", 1, True, w["cost_grad"], strict=False)
+    check(got, want, np.float32, exact_cost=False)
