@@ -281,7 +281,7 @@ def gpu_main(args):
     value = units_total / (ms_per_step * 1e-3)
 
     # a short probe loop after the timed region so the clock sampler sees load even for small K
-    if rank == 0 and (t_wall1 - t_wall0) < 1.0:
+    if rank == 0 and (t_wall1 - t_wall0) < 1.0 and not args.profile:
         t_end = time.time() + 1.0
         while time.time() < t_end:
             for _ in range(50):
@@ -293,7 +293,7 @@ def gpu_main(args):
 
     # ---- end to end through the public op functions with host buffers (rank-local, N-way total) ----
     e2e = None
-    if args.shard == "batch":
+    if args.shard == "batch" and not args.profile:
         h_cg = torch.empty(cost_grad.shape, dtype=torch.float32).pin_memory()
         h_cg.copy_(cost_grad)
         h_out = dict(cost=torch.empty(cost.shape).pin_memory(), mask=torch.empty(mask.shape, dtype=torch.int32).pin_memory(),
@@ -342,7 +342,7 @@ def gpu_main(args):
                         "note": "includes the three zero-fill memsets of the gradient outputs"},
                 "fwd_plus_bwd_frac": (fwd_b + bwd_b) / (ms_per_step * 1e-3) / 1e9 / peak}
         cpu = None
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and not args.profile:
             v, info = cpu_reference_run(args.workload, budget_s=6.0, steps=3)
             cpu = {"value": v, "unit": UNIT, "cores": info["cores"], "kind": info["kind"], "sample": info["sample"]}
         out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K,
@@ -392,6 +392,8 @@ def main():
     ap.add_argument("--workload", default="c1_mvsnet")
     ap.add_argument("--shard", default="batch", choices=["batch", "depth"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="device-timed loop only (no clock probe loop, e2e leg or CPU baseline): the command to run under ncu")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_main(args)
