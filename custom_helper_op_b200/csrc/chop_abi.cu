@@ -15,7 +15,7 @@ namespace {
 using chop::CvArgs;
 using chop::CvPlan;
 
-std::atomic<int> g_fwd_chunk{0}, g_bwd_chunk{0}, g_bwd_views{0};
+std::atomic<int> g_fwd_chunk{0}, g_bwd_chunk{0}, g_bwd_views{0}, g_tuned{1};
 
 inline int pow2ceil_log2(int x) {
   int l = 0;
@@ -149,6 +149,7 @@ int chop_cost_volume_fwd(const chop_cv_desc* d, const void* ref, const void* src
   std::memset(&p, 0, sizeof(p));
   p.kind = d->kind;
   p.mode = mode;
+  p.use_tuned = g_tuned.load();
   // how lanes combine channels into groups (kinds 2 and 3)
   p.fwd.group_mode = chop::GROUP_IN_LANE;
   p.fwd.sub = 1;
@@ -241,6 +242,7 @@ int chop_cost_volume_bwd(const chop_cv_desc* d, const void* ref, const void* src
   std::memset(&p, 0, sizeof(p));
   p.kind = d->kind;
   p.cpl = cpl;
+  p.use_tuned = g_tuned.load();
   p.rmin = d->reduce == CHOP_REDUCE_MIN;
   int nv = g_bwd_views.load();
   if (nv <= 0) {
@@ -293,6 +295,7 @@ int chop_set_tuning(const char* name, int value) {
   if (!std::strcmp(name, "fwd_chunk")) { g_fwd_chunk = value; return CHOP_OK; }
   if (!std::strcmp(name, "bwd_chunk")) { g_bwd_chunk = value; return CHOP_OK; }
   if (!std::strcmp(name, "bwd_views")) { g_bwd_views = value; return CHOP_OK; }
+  if (!std::strcmp(name, "tuned")) { g_tuned = value; return CHOP_OK; }
   return CHOP_ERR_ATTR;
 }
 

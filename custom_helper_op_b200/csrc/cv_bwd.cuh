@@ -94,17 +94,29 @@ __global__ void __launch_bounds__(256) cv_bwd_kernel(const CvArgs a, const BwdCf
       const bool dv = pvalid && dA < dhi;
       {
         R depth = (R)0;
+        R scale = (R)0;
+        bool live = false;  // the voxel contributes at all
         if (dv) {
           if (KIND == 2) depth = static_cast<const R*>(a.depth)[pix * a.D + dA];
           else depth = xadd(base, static_cast<const R*>(a.offsets)[(long long)b * a.D + dA]);
+          const int m0 = __ldg(a.mask + (pix * a.D + dA) * MC);
+          // :367 (MEAN: no view saw the voxel) and :484 (MIN: first channel has no winner)
+          live = RMIN ? (m0 >= 0) : (m0 > 0);
+          // constant factors of d(cost)/d(sample), folded into the upstream gradient in phase B
+          if (live) {
+            if (KIND == 1) scale = RMIN ? (R)2 : (R)2 / (R)m0;          // :439, :560
+            else if (KIND == 2) scale = RMIN ? (R)1 : (R)1 / (R)m0;     // v2:461, v2:583
+            else scale = RMIN ? (R)2 / (R)C : (R)2 / (R)(m0 * C);       // aggregate :385, :500
+          }
         }
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
           ProjB<R> pr;
           pr.texel = -1;
-          pr.dh = pr.dw = pr.gh = pr.gw = pr.pad0 = pr.pad1 = pr.pad2 = (R)0;
+          pr.dh = pr.dw = pr.gh = pr.gw = pr.pad1 = pr.pad2 = (R)0;
+          pr.aux = scale;
           const int n = n0 + v;
-          if (dv && n < a.N)
+          if (live && n < a.N)
             pr.texel = project<R, true>(coef[n * G + g], depth, a.half_centor, a.Hs, Ws, pr.dh, pr.dw, pr.gh, pr.gw);
           proj[v * 32 + lane] = pr;
         }
@@ -116,12 +128,12 @@ __global__ void __launch_bounds__(256) cv_bwd_kernel(const CvArgs a, const BwdCf
       const int jn = min(LG, dhi - dblk);
       for (int j = 0; j < jn; ++j) {
         const long long vox = pix * a.D + dblk + j;
-        int m0 = RMIN ? -1 : 0;
-        if (pvalid) m0 = __ldg(a.mask + vox * MC);
-        // :367 (MEAN: no view saw the voxel) and :484 (MIN: first channel has no winner)
-        const bool vskip = RMIN ? (m0 < 0) : (m0 <= 0);
+        const ProjB<R>* rec = proj + (g << lgl) + j;
+        bool any = false;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) any |= rec[v * 32].texel >= 0;
         R dvox = (R)0;
-        if (!vskip && lane_on) {
+        if (any && lane_on) {
           R cgv[CPL];
           int mk[CPL];
           if (KIND == 1) {
@@ -137,22 +149,18 @@ __global__ void __launch_bounds__(256) cv_bwd_kernel(const CvArgs a, const BwdCf
             }
           } else {
             const R c0 = __ldg(cgp + vox);
+            const int m0 = RMIN ? __ldg(a.mask + vox) : 0;
 #pragma unroll
             for (int k = 0; k < CPL; ++k) { cgv[k] = c0; mk[k] = m0; }
           }
-          // fold the constant factors of d(cost)/d(sample) into the upstream gradient
-          R scale;
-          if (KIND == 1) scale = RMIN ? (R)2 : (R)2 / (R)m0;                 // :439, :560
-          else if (KIND == 2) scale = RMIN ? (R)1 : (R)1 / (R)m0;            // v2:461, v2:583
-          else scale = RMIN ? (R)2 / (R)C : (R)2 / (R)(m0 * C);              // aggregate :385, :500
+          const R scale = rec->aux;
 #pragma unroll
           for (int k = 0; k < CPL; ++k) cgv[k] *= scale;
 
 #pragma unroll
           for (int v = 0; v < NV; ++v) {
             const int n = n0 + v;
-            if (n >= a.N) continue;
-            const ProjB<R> pr = proj[v * 32 + (g << lgl) + j];
+            const ProjB<R> pr = rec[v * 32];
             if (pr.texel < 0) continue;
             if (pr.texel != cur[v]) {
               // footprint changed: flush the four corner sums of the old one
@@ -170,7 +178,7 @@ __global__ void __launch_bounds__(256) cv_bwd_kernel(const CvArgs a, const BwdCf
                 for (int k = 0; k < CPL; ++k) acc[v][q][k] = (R)0;
             }
             R w00, w01, w11, w10;
-            bilinear_weights(pr.dh, pr.dw, w00, w01, w11, w10);
+            bilinear_weights_fast(pr.dh, pr.dw, w00, w01, w11, w10);
             const T* p00 = src + (size_t)pr.texel * C + li * CPL;
             R t00[CPL], t01[CPL], t10[CPL], t11[CPL];
             Vec<T, R, CPL>::load(p00, t00);

@@ -1,12 +1,31 @@
-// float32 features: channel slices of 1 or 4 per lane.
+// float32 features: channel slices of 1 or 4 per lane; compile-time-C kernels for the common
+// CostVolume MEAN configurations.
 #include "cv_launch.cuh"
 #include "cv_entry.h"
 
 namespace chop {
 int cv_fwd_f32(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
+  if (p.use_tuned && p.kind == 1 && p.mode == 0 && p.cpl == 4) {
+    switch (a.C) {
+      case 8: return fwd_tuned_go<float, 8, 4>(a, st);
+      case 16: return fwd_tuned_go<float, 16, 4>(a, st);
+      case 32: return fwd_tuned_go<float, 32, 4>(a, st);
+      case 64: return fwd_tuned_go<float, 64, 4>(a, st);
+      default: break;
+    }
+  }
   return p.cpl == 4 ? fwd_kind<float, float, 4>(a, p, st) : fwd_kind<float, float, 1>(a, p, st);
 }
 int cv_bwd_f32(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
+  if (p.use_tuned && p.kind == 1 && !p.rmin && p.cpl == 4) {
+    switch (a.C) {
+      case 8: return bwd_tuned_nv<float, 8, 4>(a, p.nv, st);
+      case 16: return bwd_tuned_nv<float, 16, 4>(a, p.nv, st);
+      case 32: return bwd_tuned_nv<float, 32, 4>(a, p.nv, st);
+      case 64: return bwd_tuned_nv<float, 64, 4>(a, p.nv, st);
+      default: break;
+    }
+  }
   return p.cpl == 4 ? bwd_kind<float, float, 4>(a, p, st) : bwd_kind<float, float, 1>(a, p, st);
 }
 }  // namespace chop

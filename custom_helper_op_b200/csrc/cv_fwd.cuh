@@ -159,7 +159,7 @@ __global__ void __launch_bounds__(256) cv_fwd_kernel(const CvArgs a, const FwdCf
       for (int n = 0; n < a.N; ++n) {
         ProjF<R> pr;
         pr.texel = -1;
-        pr.dh = pr.dw = pr.unused = (R)0;
+        pr.dh = pr.dw = pr.aux = (R)0;
         if (dv) {
           R gh, gw;
           pr.texel = project<R, false>(coef[n * G + g], depth, a.half_centor, a.Hs, Ws, pr.dh, pr.dw, gh, gw);
@@ -168,8 +168,49 @@ __global__ void __launch_bounds__(256) cv_fwd_kernel(const CvArgs a, const FwdCf
         proj[n * 32 + lane] = pr;
       }
       if (!RMIN && dv) __stcs(a.mask + pix * a.D + d, used);
+      if (KIND == 1 && MODE == 0) proj[lane].aux = used > 0 ? (R)1 / (R)used : (R)0;
     }
     __syncwarp();
+
+    if constexpr (KIND == 1 && MODE == 0) {
+      // ---- phase B, tuned path: per-channel mean of squared differences, fused arithmetic ---------
+      const int jn = min(LG, dhi - dblk);
+      const T* src_lane = src + li * CPL;
+      const size_t row = (size_t)Ws * C;
+      if (lane_on) {
+        R* out = cost + (pix * a.D + dblk) * C + li * CPL;
+        for (int j = 0; j < jn; ++j, out += C) {
+          R acc[CPL];
+#pragma unroll
+          for (int k = 0; k < CPL; ++k) acc[k] = (R)0;
+          const ProjF<R>* rec = proj + (g << lgl) + j;
+          const R inv = rec->aux;
+          for (int n = 0; n < a.N; ++n) {
+            const ProjF<R> pr = rec[n * 32];
+            if (pr.texel < 0) continue;
+            R w00, w01, w11, w10;
+            bilinear_weights_fast(pr.dh, pr.dw, w00, w01, w11, w10);
+            const T* p00 = src_lane + (size_t)pr.texel * C;
+            R t00[CPL], t01[CPL], t10[CPL], t11[CPL];
+            Vec<T, R, CPL>::load(p00, t00);
+            Vec<T, R, CPL>::load(p00 + C, t01);
+            Vec<T, R, CPL>::load(p00 + row, t10);
+            Vec<T, R, CPL>::load(p00 + row + C, t11);
+#pragma unroll
+            for (int k = 0; k < CPL; ++k) {
+              const R s = xfma(w10, t10[k], xfma(w11, t11[k], xfma(w01, t01[k], w00 * t00[k])));
+              const R df = s - refv[k];
+              acc[k] = xfma(df, df, acc[k]);
+            }
+          }
+#pragma unroll
+          for (int k = 0; k < CPL; ++k) acc[k] *= inv;
+          store_stream<R, CPL>(out, acc);
+        }
+      }
+      __syncwarp();
+      continue;
+    }
 
     // ---- phase B: channel work, one depth plane at a time -----------------------------------------
     const int jn = min(LG, dhi - dblk);

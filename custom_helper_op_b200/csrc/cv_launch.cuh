@@ -3,6 +3,7 @@
 #pragma once
 #include "cv_bwd.cuh"
 #include "cv_fwd.cuh"
+#include "cv_tuned.cuh"
 
 namespace chop {
 
@@ -13,6 +14,7 @@ struct CvPlan {
   int rmin;   // backward: MIN
   int nv;     // backward: source views tracked per pass
   int blocks;
+  int use_tuned;  // allow the compile-time-C kernels of cv_tuned.cuh where one exists
   FwdCfg fwd;
   BwdCfg bwd;
 };
@@ -79,6 +81,55 @@ inline int bwd_kind(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
     case 1: return p.rmin ? bwd_nv<T, R, CPL, 1, true>(a, p, st) : bwd_nv<T, R, CPL, 1, false>(a, p, st);
     case 2: return p.rmin ? bwd_nv<T, R, CPL, 2, true>(a, p, st) : bwd_nv<T, R, CPL, 2, false>(a, p, st);
     default: return p.rmin ? bwd_nv<T, R, CPL, 3, true>(a, p, st) : bwd_nv<T, R, CPL, 3, false>(a, p, st);
+  }
+}
+
+// ---- compile-time-C kernels -------------------------------------------------------------------------
+inline int tuned_warps(size_t smem_per_warp) {
+  int w = 8;
+  while (w > 1 && smem_per_warp * w > 96 * 1024) w >>= 1;
+  return w;
+}
+
+template <typename T, int C, int CPL>
+inline int fwd_tuned_go(const CvArgs& a, cudaStream_t st) {
+  auto k = cv_fwd_tuned<T, C, CPL>;
+  const size_t spw = tuned_fwd_smem_per_warp<T>(a.N, 32 / (C / CPL));
+  const int warps = tuned_warps(spw);
+  const size_t smem = spw * warps;
+  if (smem > 200 * 1024) return -4;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const long long items = (long long)a.npb * a.nchunks;
+  k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw);
+  return (int)cudaGetLastError();
+}
+
+template <typename T, int C, int CPL, int NV>
+inline int bwd_tuned_go(const CvArgs& a, cudaStream_t st) {
+  auto k = cv_bwd_tuned<T, C, CPL, NV>;
+  const size_t spw = tuned_bwd_smem_per_warp<T>(a.N, 32 / (C / CPL), NV);
+  const int warps = tuned_warps(spw);
+  const size_t smem = spw * warps;
+  if (smem > 200 * 1024) return -4;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const long long items = (long long)a.npb * a.nchunks;
+  k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw);
+  return (int)cudaGetLastError();
+}
+
+template <typename T, int C, int CPL>
+inline int bwd_tuned_nv(const CvArgs& a, int nv, cudaStream_t st) {
+  switch (nv) {
+    case 1: return bwd_tuned_go<T, C, CPL, 1>(a, st);
+    case 2: return bwd_tuned_go<T, C, CPL, 2>(a, st);
+    case 3: return bwd_tuned_go<T, C, CPL, 3>(a, st);
+    default: return bwd_tuned_go<T, C, CPL, 4>(a, st);
   }
 }
 

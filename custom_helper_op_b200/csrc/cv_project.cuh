@@ -26,16 +26,17 @@ template <typename R>
 struct alignas(16) ProjF {
   int texel;  // index of the top-left texel in [B*N*Hs*Ws), or -1 when the view does not see the voxel
   R dh, dw;
-  R unused;
+  R aux;      // in the record of view 0: 1/(number of views that see the voxel), 0 if none
 };
 
 // Phase-A record, backward: also the factors of d(sample row)/d(depth) and d(sample col)/d(depth).
 template <typename R>
 struct alignas(16) ProjB {
-  int texel;
+  int texel;  // -1 also when the whole voxel is skipped (no view counted in the forward pass)
   R dh, dw;
   R gh, gw;
-  R pad0, pad1, pad2;
+  R aux;      // in the record of the pass's first view: constant factor of d(cost)/d(sample)
+  R pad1, pad2;
 };
 
 // Row products for (pixel, view) pairs of one warp: entry [n*G + gg] for pixel pix0+gg.
@@ -105,6 +106,16 @@ __device__ __forceinline__ int project(const Coef<R>& c, R depth, int half_cento
 
 // Bilinear weights, reference naming in brackets (:105-108): w00 [coef_cc] for texel (fh,fw), w01
 // [coef_cf] for (fh,fw+1), w11 [coef_ff] for (fh+1,fw+1), w10 [coef_fc] for (fh+1,fw).
+// The same weights with 4 operations instead of 6 (differs from the reference in the last bit; used
+// where the result only has to meet a floating tolerance).
+template <typename R>
+__device__ __forceinline__ void bilinear_weights_fast(R dh, R dw, R& w00, R& w01, R& w11, R& w10) {
+  w11 = dh * dw;
+  w10 = dh - w11;
+  w01 = dw - w11;
+  w00 = ((R)1 - dh) - w01;
+}
+
 template <typename R>
 __device__ __forceinline__ void bilinear_weights(R dh, R dw, R& w00, R& w01, R& w11, R& w10) {
   const R omh = xsub((R)1, dh);

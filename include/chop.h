@@ -110,7 +110,8 @@ CHOP_API const char *chop_status_string(int status);
 CHOP_API int chop_version(void);
 
 /* Tuning knobs for experiments: "fwd_chunk", "bwd_chunk" (depth planes per warp work item, 0 =
- * heuristic), "bwd_views" (source views per backward pass, 0 = heuristic).  Returns CHOP_ERR_ATTR
+ * heuristic), "bwd_views" (source views per backward pass, 0 = heuristic), "tuned" (1 = use the compile-time-C
+ * kernels where one exists, 0 = always the generic kernels).  Returns CHOP_ERR_ATTR
  * for an unknown name.  Process-wide; not part of the reference surface. */
 CHOP_API int chop_set_tuning(const char *name, int value);
 

@@ -162,6 +162,22 @@ def test_tuning_knobs_do_not_change_results(chunk, views):
     check(got, want, np.float32, exact_cost=True)
 
 
+@pytest.mark.parametrize("C", [8, 16, 32, 64])
+@pytest.mark.parametrize("N", [1, 2, 3, 5])
+def test_generic_and_tuned_kernels_agree_with_oracle(C, N):
+    """CostVolume MEAN has compile-time-C kernels for common channel counts; the generic kernels must
+    stay correct for the same inputs (knob tuned=0), including ragged pixel counts and depth tails."""
+    c = helpers.make_case(1, 600 + C + N, 1, N, 9, 13, C, 21, "random", np.float32)
+    want = helpers.oracle_fwd_bwd(1, c, "MEAN", 1, True, np.float32)
+    for tuned in (1, 0):
+        try:
+            _lib.set_tuning("tuned", tuned)
+            got = run_gpu(1, c, "MEAN", 1, True, want["cost_grad"], strict=False)
+        finally:
+            _lib.set_tuning("tuned", 1)
+        check(got, want, np.float32, exact_cost=False)
+
+
 def test_autograd_wrapper_matches_raw_ops():
     c = helpers.make_case(1, 41, 1, 2, 10, 12, 8, 6, "random", np.float32)
     want = helpers.oracle_fwd_bwd(1, c, "MEAN", 1, True, np.float32)
