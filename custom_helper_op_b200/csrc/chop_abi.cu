@@ -189,7 +189,7 @@ int chop_cost_volume_fwd(const chop_cv_desc* d, const void* ref, const void* src
     return CHOP_ERR_ALIGN;
   if (d->kind == CHOP_COST_VOLUME && d->reduce == CHOP_REDUCE_MIN && !aligned(mask, cpl * 4)) return CHOP_ERR_ALIGN;
 
-  plan_chunks(&a, LG, 148 * 64, 16, g_fwd_chunk.load());
+  plan_chunks(&a, LG, 148 * 128, 16, g_fwd_chunk.load());
   p.fwd.smem_per_warp = ty.real_size == 8
       ? chop::fwd_smem_per_warp<double>(a.N, 32 / LG, LG, cpl, p.fwd.group_mode == chop::GROUP_SMEM)
       : chop::fwd_smem_per_warp<float>(a.N, 32 / LG, LG, cpl, p.fwd.group_mode == chop::GROUP_SMEM);
@@ -256,7 +256,7 @@ int chop_cost_volume_bwd(const chop_cv_desc* d, const void* ref, const void* src
   if (p.rmin) nv = 2;
   p.nv = nv;
   p.bwd.sub = d->kind == CHOP_COST_VOLUME_V2 ? a.C / a.G : 1;
-  plan_chunks(&a, LG, 148 * 24, 32, g_bwd_chunk.load());
+  plan_chunks(&a, LG, 148 * 128, 32, g_bwd_chunk.load());
   p.bwd.smem_per_warp = ty.real_size == 8 ? chop::bwd_smem_per_warp<double>(a.N, 32 / LG, nv)
                                          : chop::bwd_smem_per_warp<float>(a.N, 32 / LG, nv);
   p.bwd.warps = pick_warps(p.bwd.smem_per_warp);

@@ -19,10 +19,10 @@ int cv_fwd_f32(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
 int cv_bwd_f32(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
   if (p.use_tuned && p.kind == 1 && !p.rmin && p.cpl == 4) {
     switch (a.C) {
-      case 8: return bwd_tuned_nv<float, 8, 4>(a, p.nv, st);
-      case 16: return bwd_tuned_nv<float, 16, 4>(a, p.nv, st);
-      case 32: return bwd_tuned_nv<float, 32, 4>(a, p.nv, st);
-      case 64: return bwd_tuned_nv<float, 64, 4>(a, p.nv, st);
+      case 8: return bwd_tuned_go<float, 8, 4>(a, st);
+      case 16: return bwd_tuned_go<float, 16, 4>(a, st);
+      case 32: return bwd_tuned_go<float, 32, 4>(a, st);
+      case 64: return bwd_tuned_go<float, 64, 4>(a, st);
       default: break;
     }
   }

@@ -107,11 +107,11 @@ inline int fwd_tuned_go(const CvArgs& a, cudaStream_t st) {
   return (int)cudaGetLastError();
 }
 
-template <typename T, int C, int CPL, int NV>
+template <typename T, int C, int CPL>
 inline int bwd_tuned_go(const CvArgs& a, cudaStream_t st) {
-  auto k = cv_bwd_tuned<T, C, CPL, NV>;
-  const size_t spw = tuned_bwd_smem_per_warp<T>(a.N, 32 / (C / CPL), NV);
-  const int warps = tuned_warps(spw);
+  auto k = cv_bwd_tuned<T, C, CPL>;
+  const size_t spw = tuned_bwd_smem_per_warp<C>(a.N, 32 / (C / CPL));
+  const int warps = 4;
   const size_t smem = spw * warps;
   if (smem > 200 * 1024) return -4;
   if (smem > 48 * 1024) {
@@ -121,16 +121,6 @@ inline int bwd_tuned_go(const CvArgs& a, cudaStream_t st) {
   const long long items = (long long)a.npb * a.nchunks;
   k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw);
   return (int)cudaGetLastError();
-}
-
-template <typename T, int C, int CPL>
-inline int bwd_tuned_nv(const CvArgs& a, int nv, cudaStream_t st) {
-  switch (nv) {
-    case 1: return bwd_tuned_go<T, C, CPL, 1>(a, st);
-    case 2: return bwd_tuned_go<T, C, CPL, 2>(a, st);
-    case 3: return bwd_tuned_go<T, C, CPL, 3>(a, st);
-    default: return bwd_tuned_go<T, C, CPL, 4>(a, st);
-  }
 }
 
 }  // namespace chop

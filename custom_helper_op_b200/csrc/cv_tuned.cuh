@@ -1,38 +1,19 @@
 // Tuned CostVolume (KIND 1, MEAN, fused arithmetic) kernels for compile-time channel counts.
 //
-// Same decomposition as the generic kernels in cv_fwd.cuh / cv_bwd.cuh - LG = C/CPL lanes per pixel,
-// phase A projects one voxel per lane, phase B does the channel work - with the per-channel-lane
-// overhead stripped out of phase B:
-//   * phase A leaves a ready texel POINTER and the four bilinear weights in the record, so the
-//     redundant per-lane index arithmetic disappears (C is a template constant: the +C neighbour is an
-//     immediate offset of the load);
-//   * views that do not see the voxel get zero weights and a zero validity factor instead of a branch,
-//     so phase B of the forward kernel has uniform control flow and the depth loop is fully unrolled
-//     (record and output addresses become immediates);
-//   * the number of valid views and its reciprocal are produced once per voxel in phase A.
-// Results: mask bit-exact (projection stays unfused), cost / gradients within the float tolerances.
+// Same warp decomposition as the generic kernels in cv_fwd.cuh / cv_bwd.cuh - LG = C/CPL lanes per
+// pixel, phase A projects one voxel per lane into every view, phase B does the channel work - but the
+// loop nest of phase B is  depth block -> view -> plane  and the 2x2 texel footprint of a view is kept
+// in registers while consecutive planes keep hitting it.  Results: mask bit-exact (the projection stays
+// unfused), cost and gradients within the float tolerances.
 #pragma once
 #include "cv_project.cuh"
 
 namespace chop {
 
 template <typename T>
-struct alignas(16) RecB {
-  const T* p;
-  float dh, dw, gh, gw;
-  float scale;  // record of the pass's first view only: 2/(valid views), 0 when the voxel is skipped
-  int texel;    // -1: nothing to do for this view
-};
-
-template <typename T>
 __host__ __device__ inline size_t tuned_fwd_smem_per_warp(int N, int G) {
   return (size_t)N * G * sizeof(Coef<float>) + (size_t)N * 32 * sizeof(ProjF<float>);
 }
-template <typename T>
-__host__ __device__ inline size_t tuned_bwd_smem_per_warp(int N, int G, int NV) {
-  return (size_t)N * G * sizeof(Coef<float>) + (size_t)NV * 32 * sizeof(RecB<T>);
-}
-
 // ---------------------------------------------------------------------------------------------------
 // forward
 //
@@ -166,12 +147,39 @@ __global__ void __launch_bounds__(256) cv_fwd_tuned(const CvArgs a, const int wa
 
 // ---------------------------------------------------------------------------------------------------
 // backward
+//
+// Loop nest as in the forward kernel: depth block (LG planes) -> view -> plane, with the footprint's
+// corner differences (a0, u, v, t1) AND the four corner gradient sums in registers along the innermost
+// loop.  A footprint change (or the end of the block) flushes the sums with four 16-byte vector
+// reductions and reloads the corners.  Register use does not depend on the number of views, and the
+// upstream gradient is read from HBM exactly once: each block's slice of cost_grad (LG planes x C
+// floats per pixel, contiguous) is staged in shared memory with cp.async one block ahead of its use, so
+// its latency hides behind the previous block's arithmetic and every view reads it from shared memory.
+// d(ref) and d(base_plane) are register sums written once per work item.
 // ---------------------------------------------------------------------------------------------------
-template <typename T, int C, int CPL, int NV>
-__global__ void __launch_bounds__(256) cv_bwd_tuned(const CvArgs a, const int warps, const size_t smem_per_warp) {
+struct alignas(8) RecG {
+  float gh, gw;  // d(sample row)/d(depth), d(sample column)/d(depth)
+};
+
+template <int C>
+__host__ __device__ inline size_t tuned_bwd_smem_per_warp(int N, int G) {
+  return (size_t)N * G * sizeof(Coef<float>) + (size_t)N * 32 * (sizeof(ProjF<float>) + sizeof(RecG)) +
+         (size_t)2 * 128 * C;  // two cost_grad buffers of G*LG*C floats = 128*C bytes each
+}
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+template <typename T, int C, int CPL>
+__global__ void __launch_bounds__(128) cv_bwd_tuned(const CvArgs a, const int warps, const size_t smem_per_warp) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int LG = C / CPL;
   constexpr int G = 32 / LG;
+  static_assert(CPL == 4, "the cost_grad staging copies 16 bytes per lane and plane");
   static_assert(LG * CPL == C && (LG & (LG - 1)) == 0 && LG <= 32, "C/CPL must be a power of two <= 32");
   const int lane = threadIdx.x & 31;
   const int wib = threadIdx.x >> 5;
@@ -192,13 +200,15 @@ __global__ void __launch_bounds__(256) cv_bwd_tuned(const CvArgs a, const int wa
 
   unsigned char* mine = smem_raw + (size_t)wib * smem_per_warp;
   Coef<float>* coef = reinterpret_cast<Coef<float>*>(mine);
-  RecB<T>* proj = reinterpret_cast<RecB<T>*>(coef + N * G);
+  ProjF<float>* recA = reinterpret_cast<ProjF<float>*>(coef + N * G);  // aux = 2/(valid views)
+  RecG* recG = reinterpret_cast<RecG*>(recA + N * 32);
+  float* cgbuf = reinterpret_cast<float*>(recG + N * 32);             // [2][G][LG][C]
+  float* cg_mine = cgbuf + (g * LG) * C + li * CPL;                    // + buf*32*C + j*C
 
   stage_coefs<float>(a, coef, lane, G, pix0);
-  __syncwarp();
 
-  const T* src = static_cast<const T*>(a.src);
-  float* src_grad = static_cast<float*>(a.src_grad);
+  const T* src_lane = static_cast<const T*>(a.src) + li * CPL;
+  float* sg_lane = static_cast<float*>(a.src_grad) + li * CPL;
   float refv[CPL], rg[CPL];
   Vec<T, float, CPL>::load(static_cast<const T*>(a.ref) + pix * C + li * CPL, refv);
 #pragma unroll
@@ -207,135 +217,129 @@ __global__ void __launch_bounds__(256) cv_bwd_tuned(const CvArgs a, const int wa
   const float base = static_cast<const float*>(a.depth)[pix];
   const float* offs = static_cast<const float*>(a.offsets) + (long long)b * D;
   const size_t row = (size_t)a.Ws * C;
-  const RecB<T>* myrec = proj + g * LG;
   float dsum = 0.0f;
+  const float* cg_src = static_cast<const float*>(a.cost_grad) + (pix * D + dlo) * C + li * CPL;
 
-  for (int n0 = 0; n0 < N; n0 += NV) {
-    float acc[NV][4][CPL];
-    int cur[NV];
+  // stage the first block's upstream gradient
 #pragma unroll
-    for (int v = 0; v < NV; ++v) {
-      cur[v] = -1;
+  for (int j = 0; j < LG; ++j)
+    if (dlo + j < dhi) cp_async16(cg_mine + j * C, cg_src + j * C);
+  cp_async_commit();
+  __syncwarp();
+
+  int buf = 0;
+  for (int dblk = dlo; dblk < dhi; dblk += LG, cg_src += LG * C, buf ^= 1) {
+    cp_async_wait_all();  // this block's slice has landed (each lane reads back only what it copied)
+    __syncwarp();         // and every lane is done with the other buffer and with the records
+    {
+      const int nxt = dblk + LG;
+      float* dst = cg_mine + (buf ^ 1) * 32 * C;
 #pragma unroll
-      for (int q = 0; q < 4; ++q)
-#pragma unroll
-        for (int k = 0; k < CPL; ++k) acc[v][q][k] = 0.0f;
+      for (int j = 0; j < LG; ++j)
+        if (nxt + j < dhi) cp_async16(dst + j * C, cg_src + (LG + j) * C);
+      cp_async_commit();
     }
-    const float* cgb = static_cast<const float*>(a.cost_grad) + (pix * D + dlo) * C + li * CPL;
 
-    for (int dblk = dlo; dblk < dhi; dblk += LG, cgb += LG * C) {
-      // the upstream gradient of the block's first plane is requested before the projection math
-      float cgn[CPL];
-      load_stream<float, CPL>(cgb, cgn);
-
-      // ---- phase A ---------------------------------------------------------------------------------
-      {
-        const int d = dblk + li;
-        const bool dv = pvalid && d < dhi;
-        float depth = 0.0f, scale = 0.0f;
-        bool live = false;
-        if (dv) {
-          depth = xadd(base, offs[d]);
-          const int m0 = __ldg(a.mask + pix * D + d);
-          live = m0 > 0;                          // cost_volume_kernels_gpu.cu.cc:367
-          if (live) scale = 2.0f / (float)m0;     // :439
-        }
-#pragma unroll
-        for (int v = 0; v < NV; ++v) {
-          RecB<T> r;
-          r.p = src;
-          r.dh = r.dw = r.gh = r.gw = 0.0f;
-          r.scale = scale;
-          r.texel = -1;
-          const int n = n0 + v;
-          if (live && n < N) {
-            r.texel = project<float, true>(coef[n * G + g], depth, a.half_centor, a.Hs, a.Ws, r.dh, r.dw, r.gh, r.gw);
-            if (r.texel >= 0) r.p = src + (size_t)r.texel * C;
-          }
-          proj[v * 32 + lane] = r;
-        }
+    // ---- phase A: lane (g, li) projects plane dblk+li of pixel g into every view ---------------------
+    {
+      const int d = dblk + li;
+      const bool dv = pvalid && d < dhi;
+      float depth = 0.0f, scale = 0.0f;
+      bool live = false;
+      if (dv) {
+        depth = xadd(base, offs[d]);
+        const int m0 = __ldg(a.mask + pix * D + d);
+        live = m0 > 0;                       // cost_volume_kernels_gpu.cu.cc:367
+        if (live) scale = 2.0f / (float)m0;  // :439
       }
-      __syncwarp();
+      for (int n = 0; n < N; ++n) {
+        ProjF<float> r;
+        RecG q;
+        r.texel = -1;
+        r.dh = r.dw = 0.0f;
+        r.aux = scale;
+        q.gh = q.gw = 0.0f;
+        if (live) r.texel = project<float, true>(coef[n * G + g], depth, a.half_centor, a.Hs, a.Ws, r.dh, r.dw, q.gh, q.gw);
+        recA[n * 32 + lane] = r;
+        recG[n * 32 + lane] = q;
+      }
+    }
+    __syncwarp();
 
-      // ---- phase B ---------------------------------------------------------------------------------
-      const int jn = dhi - dblk;
+    // ---- phase B ---------------------------------------------------------------------------------------
+    const float* cgb = cg_mine + buf * 32 * C;
+    for (int n = 0; n < N; ++n) {
+      const ProjF<float>* rA = recA + n * 32 + g * LG;
+      const RecG* rGp = recG + n * 32 + g * LG;
+      int cur = -1;
+      float a0[CPL], u[CPL], v[CPL], t1[CPL], acc[4][CPL];
+#pragma unroll
+      for (int k = 0; k < CPL; ++k) {
+        a0[k] = u[k] = v[k] = t1[k] = 0.0f;
+        acc[0][k] = acc[1][k] = acc[2][k] = acc[3][k] = 0.0f;
+      }
 #pragma unroll
       for (int j = 0; j < LG; ++j) {
-        if (j < jn) {
-          float cgv[CPL];
-#pragma unroll
-          for (int k = 0; k < CPL; ++k) cgv[k] = cgn[k];
-          if (j + 1 < LG && j + 1 < jn) load_stream<float, CPL>(cgb + (j + 1) * C, cgn);
-          const RecB<T>* r = myrec + j;
-          const float scale = r->scale;
-#pragma unroll
-          for (int k = 0; k < CPL; ++k) cgv[k] *= scale;
-          float dvox = 0.0f;
-#pragma unroll
-          for (int v = 0; v < NV; ++v) {
-            const RecB<T> rc = r[v * 32];
-            if (rc.texel < 0) continue;
-            if (rc.texel != cur[v]) {
-              if (cur[v] >= 0) {
-                float* gp = src_grad + (size_t)cur[v] * C + li * CPL;
-                red_add<float, CPL>(gp, acc[v][0]);
-                red_add<float, CPL>(gp + C, acc[v][1]);
-                red_add<float, CPL>(gp + row, acc[v][2]);
-                red_add<float, CPL>(gp + row + C, acc[v][3]);
-              }
-              cur[v] = rc.texel;
-#pragma unroll
-              for (int q = 0; q < 4; ++q)
-#pragma unroll
-                for (int k = 0; k < CPL; ++k) acc[v][q][k] = 0.0f;
+        const ProjF<float> rc = rA[j];
+        if (rc.texel >= 0) {
+          if (rc.texel != cur) {
+            if (cur >= 0) {
+              float* gp = sg_lane + (size_t)cur * C;
+              red_add<float, CPL>(gp, acc[0]);
+              red_add<float, CPL>(gp + C, acc[1]);
+              red_add<float, CPL>(gp + row, acc[2]);
+              red_add<float, CPL>(gp + row + C, acc[3]);
             }
-            float w00, w01, w11, w10;
-            bilinear_weights_fast(rc.dh, rc.dw, w00, w01, w11, w10);
-            const T* p00 = rc.p + li * CPL;
+            cur = rc.texel;
+            const T* p00 = src_lane + (size_t)rc.texel * C;
             const T* p10 = p00 + row;
             float t00[CPL], t01[CPL], t10[CPL], t11[CPL];
             Vec<T, float, CPL>::load(p00, t00);
             Vec<T, float, CPL>::load(p00 + C, t01);
             Vec<T, float, CPL>::load(p10, t10);
             Vec<T, float, CPL>::load(p10 + C, t11);
-            float hg = 0.0f, wg = 0.0f;
 #pragma unroll
             for (int k = 0; k < CPL; ++k) {
-              // bilinear sample and its two spatial derivatives share the corner differences
-              const float u = t10[k] - t00[k];             // d/dh at dw = 0
-              const float vv = t01[k] - t00[k];            // d/dw at dh = 0
-              const float t1 = (t11[k] - t01[k]) - u;      // :447
-              const float X = fmaf(t1, rc.dw, u);          // d(sample)/dh
-              const float Y = fmaf(t1, rc.dh, vv);         // d(sample)/dw
-              const float s = fmaf(rc.dh, X, fmaf(rc.dw, vv, t00[k]));
-              const float gs = (s - refv[k]) * cgv[k];     // :439
-              rg[k] -= gs;                                 // :440
-              acc[v][0][k] = fmaf(gs, w00, acc[v][0][k]);  // :441-444 (acc[2] is corner (fh+1,fw))
-              acc[v][1][k] = fmaf(gs, w01, acc[v][1][k]);
-              acc[v][2][k] = fmaf(gs, w10, acc[v][2][k]);
-              acc[v][3][k] = fmaf(gs, w11, acc[v][3][k]);
-              hg = fmaf(gs, X, hg);                        // :448
-              wg = fmaf(gs, Y, wg);                        // :449
+              a0[k] = t00[k] - refv[k];
+              u[k] = t10[k] - t00[k];
+              v[k] = t01[k] - t00[k];
+              t1[k] = (t11[k] - t01[k]) - u[k];  // :447
+              acc[0][k] = acc[1][k] = acc[2][k] = acc[3][k] = 0.0f;
             }
-            dvox = fmaf(rc.gh, hg, fmaf(rc.gw, wg, dvox));  // :451
           }
-          dsum += dvox;
+          const RecG rq = rGp[j];
+          const float4 cg4 = *reinterpret_cast<const float4*>(cgb + j * C);
+          const float cgs[4] = {cg4.x * rc.aux, cg4.y * rc.aux, cg4.z * rc.aux, cg4.w * rc.aux};
+          float w00, w01, w11, w10;
+          bilinear_weights_fast(rc.dh, rc.dw, w00, w01, w11, w10);
+          float hg = 0.0f, wg = 0.0f;
+#pragma unroll
+          for (int k = 0; k < CPL; ++k) {
+            const float X = fmaf(t1[k], rc.dw, u[k]);  // d(sample)/dh
+            const float Y = fmaf(t1[k], rc.dh, v[k]);  // d(sample)/dw
+            const float df = fmaf(rc.dh, X, fmaf(rc.dw, v[k], a0[k]));  // sample - ref
+            const float gs = df * cgs[k];                // :439
+            rg[k] -= gs;                                 // :440
+            acc[0][k] = fmaf(gs, w00, acc[0][k]);        // :441-444
+            acc[1][k] = fmaf(gs, w01, acc[1][k]);
+            acc[2][k] = fmaf(gs, w10, acc[2][k]);
+            acc[3][k] = fmaf(gs, w11, acc[3][k]);
+            hg = fmaf(gs, X, hg);                        // :448
+            wg = fmaf(gs, Y, wg);                        // :449
+          }
+          dsum = fmaf(rq.gh, hg, fmaf(rq.gw, wg, dsum));  // :451
         }
       }
-      __syncwarp();
-    }
-
-#pragma unroll
-    for (int v = 0; v < NV; ++v) {
-      if (cur[v] >= 0) {
-        float* gp = src_grad + (size_t)cur[v] * C + li * CPL;
-        red_add<float, CPL>(gp, acc[v][0]);
-        red_add<float, CPL>(gp + C, acc[v][1]);
-        red_add<float, CPL>(gp + row, acc[v][2]);
-        red_add<float, CPL>(gp + row + C, acc[v][3]);
+      if (cur >= 0) {
+        float* gp = sg_lane + (size_t)cur * C;
+        red_add<float, CPL>(gp, acc[0]);
+        red_add<float, CPL>(gp + C, acc[1]);
+        red_add<float, CPL>(gp + row, acc[2]);
+        red_add<float, CPL>(gp + row + C, acc[3]);
       }
     }
   }
+  cp_async_wait_all();
 
   if (pvalid) red_add<float, CPL>(static_cast<float*>(a.ref_grad) + pix * C + li * CPL, rg);
 #pragma unroll
