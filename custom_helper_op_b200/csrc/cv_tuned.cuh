@@ -99,6 +99,8 @@ __global__ void __launch_bounds__(256) cv_fwd_tuned(const CvArgs a, const int wa
 
     for (int n = 0; n < N; ++n) {
       const ProjF<float>* r = myrec + n * 32;
+      // A view that does not see a plane is the "empty footprint" (-1): all differences zero, so the
+      // plane contributes exactly zero and the arithmetic below needs no validity branch.
       int cur = -1;
       float a0[CPL], u[CPL], v[CPL], t1[CPL];
 #pragma unroll
@@ -106,9 +108,9 @@ __global__ void __launch_bounds__(256) cv_fwd_tuned(const CvArgs a, const int wa
 #pragma unroll
       for (int j = 0; j < LG; ++j) {
         const ProjF<float> rc = r[j];
-        if (rc.texel >= 0) {
-          if (rc.texel != cur) {
-            cur = rc.texel;
+        if (rc.texel != cur) {
+          cur = rc.texel;
+          if (rc.texel >= 0) {
             const T* p00 = src_lane + (size_t)rc.texel * C;
             const T* p10 = p00 + row;
             float t00[CPL], t01[CPL], t10[CPL], t11[CPL];
@@ -123,13 +125,16 @@ __global__ void __launch_bounds__(256) cv_fwd_tuned(const CvArgs a, const int wa
               v[k] = t01[k] - t00[k];
               t1[k] = (t11[k] - t01[k]) - u[k];
             }
-          }
+          } else {
 #pragma unroll
-          for (int k = 0; k < CPL; ++k) {
-            const float X = fmaf(t1[k], rc.dw, u[k]);
-            const float df = fmaf(rc.dh, X, fmaf(rc.dw, v[k], a0[k]));
-            acc[j][k] = fmaf(df, df, acc[j][k]);
+            for (int k = 0; k < CPL; ++k) a0[k] = u[k] = v[k] = t1[k] = 0.0f;
           }
+        }
+#pragma unroll
+        for (int k = 0; k < CPL; ++k) {
+          const float X = fmaf(t1[k], rc.dw, u[k]);
+          const float df = fmaf(rc.dh, X, fmaf(rc.dw, v[k], a0[k]));
+          acc[j][k] = fmaf(df, df, acc[j][k]);
         }
       }
     }
@@ -222,8 +227,10 @@ __global__ void __launch_bounds__(128) cv_bwd_tuned(const CvArgs a, const int wa
 
   // stage the first block's upstream gradient
 #pragma unroll
-  for (int j = 0; j < LG; ++j)
+  for (int j = 0; j < LG; ++j) {
     if (dlo + j < dhi) cp_async16(cg_mine + j * C, cg_src + j * C);
+    else *reinterpret_cast<float4*>(cg_mine + j * C) = make_float4(0.f, 0.f, 0.f, 0.f);  // never left uninitialised
+  }
   cp_async_commit();
   __syncwarp();
 
@@ -235,8 +242,10 @@ __global__ void __launch_bounds__(128) cv_bwd_tuned(const CvArgs a, const int wa
       const int nxt = dblk + LG;
       float* dst = cg_mine + (buf ^ 1) * 32 * C;
 #pragma unroll
-      for (int j = 0; j < LG; ++j)
+      for (int j = 0; j < LG; ++j) {
         if (nxt + j < dhi) cp_async16(dst + j * C, cg_src + (LG + j) * C);
+        else *reinterpret_cast<float4*>(dst + j * C) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
       cp_async_commit();
     }
 
