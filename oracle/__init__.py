@@ -118,3 +118,59 @@ def cost_bwd(kind, ref, src, depth, offsets, Rs, Ts, cost_grad, mask, reduce_met
        _p(depth), _p(offsets), _p(Rs), _p(Ts), _p(cost_grad), _p(mask), _p(ref_grad), _p(src_grad),
        _p(depth_grad), ctypes.c_int(nthreads))
     return ref_grad, src_grad, depth_grad
+
+
+# ---- manifold 3-D convolution -------------------------------------------------------------------------
+def _sc_params(images, filters, strides, dilations):
+    B, H, W, D, Cin = images.shape
+    fh, fw, fd, Cin2, Cout = filters.shape
+    assert Cin == Cin2
+    p = (ctypes.c_int * 15)(B, H, W, D, Cin, Cout, fh, fw, fd, *[int(x) for x in strides], *[int(x) for x in dilations])
+    out_shape = (B, (H + strides[0] - 1) // strides[0], (W + strides[1] - 1) // strides[1],
+                 (D + strides[2] - 1) // strides[2], Cout)
+    return p, out_shape
+
+
+def sparse_conv3d_fwd(images, filters, default_value, base_plane, strides=(1, 1, 1), dilations=(1, 1, 1),
+                      dtype=np.float32, impl="port", nthreads=None):
+    """SparseConv3DFast forward.  impl="ref" runs the reference's older thread-per-voxel kernel compiled as
+    host code (same semantics for the forward pass)."""
+    dtype = np.dtype(dtype)
+    images, filters = _prep(dtype, images, filters)
+    base_plane = np.ascontiguousarray(base_plane, np.int32)
+    defv = np.asarray(default_value, dtype).reshape(1)
+    p, out_shape = _sc_params(images, filters, strides, dilations)
+    out = np.empty(out_shape, dtype)
+    nt = nthreads if nthreads is not None else max_threads()
+    if impl == "port":
+        rc = _lib("port").oracle_sparse_conv3d_fwd(ctypes.c_int(0 if dtype == np.float32 else 1), p, _p(images),
+                                                   _p(filters), _p(defv), _p(base_plane), _p(out), ctypes.c_int(nt))
+        assert rc == 0
+    else:
+        B, H, W, D, Cin = images.shape
+        fh, fw, fd, _, Cout = filters.shape
+        q = (ctypes.c_int * 18)(*[int(x) for x in strides], *[int(x) for x in dilations], fh, fw, fd, B, H, W, D, Cin,
+                                out_shape[1], out_shape[2], out_shape[3], Cout)
+        _lib("ref").ref_sparse_conv3d_fwd(ctypes.c_int(0 if dtype == np.float32 else 1), q, _p(images), _p(filters),
+                                          _p(defv), _p(base_plane), _p(out), ctypes.c_int(nt))
+    return out
+
+
+def sparse_conv3d_bwd(images, filters, default_value, base_plane, out_grad, strides=(1, 1, 1), dilations=(1, 1, 1),
+                      dynamic_default=False, dtype=np.float32, nthreads=None):
+    """SparseConv3DFastGrad: returns (images_grad, filter_grad, default_value_grad)."""
+    dtype = np.dtype(dtype)
+    images, filters, out_grad = _prep(dtype, images, filters, out_grad)
+    base_plane = np.ascontiguousarray(base_plane, np.int32)
+    defv = np.asarray(default_value, dtype).reshape(1)
+    p, out_shape = _sc_params(images, filters, strides, dilations)
+    assert tuple(out_grad.shape) == out_shape
+    igrad = np.empty_like(images)
+    fgrad = np.empty_like(filters)
+    dgrad = np.zeros(1, dtype)
+    nt = nthreads if nthreads is not None else max_threads()
+    rc = _lib("port").oracle_sparse_conv3d_bwd(ctypes.c_int(0 if dtype == np.float32 else 1), p, _p(images), _p(filters),
+                                               _p(defv), _p(base_plane), _p(out_grad), ctypes.c_int(int(dynamic_default)),
+                                               _p(igrad), _p(fgrad), _p(dgrad), ctypes.c_int(nt))
+    assert rc == 0
+    return igrad, fgrad, dgrad.reshape(())
