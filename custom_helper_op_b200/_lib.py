@@ -22,6 +22,15 @@ class CvDesc(ctypes.Structure):
                 ("d_begin", ctypes.c_int64), ("d_end", ctypes.c_int64)]
 
 
+class ScDesc(ctypes.Structure):
+    """struct chop_sc_desc (include/chop.h)."""
+    _fields_ = [("dtype", ctypes.c_int32), ("dynamic_default", ctypes.c_int32),
+                ("B", ctypes.c_int64), ("H", ctypes.c_int64), ("W", ctypes.c_int64), ("D", ctypes.c_int64),
+                ("Cin", ctypes.c_int64), ("Cout", ctypes.c_int64),
+                ("filter", ctypes.c_int32 * 3), ("strides", ctypes.c_int32 * 3), ("dilations", ctypes.c_int32 * 3),
+                ("reserved", ctypes.c_int32)]
+
+
 class ChopError(RuntimeError):
     def __init__(self, status, what):
         self.status = status
@@ -45,6 +54,12 @@ def lib():
         L.chop_cost_volume_fwd.argtypes = [ctypes.POINTER(CvDesc)] + [vp] * 9
         L.chop_cost_volume_bwd.restype = ctypes.c_int
         L.chop_cost_volume_bwd.argtypes = [ctypes.POINTER(CvDesc)] + [vp] * 12
+        L.chop_sparse_conv3d_bwd_workspace_size.restype = ctypes.c_size_t
+        L.chop_sparse_conv3d_bwd_workspace_size.argtypes = [ctypes.POINTER(ScDesc)]
+        L.chop_sparse_conv3d_fwd.restype = ctypes.c_int
+        L.chop_sparse_conv3d_fwd.argtypes = [ctypes.POINTER(ScDesc)] + [vp] * 6
+        L.chop_sparse_conv3d_bwd.restype = ctypes.c_int
+        L.chop_sparse_conv3d_bwd.argtypes = [ctypes.POINTER(ScDesc)] + [vp] * 9 + [ctypes.c_size_t, vp]
         L.chop_status_string.restype = ctypes.c_char_p
         L.chop_status_string.argtypes = [ctypes.c_int]
         L.chop_version.restype = ctypes.c_int

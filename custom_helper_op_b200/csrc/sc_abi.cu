@@ -1,0 +1,84 @@
+// extern "C" surface for the manifold 3-D convolution: validation (the checks of
+// SparseConv3DFastOpBase::Compute, custom_helper_op/cc/kernels/sparse_conv3d_fast_op.cc:54-146),
+// derived extents and padding, kernel selection.
+#include <cuda_runtime.h>
+
+#include <cstring>
+
+#include "../../include/chop.h"
+#include "sc_common.cuh"
+#include "sc_entry.h"
+
+namespace {
+
+using chop::ScArgs;
+
+int fill(const chop_sc_desc* d, ScArgs* a) {
+  if (!d) return CHOP_ERR_NULL;
+  if (d->dtype < CHOP_F32 || d->dtype > CHOP_BF16) return CHOP_ERR_ATTR;
+  const int64_t dims[] = {d->B, d->H, d->W, d->D, d->Cin, d->Cout};
+  for (int64_t v : dims)
+    if (v < 1 || v > INT32_MAX) return CHOP_ERR_SHAPE;
+  for (int i = 0; i < 3; ++i)
+    if (d->filter[i] < 1 || d->strides[i] < 1 || d->dilations[i] < 1) return CHOP_ERR_ATTR;
+  std::memset(a, 0, sizeof(*a));
+  a->B = (int)d->B; a->H = (int)d->H; a->W = (int)d->W; a->D = (int)d->D;
+  a->Cin = (int)d->Cin; a->Cout = (int)d->Cout;
+  a->fh = d->filter[0]; a->fw = d->filter[1]; a->fd = d->filter[2];
+  a->sr = d->strides[0]; a->sc = d->strides[1]; a->sd = d->strides[2];
+  a->dr = d->dilations[0]; a->dc = d->dilations[1]; a->dd = d->dilations[2];
+  a->oH = (a->H + a->sr - 1) / a->sr;
+  a->oW = (a->W + a->sc - 1) / a->sc;
+  a->oD = (a->D + a->sd - 1) / a->sd;
+  a->pr = a->fh / 2 * a->dr;
+  a->pc = a->fw / 2 * a->dc;
+  a->pd = a->fd / 2 * a->dd;
+  a->dynamic_default = d->dynamic_default ? 1 : 0;
+  a->nvox_in = d->B * d->H * d->W * d->D;
+  a->nvox_out = (long long)a->B * a->oH * a->oW * a->oD;
+  // the reference indexes these tensors with int32 (fixed_param_op_gpu.cu.cc:171-174); pixel indices here
+  // are int32 too, element offsets 64-bit
+  if (d->B * d->H * d->W > INT32_MAX) return CHOP_ERR_SHAPE;
+  if ((int64_t)a->fh * a->fw * a->fd * a->Cin > 1024) return CHOP_ERR_UNSUPPORTED;
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t chop_sparse_conv3d_bwd_workspace_size(const chop_sc_desc* d) {
+  ScArgs a;
+  if (fill(d, &a)) return 0;
+  return chop::sc_wgrad_workspace_bytes(d->dtype, a.fh * a.fw * a.fd, a.Cin, a.Cout, a.nvox_out);
+}
+
+int chop_sparse_conv3d_fwd(const chop_sc_desc* d, const void* images, const void* filters, const void* default_value,
+                           const int32_t* base_plane, void* output, void* stream) {
+  ScArgs a;
+  if (int e = fill(d, &a)) return e;
+  if (!images || !filters || !default_value || !base_plane || !output) return CHOP_ERR_NULL;
+  a.images = images; a.filters = filters; a.default_value = default_value; a.base_plane = base_plane;
+  a.output = output;
+  return chop::sc_fwd_simt_launch(d->dtype, a, static_cast<cudaStream_t>(stream));
+}
+
+int chop_sparse_conv3d_bwd(const chop_sc_desc* d, const void* images, const void* filters, const void* default_value,
+                           const int32_t* base_plane, const void* out_grad, void* images_grad, void* filter_grad,
+                           void* default_value_grad, void* workspace, size_t workspace_bytes, void* stream) {
+  ScArgs a;
+  if (int e = fill(d, &a)) return e;
+  if (!images || !filters || !default_value || !base_plane || !out_grad || !images_grad || !filter_grad ||
+      !default_value_grad)
+    return CHOP_ERR_NULL;
+  const size_t need = chop::sc_wgrad_workspace_bytes(d->dtype, a.fh * a.fw * a.fd, a.Cin, a.Cout, a.nvox_out);
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15)) return CHOP_ERR_WORKSPACE;
+  a.images = images; a.filters = filters; a.default_value = default_value; a.base_plane = base_plane;
+  a.out_grad = out_grad; a.images_grad = images_grad; a.filter_grad = filter_grad;
+  a.default_grad = default_value_grad; a.workspace = workspace;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (int e = chop::sc_wgrad_simt_launch(d->dtype, a, st)) return e;
+  return chop::sc_dgrad_simt_launch(d->dtype, a, st);
+}
+
+}  // extern "C"

@@ -1,0 +1,64 @@
+// Manifold ("sparse") 3-D convolution: shared argument block and index helpers.
+//
+// images [B,H,W,D,Cin] holds, for every pixel, a band of D depth planes starting at absolute plane
+// base_plane[b,h,w]; the convolution runs in absolute depth, so a filter tap that lands in a neighbour
+// pixel has to be shifted by the difference of the two base planes.  Taps outside the image plane or
+// outside the neighbour's band read default_value (reference:
+// custom_helper_op/cc/kernels/sparse_conv3d_fast_fixed_param_op_gpu.cu.cc:78-113).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace chop {
+
+struct ScArgs {
+  const void* images;
+  const void* filters;        // [fh,fw,fd,Cin,Cout]
+  const void* default_value;  // device scalar
+  const int* base_plane;      // [B,H,W]
+  const void* out_grad;       // [B,oH,oW,oD,Cout]
+  void* output;               // [B,oH,oW,oD,Cout]
+  void* images_grad;          // [B,H,W,D,Cin]
+  void* filter_grad;          // [fh,fw,fd,Cin,Cout]
+  void* default_grad;         // scalar
+  void* workspace;
+  int B, H, W, D, Cin, Cout;
+  int fh, fw, fd, sr, sc, sd, dr, dc, dd;
+  int oH, oW, oD, pr, pc, pd;
+  int dynamic_default;
+  long long nvox_in, nvox_out;
+};
+
+__device__ __forceinline__ bool oob(int a, int b) { return (unsigned)a >= (unsigned)b; }
+
+template <typename T> struct ScIo;
+template <> struct ScIo<float> {
+  static __device__ __forceinline__ float ld(const float* p) { return __ldg(p); }
+  static __device__ __forceinline__ void st(float* p, float v) { *p = v; }
+};
+template <> struct ScIo<double> {
+  static __device__ __forceinline__ double ld(const double* p) { return __ldg(p); }
+  static __device__ __forceinline__ void st(double* p, double v) { *p = v; }
+};
+template <> struct ScIo<__nv_bfloat16> {
+  static __device__ __forceinline__ float ld(const __nv_bfloat16* p) {
+    return __uint_as_float(((unsigned)__ldg(reinterpret_cast<const unsigned short*>(p))) << 16);
+  }
+  static __device__ __forceinline__ void st(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+};
+
+// Element offset (in units of Cin) of the input voxel that tap (fr,fc,fz) of output voxel (b,ro,co,dz)
+// reads, or -1 when the tap is padding.
+__device__ __forceinline__ long long sc_tap(const ScArgs& a, int b, int ro, int co, int dz, int fr, int fc, int fz) {
+  const int row = ro * a.sr, col = co * a.sc;
+  const int depth = (dz + (__ldg(a.base_plane + (b * a.H + row) * a.W + col) + a.sd - 1) / a.sd) * a.sd;
+  const int orow = row - a.pr + fr * a.dr, ocol = col - a.pc + fc * a.dc;
+  if (oob(orow, a.H) || oob(ocol, a.W)) return -1;
+  const int pix = (b * a.H + orow) * a.W + ocol;
+  const int ind = depth - a.pd + fz * a.dd - __ldg(a.base_plane + pix);
+  if (oob(ind, a.D)) return -1;
+  return (long long)pix * a.D + ind;
+}
+
+}  // namespace chop

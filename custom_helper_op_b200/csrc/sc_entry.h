@@ -1,0 +1,13 @@
+// Launch entry points of the manifold-convolution kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+namespace chop {
+struct ScArgs;
+int sc_fwd_simt_launch(int dtype, const ScArgs& a, cudaStream_t st);
+int sc_dgrad_simt_launch(int dtype, const ScArgs& a, cudaStream_t st);
+int sc_wgrad_simt_launch(int dtype, const ScArgs& a, cudaStream_t st);
+int sc_wgrad_parts(long long nvox_out);
+size_t sc_wgrad_workspace_bytes(int dtype, int taps, int Cin, int Cout, long long nvox_out);
+}  // namespace chop

@@ -189,3 +189,99 @@ def cost_aggregate(ref_image, src_images, base_plane, offsets, Rs, Ts, reduce_me
     return _CostFn.apply(_lib.KIND_AGG, reduce_method, None, half_centor, ref_image, src_images, base_plane,
                          torch.as_tensor(offsets, device=dev), torch.as_tensor(Rs, device=dev),
                          torch.as_tensor(Ts, device=dev))
+
+
+# ---- manifold ("sparse") 3-D convolution --------------------------------------------------------------
+def _sc_desc(images, filters, strides, dilations, dynamic_default):
+    _require(images.is_cuda, "sparse_conv3d_fast runs on CUDA tensors only (no CPU kernel is registered)")
+    _require(images.dtype in _DT, "dtype must be float32, float64 or bfloat16")
+    _require(images.dim() == 5, "images must have rank 5")
+    _require(filters.dim() == 5, "filter must have rank 5")
+    _require(len(strides) == 3, "strides must be a vector have 3 element")
+    _require(len(dilations) == 3, "dilations must be a vector have 3 element")
+    _require(images.shape[4] == filters.shape[3], "images channel size wrong")
+    d = _lib.ScDesc()
+    d.dtype = _DT[images.dtype]
+    d.dynamic_default = int(bool(dynamic_default))
+    d.B, d.H, d.W, d.D, d.Cin = images.shape
+    d.Cout = filters.shape[4]
+    for i in range(3):
+        d.filter[i] = int(filters.shape[i])
+        d.strides[i] = int(strides[i])
+        d.dilations[i] = int(dilations[i])
+    out_shape = (d.B, (d.H + d.strides[0] - 1) // d.strides[0], (d.W + d.strides[1] - 1) // d.strides[1],
+                 (d.D + d.strides[2] - 1) // d.strides[2], d.Cout)
+    return d, out_shape
+
+
+def _scalar(value, like):
+    """default_value as a device scalar of the images' dtype (python floats keep full precision)."""
+    if torch.is_tensor(value):
+        return value.to(device=like.device, dtype=like.dtype).reshape(())
+    return torch.tensor(value, dtype=like.dtype, device=like.device)
+
+
+def sparse_conv3d_forward(images, filters, default_value, base_plane, strides=(1, 1, 1), dilations=(1, 1, 1)):
+    """Raw op SparseConv3DFast."""
+    images = images.contiguous()
+    filters = filters.to(images.dtype).contiguous()
+    default_value = _scalar(default_value, images)
+    base_plane = base_plane.contiguous()
+    d, out_shape = _sc_desc(images, filters, strides, dilations, False)
+    _require(base_plane.dtype == torch.int32 and tuple(base_plane.shape) == (d.B, d.H, d.W, 1),
+             "base_plane must have rank 4, and must compate to ref_image")
+    out = torch.empty(out_shape, dtype=images.dtype, device=images.device)
+    st = _lib.lib().chop_sparse_conv3d_fwd(ctypes.byref(d), _ptr(images), _ptr(filters), _ptr(default_value),
+                                           _ptr(base_plane), _ptr(out), _stream())
+    _lib.check(st, "chop_sparse_conv3d_fwd")
+    return out
+
+
+def sparse_conv3d_backward(images, filters, default_value, base_plane, out_grad, strides=(1, 1, 1),
+                           dilations=(1, 1, 1), dynamic_default=False):
+    """Raw op SparseConv3DFastGrad: (images_grad, filter_grad, default_value_grad)."""
+    images = images.contiguous()
+    filters = filters.to(images.dtype).contiguous()
+    default_value = _scalar(default_value, images)
+    base_plane = base_plane.contiguous()
+    out_grad = out_grad.to(images.dtype).contiguous()
+    d, out_shape = _sc_desc(images, filters, strides, dilations, dynamic_default)
+    _require(tuple(out_grad.shape) == out_shape, "out_grad must have rank 5, and must compate to ref_image")
+    wdt = torch.float32 if images.dtype == torch.bfloat16 else images.dtype
+    images_grad = torch.empty_like(images)
+    filter_grad = torch.empty(filters.shape, dtype=wdt, device=images.device)
+    default_grad = torch.empty((), dtype=wdt, device=images.device)
+    nbytes = _lib.lib().chop_sparse_conv3d_bwd_workspace_size(ctypes.byref(d))
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=images.device)
+    st = _lib.lib().chop_sparse_conv3d_bwd(ctypes.byref(d), _ptr(images), _ptr(filters), _ptr(default_value),
+                                           _ptr(base_plane), _ptr(out_grad), _ptr(images_grad), _ptr(filter_grad),
+                                           _ptr(default_grad), _ptr(ws), ctypes.c_size_t(ws.numel()), _stream())
+    _lib.check(st, "chop_sparse_conv3d_bwd")
+    return images_grad, filter_grad, default_grad
+
+
+class _SparseConvFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, images, filters, default_value, base_plane, strides, dilations, dynamic_default):
+        out = sparse_conv3d_forward(images, filters, default_value, base_plane, strides, dilations)
+        ctx.save_for_backward(images, filters, default_value, base_plane)
+        ctx.conf = (tuple(strides), tuple(dilations), bool(dynamic_default))
+        return out
+
+    @staticmethod
+    def backward(ctx, out_grad):
+        images, filters, default_value, base_plane = ctx.saved_tensors
+        strides, dilations, dynamic_default = ctx.conf
+        ig, fg, dg = sparse_conv3d_backward(images, filters, default_value, base_plane, out_grad, strides, dilations,
+                                            dynamic_default)
+        # the reference drops the default-value gradient unless dynamic_default (custom_helper_ops.py:284-286)
+        dg = dg.to(default_value.dtype) if dynamic_default else None
+        return ig, fg.to(filters.dtype), dg, None, None, None, None
+
+
+def sparse_conv3d_fast(images, filters, default_value, base_plane, data_format='NDHWC', strides=(1, 1, 1),
+                       dilations=(1, 1, 1), dynamic_default=False, name=None):
+    """output [B,ceil(H/s),ceil(W/s),ceil(D/s),Cout] (reference: custom_helper_ops.py:263-267)."""
+    _require(data_format == 'NDHWC', "data_format must be NDHWC")
+    default_value = _scalar(default_value, images)
+    return _SparseConvFn.apply(images, filters, default_value, base_plane, strides, dilations, dynamic_default)

@@ -103,6 +103,41 @@ CHOP_API int chop_cost_volume_bwd(const chop_cv_desc *desc, const void *ref, con
                          const int32_t *mask, void *ref_grad, void *src_grad, void *depth_grad,
                          void *stream);
 
+/* Describes one manifold ("sparse") 3-D convolution call.  Replaces the reference's SparseConv3DFastParams
+ * (custom_helper_op/cc/kernels/sparse_conv3d_fast_op.h:26-49); output extents are ceil(input/stride) and
+ * the left padding is (filter/2)*dilation as in sparse_conv3d_fast_op.cc:104-109.
+ *   images [B,H,W,D,Cin]  filters [fh,fw,fd,Cin,Cout]  default_value: DEVICE scalar  base_plane int32 [B,H,W,1]
+ *   output / out_grad [B,ceil(H/sr),ceil(W/sc),ceil(D/sd),Cout]
+ * dtype CHOP_BF16: images, filters, default_value, output, out_grad and images_grad are bfloat16;
+ * filter_grad and default_value_grad are float32. */
+typedef struct chop_sc_desc {
+  int32_t dtype;           /* chop_dtype */
+  int32_t dynamic_default; /* attr dynamic_default: also produce d(default_value) */
+  int64_t B, H, W, D, Cin, Cout;
+  int32_t filter[3];       /* fh, fw, fd */
+  int32_t strides[3];      /* attr strides */
+  int32_t dilations[3];    /* attr dilations */
+  int32_t reserved;
+} chop_sc_desc;
+
+/* Scratch bytes the backward call needs (per-CTA partial filter gradients, summed in a fixed order so
+ * the result is deterministic).  The forward call needs none. */
+CHOP_API size_t chop_sparse_conv3d_bwd_workspace_size(const chop_sc_desc *desc);
+
+/* Forward.  Replaces SparseConv3DFastFunctor<GPUDevice,T,true>::operator() together with the filter
+ * transpose the reference launches before it (sparse_conv3d_fast_op.cc:186-201). */
+CHOP_API int chop_sparse_conv3d_fwd(const chop_sc_desc *desc, const void *images, const void *filters,
+                                    const void *default_value, const int32_t *base_plane, void *output,
+                                    void *stream);
+
+/* Gradient.  Replaces SparseConv3DFastGradOp::Compute's device work (sparse_conv3d_fast_op.cc:232-325):
+ * filter gradient, default-value gradient (zero unless dynamic_default) and image gradient.  workspace:
+ * caller-owned device memory of at least chop_sparse_conv3d_bwd_workspace_size() bytes, 16-byte aligned. */
+CHOP_API int chop_sparse_conv3d_bwd(const chop_sc_desc *desc, const void *images, const void *filters,
+                                    const void *default_value, const int32_t *base_plane, const void *out_grad,
+                                    void *images_grad, void *filter_grad, void *default_value_grad,
+                                    void *workspace, size_t workspace_bytes, void *stream);
+
 /* Text for a status returned by any entry point (negative: chop_status, positive: CUDA). */
 CHOP_API const char *chop_status_string(int status);
 

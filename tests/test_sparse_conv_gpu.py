@@ -1,0 +1,81 @@
+"""Parity of the CUDA manifold-convolution kernels (through the C ABI) with the CPU oracle.
+Tolerances: float32 1e-5 (scale-relative, the reference tests' rtol), float64 1e-12, bfloat16 storage 1e-2
+(outputs are rounded to bf16: 2^-8 relative) with float32 filter gradients at 2e-3."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from custom_helper_op_b200.python.ops import custom_helper_ops as ops
+from tests import helpers
+from tests.test_oracle_sparse import CASES, make_case
+
+pytestmark = pytest.mark.gpu
+
+
+def run_gpu(images, filters, defv, bp, og, st, dl, dynamic_default, tdtype):
+    dev = "cuda:0"
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev).to(tdtype)
+    out = ops.sparse_conv3d_forward(t(images), t(filters), float(defv), torch.from_numpy(bp).to(dev), st, dl)
+    ig, fg, dg = ops.sparse_conv3d_backward(t(images), t(filters), float(defv), torch.from_numpy(bp).to(dev), t(og), st,
+                                            dl, dynamic_default)
+    torch.cuda.synchronize()
+    f = lambda x: x.float().cpu().numpy() if x.dtype == torch.bfloat16 else x.cpu().numpy()
+    return f(out), f(ig), f(fg), f(dg)
+
+
+@pytest.mark.parametrize("case", CASES)
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("dynamic_default", [False, True])
+def test_generic_kernels(case, dtype, dynamic_default):
+    B, H, W, D, Cin, Cout, ks, st, dl, vd = case
+    images, filters, defv, bp, _ = make_case(7, B, H, W, D, Cin, Cout, ks, vd, dtype)
+    want = oracle.sparse_conv3d_fwd(images, filters, defv, bp, st, dl, dtype)
+    og = np.random.default_rng(8).uniform(-1, 1, want.shape).astype(dtype)
+    ig_w, fg_w, dg_w = oracle.sparse_conv3d_bwd(images, filters, defv, bp, og, st, dl, dynamic_default, dtype)
+    out, ig, fg, dg = run_gpu(images, filters, defv, bp, og, st, dl, dynamic_default,
+                              torch.float32 if dtype == np.float32 else torch.float64)
+    tol = 1e-5 if dtype == np.float32 else 1e-12
+    assert helpers.rel_err(out, want) <= tol
+    assert helpers.rel_err(ig, ig_w) <= tol
+    assert helpers.rel_err(fg, fg_w) <= tol
+    assert abs(float(dg) - float(dg_w)) <= tol * max(1.0, abs(float(dg_w)))
+    if not dynamic_default:
+        assert float(dg) == 0.0
+
+
+@pytest.mark.parametrize("shape", [(1, 12, 14, 9, 16, 16), (2, 9, 11, 9, 16, 16), (1, 8, 8, 5, 32, 16), (1, 7, 9, 9, 16, 32)])
+def test_bfloat16(shape):
+    """bf16 storage with float32 accumulation; oracle on the bf16-rounded inputs."""
+    B, H, W, D, Cin, Cout = shape
+    images, filters, defv, bp, _ = make_case(9, B, H, W, D, Cin, Cout, (3, 3, 3), 2 * D + 6, np.float32)
+    r = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(torch.bfloat16).float().numpy()
+    images, filters = r(images - 0.5), r(filters * 0.3)
+    defv = float(r(np.array([defv]))[0])
+    want = oracle.sparse_conv3d_fwd(images, filters, defv, bp, dtype=np.float32)
+    og = r(np.random.default_rng(10).uniform(-1, 1, want.shape))
+    ig_w, fg_w, dg_w = oracle.sparse_conv3d_bwd(images, filters, defv, bp, og, dynamic_default=True, dtype=np.float32)
+    out, ig, fg, dg = run_gpu(images, filters, defv, bp, og, (1, 1, 1), (1, 1, 1), True, torch.bfloat16)
+    assert helpers.rel_err(out, want) <= 1e-2
+    assert helpers.rel_err(ig, ig_w) <= 1e-2
+    assert helpers.rel_err(fg, fg_w) <= 2e-3
+    assert abs(float(dg) - float(dg_w)) <= 2e-3 * max(1.0, abs(float(dg_w)))
+
+
+def test_autograd_wrapper():
+    images, filters, defv, bp, _ = make_case(11, 1, 6, 7, 5, 4, 3, (3, 3, 3), 12, np.float32)
+    want = oracle.sparse_conv3d_fwd(images, filters, defv, bp, dtype=np.float32)
+    og = np.random.default_rng(12).uniform(-1, 1, want.shape).astype(np.float32)
+    ig_w, fg_w, dg_w = oracle.sparse_conv3d_bwd(images, filters, defv, bp, og, dynamic_default=True, dtype=np.float32)
+    dev = "cuda:0"
+    ti = torch.from_numpy(images).to(dev).requires_grad_()
+    tf = torch.from_numpy(filters).to(dev).requires_grad_()
+    td = torch.tensor(float(defv), device=dev, requires_grad=True)
+    out = ops.sparse_conv3d_fast(ti, tf, td, torch.from_numpy(bp).to(dev), dynamic_default=True)
+    (out * torch.from_numpy(og).to(dev)).sum().backward()
+    assert helpers.rel_err(out.detach().cpu().numpy(), want) <= 1e-5
+    assert helpers.rel_err(ti.grad.cpu().numpy(), ig_w) <= 1e-5
+    assert helpers.rel_err(tf.grad.cpu().numpy(), fg_w) <= 1e-5
+    assert abs(float(td.grad) - float(dg_w)) <= 1e-4 * max(1.0, abs(float(dg_w)))
+    with pytest.raises(ValueError):
+        ops.sparse_conv3d_fast(ti.cpu(), tf.cpu(), 0.0, torch.from_numpy(bp))
