@@ -81,4 +81,39 @@ int chop_sparse_conv3d_bwd(const chop_sc_desc* d, const void* images, const void
   return chop::sc_dgrad_simt_launch(d->dtype, a, st);
 }
 
+// Same gradient as chop_sparse_conv3d_bwd, but the partial filter gradients go to a fixed 4 MiB array
+// inside the library instead of a caller workspace, so the call allocates nothing and asks the caller
+// for no scratch.  It serves hosts that must not touch the CUDA allocator while they run: a framework
+// whose device memory is owned by its own pool (a raw cudaMalloc there fragments the pool's address
+// space and synchronises the whole device), or a latency-critical loop with a fixed memory budget.
+//   * The first call on each device looks up the array's device address (cudaGetSymbolAddress); make
+//     that first call during set-up, before any stream capture begins.
+//   * The number of partial slabs shrinks to what fits; a problem whose single slab
+//     ((fh*fw*fd*Cin*Cout + 1) accumulators) exceeds 4 MiB is rejected with CHOP_ERR_WORKSPACE.
+//   * All calls on a device share the array.  Nothing in it needs clearing - every slab element that is
+//     read was written by the same call - but two calls that overlap on the GPU (different streams)
+//     race on it; serialise them.
+int chop_sparse_conv3d_bwd_noalloc(const chop_sc_desc* d, const void* images, const void* filters,
+                                   const void* default_value, const int32_t* base_plane, const void* out_grad,
+                                   void* images_grad, void* filter_grad, void* default_value_grad, void* stream) {
+  ScArgs a;
+  if (int e = fill(d, &a)) return e;
+  if (!images || !filters || !default_value || !base_plane || !out_grad || !images_grad || !filter_grad ||
+      !default_value_grad)
+    return CHOP_ERR_NULL;
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  if (int e = chop::sc_static_scratch(&scratch, &scratch_bytes)) return e;
+  const size_t slab = ((size_t)a.fh * a.fw * a.fd * a.Cin * a.Cout + 1) * (d->dtype == CHOP_F64 ? 8 : 4);
+  if (slab > scratch_bytes) return CHOP_ERR_WORKSPACE;  // larger than the built-in scratch: use chop_sparse_conv3d_bwd
+  int nparts = chop::sc_wgrad_parts(a.nvox_out);
+  if ((size_t)nparts * slab > scratch_bytes) nparts = (int)(scratch_bytes / slab);
+  a.images = images; a.filters = filters; a.default_value = default_value; a.base_plane = base_plane;
+  a.out_grad = out_grad; a.images_grad = images_grad; a.filter_grad = filter_grad;
+  a.default_grad = default_value_grad; a.workspace = scratch;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (int e = chop::sc_wgrad_simt_launch_parts(d->dtype, a, nparts, st)) return e;
+  return chop::sc_dgrad_simt_launch(d->dtype, a, st);
+}
+
 }  // extern "C"

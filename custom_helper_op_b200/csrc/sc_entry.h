@@ -9,5 +9,7 @@ int sc_fwd_simt_launch(int dtype, const ScArgs& a, cudaStream_t st);
 int sc_dgrad_simt_launch(int dtype, const ScArgs& a, cudaStream_t st);
 int sc_wgrad_simt_launch(int dtype, const ScArgs& a, cudaStream_t st);
 int sc_wgrad_parts(long long nvox_out);
+int sc_wgrad_simt_launch_parts(int dtype, const ScArgs& a, int nparts, cudaStream_t st);
+int sc_static_scratch(void** ptr, size_t* bytes);
 size_t sc_wgrad_workspace_bytes(int dtype, int taps, int Cin, int Cout, long long nvox_out);
 }  // namespace chop

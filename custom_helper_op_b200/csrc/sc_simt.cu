@@ -11,8 +11,17 @@
 #include "sc_common.cuh"
 #include "sc_entry.h"
 
+#include <mutex>
+
 namespace chop {
 namespace {
+
+// Scratch for chop_sparse_conv3d_bwd_noalloc: the per-CTA partial filter gradients live in this
+// file-scope device array instead of caller memory.  Every GPU that loads the library holds these
+// 4 MiB until the process exits.  In host code the name below is only a host-side stand-in for the
+// symbol - it is NOT a device address; the address a kernel may use comes from cudaGetSymbolAddress.
+constexpr size_t kStaticScratchBytes = (size_t)4 << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 template <typename T, typename ACC>
 __global__ void __launch_bounds__(256) sc_fwd_simt(const ScArgs a) {
@@ -210,6 +219,37 @@ int wgrad_t(const ScArgs& a, int nparts, cudaStream_t st) {
 }
 
 }  // namespace
+
+// Device address of g_static_scratch for the CURRENT device, looked up once per device (first call on
+// that device, with that device current) and cached.  Returns a cudaError_t value.
+int sc_static_scratch(void** ptr, size_t* bytes) {
+  constexpr int kMaxDevices = 64;
+  static void* cached[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return (int)cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    cached[dev] = p;
+  }
+  *ptr = cached[dev];
+  *bytes = kStaticScratchBytes;
+  return 0;
+}
+
+// Filter gradient with a caller-chosen number of partial slabs (the workspace holds nparts slabs).
+int sc_wgrad_simt_launch_parts(int dtype, const ScArgs& a, int nparts, cudaStream_t st) {
+  switch (dtype) {
+    case 0: return wgrad_t<float, float, float>(a, nparts, st);
+    case 1: return wgrad_t<double, double, double>(a, nparts, st);
+    default: return wgrad_t<__nv_bfloat16, float, float>(a, nparts, st);
+  }
+}
 
 int sc_wgrad_parts(long long nvox_out) {
   long long p = (nvox_out + 511) / 512;  // at least 512 voxels per CTA

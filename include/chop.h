@@ -138,6 +138,19 @@ CHOP_API int chop_sparse_conv3d_bwd(const chop_sc_desc *desc, const void *images
                                     void *images_grad, void *filter_grad, void *default_value_grad,
                                     void *workspace, size_t workspace_bytes, void *stream);
 
+/* No counterpart in the reference.  chop_sparse_conv3d_bwd without the workspace argument: the partial
+ * filter gradients are kept in a fixed 4 MiB device array inside the library, so the call allocates
+ * nothing and needs no scratch from the caller.  For hosts that may not call the CUDA allocator where
+ * this runs - their device memory belongs to a framework pool, or the loop has a fixed memory budget and
+ * cannot afford the device-wide synchronisation of cudaMalloc.  Limits: one partial slab
+ * ((fh*fw*fd*Cin*Cout + 1) accumulators of 4 bytes, 8 for float64) must fit in 4 MiB, else
+ * CHOP_ERR_WORKSPACE; the first call on a device resolves the array's address and should happen during
+ * set-up, before any stream capture; calls that overlap on one GPU race on the shared array. */
+CHOP_API int chop_sparse_conv3d_bwd_noalloc(const chop_sc_desc *desc, const void *images, const void *filters,
+                                            const void *default_value, const int32_t *base_plane,
+                                            const void *out_grad, void *images_grad, void *filter_grad,
+                                            void *default_value_grad, void *stream);
+
 /* Text for a status returned by any entry point (negative: chop_status, positive: CUDA). */
 CHOP_API const char *chop_status_string(int status);
 
