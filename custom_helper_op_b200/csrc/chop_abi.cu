@@ -10,6 +10,10 @@
 #include "cv_entry.h"
 #include "cv_launch.cuh"
 
+namespace chop {
+extern std::atomic<int> g_use_umma;
+}
+
 namespace {
 
 using chop::CvArgs;
@@ -296,6 +300,7 @@ int chop_set_tuning(const char* name, int value) {
   if (!std::strcmp(name, "bwd_chunk")) { g_bwd_chunk = value; return CHOP_OK; }
   if (!std::strcmp(name, "bwd_views")) { g_bwd_views = value; return CHOP_OK; }
   if (!std::strcmp(name, "tuned")) { g_tuned = value; return CHOP_OK; }
+  if (!std::strcmp(name, "umma")) { chop::g_use_umma = value; return CHOP_OK; }
   return CHOP_ERR_ATTR;
 }
 

@@ -9,9 +9,24 @@
 #include "sc_common.cuh"
 #include "sc_entry.h"
 
+#include <atomic>
+
+namespace chop {
+std::atomic<int> g_use_umma{1};  // tuning knob "umma": 0 forces the generic kernels
+}
+
 namespace {
 
 using chop::ScArgs;
+
+int run_fwd(int dtype, const ScArgs& a, cudaStream_t st) {
+  if (chop::g_use_umma.load() && chop::sc_umma_supported(dtype, a)) return chop::sc_umma_fwd_launch(a, st);
+  return chop::sc_fwd_simt_launch(dtype, a, st);
+}
+int run_dgrad(int dtype, const ScArgs& a, cudaStream_t st) {
+  if (chop::g_use_umma.load() && chop::sc_umma_supported(dtype, a)) return chop::sc_umma_dgrad_launch(a, st);
+  return chop::sc_dgrad_simt_launch(dtype, a, st);
+}
 
 int fill(const chop_sc_desc* d, ScArgs* a) {
   if (!d) return CHOP_ERR_NULL;
@@ -60,7 +75,7 @@ int chop_sparse_conv3d_fwd(const chop_sc_desc* d, const void* images, const void
   if (!images || !filters || !default_value || !base_plane || !output) return CHOP_ERR_NULL;
   a.images = images; a.filters = filters; a.default_value = default_value; a.base_plane = base_plane;
   a.output = output;
-  return chop::sc_fwd_simt_launch(d->dtype, a, static_cast<cudaStream_t>(stream));
+  return run_fwd(d->dtype, a, static_cast<cudaStream_t>(stream));
 }
 
 int chop_sparse_conv3d_bwd(const chop_sc_desc* d, const void* images, const void* filters, const void* default_value,
@@ -78,7 +93,7 @@ int chop_sparse_conv3d_bwd(const chop_sc_desc* d, const void* images, const void
   a.default_grad = default_value_grad; a.workspace = workspace;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (int e = chop::sc_wgrad_simt_launch(d->dtype, a, st)) return e;
-  return chop::sc_dgrad_simt_launch(d->dtype, a, st);
+  return run_dgrad(d->dtype, a, st);
 }
 
 // Same gradient as chop_sparse_conv3d_bwd, but the partial filter gradients go to a fixed 4 MiB array
@@ -113,7 +128,9 @@ int chop_sparse_conv3d_bwd_noalloc(const chop_sc_desc* d, const void* images, co
   a.default_grad = default_value_grad; a.workspace = scratch;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (int e = chop::sc_wgrad_simt_launch_parts(d->dtype, a, nparts, st)) return e;
-  return chop::sc_dgrad_simt_launch(d->dtype, a, st);
+  return run_dgrad(d->dtype, a, st);
 }
+
+int chop_umma_timeouts(void) { return chop::sc_umma_timeouts(); }
 
 }  // extern "C"

@@ -11,5 +11,9 @@ int sc_wgrad_simt_launch(int dtype, const ScArgs& a, cudaStream_t st);
 int sc_wgrad_parts(long long nvox_out);
 int sc_wgrad_simt_launch_parts(int dtype, const ScArgs& a, int nparts, cudaStream_t st);
 int sc_static_scratch(void** ptr, size_t* bytes);
+bool sc_umma_supported(int dtype, const ScArgs& a);
+int sc_umma_fwd_launch(const ScArgs& a, cudaStream_t st);
+int sc_umma_dgrad_launch(const ScArgs& a, cudaStream_t st);
+int sc_umma_timeouts();
 size_t sc_wgrad_workspace_bytes(int dtype, int taps, int Cin, int Cout, long long nvox_out);
 }  // namespace chop

@@ -1,0 +1,286 @@
+// Manifold 3-D convolution as an implicit GEMM on the 5th-generation tensor cores (tcgen05), for the
+// case the depth-band networks actually run: 3x3x3 filter, stride 1, dilation 1, bfloat16 storage,
+// float32 accumulation, 16 or 32 channels.
+//
+//   D[m][n] = sum_k A[m][k] * B[n][k]     m: 128 output voxels of a tile (one per thread)
+//                                          n: output channels (16 / 32)
+//                                          k: tap * CIN + input channel  (27 taps)
+// A is never materialised in global memory: every thread gathers, for its voxel and each tap, the CIN
+// contiguous bf16 channels of the neighbour voxel - resolving the per-pixel depth shift
+// d + base_plane[out] - base_plane[nbr] (custom_helper_op/cc/kernels/
+// sparse_conv3d_fast_fixed_param_op_gpu.cu.cc:78-113), padding with default_value - and writes them into
+// shared memory in the tensor core's canonical K-major layout (8-row x 16-byte core matrices, no
+// swizzle).  The filter (27*CIN*COUT bf16) is laid out once per CTA in the same form.  One elected thread
+// issues tcgen05.mma (M=128, N=COUT, K=16) per tap and 16 input channels, accumulating in tensor memory;
+// tcgen05.commit signals an mbarrier; the four warps then read their 32 accumulator rows back with
+// tcgen05.ld, round to bf16 and store 2*COUT contiguous bytes per voxel.
+//
+// A tile is processed in three rounds of nine taps (one filter row each) so that the A staging buffer is
+// 9*128*CIN*2 bytes and several CTAs fit on an SM: while one CTA waits for its MMAs another gathers.
+// The image gradient is the same kernel run over out_grad with the filter flipped in all three
+// dimensions, channels swapped and zero padding (sparse_conv3d_fast_op.cc:298-323).
+//
+// Every wait on the mbarrier is bounded; if it ever gives up the kernel raises a device-side flag
+// (readable through sc_umma_timeouts()), stops issuing work, frees its tensor memory and returns.
+#include <cuda_bf16.h>
+
+#include "sc_common.cuh"
+#include "sc_entry.h"
+
+namespace chop {
+namespace {
+
+__device__ int g_umma_timeouts = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// Shared-memory matrix descriptor, K-major, no swizzle: start address, leading byte offset (distance
+// between core matrices adjacent in K), stride byte offset (distance between 8-row groups), version 1.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t mbar, uint32_t parity) {
+  uint32_t ok = 0;
+  for (int it = 0; it < (1 << 24) && !ok; ++it) {
+    asm volatile(
+        "{\n.reg .pred P1;\nmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\nselp.u32 %0, 1, 0, P1;\n}\n"
+        : "=r"(ok)
+        : "r"(mbar), "r"(parity)
+        : "memory");
+  }
+  return ok != 0;
+}
+
+template <int N>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t* r);
+template <>
+__device__ __forceinline__ void tmem_ld<16>(uint32_t taddr, uint32_t* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                 "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr)
+               : "memory");
+}
+template <>
+__device__ __forceinline__ void tmem_ld<32>(uint32_t taddr, uint32_t* r) {
+  tmem_ld<16>(taddr, r);
+  tmem_ld<16>(taddr + 16, r + 16);
+}
+
+// CIN: channels of the gathered tensor (K per tap), COUT: channels produced (N).
+template <int CIN, int COUT, bool DGRAD>
+__global__ void __launch_bounds__(128) sc_umma_kernel(const ScArgs a, const long long nvox, const int ntiles) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t mbar_s;
+  __shared__ uint32_t tmem_base_s;
+  constexpr int KC = CIN / 8;                     // 16-byte k-chunks per tap
+  constexpr uint32_t LBO = 128, SBO = KC * 128;   // core-matrix strides in K and in M/N
+  constexpr int A_TAP_BYTES = 128 * CIN * 2;
+  constexpr int B_TAP_BYTES = COUT * CIN * 2;
+  unsigned char* sB = smem;                       // 27 taps
+  unsigned char* sA = smem + 27 * B_TAP_BYTES;    // 9 taps (one filter row)
+  const int tid = threadIdx.x, warp = tid >> 5;
+
+  const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(DGRAD ? a.out_grad : a.images);
+  __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(DGRAD ? a.images_grad : a.output);
+
+  // ---- filter -> canonical K-major B tiles: B[n][k] of tap t at sB + t*B_TAP_BYTES -----------------------
+  {
+    const unsigned short* flt = static_cast<const unsigned short*>(a.filters);  // [27][Cin_f][Cout_f]
+    for (int e = tid; e < 27 * COUT * CIN; e += 128) {
+      const int k = e % CIN, n = (e / CIN) % COUT, t = e / (CIN * COUT);
+      unsigned short w;
+      if (!DGRAD) w = __ldg(flt + ((size_t)t * CIN + k) * COUT + n);         // B[n=oc][k=ci] = f[t][ci][oc]
+      else w = __ldg(flt + ((size_t)(26 - t) * COUT + n) * CIN + k);          // B[n=ci][k=oc] = f[flip t][ci][oc]
+      *reinterpret_cast<unsigned short*>(sB + t * B_TAP_BYTES + (n / 8) * SBO + (k / 8) * LBO + (n % 8) * 16 + (k % 8) * 2) = w;
+    }
+  }
+  if (warp == 0) {
+    uint32_t slot = smem_u32(&tmem_base_s), ncols = 32;
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&mbar_s)), "r"(1) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t mbar = smem_u32(&mbar_s);
+  // instruction descriptor: D f32, A/B bf16, both K-major, N = COUT, M = 128
+  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(COUT >> 3) << 17) | ((128u >> 4) << 24);
+
+  // padding value of the gathered tensor, replicated over 8 bf16 (zero for the image gradient)
+  uint4 padv = make_uint4(0, 0, 0, 0);
+  if (!DGRAD) {
+    const unsigned d16 = __ldg(static_cast<const unsigned short*>(a.default_value));
+    const unsigned d32 = d16 | (d16 << 16);
+    padv = make_uint4(d32, d32, d32, d32);
+  }
+
+  uint32_t phase = 0;
+  bool alive = true;
+  const int H = a.H, W = a.W, D = a.D;
+  for (int tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
+    const long long v = (long long)tile * 128 + tid;
+    const bool vvalid = v < nvox;
+    int d = 0, c = 0, r = 0, b = 0, depth_abs = 0;
+    if (vvalid) {
+      long long t = v;
+      d = (int)(t % D); t /= D;
+      c = (int)(t % W); t /= W;
+      r = (int)(t % H);
+      b = (int)(t / H);
+      depth_abs = d + __ldg(a.base_plane + (b * H + r) * W + c);
+    }
+    unsigned char* a_row = sA + (tid / 8) * SBO + (tid % 8) * 16;
+
+    for (int fr = 0; fr < 3; ++fr) {
+      // ---- gather nine taps (filter row fr) into the staging buffer ---------------------------------------
+      const int orow = r - 1 + fr;
+#pragma unroll
+      for (int fc = 0; fc < 3; ++fc) {
+        const int ocol = c - 1 + fc;
+        const bool inb = vvalid && !oob(orow, H) && !oob(ocol, W);
+        int pix = 0, ind0 = 0;
+        if (inb) {
+          pix = (b * H + orow) * W + ocol;
+          ind0 = depth_abs - 1 - __ldg(a.base_plane + pix);  // band-local depth of tap fz = 0
+        }
+#pragma unroll
+        for (int fz = 0; fz < 3; ++fz) {
+          const int ind = ind0 + fz;
+          const bool ok = inb && !oob(ind, D);
+          const uint4* p = reinterpret_cast<const uint4*>(src + ((size_t)pix * D + (ok ? ind : 0)) * CIN);
+          unsigned char* dstA = a_row + (fc * 3 + fz) * A_TAP_BYTES;
+#pragma unroll
+          for (int kc = 0; kc < KC; ++kc) {
+            uint4 x = vvalid ? padv : make_uint4(0, 0, 0, 0);
+            if (ok) x = __ldg(p + kc);
+            *reinterpret_cast<uint4*>(dstA + kc * LBO) = x;
+          }
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncthreads();
+      // ---- one thread issues the round's MMAs ----------------------------------------------------------------
+      if (tid == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int tt = 0; tt < 9; ++tt) {
+#pragma unroll
+          for (int k16 = 0; k16 < CIN / 16; ++k16) {
+            const uint64_t da = umma_desc(smem_u32(sA + tt * A_TAP_BYTES + k16 * 2 * LBO), LBO, SBO);
+            const uint64_t db = umma_desc(smem_u32(sB + (fr * 9 + tt) * B_TAP_BYTES + k16 * 2 * LBO), LBO, SBO);
+            umma_bf16(tmem, da, db, IDESC, (fr | tt | k16) != 0 ? 1u : 0u);
+          }
+        }
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
+      }
+      // ---- everyone waits until the tensor core has consumed the staging buffer ------------------------------
+      const bool done = mbar_wait(mbar, phase);
+      phase ^= 1;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (!__syncthreads_and(done)) {
+        if (tid == 0) atomicAdd(&g_umma_timeouts, 1);
+        alive = false;
+        break;
+      }
+    }
+    if (!alive) break;
+
+    // ---- epilogue: accumulator rows -> bf16 -> global ------------------------------------------------------------
+    uint32_t acc[COUT];
+    tmem_ld<COUT>(tmem + ((uint32_t)(warp * 32) << 16), acc);
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    if (vvalid) {
+      uint4* o = reinterpret_cast<uint4*>(dst + (size_t)v * COUT);
+#pragma unroll
+      for (int q = 0; q < COUT / 8; ++q) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(acc[q * 8 + 2 * i]), __uint_as_float(acc[q * 8 + 2 * i + 1]));
+          w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        o[q] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    uint32_t ncols = 32;
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(ncols) : "memory");
+  }
+}
+
+template <int CIN, int COUT, bool DGRAD>
+int launch(const ScArgs& a, long long nvox, cudaStream_t st) {
+  auto k = sc_umma_kernel<CIN, COUT, DGRAD>;
+  const size_t smem = (size_t)27 * COUT * CIN * 2 + (size_t)9 * 128 * CIN * 2 + 1024;
+  static bool attr_set = false;  // per instantiation; setting it again is harmless
+  if (smem > 48 * 1024 && !attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int ntiles = (int)((nvox + 127) / 128);
+  int per_sm = (int)((size_t)220 * 1024 / (smem + 2048));
+  if (per_sm > 8) per_sm = 8;
+  if (per_sm < 1) per_sm = 1;
+  int grid = 148 * per_sm;
+  if (grid > ntiles) grid = ntiles;
+  k<<<grid, 128, smem, st>>>(a, nvox, ntiles);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+bool sc_umma_supported(int dtype, const ScArgs& a) {
+  return dtype == 2 && a.fh == 3 && a.fw == 3 && a.fd == 3 && a.sr == 1 && a.sc == 1 && a.sd == 1 && a.dr == 1 && a.dc == 1 &&
+         a.dd == 1 && (a.Cin == 16 || a.Cin == 32) && (a.Cout == 16 || a.Cout == 32) &&
+         a.nvox_in < ((long long)1 << 31) - 128;
+}
+
+int sc_umma_fwd_launch(const ScArgs& a, cudaStream_t st) {
+  if (a.Cin == 16 && a.Cout == 16) return launch<16, 16, false>(a, a.nvox_out, st);
+  if (a.Cin == 16 && a.Cout == 32) return launch<16, 32, false>(a, a.nvox_out, st);
+  if (a.Cin == 32 && a.Cout == 16) return launch<32, 16, false>(a, a.nvox_out, st);
+  return launch<32, 32, false>(a, a.nvox_out, st);
+}
+
+// gathers out_grad (Cout channels) and produces images_grad (Cin channels)
+int sc_umma_dgrad_launch(const ScArgs& a, cudaStream_t st) {
+  if (a.Cin == 16 && a.Cout == 16) return launch<16, 16, true>(a, a.nvox_in, st);
+  if (a.Cin == 16 && a.Cout == 32) return launch<32, 16, true>(a, a.nvox_in, st);
+  if (a.Cin == 32 && a.Cout == 16) return launch<16, 32, true>(a, a.nvox_in, st);
+  return launch<32, 32, true>(a, a.nvox_in, st);
+}
+
+int sc_umma_timeouts() {
+  int v = -1;
+  if (cudaMemcpyFromSymbol(&v, g_umma_timeouts, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+
+}  // namespace chop

@@ -151,6 +151,11 @@ CHOP_API int chop_sparse_conv3d_bwd_noalloc(const chop_sc_desc *desc, const void
                                             const void *out_grad, void *images_grad, void *filter_grad,
                                             void *default_value_grad, void *stream);
 
+/* Diagnostic: how many times a tensor-core convolution kernel gave up waiting for its MMAs since the
+ * library was loaded (0 in a healthy run; the affected call's output is then incomplete).  Copies one
+ * int from the device, so it synchronises with the current device; -1 if that copy fails. */
+CHOP_API int chop_umma_timeouts(void);
+
 /* Text for a status returned by any entry point (negative: chop_status, positive: CUDA). */
 CHOP_API const char *chop_status_string(int status);
 
@@ -159,7 +164,8 @@ CHOP_API int chop_version(void);
 
 /* Tuning knobs for experiments: "fwd_chunk", "bwd_chunk" (depth planes per warp work item, 0 =
  * heuristic), "bwd_views" (source views per backward pass, 0 = heuristic), "tuned" (1 = use the compile-time-C
- * kernels where one exists, 0 = always the generic kernels).  Returns CHOP_ERR_ATTR
+ * kernels where one exists, 0 = always the generic kernels), "umma" (1 = tensor-core manifold convolution
+ * where supported, 0 = always the generic kernels).  Returns CHOP_ERR_ATTR
  * for an unknown name.  Process-wide; not part of the reference surface. */
 CHOP_API int chop_set_tuning(const char *name, int value);
 

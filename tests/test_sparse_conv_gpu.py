@@ -62,6 +62,28 @@ def test_bfloat16(shape):
     assert abs(float(dg) - float(dg_w)) <= 2e-3 * max(1.0, abs(float(dg_w)))
 
 
+@pytest.mark.parametrize("shape", [(1, 12, 14, 9, 16, 16), (2, 9, 11, 9, 16, 32), (1, 8, 8, 5, 32, 16), (1, 7, 9, 9, 32, 32),
+                                   (1, 40, 48, 9, 16, 16)])
+def test_tensor_core_kernel_matches_generic_kernel(shape):
+    """The tcgen05 implicit-GEMM path (bf16, 3x3x3, stride 1) against the generic kernels on the same bf16
+    inputs: both accumulate the same bf16 products in float32, so they agree to accumulation order, and
+    after rounding the output to bf16 they may differ by one bf16 ulp at most."""
+    from custom_helper_op_b200 import _lib
+    B, H, W, D, Cin, Cout = shape
+    images, filters, defv, bp, _ = make_case(13, B, H, W, D, Cin, Cout, (3, 3, 3), 2 * D + 6, np.float32)
+    og = np.random.default_rng(14).uniform(-1, 1, (B, H, W, D, Cout)).astype(np.float32)
+    res = {}
+    for umma in (1, 0):
+        try:
+            _lib.set_tuning("umma", umma)
+            res[umma] = run_gpu(images - 0.5, filters * 0.3, defv, bp, og, (1, 1, 1), (1, 1, 1), True, torch.bfloat16)
+        finally:
+            _lib.set_tuning("umma", 1)
+    assert _lib.lib().chop_umma_timeouts() == 0
+    for x, y in zip(res[1][:2], res[0][:2]):   # output and images_grad
+        assert helpers.rel_err(x, y) <= 2.0 ** -7
+
+
 def test_autograd_wrapper():
     images, filters, defv, bp, _ = make_case(11, 1, 6, 7, 5, 4, 3, (3, 3, 3), 12, np.float32)
     want = oracle.sparse_conv3d_fwd(images, filters, defv, bp, dtype=np.float32)
