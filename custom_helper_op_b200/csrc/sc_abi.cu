@@ -23,6 +23,15 @@ int run_fwd(int dtype, const ScArgs& a, cudaStream_t st) {
   if (chop::g_use_umma.load() && chop::sc_umma_supported(dtype, a)) return chop::sc_umma_fwd_launch(a, st);
   return chop::sc_fwd_simt_launch(dtype, a, st);
 }
+int run_wgrad(int dtype, const ScArgs& a, int nparts, cudaStream_t st) {
+  if (chop::g_use_umma.load() && chop::sc_umma_supported(dtype, a)) {
+    // a persistent CTA per partial slab; more CTAs than 128-voxel tiles would leave slabs unwritten
+    const long long ntiles = (a.nvox_out + 127) / 128;
+    if (nparts > ntiles) nparts = (int)ntiles;
+    return chop::sc_umma_wgrad_launch(a, nparts, st);
+  }
+  return chop::sc_wgrad_simt_launch_parts(dtype, a, nparts, st);
+}
 int run_dgrad(int dtype, const ScArgs& a, cudaStream_t st) {
   if (chop::g_use_umma.load() && chop::sc_umma_supported(dtype, a)) return chop::sc_umma_dgrad_launch(a, st);
   return chop::sc_dgrad_simt_launch(dtype, a, st);
@@ -92,7 +101,7 @@ int chop_sparse_conv3d_bwd(const chop_sc_desc* d, const void* images, const void
   a.out_grad = out_grad; a.images_grad = images_grad; a.filter_grad = filter_grad;
   a.default_grad = default_value_grad; a.workspace = workspace;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (int e = chop::sc_wgrad_simt_launch(d->dtype, a, st)) return e;
+  if (int e = run_wgrad(d->dtype, a, chop::sc_wgrad_parts(a.nvox_out), st)) return e;
   return run_dgrad(d->dtype, a, st);
 }
 
@@ -127,7 +136,7 @@ int chop_sparse_conv3d_bwd_noalloc(const chop_sc_desc* d, const void* images, co
   a.out_grad = out_grad; a.images_grad = images_grad; a.filter_grad = filter_grad;
   a.default_grad = default_value_grad; a.workspace = scratch;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (int e = chop::sc_wgrad_simt_launch_parts(d->dtype, a, nparts, st)) return e;
+  if (int e = run_wgrad(d->dtype, a, nparts, st)) return e;
   return run_dgrad(d->dtype, a, st);
 }
 

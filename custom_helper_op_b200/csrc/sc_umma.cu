@@ -234,6 +234,230 @@ __global__ void __launch_bounds__(128) sc_umma_kernel(const ScArgs a, const long
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------
+// Filter gradient on the tensor cores:  dW[k][n] = sum over voxels m of A[m][k] * G[m][n]
+// (k = tap*CIN + input channel, n = output channel, A = the same gathered tile as in the forward pass,
+// G = out_grad).  The reduction runs over voxels, so both operands are used "MN-major": the staging
+// buffers hold [8 voxels][8 channels] core matrices, 16 voxels per MMA step, and the M dimension of
+// the MMA is a group of 128 consecutive k (128/CIN taps).  ceil(27*CIN/128) such groups each own COUT
+// tensor-memory columns, and the accumulators stay in tensor memory across ALL voxel tiles of the CTA;
+// they are read once at the end and written as this CTA's partial [27*CIN][COUT] slab, which the same
+// fixed-order reduction kernel as the generic path sums over the CTAs.
+// d(default_value) (dynamic_default only) is accumulated on the CUDA cores while gathering.
+// ---------------------------------------------------------------------------------------------------------
+template <int CIN, int COUT>
+__global__ void __launch_bounds__(128) sc_umma_wgrad_kernel(const ScArgs a, const int ntiles) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t mbar_s;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ float red_s[128];
+  constexpr int KC = CIN / 8;            // 16-byte channel chunks per tap
+  constexpr int TPR = 128 / CIN;         // taps per round (one 128-row M group)
+  constexpr int NT = (27 + TPR - 1) / TPR;
+  constexpr int TMEM_COLS = NT * COUT <= 32 ? 32 : (NT * COUT <= 64 ? 64 : (NT * COUT <= 128 ? 128 : 256));
+  constexpr uint32_t SBO = 128;                    // between 8-channel groups (M / N direction)
+  constexpr uint32_t LBO_A = 16 * 128;             // between 8-voxel groups of the A staging tile
+  constexpr uint32_t LBO_G = (COUT / 8) * 128;     // between 8-voxel groups of the G tile
+  unsigned char* sA = smem;                        // 16 voxel groups x 2048 B
+  unsigned char* sG = smem + 16 * LBO_A;           // 16 voxel groups x LBO_G
+  float* wsum = reinterpret_cast<float*>(sG + 16 * LBO_G);  // [27][COUT], dynamic_default only
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const __nv_bfloat16* img = static_cast<const __nv_bfloat16*>(a.images);
+  const __nv_bfloat16* og = static_cast<const __nv_bfloat16*>(a.out_grad);
+
+  if (a.dynamic_default) {
+    const __nv_bfloat16* flt = static_cast<const __nv_bfloat16*>(a.filters);
+    for (int e = tid; e < 27 * COUT; e += 128) {
+      const int t = e / COUT, n = e % COUT;
+      float s = 0.f;
+      for (int ci = 0; ci < CIN; ++ci) s += __bfloat162float(flt[((size_t)t * CIN + ci) * COUT + n]);
+      wsum[e] = s;
+    }
+  }
+  if (warp == 0) {
+    uint32_t slot = smem_u32(&tmem_base_s), ncols = TMEM_COLS;
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&mbar_s)), "r"(1) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t mbar = smem_u32(&mbar_s);
+  // D f32, A/B bf16, both operands MN-major (bits 15, 16), N = COUT, M = 128
+  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(COUT >> 3) << 17) |
+                             ((128u >> 4) << 24);
+  const unsigned d16 = __ldg(static_cast<const unsigned short*>(a.default_value));
+  const unsigned d32 = d16 | (d16 << 16);
+  const uint4 padv = make_uint4(d32, d32, d32, d32);
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+
+  uint32_t phase = 0;
+  bool alive = true;
+  bool first = true;
+  float dacc = 0.f;
+  const int H = a.H, W = a.W, D = a.D;
+  unsigned char* a_row = sA + (tid / 8) * LBO_A + (tid % 8) * 16;
+  unsigned char* g_row = sG + (tid / 8) * LBO_G + (tid % 8) * 16;
+
+  for (int tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
+    const long long v = (long long)tile * 128 + tid;
+    const bool vvalid = v < a.nvox_out;
+    int d = 0, c = 0, r = 0, b = 0, depth_abs = 0;
+    float gf[COUT];
+#pragma unroll
+    for (int n = 0; n < COUT; ++n) gf[n] = 0.f;
+    if (vvalid) {
+      long long t = v;
+      d = (int)(t % D); t /= D;
+      c = (int)(t % W); t /= W;
+      r = (int)(t % H);
+      b = (int)(t / H);
+      depth_abs = d + __ldg(a.base_plane + (b * H + r) * W + c);
+    }
+    // out_grad row of this voxel -> G tile (previous tile's MMAs have completed: every round waits)
+#pragma unroll
+    for (int nc = 0; nc < COUT / 8; ++nc) {
+      uint4 x = zero4;
+      if (vvalid) x = __ldg(reinterpret_cast<const uint4*>(og + (size_t)v * COUT) + nc);
+      *reinterpret_cast<uint4*>(g_row + nc * SBO) = x;
+      if (a.dynamic_default) {
+        const unsigned w4[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          gf[nc * 8 + 2 * i] = __uint_as_float(w4[i] << 16);
+          gf[nc * 8 + 2 * i + 1] = __uint_as_float(w4[i] & 0xffff0000u);
+        }
+      }
+    }
+
+    for (int rd = 0; rd < NT; ++rd) {
+      // ---- gather the taps of M group rd ---------------------------------------------------------------------
+#pragma unroll
+      for (int tt = 0; tt < TPR; ++tt) {
+        const int t = rd * TPR + tt;
+        bool ok = false;
+        bool real_tap = t < 27;
+        size_t off = 0;
+        if (real_tap && vvalid) {
+          const int fz = t % 3, fc = (t / 3) % 3, fr = t / 9;
+          const int orow = r - 1 + fr, ocol = c - 1 + fc;
+          if (!oob(orow, H) && !oob(ocol, W)) {
+            const int pix = (b * H + orow) * W + ocol;
+            const int ind = depth_abs - 1 + fz - __ldg(a.base_plane + pix);
+            if (!oob(ind, D)) {
+              ok = true;
+              off = ((size_t)pix * D + ind) * CIN;
+            }
+          }
+          if (!ok && a.dynamic_default) {
+            // fixed_param_op_gpu.cu.cc:273-277: d(default) += sum_n (sum_ci filter[t][ci][n]) * out_grad[m][n]
+            const float* ws = wsum + t * COUT;
+#pragma unroll
+            for (int n = 0; n < COUT; ++n) dacc = fmaf(ws[n], gf[n], dacc);
+          }
+        }
+#pragma unroll
+        for (int kc = 0; kc < KC; ++kc) {
+          uint4 x = (real_tap && vvalid) ? padv : zero4;
+          if (ok) x = __ldg(reinterpret_cast<const uint4*>(img + off) + kc);
+          *reinterpret_cast<uint4*>(a_row + (tt * KC + kc) * SBO) = x;
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncthreads();
+      if (tid == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {  // 16 voxels (two 8-voxel groups) per MMA
+          const uint64_t da = umma_desc(smem_u32(sA + ks * 2 * LBO_A), LBO_A, SBO);
+          const uint64_t db = umma_desc(smem_u32(sG + ks * 2 * LBO_G), LBO_G, SBO);
+          umma_bf16(tmem + rd * COUT, da, db, IDESC, (first && ks == 0) ? 0u : 1u);
+        }
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
+      }
+      const bool done = mbar_wait(mbar, phase);
+      phase ^= 1;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (!__syncthreads_and(done)) {
+        if (tid == 0) atomicAdd(&g_umma_timeouts, 1);
+        alive = false;
+        break;
+      }
+    }
+    first = false;
+  }
+
+  // ---- accumulators -> this CTA's partial slab -----------------------------------------------------------------
+  constexpr int K = 27 * CIN;
+  float* part = static_cast<float*>(a.workspace) + (size_t)blockIdx.x * ((size_t)K * COUT + 1);
+  if (alive) {
+#pragma unroll
+    for (int rd = 0; rd < NT; ++rd) {
+      uint32_t acc[COUT];
+      if (!first) {
+        tmem_ld<COUT>(tmem + ((uint32_t)(warp * 32) << 16) + rd * COUT, acc);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      }
+      const int k = rd * 128 + tid;
+      if (k < K) {
+#pragma unroll
+        for (int n = 0; n < COUT; ++n) part[(size_t)k * COUT + n] = first ? 0.f : __uint_as_float(acc[n]);
+      }
+    }
+  }
+  red_s[tid] = dacc;
+  __syncthreads();
+  for (int o = 64; o > 0; o >>= 1) {
+    if (tid < o) red_s[tid] += red_s[tid + o];
+    __syncthreads();
+  }
+  if (tid == 0) part[(size_t)K * COUT] = red_s[0];
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    uint32_t ncols = TMEM_COLS;
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(ncols) : "memory");
+  }
+}
+
+__global__ void sc_umma_wgrad_reduce(const float* part, int nparts, long long n_el, float* filter_grad, float* default_grad) {
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e > n_el) return;
+  float s = 0.f;
+  for (int p = 0; p < nparts; ++p) s += part[(size_t)p * (n_el + 1) + e];
+  if (e < n_el) filter_grad[e] = s;
+  else *default_grad = s;
+}
+
+template <int CIN, int COUT>
+int launch_wgrad(const ScArgs& a, int nparts, cudaStream_t st) {
+  auto k = sc_umma_wgrad_kernel<CIN, COUT>;
+  const size_t smem = (size_t)16 * 2048 + (size_t)16 * (COUT / 8) * 128 + (size_t)27 * COUT * 4 + 1024;
+  static bool attr_set = false;
+  if (smem > 48 * 1024 && !attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int ntiles = (int)((a.nvox_out + 127) / 128);
+  k<<<nparts, 128, smem, st>>>(a, ntiles);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  const long long n_el = (long long)27 * CIN * COUT;
+  sc_umma_wgrad_reduce<<<(unsigned)((n_el + 1 + 255) / 256), 256, 0, st>>>(static_cast<const float*>(a.workspace), nparts, n_el,
+                                                                           static_cast<float*>(a.filter_grad),
+                                                                           static_cast<float*>(a.default_grad));
+  return (int)cudaGetLastError();
+}
+
 template <int CIN, int COUT, bool DGRAD>
 int launch(const ScArgs& a, long long nvox, cudaStream_t st) {
   auto k = sc_umma_kernel<CIN, COUT, DGRAD>;
@@ -275,6 +499,14 @@ int sc_umma_dgrad_launch(const ScArgs& a, cudaStream_t st) {
   if (a.Cin == 16 && a.Cout == 32) return launch<32, 16, true>(a, a.nvox_in, st);
   if (a.Cin == 32 && a.Cout == 16) return launch<16, 32, true>(a, a.nvox_in, st);
   return launch<32, 32, true>(a, a.nvox_in, st);
+}
+
+// nparts partial slabs of (27*Cin*Cout + 1) floats must fit in the workspace; every CTA writes one.
+int sc_umma_wgrad_launch(const ScArgs& a, int nparts, cudaStream_t st) {
+  if (a.Cin == 16 && a.Cout == 16) return launch_wgrad<16, 16>(a, nparts, st);
+  if (a.Cin == 16 && a.Cout == 32) return launch_wgrad<16, 32>(a, nparts, st);
+  if (a.Cin == 32 && a.Cout == 16) return launch_wgrad<32, 16>(a, nparts, st);
+  return launch_wgrad<32, 32>(a, nparts, st);
 }
 
 int sc_umma_timeouts() {

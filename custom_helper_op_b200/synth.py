@@ -127,6 +127,21 @@ def test_case(seed, B, N, H, W, C, D, camera="random", dtype=np.float64):
                 Ts=cast(Ts))
 
 
+def manifold_conv(seed, B=1, H=256, W=320, D=9, Cin=16, Cout=16, planes=64, with_grad=True):
+    """Manifold-convolution workload: a band of D planes around a smooth coarse depth index.
+    Activations and weights ~ N(0, 0.1^2), default_value 0; base_plane = clip(idx - D//2, 0, planes - D)."""
+    rng = np.random.default_rng(seed)
+    images = (rng.standard_normal((B, H, W, D, Cin)) * 0.1).astype(np.float32)
+    filters = (rng.standard_normal((3, 3, 3, Cin, Cout)) * 0.1).astype(np.float32)
+    centre = smooth_depth_map(rng, B, H, W)
+    idx = np.rint((centre - 500.0) * (planes - 1) / 400.0)
+    base_plane = np.clip(idx - D // 2, 0, planes - D).astype(np.int32)[..., None]
+    out = dict(images=images, filters=filters, default_value=np.float32(0.0), base_plane=base_plane)
+    if with_grad:
+        out["out_grad"] = rng.standard_normal((B, H, W, D, Cout)).astype(np.float32)
+    return out
+
+
 # The benchmark / parity configurations.
 CONFIGS = {
     # name: kind, kwargs
