@@ -207,8 +207,9 @@ def gpu_main(args):
     t = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
     d_lo, d_hi = 0, D
     if args.shard == "depth" and world > 1:
-        per = (D + world - 1) // world
-        d_lo, d_hi = min(D, rank * per), min(D, (rank + 1) * per)
+        from custom_helper_op_b200 import shard
+        mine = shard.partition(B, D, world)[rank][0]   # B = 1: every rank gets one depth range of the item
+        d_lo, d_hi = mine.d_begin, mine.d_end
     gen = torch.Generator(device=dev)
     gen.manual_seed(1234 + rank)
     cost_grad = torch.randn((B, H, W, D, C), device=dev, generator=gen)
