@@ -281,14 +281,15 @@ def gpu_main(args):
     units_total = units_rank * world if args.shard == "batch" else B * H * W * D * N
     value = units_total / (ms_per_step * 1e-3)
 
-    # a short probe loop after the timed region so the clock sampler sees load even for small K
-    if rank == 0 and (t_wall1 - t_wall0) < 1.0 and not args.profile:
-        t_end = time.time() + 1.0
-        while time.time() < t_end:
-            for _ in range(50):
-                fwd()
-                bwd()
-            torch.cuda.synchronize()
+    # A short probe loop after the timed region so the clock sampler sees load even for small K.  Every
+    # rank runs the same number of steps (derived from the reduced step time, identical on all ranks):
+    # with depth sharding a step contains a collective, so the ranks must stay in lockstep.
+    if ms_per_step * K < 1000.0 and not args.profile:
+        n_probe = int(min(20000, max(1, 1000.0 / max(ms_per_step, 1e-3))))
+        for _ in range(n_probe):
+            fwd()
+            bwd()
+        barrier()
     if rank == 0:
         sampler.stop()
 
