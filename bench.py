@@ -362,6 +362,75 @@ def gpu_main(args):
         dist.destroy_process_group()
 
 
+def sparse_conv_main(args):
+    """Secondary workload (not the headline line): manifold 3-D convolution forward + backward, c4:
+    B=1, 256x320, 9-plane band, 3x3x3, 16->16 channels, bf16 storage / fp32 accumulate.  Single GPU."""
+    import torch
+
+    from custom_helper_op_b200 import _lib, synth
+    from custom_helper_op_b200.python.ops import custom_helper_ops as ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    w = synth.manifold_conv(20246)
+    img = torch.from_numpy(w["images"]).to(dev).to(torch.bfloat16)
+    flt = torch.from_numpy(w["filters"]).to(dev).to(torch.bfloat16)
+    og = torch.from_numpy(w["out_grad"]).to(dev).to(torch.bfloat16)
+    bp = torch.from_numpy(w["base_plane"]).to(dev)
+    defv = torch.zeros((), dtype=torch.bfloat16, device=dev)
+    B, H, W, D, Cin = img.shape
+    Cout = flt.shape[4]
+    nvox = B * H * W * D
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > L2: the tensors (24 MB each) would stay resident
+
+    def step():
+        ops.sparse_conv3d_forward(img, flt, defv, bp)
+        ops.sparse_conv3d_backward(img, flt, defv, bp, og)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    K = args.steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    for i in range(K):
+        if not args.profile:
+            flush.zero_()
+        ev[i][0].record()
+        ops.sparse_conv3d_forward(img, flt, defv, bp)
+        ev[i][1].record()
+        ops.sparse_conv3d_backward(img, flt, defv, bp, og)
+        ev[i][2].record()
+    torch.cuda.synchronize()
+    fwd_ms = float(np.mean([e[0].elapsed_time(e[1]) for e in ev]))
+    bwd_ms = float(np.mean([e[1].elapsed_time(e[2]) for e in ev]))
+    # algorithmic bytes: every activation tensor once (bf16), weights, base_plane
+    act = nvox * Cin * 2
+    fwd_b = act + nvox * Cout * 2 + 27 * Cin * Cout * 2 + B * H * W * 4
+    bwd_b = 2 * (act + nvox * Cout * 2) + act + 27 * Cin * Cout * 6 + 2 * B * H * W * 4   # wgrad reads img+og, dgrad reads og writes img_grad
+    flops_fwd = 2.0 * nvox * 27 * Cin * Cout
+    peak, peak_kind = measured_peak()
+    tpeak = 1643.8
+    try:
+        tpeak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        pass
+    ms = fwd_ms + bwd_ms
+    out = {"metric": "sparse_conv3d_fwd_bwd_voxels_per_s", "value": nvox / (ms * 1e-3), "unit": "voxels/s", "n_gpus": 1,
+           "steps": K, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+           "config": {"workload": "c4_sparse_conv: SparseConv3DFast fwd+bwd, B=%d, %dx%d, band of %d planes, 3x3x3, %d->%d, bf16/fp32-acc"
+                                  % (B, H, W, D, Cin, Cout), "l2": "flushed between steps (256 MB write)"},
+           "gpu_launches": 4 * K, "umma_timeouts": _lib.lib().chop_umma_timeouts(),
+           "roofline": {"bound": "hbm", "kernel": "sc_umma_kernel (forward)", "achieved": fwd_b / (fwd_ms * 1e-3) / 1e9, "peak": peak,
+                        "peak_source": peak_kind, "unit": "GB/s", "frac": fwd_b / (fwd_ms * 1e-3) / 1e9 / peak, "traffic": None,
+                        "fwd": {"ms": fwd_ms, "algorithmic_bytes": fwd_b, "tflops": flops_fwd / (fwd_ms * 1e-3) / 1e12,
+                                "tensor_frac_of_measured": flops_fwd / (fwd_ms * 1e-3) / 1e12 / tpeak},
+                        "bwd": {"ms": bwd_ms, "algorithmic_bytes": bwd_b, "tflops": 2 * flops_fwd / (bwd_ms * 1e-3) / 1e12,
+                                "tensor_frac_of_measured": 2 * flops_fwd / (bwd_ms * 1e-3) / 1e12 / tpeak}},
+           "cpu_baseline": None, "e2e": None}
+    print(json.dumps(out), flush=True)
+
+
 def reference_main(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -397,7 +466,13 @@ def main():
     ap.add_argument("--profile", action="store_true",
                     help="device-timed loop only (no clock probe loop, e2e leg or CPU baseline): the command to run under ncu")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload == "c4_sparse_conv":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference has no CPU kernel for SparseConv3DFast and its "
+                                                                  "GPU kernels are warp-cooperative (not compilable for the host)"}))
+        else:
+            sparse_conv_main(args)
+    elif args.impl == "reference":
         reference_main(args)
     else:
         gpu_main(args)

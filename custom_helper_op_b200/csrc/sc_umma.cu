@@ -428,13 +428,26 @@ __global__ void __launch_bounds__(128) sc_umma_wgrad_kernel(const ScArgs a, cons
   }
 }
 
-__global__ void sc_umma_wgrad_reduce(const float* part, int nparts, long long n_el, float* filter_grad, float* default_grad) {
-  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (e > n_el) return;
+// Sum of the per-CTA partial slabs in a fixed order (deterministic).  A block owns 32 consecutive
+// elements; its 8 warps each add every 8th slab with coalesced 128-byte reads, then the 8 warp sums are
+// added in warp order.  Element n_el is the default-value gradient.
+__global__ void __launch_bounds__(256) sc_umma_wgrad_reduce(const float* part, int nparts, long long n_el, float* filter_grad,
+                                                            float* default_grad) {
+  __shared__ float sm[8][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long e = (long long)blockIdx.x * 32 + lane;
   float s = 0.f;
-  for (int p = 0; p < nparts; ++p) s += part[(size_t)p * (n_el + 1) + e];
-  if (e < n_el) filter_grad[e] = s;
-  else *default_grad = s;
+  if (e <= n_el)
+    for (int p = warp; p < nparts; p += 8) s += part[(size_t)p * (n_el + 1) + e];
+  sm[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0 && e <= n_el) {
+    float t = sm[0][lane];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) t += sm[w][lane];
+    if (e < n_el) filter_grad[e] = t;
+    else *default_grad = t;
+  }
 }
 
 template <int CIN, int COUT>
@@ -452,7 +465,7 @@ int launch_wgrad(const ScArgs& a, int nparts, cudaStream_t st) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   const long long n_el = (long long)27 * CIN * COUT;
-  sc_umma_wgrad_reduce<<<(unsigned)((n_el + 1 + 255) / 256), 256, 0, st>>>(static_cast<const float*>(a.workspace), nparts, n_el,
+  sc_umma_wgrad_reduce<<<(unsigned)((n_el + 1 + 31) / 32), 256, 0, st>>>(static_cast<const float*>(a.workspace), nparts, n_el,
                                                                            static_cast<float*>(a.filter_grad),
                                                                            static_cast<float*>(a.default_grad));
   return (int)cudaGetLastError();
