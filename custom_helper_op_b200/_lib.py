@@ -62,6 +62,8 @@ def lib():
         L.chop_sparse_conv3d_bwd.argtypes = [ctypes.POINTER(ScDesc)] + [vp] * 9 + [ctypes.c_size_t, vp]
         L.chop_sparse_conv3d_bwd_noalloc.restype = ctypes.c_int
         L.chop_sparse_conv3d_bwd_noalloc.argtypes = [ctypes.POINTER(ScDesc)] + [vp] * 9
+        L.chop_copy_2d_async.restype = ctypes.c_int
+        L.chop_copy_2d_async.argtypes = [vp, ctypes.c_size_t, vp, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, vp]
         L.chop_umma_timeouts.restype = ctypes.c_int
         L.chop_status_string.restype = ctypes.c_char_p
         L.chop_status_string.argtypes = [ctypes.c_int]

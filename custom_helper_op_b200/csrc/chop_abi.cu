@@ -76,12 +76,20 @@ int validate(const chop_cv_desc* d, CvArgs* a, Typed* ty) {
   return 0;
 }
 
+// CostVolume MEAN (fused arithmetic) with a common channel count runs the compile-time-C kernels of
+// cv_tuned.cuh, which use four channels per lane for float32 and bfloat16 features alike.
+bool tuned_eligible(const chop_cv_desc* d, const CvArgs& a) {
+  return g_tuned.load() && d->kind == CHOP_COST_VOLUME && d->reduce == CHOP_REDUCE_MEAN &&
+         (d->dtype == CHOP_F32 || d->dtype == CHOP_BF16) && (a.C == 8 || a.C == 16 || a.C == 32 || a.C == 64);
+}
+
 // Channel slice per lane and lanes per pixel.
-int plan_lanes(const chop_cv_desc* d, const CvArgs& a, int* cpl, int* lgl) {
+int plan_lanes(const chop_cv_desc* d, const CvArgs& a, int* cpl, int* lgl, bool strict) {
   int c = 1;
   if (d->dtype == CHOP_F32 && a.C % 4 == 0) c = 4;
   if (d->dtype == CHOP_F64 && a.C % 2 == 0) c = 2;
   if (d->dtype == CHOP_BF16 && a.C % 8 == 0) c = 8;
+  if (!strict && tuned_eligible(d, a)) c = 4;
   const int lanes = (a.C + c - 1) / c;
   if (lanes > 32) return CHOP_ERR_UNSUPPORTED;
   *cpl = c;
@@ -146,7 +154,7 @@ int chop_cost_volume_fwd(const chop_cv_desc* d, const void* ref, const void* src
   if (d->kind != CHOP_COST_VOLUME_V2 && !offsets) return CHOP_ERR_NULL;
   if (a.d_begin == a.d_end) return CHOP_OK;
   int cpl, lgl;
-  if (int e = plan_lanes(d, a, &cpl, &lgl)) return e;
+  if (int e = plan_lanes(d, a, &cpl, &lgl, (d->flags & CHOP_FLAG_STRICT) != 0)) return e;
   const int mode = d->reduce == CHOP_REDUCE_MIN ? 2 : ((d->flags & CHOP_FLAG_STRICT) ? 1 : 0);
 
   CvPlan p;
@@ -220,7 +228,7 @@ int chop_cost_volume_bwd(const chop_cv_desc* d, const void* ref, const void* src
     return CHOP_ERR_NULL;
   if (d->kind != CHOP_COST_VOLUME_V2 && !offsets) return CHOP_ERR_NULL;
   int cpl, lgl;
-  if (int e = plan_lanes(d, a, &cpl, &lgl)) return e;
+  if (int e = plan_lanes(d, a, &cpl, &lgl, false)) return e;
   a.lg_log2 = lgl;
   const int LG = 1 << lgl;
   if (!aligned(ref, cpl * ty.feat_size) || !aligned(src, cpl * ty.feat_size) || !aligned(depth, ty.real_size) ||
@@ -274,6 +282,15 @@ int chop_cost_volume_bwd(const chop_cv_desc* d, const void* ref, const void* src
   a.cost_grad = cost_grad; a.mask = const_cast<int32_t*>(mask);
   a.ref_grad = ref_grad; a.src_grad = src_grad; a.depth_grad = depth_grad;
   return dispatch_bwd(d->dtype, a, p, st);
+}
+
+int chop_copy_2d_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t rows,
+                       void* stream) {
+  if (!dst || !src) return CHOP_ERR_NULL;
+  if (width_bytes == 0 || rows == 0) return CHOP_OK;
+  if (dst_pitch < width_bytes || src_pitch < width_bytes) return CHOP_ERR_SHAPE;
+  return (int)cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyDefault,
+                                static_cast<cudaStream_t>(stream));
 }
 
 const char* chop_status_string(int status) {

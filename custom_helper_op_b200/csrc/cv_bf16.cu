@@ -1,12 +1,31 @@
-// bfloat16 features with float32 arithmetic and outputs: channel slices of 1 or 8 per lane.
+// bfloat16 features with float32 arithmetic and outputs: channel slices of 1 or 8 per lane in the
+// generic kernels, 4 per lane in the compile-time-C CostVolume MEAN kernels.
 #include "cv_launch.cuh"
 #include "cv_entry.h"
 
 namespace chop {
 int cv_fwd_bf16(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
+  if (p.use_tuned && p.kind == 1 && p.mode == 0 && p.cpl == 4) {
+    switch (a.C) {
+      case 8: return fwd_tuned_go<__nv_bfloat16, 8, 4>(a, st);
+      case 16: return fwd_tuned_go<__nv_bfloat16, 16, 4>(a, st);
+      case 32: return fwd_tuned_go<__nv_bfloat16, 32, 4>(a, st);
+      case 64: return fwd_tuned_go<__nv_bfloat16, 64, 4>(a, st);
+      default: break;
+    }
+  }
   return p.cpl == 8 ? fwd_kind<__nv_bfloat16, float, 8>(a, p, st) : fwd_kind<__nv_bfloat16, float, 1>(a, p, st);
 }
 int cv_bwd_bf16(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
+  if (p.use_tuned && p.kind == 1 && !p.rmin && p.cpl == 4) {
+    switch (a.C) {
+      case 8: return bwd_tuned_go<__nv_bfloat16, 8, 4>(a, st);
+      case 16: return bwd_tuned_go<__nv_bfloat16, 16, 4>(a, st);
+      case 32: return bwd_tuned_go<__nv_bfloat16, 32, 4>(a, st);
+      case 64: return bwd_tuned_go<__nv_bfloat16, 64, 4>(a, st);
+      default: break;
+    }
+  }
   return p.cpl == 8 ? bwd_kind<__nv_bfloat16, float, 8>(a, p, st) : bwd_kind<__nv_bfloat16, float, 1>(a, p, st);
 }
 }  // namespace chop

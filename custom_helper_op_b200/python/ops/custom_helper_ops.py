@@ -110,7 +110,8 @@ def cost_forward(kind, ref_image, src_images, depth, offsets, Rs, Ts, reduce_met
 
 
 def cost_backward(kind, ref_image, src_images, depth, offsets, Rs, Ts, cost_grad, cost_mask,
-                  reduce_method="MEAN", groups=None, half_centor=True, d_range=None, accumulate_into=None):
+                  reduce_method="MEAN", groups=None, half_centor=True, d_range=None, accumulate_into=None,
+                  zero_into=None):
     """Raw gradient op (CostVolumeGrad / CostVolumeGradV2 / CostAggregateGrad).
     Returns (ref_image_grad, src_images_grad, depth_grad)."""
     ref_image, src_images, depth, offsets, Rs, Ts, dims, real = _prep(ref_image, src_images, depth, offsets, Rs, Ts, kind)
@@ -123,7 +124,9 @@ def cost_backward(kind, ref_image, src_images, depth, offsets, Rs, Ts, cost_grad
     _require(cost_mask.dtype == torch.int32 and cost_mask.numel() == B * H * W * D * MC,
              "cost_mask must be the int32 mask returned by the forward op")
     flags = 0
-    if accumulate_into is None:
+    if zero_into is not None:          # caller-owned output buffers, zero-filled by the library
+        ref_grad, src_grad, depth_grad = zero_into
+    elif accumulate_into is None:
         ref_grad = torch.empty((B, H, W, C), dtype=real, device=ref_image.device)
         src_grad = torch.empty((B, N, H, W, C), dtype=real, device=ref_image.device)
         depth_grad = torch.empty_like(depth) if d_range is None else torch.zeros_like(depth)

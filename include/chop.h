@@ -156,6 +156,13 @@ CHOP_API int chop_sparse_conv3d_bwd_noalloc(const chop_sc_desc *desc, const void
  * int from the device, so it synchronises with the current device; -1 if that copy fails. */
 CHOP_API int chop_umma_timeouts(void);
 
+/* Strided host<->device copy of a depth range: `rows` rows of `width_bytes` bytes, row pitches given
+ * (cudaMemcpy2DAsync with cudaMemcpyDefault).  A [d0,d1) slice of a [...,D,C] tensor is rows = B*H*W,
+ * width = (d1-d0)*C*elem, pitch = D*C*elem.  Used by hosts that stream cost / cost_grad between pinned
+ * host memory and the device chunk by chunk while the kernels run on another stream. */
+CHOP_API int chop_copy_2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes,
+                                size_t rows, void *stream);
+
 /* Text for a status returned by any entry point (negative: chop_status, positive: CUDA). */
 CHOP_API const char *chop_status_string(int status);
 

@@ -109,7 +109,7 @@ def test_no_half_centor():
     check(got, want, np.float32, exact_cost=True)
 
 
-@pytest.mark.parametrize("kind,C,G", [(1, 32, 1), (2, 32, 8), (2, 16, 8), (2, 8, 8)])
+@pytest.mark.parametrize("kind,C,G", [(1, 32, 1), (1, 8, 1), (1, 64, 1), (2, 32, 8), (2, 16, 8), (2, 8, 8)])
 def test_bfloat16_features(kind, C, G):
     """bf16 features are an extension; the oracle is the float32 reference arithmetic on the
     bf16-rounded features."""
@@ -119,6 +119,8 @@ def test_bfloat16_features(kind, C, G):
     want = helpers.oracle_fwd_bwd(kind, c, "MEAN", G, True, np.float32)
     got = run_gpu(kind, c, "MEAN", G, True, want["cost_grad"], strict=True, bf16=True)
     check(got, want, np.float32, exact_cost=True)
+    got = run_gpu(kind, c, "MEAN", G, True, want["cost_grad"], strict=False, bf16=True)   # compile-time-C kernels for kind 1
+    check(got, want, np.float32, exact_cost=False)
 
 
 def test_depth_range_calls_compose():
@@ -217,3 +219,23 @@ def test_benchmark_configs_scaled(name):
     check(got, want, np.float32, exact_cost=True)
     got = run_gpu(1, c, "MEAN", 1, True, w["cost_grad"], strict=False)
     check(got, want, np.float32, exact_cost=False)
+
+
+def test_host_pipeline_matches_device_ops():
+    """The host-buffer pipeline (depth chunks on three streams) returns what one device-resident call returns."""
+    from custom_helper_op_b200.host import HostPipeline
+    c = helpers.make_case(1, 77, 2, 2, 10, 12, 8, 21, "random", np.float32)
+    want = helpers.oracle_fwd_bwd(1, c, "MEAN", 1, True, np.float32)
+    B, N, H, W, C, D = 2, 2, 10, 12, 8, 21
+    pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
+    host = dict(ref=pin(c["ref"]), src=pin(c["src"]), base_plane=pin(c["depth"]), offsets=pin(c["offsets"]), Rs=pin(c["Rs"]),
+                Ts=pin(c["Ts"]))
+    out = dict(cost=torch.empty((B, H, W, D, C)).pin_memory(), mask=torch.empty((B, H, W, D, 1), dtype=torch.int32).pin_memory(),
+               ref_grad=torch.empty((B, H, W, C)).pin_memory(), src_grad=torch.empty((B, N, H, W, C)).pin_memory(),
+               base_plane_grad=torch.empty((B, H, W, 1)).pin_memory())
+    pipe = HostPipeline(B, N, H, W, C, D, "cuda:0", nchunks=4)
+    for _ in range(2):   # the second run reuses every buffer
+        pipe.run(host, pin(want["cost_grad"]), out)
+        got = dict(cost=out["cost"].numpy(), mask=out["mask"].numpy(), ref_grad=out["ref_grad"].numpy(),
+                   src_grad=out["src_grad"].numpy(), depth_grad=out["base_plane_grad"].numpy())
+        check(got, want, np.float32, exact_cost=False)
