@@ -26,8 +26,12 @@ __host__ __device__ inline size_t tuned_fwd_smem_per_warp(int N, int G) {
 // (a0 = t00 - ref, u = t10 - t00, v = t01 - t00, t1 = t11 - t01 - u), after which a plane costs four
 // fused operations per channel:  df = a0 + dw*v + dh*(u + dw*t1),  acc += df*df.
 // ---------------------------------------------------------------------------------------------------
+// three 256-thread CTAs per SM (<= 85 registers) measured fastest: 4 still fits, 5 and up spill
+#ifndef CHOP_FWD_MIN_BLOCKS
+#define CHOP_FWD_MIN_BLOCKS 3
+#endif
 template <typename T, int C, int CPL>
-__global__ void __launch_bounds__(256) cv_fwd_tuned(const CvArgs a, const int warps, const size_t smem_per_warp) {
+__global__ void __launch_bounds__(256, CHOP_FWD_MIN_BLOCKS) cv_fwd_tuned(const CvArgs a, const int warps, const size_t smem_per_warp) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int LG = C / CPL;
   constexpr int G = 32 / LG;
@@ -162,6 +166,17 @@ __global__ void __launch_bounds__(256) cv_fwd_tuned(const CvArgs a, const int wa
 // its latency hides behind the previous block's arithmetic and every view reads it from shared memory.
 // d(ref) and d(base_plane) are register sums written once per work item.
 // ---------------------------------------------------------------------------------------------------
+// six 128-thread CTAs per SM with a single staging buffer measured fastest (271 us at c1 against 288 us
+// with two buffers and five CTAs: the extra shared memory costs more L1 and occupancy than the deeper
+// prefetch gains)
+#ifndef CHOP_BWD_MIN_BLOCKS
+#define CHOP_BWD_MIN_BLOCKS 6
+#endif
+#ifndef CHOP_BWD_CG_BUFS
+#define CHOP_BWD_CG_BUFS 1
+#endif
+constexpr int CG_BUFS = CHOP_BWD_CG_BUFS;  // 2: copy a block ahead into the other buffer; 1: copy after use
+
 struct alignas(8) RecG {
   float gh, gw;  // d(sample row)/d(depth), d(sample column)/d(depth)
 };
@@ -169,7 +184,7 @@ struct alignas(8) RecG {
 template <int C>
 __host__ __device__ inline size_t tuned_bwd_smem_per_warp(int N, int G) {
   return (size_t)N * G * sizeof(Coef<float>) + (size_t)N * 32 * (sizeof(ProjF<float>) + sizeof(RecG)) +
-         (size_t)2 * 128 * C;  // two cost_grad buffers of G*LG*C floats = 128*C bytes each
+         (size_t)CG_BUFS * 128 * C;  // cost_grad buffers of G*LG*C floats = 128*C bytes each
 }
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
@@ -180,7 +195,7 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 template <typename T, int C, int CPL>
-__global__ void __launch_bounds__(128) cv_bwd_tuned(const CvArgs a, const int warps, const size_t smem_per_warp) {
+__global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const CvArgs a, const int warps, const size_t smem_per_warp) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int LG = C / CPL;
   constexpr int G = 32 / LG;
@@ -235,10 +250,10 @@ __global__ void __launch_bounds__(128) cv_bwd_tuned(const CvArgs a, const int wa
   __syncwarp();
 
   int buf = 0;
-  for (int dblk = dlo; dblk < dhi; dblk += LG, cg_src += LG * C, buf ^= 1) {
-    cp_async_wait_all();  // this block's slice has landed (each lane reads back only what it copied)
-    __syncwarp();         // and every lane is done with the other buffer and with the records
-    {
+  for (int dblk = dlo; dblk < dhi; dblk += LG, cg_src += LG * C, buf ^= (CG_BUFS - 1)) {
+    if (CG_BUFS == 2) {
+      cp_async_wait_all();  // this block's slice has landed (each lane reads back only what it copied)
+      __syncwarp();         // and every lane is done with the other buffer and with the records
       const int nxt = dblk + LG;
       float* dst = cg_mine + (buf ^ 1) * 32 * C;
 #pragma unroll
@@ -247,6 +262,8 @@ __global__ void __launch_bounds__(128) cv_bwd_tuned(const CvArgs a, const int wa
         else *reinterpret_cast<float4*>(dst + j * C) = make_float4(0.f, 0.f, 0.f, 0.f);
       }
       cp_async_commit();
+    } else {
+      __syncwarp();
     }
 
     // ---- phase A: lane (g, li) projects plane dblk+li of pixel g into every view ---------------------
@@ -273,6 +290,7 @@ __global__ void __launch_bounds__(128) cv_bwd_tuned(const CvArgs a, const int wa
         recG[n * 32 + lane] = q;
       }
     }
+    if (CG_BUFS == 1) cp_async_wait_all();  // the slice requested at the end of the previous block
     __syncwarp();
 
     // ---- phase B ---------------------------------------------------------------------------------------
@@ -346,6 +364,16 @@ __global__ void __launch_bounds__(128) cv_bwd_tuned(const CvArgs a, const int wa
         red_add<float, CPL>(gp + row, acc[2]);
         red_add<float, CPL>(gp + row + C, acc[3]);
       }
+    }
+    if (CG_BUFS == 1) {
+      // single buffer: each lane has finished reading its own slots, request the next block's slice now
+      const int nxt = dblk + LG;
+#pragma unroll
+      for (int j = 0; j < LG; ++j) {
+        if (nxt + j < dhi) cp_async16(cg_mine + j * C, cg_src + (LG + j) * C);
+        else *reinterpret_cast<float4*>(cg_mine + j * C) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      cp_async_commit();
     }
   }
   cp_async_wait_all();
