@@ -123,4 +123,49 @@ inline int bwd_tuned_go(const CvArgs& a, cudaStream_t st) {
   return (int)cudaGetLastError();
 }
 
+template <typename T, int C, int SUB>
+inline int fwd2_tuned_go(const CvArgs& a, cudaStream_t st) {
+  auto k = cv2_fwd_tuned<T, C, SUB>;
+  const size_t spw = tuned_fwd_smem_per_warp<T>(a.N, 32 / (C / 4));
+  const int warps = tuned_warps(spw);
+  const size_t smem = spw * warps;
+  if (smem > 200 * 1024) return -4;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const long long items = (long long)a.npb * a.nchunks;
+  k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw);
+  return (int)cudaGetLastError();
+}
+
+template <typename T, int C, int SUB>
+inline int bwd2_tuned_go(const CvArgs& a, cudaStream_t st) {
+  auto k = cv2_bwd_tuned<T, C, SUB>;
+  const size_t spw = tuned2_bwd_smem_per_warp<T>(a.N, 32 / (C / 4));
+  const int warps = 4;
+  const size_t smem = spw * warps;
+  if (smem > 200 * 1024) return -4;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const long long items = (long long)a.npb * a.nchunks;
+  k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw);
+  return (int)cudaGetLastError();
+}
+
+// C in {8,16,32}, channels per group in {1,2,4}; returns -4 if there is no such kernel
+template <typename T>
+inline int tuned2_dispatch(bool backward, const CvArgs& a, cudaStream_t st) {
+  const int sub = a.C / a.G;
+#define CHOP_V2_CASE(CC, SS)                                                        \
+  if (a.C == CC && sub == SS) return backward ? bwd2_tuned_go<T, CC, SS>(a, st) : fwd2_tuned_go<T, CC, SS>(a, st);
+  CHOP_V2_CASE(8, 1) CHOP_V2_CASE(8, 2) CHOP_V2_CASE(8, 4)
+  CHOP_V2_CASE(16, 1) CHOP_V2_CASE(16, 2) CHOP_V2_CASE(16, 4)
+  CHOP_V2_CASE(32, 1) CHOP_V2_CASE(32, 2) CHOP_V2_CASE(32, 4)
+#undef CHOP_V2_CASE
+  return -4;
+}
+
 }  // namespace chop

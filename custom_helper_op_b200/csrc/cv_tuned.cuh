@@ -384,4 +384,312 @@ __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const C
   if (pvalid && li == 0) atomicAdd(static_cast<float*>(a.depth_grad) + pix, dsum);  // :454
 }
 
+// ---------------------------------------------------------------------------------------------------
+// CostVolumeV2 (group-wise correlation, per-pixel depth hypotheses), MEAN, compile-time C and channels
+// per group SUB in {1,2,4} (a lane's four channels cover whole groups).  Same loop nest and footprint
+// caching as above.  Reference: cost_volume_kernels_gpu_v2.cu.cc:33-135 (forward), :349-479 (gradient).
+// ---------------------------------------------------------------------------------------------------
+template <typename T>
+__host__ __device__ inline size_t tuned2_bwd_smem_per_warp(int N, int G) {
+  return (size_t)N * G * sizeof(Coef<float>) + (size_t)N * 32 * (sizeof(ProjF<float>) + sizeof(RecG));
+}
+
+// Forward: the corner differences are pre-multiplied by the reference pixel on a reload, so a plane costs
+// acc += a0' + dw*v' + dh*(u' + dw*t1')  =  sample*ref  per channel; groups are summed inside the lane.
+template <typename T, int C, int SUB>
+__global__ void __launch_bounds__(256, 3) cv2_fwd_tuned(const CvArgs a, const int warps, const size_t smem_per_warp) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int CPL = 4;
+  constexpr int LG = C / CPL;
+  constexpr int G = 32 / LG;
+  constexpr int NG = CPL / SUB;   // groups per lane
+  constexpr int GR = C / SUB;     // groups per voxel
+  static_assert(LG * CPL == C && (LG & (LG - 1)) == 0 && LG <= 32 && NG * SUB == CPL, "unsupported C / SUB");
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  const int li = lane & (LG - 1);
+  const int g = lane / LG;
+
+  const long long item = (long long)blockIdx.x * warps + wib;
+  if (item >= (long long)a.npb * a.nchunks) return;
+  const int chunk_id = (int)(item / a.npb);
+  const int pb = (int)(item - (long long)chunk_id * a.npb);
+  const long long pix0 = (long long)pb * G;
+  const bool pvalid = pix0 + g < a.npix;
+  const long long pix = pvalid ? pix0 + g : a.npix - 1;
+  const int dlo = a.d_begin + chunk_id * a.chunk;
+  const int dhi = min(a.d_end, dlo + a.chunk);
+  const int N = a.N;
+  const int D = a.D;
+
+  unsigned char* mine = smem_raw + (size_t)wib * smem_per_warp;
+  Coef<float>* coef = reinterpret_cast<Coef<float>*>(mine);
+  ProjF<float>* proj = reinterpret_cast<ProjF<float>*>(coef + N * G);
+
+  stage_coefs<float>(a, coef, lane, G, pix0);
+  __syncwarp();
+
+  const T* src_lane = static_cast<const T*>(a.src) + li * CPL;
+  float refv[CPL];
+  Vec<T, float, CPL>::load(static_cast<const T*>(a.ref) + pix * C + li * CPL, refv);
+  const float* dgrid = static_cast<const float*>(a.depth) + pix * D;
+  const size_t row = (size_t)a.Ws * C;
+  const ProjF<float>* myrec = proj + g * LG;
+  float* out = static_cast<float*>(a.cost) + (pix * D + dlo) * GR + li * NG;
+
+  for (int dblk = dlo; dblk < dhi; dblk += LG, out += LG * GR) {
+    float inv_mine;
+    {
+      const int d = dblk + li;
+      const bool dv = pvalid && d < dhi;
+      const float depth = dv ? __ldg(dgrid + d) : 0.0f;
+      int used = 0;
+      for (int n = 0; n < N; ++n) {
+        ProjF<float> r;
+        r.texel = -1;
+        r.dh = r.dw = r.aux = 0.0f;
+        if (dv) {
+          float gh, gw;
+          r.texel = project<float, false>(coef[n * G + g], depth, a.half_centor, a.Hs, a.Ws, r.dh, r.dw, gh, gw);
+          used += r.texel >= 0;
+        }
+        proj[n * 32 + lane] = r;
+      }
+      if (dv) __stcs(a.mask + pix * D + d, used);
+      inv_mine = used > 0 ? 1.0f / (float)used : 0.0f;
+    }
+    __syncwarp();
+
+    float acc[LG][CPL];
+#pragma unroll
+    for (int j = 0; j < LG; ++j)
+#pragma unroll
+      for (int k = 0; k < CPL; ++k) acc[j][k] = 0.0f;
+
+    for (int n = 0; n < N; ++n) {
+      const ProjF<float>* r = myrec + n * 32;
+      int cur = -1;  // the empty footprint: all terms zero
+      float a0[CPL], u[CPL], v[CPL], t1[CPL];
+#pragma unroll
+      for (int k = 0; k < CPL; ++k) a0[k] = u[k] = v[k] = t1[k] = 0.0f;
+#pragma unroll
+      for (int j = 0; j < LG; ++j) {
+        const ProjF<float> rc = r[j];
+        if (rc.texel != cur) {
+          cur = rc.texel;
+          if (rc.texel >= 0) {
+            const T* p00 = src_lane + (size_t)rc.texel * C;
+            const T* p10 = p00 + row;
+            float t00[CPL], t01[CPL], t10[CPL], t11[CPL];
+            Vec<T, float, CPL>::load(p00, t00);
+            Vec<T, float, CPL>::load(p00 + C, t01);
+            Vec<T, float, CPL>::load(p10, t10);
+            Vec<T, float, CPL>::load(p10 + C, t11);
+#pragma unroll
+            for (int k = 0; k < CPL; ++k) {
+              const float uu = t10[k] - t00[k];
+              a0[k] = t00[k] * refv[k];
+              u[k] = uu * refv[k];
+              v[k] = (t01[k] - t00[k]) * refv[k];
+              t1[k] = ((t11[k] - t01[k]) - uu) * refv[k];
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < CPL; ++k) a0[k] = u[k] = v[k] = t1[k] = 0.0f;
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < CPL; ++k) {
+          const float X = fmaf(t1[k], rc.dw, u[k]);
+          acc[j][k] = fmaf(rc.dh, X, fmaf(rc.dw, v[k], acc[j][k] + a0[k]));   // += sample*ref  (v2:118-120)
+        }
+      }
+    }
+
+#pragma unroll
+    for (int j = 0; j < LG; ++j) {
+      const float inv = __shfl_sync(0xffffffffu, inv_mine, g * LG + j);
+      float o[NG];
+#pragma unroll
+      for (int q = 0; q < NG; ++q) {
+        float sgrp = acc[j][q * SUB];
+#pragma unroll
+        for (int k = 1; k < SUB; ++k) sgrp += acc[j][q * SUB + k];
+        o[q] = sgrp * inv;   // v2:128-133
+      }
+      if (pvalid && dblk + j < dhi) store_stream<float, NG>(out + j * GR, o);
+    }
+    __syncwarp();
+  }
+}
+
+// Gradient.  d(ref) is a register sum; d(src) corner sums are flushed on a footprint change; the
+// depth-hypothesis gradient is per voxel: every lane keeps one partial per plane of the block, the
+// partials are reduce-scattered over the pixel's lanes (lane li ends up with plane li) and stored
+// coalesced (zero where no view saw the voxel, v2:375-378).
+template <typename T, int C, int SUB>
+__global__ void __launch_bounds__(128, 5) cv2_bwd_tuned(const CvArgs a, const int warps, const size_t smem_per_warp) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int CPL = 4;
+  constexpr int LG = C / CPL;
+  constexpr int G = 32 / LG;
+  constexpr int NG = CPL / SUB;
+  constexpr int GR = C / SUB;
+  static_assert(LG * CPL == C && (LG & (LG - 1)) == 0 && LG <= 32 && NG * SUB == CPL, "unsupported C / SUB");
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  const int li = lane & (LG - 1);
+  const int g = lane / LG;
+
+  const long long item = (long long)blockIdx.x * warps + wib;
+  if (item >= (long long)a.npb * a.nchunks) return;
+  const int chunk_id = (int)(item / a.npb);
+  const int pb = (int)(item - (long long)chunk_id * a.npb);
+  const long long pix0 = (long long)pb * G;
+  const bool pvalid = pix0 + g < a.npix;
+  const long long pix = pvalid ? pix0 + g : a.npix - 1;
+  const int dlo = a.d_begin + chunk_id * a.chunk;
+  const int dhi = min(a.d_end, dlo + a.chunk);
+  const int N = a.N;
+  const int D = a.D;
+
+  unsigned char* mine = smem_raw + (size_t)wib * smem_per_warp;
+  Coef<float>* coef = reinterpret_cast<Coef<float>*>(mine);
+  ProjF<float>* recA = reinterpret_cast<ProjF<float>*>(coef + N * G);  // aux = 1/(valid views)
+  RecG* recG = reinterpret_cast<RecG*>(recA + N * 32);
+
+  stage_coefs<float>(a, coef, lane, G, pix0);
+  __syncwarp();
+
+  const T* src_lane = static_cast<const T*>(a.src) + li * CPL;
+  float* sg_lane = static_cast<float*>(a.src_grad) + li * CPL;
+  float refv[CPL], rg[CPL];
+  Vec<T, float, CPL>::load(static_cast<const T*>(a.ref) + pix * C + li * CPL, refv);
+#pragma unroll
+  for (int k = 0; k < CPL; ++k) rg[k] = 0.0f;
+  const float* dgrid = static_cast<const float*>(a.depth) + pix * D;
+  float* dgrad = static_cast<float*>(a.depth_grad) + pix * D;
+  const size_t row = (size_t)a.Ws * C;
+  const float* cg_lane = static_cast<const float*>(a.cost_grad) + (pix * D + dlo) * GR + li * NG;
+
+  for (int dblk = dlo; dblk < dhi; dblk += LG, cg_lane += LG * GR) {
+    __syncwarp();
+    // ---- phase A -----------------------------------------------------------------------------------------
+    const int dA = dblk + li;
+    const bool dvA = pvalid && dA < dhi;
+    {
+      float depth = 0.0f, scale = 0.0f;
+      bool live = false;
+      if (dvA) {
+        depth = __ldg(dgrid + dA);
+        const int m0 = __ldg(a.mask + pix * D + dA);
+        live = m0 > 0;                       // v2:375
+        if (live) scale = 1.0f / (float)m0;  // v2:461
+      }
+      for (int n = 0; n < N; ++n) {
+        ProjF<float> r;
+        RecG q;
+        r.texel = -1;
+        r.dh = r.dw = 0.0f;
+        r.aux = scale;
+        q.gh = q.gw = 0.0f;
+        if (live) r.texel = project<float, true>(coef[n * G + g], depth, a.half_centor, a.Hs, a.Ws, r.dh, r.dw, q.gh, q.gw);
+        recA[n * 32 + lane] = r;
+        recG[n * 32 + lane] = q;
+      }
+    }
+    __syncwarp();
+
+    // ---- phase B -----------------------------------------------------------------------------------------
+    float dv[LG];
+#pragma unroll
+    for (int j = 0; j < LG; ++j) dv[j] = 0.0f;
+    for (int n = 0; n < N; ++n) {
+      const ProjF<float>* rA = recA + n * 32 + g * LG;
+      const RecG* rGp = recG + n * 32 + g * LG;
+      int cur = -1;
+      float a0[CPL], u[CPL], v[CPL], t1[CPL], acc[4][CPL];
+#pragma unroll
+      for (int k = 0; k < CPL; ++k) {
+        a0[k] = u[k] = v[k] = t1[k] = 0.0f;
+        acc[0][k] = acc[1][k] = acc[2][k] = acc[3][k] = 0.0f;
+      }
+#pragma unroll
+      for (int j = 0; j < LG; ++j) {
+        const ProjF<float> rc = rA[j];
+        if (rc.texel >= 0) {
+          if (rc.texel != cur) {
+            if (cur >= 0) {
+              float* gp = sg_lane + (size_t)cur * C;
+              red_add<float, CPL>(gp, acc[0]);
+              red_add<float, CPL>(gp + C, acc[1]);
+              red_add<float, CPL>(gp + row, acc[2]);
+              red_add<float, CPL>(gp + row + C, acc[3]);
+            }
+            cur = rc.texel;
+            const T* p00 = src_lane + (size_t)rc.texel * C;
+            const T* p10 = p00 + row;
+            float t00[CPL], t01[CPL], t10[CPL], t11[CPL];
+            Vec<T, float, CPL>::load(p00, t00);
+            Vec<T, float, CPL>::load(p00 + C, t01);
+            Vec<T, float, CPL>::load(p10, t10);
+            Vec<T, float, CPL>::load(p10 + C, t11);
+#pragma unroll
+            for (int k = 0; k < CPL; ++k) {
+              a0[k] = t00[k];
+              u[k] = t10[k] - t00[k];
+              v[k] = t01[k] - t00[k];
+              t1[k] = (t11[k] - t01[k]) - u[k];
+              acc[0][k] = acc[1][k] = acc[2][k] = acc[3][k] = 0.0f;
+            }
+          }
+          const RecG rq = rGp[j];
+          float cgv[NG];
+          Vec<float, float, NG>::load(cg_lane + j * GR, cgv);
+          float w00, w01, w11, w10;
+          bilinear_weights_fast(rc.dh, rc.dw, w00, w01, w11, w10);
+          float hg = 0.0f, wg = 0.0f;
+#pragma unroll
+          for (int k = 0; k < CPL; ++k) {
+            const float bg = cgv[k / SUB] * rc.aux;                        // v2:461
+            const float X = fmaf(t1[k], rc.dw, u[k]);
+            const float Y = fmaf(t1[k], rc.dh, v[k]);
+            const float smp = fmaf(rc.dh, X, fmaf(rc.dw, v[k], a0[k]));   // bilinear sample
+            rg[k] = fmaf(bg, smp, rg[k]);                                   // v2:462
+            const float gs = bg * refv[k];                                  // v2:463
+            acc[0][k] = fmaf(gs, w00, acc[0][k]);                           // v2:464-467
+            acc[1][k] = fmaf(gs, w01, acc[1][k]);
+            acc[2][k] = fmaf(gs, w10, acc[2][k]);
+            acc[3][k] = fmaf(gs, w11, acc[3][k]);
+            hg = fmaf(gs, X, hg);                                           // v2:471
+            wg = fmaf(gs, Y, wg);                                           // v2:472
+          }
+          dv[j] = fmaf(rq.gh, hg, fmaf(rq.gw, wg, dv[j]));                  // v2:474
+        }
+      }
+      if (cur >= 0) {
+        float* gp = sg_lane + (size_t)cur * C;
+        red_add<float, CPL>(gp, acc[0]);
+        red_add<float, CPL>(gp + C, acc[1]);
+        red_add<float, CPL>(gp + row, acc[2]);
+        red_add<float, CPL>(gp + row + C, acc[3]);
+      }
+    }
+    // reduce-scatter the per-plane partials over the pixel's LG lanes: lane li keeps plane li
+#pragma unroll
+    for (int s = LG / 2; s >= 1; s >>= 1) {
+#pragma unroll
+      for (int i = 0; i < s; ++i) {
+        const bool hi = (li & s) != 0;
+        const float keep = hi ? dv[i + s] : dv[i];
+        const float send = hi ? dv[i] : dv[i + s];
+        dv[i] = keep + __shfl_xor_sync(0xffffffffu, send, s);
+      }
+    }
+    if (dvA) dgrad[dA] = dv[0];   // v2:477 (plain store; zero for a voxel no view saw)
+  }
+
+  if (pvalid) red_add<float, CPL>(static_cast<float*>(a.ref_grad) + pix * C + li * CPL, rg);
+}
+
 }  // namespace chop

@@ -71,7 +71,8 @@ def test_cost_volume_v1(shape, reduce, camera):
         check(got, want, np.float32, exact_cost=strict or reduce == "MIN")
 
 
-@pytest.mark.parametrize("cgs", [(9, 3), (8, 8), (8, 2), (32, 8), (16, 1), (12, 3), (6, 2), (64, 8), (24, 2)])
+@pytest.mark.parametrize("cgs", [(9, 3), (8, 8), (8, 2), (8, 4), (32, 8), (32, 16), (32, 32), (16, 1), (16, 4), (16, 8), (16, 16),
+                                 (12, 3), (6, 2), (64, 8), (24, 2)])
 @pytest.mark.parametrize("reduce", ["MEAN", "MIN"])
 def test_cost_volume_v2(cgs, reduce):
     C, G = cgs
