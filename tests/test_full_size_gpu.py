@@ -1,0 +1,144 @@
+"""Full-size runs of the benchmark configurations on the GPU, checked through properties that do not
+need a full CPU oracle run: the oracle on a band of image rows (cost, mask, d(ref), d(base_plane) are
+per pixel), bit-identical repeat runs of the forward pass, depth-range calls composing to the full
+call, linearity of the gradient in the upstream gradient, and the channel-wise checksum
+sum(d src) == -sum(d ref) that follows from the bilinear weights adding up to one."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from custom_helper_op_b200 import _lib, synth
+from custom_helper_op_b200.python.ops import custom_helper_ops as ops
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _band_check(w, cost, mask, rg, bg, cg, rows):
+    """Oracle on image rows [0, rows) of batch item 0 against the full GPU result."""
+    ref = np.ascontiguousarray(w["ref"][:1, :rows])
+    base = np.ascontiguousarray(w["base_plane"][:1, :rows])
+    c_o, m_o = oracle.cost_fwd(1, ref, w["src"][:1], base, w["offsets"][:1], w["Rs"][:1], w["Ts"][:1])
+    assert helpers.bits_equal(mask[:1, :rows].cpu().numpy(), m_o)
+    assert helpers.rel_err(cost[:1, :rows].cpu().numpy(), c_o) <= 1e-5
+    rg_o, _, bg_o = oracle.cost_bwd(1, ref, w["src"][:1], base, w["offsets"][:1], w["Rs"][:1], w["Ts"][:1],
+                                    cg[:1, :rows].cpu().numpy(), m_o)
+    assert helpers.rel_err(rg[:1, :rows].cpu().numpy(), rg_o) <= 1e-4
+    assert helpers.rel_err(bg[:1, :rows].cpu().numpy(), bg_o) <= 1e-4
+
+
+@pytest.mark.parametrize("name", ["c0_cpu", "c1_mvsnet"])
+def test_cost_volume_full_size(name):
+    w = synth.make(name, with_grad=False)
+    t = {k: torch.from_numpy(v).to(DEV) for k, v in w.items()}
+    args = (t["ref"], t["src"], t["base_plane"], t["offsets"], t["Rs"], t["Ts"])
+    cost, mask = ops.cost_forward(1, *args)
+    cost2, mask2 = ops.cost_forward(1, *args)
+    assert torch.equal(cost, cost2) and torch.equal(mask, mask2)            # the forward pass is deterministic
+    assert float((mask > 0).float().mean()) > 0.9                           # the synthetic cameras see the volume
+    # strict mode agrees with the fused mode to rounding
+    cost_s, mask_s = ops.cost_forward(1, *args, strict=True)
+    assert torch.equal(mask, mask_s)
+    assert float((cost - cost_s).abs().max() / cost_s.abs().max()) <= 1e-5
+    g = torch.Generator(device=DEV)
+    g.manual_seed(5)
+    g1 = torch.randn(cost.shape, device=DEV, generator=g)
+    g2 = torch.randn(cost.shape, device=DEV, generator=g)
+    r1 = ops.cost_backward(1, *args, g1, mask)
+    r2 = ops.cost_backward(1, *args, g2, mask)
+    r12 = ops.cost_backward(1, *args, 0.5 * g1 + g2, mask)
+    for a, b, c in zip(r1, r2, r12):                                         # linear in the upstream gradient
+        scale = float(c.abs().max())
+        assert float((0.5 * a + b - c).abs().max()) <= 1e-4 * scale
+    rg, sg, bg = r1
+    # checksum: every sample spreads its gradient over four corners with weights that sum to one
+    lhs = sg.double().sum(dim=(0, 1, 2, 3))
+    rhs = -rg.double().sum(dim=(0, 1, 2))
+    assert float((lhs - rhs).abs().max()) <= 1e-4 * float(rhs.abs().max())
+    # depth-range calls compose
+    D = t["offsets"].shape[1]
+    cost_r = torch.zeros_like(cost)
+    mask_r = torch.zeros_like(mask)
+    acc = None
+    for d0, d1 in ((0, D // 3), (D // 3, D // 3 + 5), (D // 3 + 5, D)):
+        ops.cost_forward(1, *args, d_range=(d0, d1), out=(cost_r, mask_r))
+        if acc is None:
+            acc = ops.cost_backward(1, *args, g1, mask, d_range=(d0, d1))
+        else:
+            ops.cost_backward(1, *args, g1, mask, d_range=(d0, d1), accumulate_into=acc)
+    assert torch.equal(cost_r, cost) and torch.equal(mask_r, mask)
+    for a, b in zip(acc, r1):
+        assert float((a - b).abs().max()) <= 1e-4 * float(b.abs().max())
+    _band_check(w, cost, mask, rg, bg, g1, rows=3)
+
+
+def test_large_item_bf16_features():
+    """One batch item of the large multi-view configuration (V=7, 296x400, D=256, inverse-depth planes),
+    bf16 features: band check against the float32 oracle on the bf16-rounded features."""
+    w = synth.make("c3_large", with_grad=False, B=1)
+    for k in ("ref", "src"):
+        w[k] = torch.from_numpy(w[k]).to(torch.bfloat16).float().numpy()
+    t = {k: torch.from_numpy(v).to(DEV) for k, v in w.items()}
+    args = (t["ref"].to(torch.bfloat16), t["src"].to(torch.bfloat16), t["base_plane"], t["offsets"], t["Rs"], t["Ts"])
+    cost, mask = ops.cost_forward(1, *args)
+    g = torch.Generator(device=DEV)
+    g.manual_seed(6)
+    cg = torch.randn(cost.shape, device=DEV, generator=g)
+    rg, sg, bg = ops.cost_backward(1, *args, cg, mask)
+    lhs = sg.double().sum(dim=(0, 1, 2, 3))
+    rhs = -rg.double().sum(dim=(0, 1, 2))
+    assert float((lhs - rhs).abs().max()) <= 1e-4 * float(rhs.abs().max())
+    _band_check(w, cost, mask, rg, bg, cg, rows=2)
+
+
+@pytest.mark.parametrize("name", ["c2_stage1", "c2_stage3"])
+def test_cascade_stage_v2(name):
+    """CostVolumeV2 stages (V=5, 8 groups, bf16 features): band check of cost, mask, d(ref) and the per-voxel
+    depth-hypothesis gradient against the oracle."""
+    w = synth.make(name, with_grad=False, scale=0.5)
+    G = w.pop("groups")
+    for k in ("ref", "src"):
+        w[k] = torch.from_numpy(w[k]).to(torch.bfloat16).float().numpy()
+    t = {k: torch.from_numpy(v).to(DEV) for k, v in w.items()}
+    args = (t["ref"].to(torch.bfloat16), t["src"].to(torch.bfloat16), t["depth_grid"], None, t["Rs"], t["Ts"])
+    cost, mask = ops.cost_forward(2, *args, groups=G)
+    g = torch.Generator(device=DEV)
+    g.manual_seed(7)
+    cg = torch.randn(cost.shape, device=DEV, generator=g)
+    rg, sg, dg = ops.cost_backward(2, *args, cg, mask, groups=G)
+    rows = 2
+    ref = np.ascontiguousarray(w["ref"][:1, :rows])
+    grid = np.ascontiguousarray(w["depth_grid"][:1, :rows])
+    c_o, m_o = oracle.cost_fwd(2, ref, w["src"][:1], grid, None, w["Rs"][:1], w["Ts"][:1], groups=G)
+    assert helpers.bits_equal(mask[:1, :rows].cpu().numpy(), m_o)
+    assert helpers.rel_err(cost[:1, :rows].cpu().numpy(), c_o) <= 1e-5
+    rg_o, _, dg_o = oracle.cost_bwd(2, ref, w["src"][:1], grid, None, w["Rs"][:1], w["Ts"][:1], cg[:1, :rows].cpu().numpy(), m_o,
+                                    groups=G)
+    assert helpers.rel_err(rg[:1, :rows].cpu().numpy(), rg_o) <= 1e-4
+    assert helpers.rel_err(dg[:1, :rows].cpu().numpy(), dg_o) <= 1e-4
+
+
+def test_manifold_conv_full_size():
+    """c4 (256x320 pixels, 9-plane band, 16 -> 16, bf16): tensor-core kernels against the generic kernels on the
+    whole problem, and the forward pass against the oracle."""
+    w = synth.manifold_conv(20246)
+    r = lambda a: torch.from_numpy(a).to(torch.bfloat16)
+    img, flt, og = r(w["images"]).to(DEV), r(w["filters"]).to(DEV), r(w["out_grad"]).to(DEV)
+    bp = torch.from_numpy(w["base_plane"]).to(DEV)
+    res = {}
+    for umma in (1, 0):
+        try:
+            _lib.set_tuning("umma", umma)
+            out = ops.sparse_conv3d_forward(img, flt, 0.0, bp)
+            res[umma] = (out,) + ops.sparse_conv3d_backward(img, flt, 0.0, bp, og)
+        finally:
+            _lib.set_tuning("umma", 1)
+    torch.cuda.synchronize()
+    assert _lib.lib().chop_umma_timeouts() == 0
+    for a, b in zip(res[1][:3], res[0][:3]):
+        a, b = a.float(), b.float()
+        assert float((a - b).abs().max()) <= 2.0 ** -7 * float(b.abs().max())
+    want = oracle.sparse_conv3d_fwd(r(w["images"]).float().numpy(), r(w["filters"]).float().numpy(), 0.0, w["base_plane"])
+    assert helpers.rel_err(res[1][0].float().cpu().numpy(), want) <= 1e-2
