@@ -1,0 +1,330 @@
+// TensorFlow binding of libchop_b200.so: op registrations and GPU OpKernels for the cost-volume path,
+// written against the C ABI in include/chop.h.  Built only where TensorFlow headers exist:
+//
+//   g++ -std=c++17 -shared -fPIC chop_tf_ops.cc -o _custom_helper_ops.so \
+//       $(python -c 'import tensorflow as tf; print(" ".join(tf.sysconfig.get_compile_flags()+tf.sysconfig.get_link_flags()))') \
+//       -I<repo>/include -L<repo>/custom_helper_op_b200 -lchop_b200 -DGOOGLE_CUDA=1
+//
+// Op names, input order, attrs and output shapes are those of the reference project
+// (custom_helper_op/cc/ops/custom_helper_ops.cc:190-307 CostVolume*, :374-411 CostAggregate*, :590-641
+// SparseConv3DFast*), so its Python wrapper and its tf.RegisterGradient functions work unchanged.  The
+// dtype list additionally admits bfloat16.  As in the reference only DEVICE_GPU kernels are registered.
+#include <string>
+#include <vector>
+
+#include "chop.h"
+#include "tensorflow/core/framework/op.h"
+#include "tensorflow/core/framework/op_kernel.h"
+#include "tensorflow/core/framework/shape_inference.h"
+#include "tensorflow/core/util/gpu_kernel_helper.h"
+
+namespace tensorflow {
+namespace chop_b200 {
+
+using shape_inference::InferenceContext;
+using shape_inference::ShapeHandle;
+
+// ---- schema ---------------------------------------------------------------------------------------------
+namespace {
+
+// cost [B,H,W,D,last], mask [B,H,W,D,1 (MEAN) | last (MIN)]
+Status CostShapes(InferenceContext* c, bool v2, bool aggregate) {
+  ShapeHandle ref, depth;
+  TF_RETURN_IF_ERROR(c->WithRank(c->input(0), 4, &ref));
+  std::string reduce;
+  TF_RETURN_IF_ERROR(c->GetAttr("reduce_method", &reduce));
+  shape_inference::DimensionHandle planes, last;
+  if (v2) {
+    TF_RETURN_IF_ERROR(c->WithRank(c->input(2), 4, &depth));
+    planes = c->Dim(depth, 3);
+    int groups;
+    TF_RETURN_IF_ERROR(c->GetAttr("groups", &groups));
+    last = c->MakeDim(groups);
+  } else {
+    TF_RETURN_IF_ERROR(c->WithRank(c->input(3), 2, &depth));
+    planes = c->Dim(depth, 1);
+    last = c->Dim(ref, 3);
+  }
+  std::vector<shape_inference::DimensionHandle> dims = {c->Dim(ref, 0), c->Dim(ref, 1), c->Dim(ref, 2), planes};
+  if (aggregate) {
+    c->set_output(0, c->MakeShape(dims));
+    c->set_output(1, c->MakeShape(dims));
+    return Status::OK();
+  }
+  auto cost = dims, mask = dims;
+  cost.push_back(last);
+  mask.push_back(reduce == "MEAN" ? c->MakeDim(1) : last);
+  c->set_output(0, c->MakeShape(cost));
+  c->set_output(1, c->MakeShape(mask));
+  return Status::OK();
+}
+
+Status GradLikeInputs(InferenceContext* c) {
+  for (int i = 0; i < 3; ++i) c->set_output(i, c->input(i));
+  return Status::OK();
+}
+
+}  // namespace
+
+#define CHOP_FLOAT_TYPES "{float, double, bfloat16}"
+
+REGISTER_OP("CostVolume")
+    .Input("ref_image: dtype").Input("src_images: dtype").Input("base_plane: dtype").Input("offsets: dtype")
+    .Input("rs: dtype").Input("ts: dtype")
+    .Output("cost: dtype").Output("cost_mask: int32")
+    .Attr("dtype: " CHOP_FLOAT_TYPES).Attr("reduce_method: {'MEAN', 'MIN'}").Attr("half_centor: bool = true")
+    .SetShapeFn([](InferenceContext* c) { return CostShapes(c, false, false); });
+
+REGISTER_OP("CostVolumeGrad")
+    .Input("ref_image: dtype").Input("src_images: dtype").Input("base_plane: dtype").Input("offsets: dtype")
+    .Input("rs: dtype").Input("ts: dtype").Input("cost_grad: dtype").Input("cost_mask: int32")
+    .Output("ref_image_grad: dtype").Output("src_images_grad: dtype").Output("base_plane_grad: dtype")
+    .Attr("dtype: " CHOP_FLOAT_TYPES).Attr("reduce_method: {'MEAN', 'MIN'}").Attr("half_centor: bool = true")
+    .SetShapeFn(GradLikeInputs);
+
+REGISTER_OP("CostVolumeV2")
+    .Input("ref_image: dtype").Input("src_images: dtype").Input("depth_grid: dtype").Input("rs: dtype").Input("ts: dtype")
+    .Output("cost: dtype").Output("cost_mask: int32")
+    .Attr("dtype: " CHOP_FLOAT_TYPES).Attr("reduce_method: {'MEAN', 'MIN'}").Attr("groups: int")
+    .Attr("half_centor: bool = true")
+    .SetShapeFn([](InferenceContext* c) { return CostShapes(c, true, false); });
+
+REGISTER_OP("CostVolumeGradV2")
+    .Input("ref_image: dtype").Input("src_images: dtype").Input("depth_grid: dtype").Input("rs: dtype").Input("ts: dtype")
+    .Input("cost_grad: dtype").Input("cost_mask: int32")
+    .Output("ref_image_grad: dtype").Output("src_images_grad: dtype").Output("base_plane_grad: dtype")
+    .Attr("dtype: " CHOP_FLOAT_TYPES).Attr("reduce_method: {'MEAN', 'MIN'}").Attr("groups: int")
+    .Attr("half_centor: bool = true")
+    .SetShapeFn(GradLikeInputs);
+
+REGISTER_OP("CostAggregate")
+    .Input("ref_image: dtype").Input("src_images: dtype").Input("base_plane: dtype").Input("offsets: dtype")
+    .Input("rs: dtype").Input("ts: dtype")
+    .Output("cost: dtype").Output("cost_mask: int32")
+    .Attr("dtype: " CHOP_FLOAT_TYPES).Attr("reduce_method: {'MEAN', 'MIN'}").Attr("half_centor: bool = true")
+    .SetShapeFn([](InferenceContext* c) { return CostShapes(c, false, true); });
+
+REGISTER_OP("CostAggregateGrad")
+    .Input("ref_image: dtype").Input("src_images: dtype").Input("base_plane: dtype").Input("offsets: dtype")
+    .Input("rs: dtype").Input("ts: dtype").Input("cost_grad: dtype").Input("cost_mask: int32")
+    .Output("ref_image_grad: dtype").Output("src_images_grad: dtype").Output("base_plane_grad: dtype")
+    .Attr("dtype: " CHOP_FLOAT_TYPES).Attr("reduce_method: {'MEAN', 'MIN'}").Attr("half_centor: bool = true")
+    .SetShapeFn(GradLikeInputs);
+
+REGISTER_OP("SparseConv3DFast")
+    .Input("images: dtype").Input("filters: dtype").Input("default_value: dtype").Input("base_plane: int32")
+    .Output("output: dtype")
+    .Attr("dtype: " CHOP_FLOAT_TYPES).Attr("strides: list(int)").Attr("dilations: list(int)")
+    .Attr("dynamic_default: bool").Attr("data_format: { 'NDHWC' }")
+    .SetShapeFn([](InferenceContext* c) {
+      std::vector<int32> s;
+      TF_RETURN_IF_ERROR(c->GetAttr("strides", &s));
+      ShapeHandle img, flt;
+      TF_RETURN_IF_ERROR(c->WithRank(c->input(0), 5, &img));
+      TF_RETURN_IF_ERROR(c->WithRank(c->input(1), 5, &flt));
+      std::vector<shape_inference::DimensionHandle> out = {c->Dim(img, 0)};
+      for (int i = 0; i < 3; ++i) {
+        const int64 n = c->Value(c->Dim(img, 1 + i));
+        out.push_back(n < 0 ? c->UnknownDim() : c->MakeDim((n + s[i] - 1) / s[i]));
+      }
+      out.push_back(c->Dim(flt, 4));
+      c->set_output(0, c->MakeShape(out));
+      return Status::OK();
+    });
+
+REGISTER_OP("SparseConv3DFastGrad")
+    .Input("images: dtype").Input("filters: dtype").Input("default_value: dtype").Input("base_plane: int32")
+    .Input("out_grad: dtype")
+    .Output("images_grad: dtype").Output("filter_grad: dtype").Output("default_value_grad: dtype")
+    .Attr("dtype: " CHOP_FLOAT_TYPES).Attr("strides: list(int)").Attr("dilations: list(int)")
+    .Attr("dynamic_default: bool").Attr("data_format: { 'NDHWC' }")
+    .SetShapeFn(GradLikeInputs);
+
+#if GOOGLE_CUDA
+// ---- kernels ---------------------------------------------------------------------------------------------
+namespace {
+
+template <typename T> struct DtypeOf;
+template <> struct DtypeOf<float> { static constexpr int value = CHOP_F32; };
+template <> struct DtypeOf<double> { static constexpr int value = CHOP_F64; };
+template <> struct DtypeOf<bfloat16> { static constexpr int value = CHOP_BF16; };
+// bfloat16 ops keep depths / cameras / cost in float32 (see chop.h); they are registered with those inputs
+// cast by the Python wrapper, which is why the kernels below read every tensor through tensor_data().
+
+inline const void* In(OpKernelContext* ctx, int i) { return ctx->input(i).tensor_data().data(); }
+inline void* Out(Tensor* t) { return const_cast<char*>(t->tensor_data().data()); }
+inline void* StreamOf(OpKernelContext* ctx) { return ctx->eigen_device<Eigen::GpuDevice>().stream(); }
+
+}  // namespace
+
+// kind: CHOP_COST_VOLUME / _V2 / _AGGREGATE;  gradient: the *Grad op
+template <typename T, int KIND, bool GRADIENT>
+class CostOp : public OpKernel {
+ public:
+  explicit CostOp(OpKernelConstruction* ctx) : OpKernel(ctx) {
+    std::string reduce;
+    OP_REQUIRES_OK(ctx, ctx->GetAttr("reduce_method", &reduce));
+    OP_REQUIRES(ctx, reduce == "MEAN" || reduce == "MIN",
+                errors::InvalidArgument("Invalid reduce method ", reduce, ". Supported types: MEAN, MIN"));
+    min_ = reduce == "MIN";
+    OP_REQUIRES_OK(ctx, ctx->GetAttr("half_centor", &half_centor_));
+    if (KIND == CHOP_COST_VOLUME_V2) OP_REQUIRES_OK(ctx, ctx->GetAttr("groups", &groups_));
+  }
+
+  void Compute(OpKernelContext* ctx) override {
+    constexpr bool V2 = KIND == CHOP_COST_VOLUME_V2;
+    const Tensor& ref = ctx->input(0);
+    const Tensor& src = ctx->input(1);
+    const Tensor& depth = ctx->input(2);
+    const int cam0 = V2 ? 3 : 4;  // index of rs
+    OP_REQUIRES(ctx, ref.dims() == 4, errors::InvalidArgument("ref image must have rank 4"));
+    const int64 B = ref.dim_size(0), H = ref.dim_size(1), W = ref.dim_size(2), C = ref.dim_size(3);
+    OP_REQUIRES(ctx, src.dims() == 5 && src.dim_size(0) == B && src.dim_size(2) == H && src.dim_size(3) == W &&
+                         src.dim_size(4) == C,
+                errors::InvalidArgument("src_images must have rank 5, and must compate to ref_image"));
+    const int64 N = src.dim_size(1);
+    int64 D;
+    if (V2) {
+      OP_REQUIRES(ctx, depth.dims() == 4 && depth.dim_size(0) == B && depth.dim_size(1) == H && depth.dim_size(2) == W,
+                  errors::InvalidArgument("depth_grid must have rank 4, and must compate to ref_image"));
+      D = depth.dim_size(3);
+      OP_REQUIRES(ctx, groups_ > 0 && C % groups_ == 0, errors::InvalidArgument("channels must be divisible by groups"));
+    } else {
+      const Tensor& offsets = ctx->input(3);
+      OP_REQUIRES(ctx, depth.dims() == 4 && depth.dim_size(0) == B && depth.dim_size(1) == H && depth.dim_size(2) == W &&
+                           depth.dim_size(3) == 1,
+                  errors::InvalidArgument("base_plane must have rank 4, and must compate to ref_image"));
+      OP_REQUIRES(ctx, offsets.dims() == 2 && offsets.dim_size(0) == B,
+                  errors::InvalidArgument("offsets must have rank 2, and must compate to ref_image"));
+      D = offsets.dim_size(1);
+    }
+    const Tensor& Rs = ctx->input(cam0);
+    const Tensor& Ts = ctx->input(cam0 + 1);
+    OP_REQUIRES(ctx, Rs.dims() == 4 && Rs.dim_size(0) == B && Rs.dim_size(1) == N && Rs.dim_size(2) == 3 && Rs.dim_size(3) == 3,
+                errors::InvalidArgument("Rs must have rank 4, and must compate to ref_image"));
+    OP_REQUIRES(ctx, Ts.dims() == 3 && Ts.dim_size(0) == B && Ts.dim_size(1) == N && Ts.dim_size(2) == 3,
+                errors::InvalidArgument("Ts must have rank 3, and must compate to ref_image"));
+
+    chop_cv_desc d = {};
+    d.kind = KIND;
+    d.dtype = DtypeOf<T>::value;
+    d.reduce = min_ ? CHOP_REDUCE_MIN : CHOP_REDUCE_MEAN;
+    d.half_centor = half_centor_;
+    d.groups = groups_;
+    d.B = B; d.H = H; d.W = W; d.C = C; d.D = D; d.N = N; d.Hs = src.dim_size(2); d.Ws = src.dim_size(3);
+    const int64 last = KIND == CHOP_COST_VOLUME ? C : (V2 ? groups_ : 1);
+    const void* offsets = V2 ? nullptr : In(ctx, 3);
+    int status;
+    if (!GRADIENT) {
+      TensorShape cs({B, H, W, D}), ms({B, H, W, D});
+      if (KIND != CHOP_COST_AGGREGATE) {
+        cs.AddDim(last);
+        ms.AddDim(min_ ? last : 1);
+      }
+      Tensor *cost = nullptr, *mask = nullptr;
+      OP_REQUIRES_OK(ctx, ctx->allocate_output(0, cs, &cost));
+      OP_REQUIRES_OK(ctx, ctx->allocate_output(1, ms, &mask));
+      status = chop_cost_volume_fwd(&d, In(ctx, 0), In(ctx, 1), In(ctx, 2), offsets, In(ctx, cam0), In(ctx, cam0 + 1), Out(cost),
+                                    static_cast<int32_t*>(Out(mask)), StreamOf(ctx));
+    } else {
+      const Tensor& cost_grad = ctx->input(cam0 + 2);
+      const Tensor& cost_mask = ctx->input(cam0 + 3);
+      OP_REQUIRES(ctx, cost_grad.NumElements() == B * H * W * D * last,
+                  errors::InvalidArgument("cost_grad must have rank 5, and must compate to ref_image"));
+      OP_REQUIRES(ctx, cost_mask.NumElements() == B * H * W * D * (min_ ? last : 1),
+                  errors::InvalidArgument("cost_mask must be the mask returned by the forward op"));
+      Tensor *rg = nullptr, *sg = nullptr, *dg = nullptr;
+      OP_REQUIRES_OK(ctx, ctx->allocate_output(0, ref.shape(), &rg));
+      OP_REQUIRES_OK(ctx, ctx->allocate_output(1, src.shape(), &sg));
+      OP_REQUIRES_OK(ctx, ctx->allocate_output(2, depth.shape(), &dg));
+      status = chop_cost_volume_bwd(&d, In(ctx, 0), In(ctx, 1), In(ctx, 2), offsets, In(ctx, cam0), In(ctx, cam0 + 1),
+                                    In(ctx, cam0 + 2), static_cast<const int32_t*>(In(ctx, cam0 + 3)), Out(rg), Out(sg), Out(dg),
+                                    StreamOf(ctx));
+    }
+    OP_REQUIRES(ctx, status == 0, errors::Internal("libchop_b200: ", chop_status_string(status)));
+  }
+
+ private:
+  bool min_ = false;
+  bool half_centor_ = true;
+  int groups_ = 1;
+};
+
+template <typename T, bool GRADIENT>
+class ManifoldConvOp : public OpKernel {
+ public:
+  explicit ManifoldConvOp(OpKernelConstruction* ctx) : OpKernel(ctx) {
+    OP_REQUIRES_OK(ctx, ctx->GetAttr("strides", &strides_));
+    OP_REQUIRES_OK(ctx, ctx->GetAttr("dilations", &dilations_));
+    OP_REQUIRES_OK(ctx, ctx->GetAttr("dynamic_default", &dynamic_default_));
+    OP_REQUIRES(ctx, strides_.size() == 3, errors::InvalidArgument("strides must be a vector have 3 element"));
+    OP_REQUIRES(ctx, dilations_.size() == 3, errors::InvalidArgument("dilations must be a vector have 3 element"));
+  }
+
+  void Compute(OpKernelContext* ctx) override {
+    const Tensor& images = ctx->input(0);
+    const Tensor& filters = ctx->input(1);
+    const Tensor& defv = ctx->input(2);
+    const Tensor& base_plane = ctx->input(3);
+    OP_REQUIRES(ctx, TensorShapeUtils::IsScalar(defv.shape()), errors::InvalidArgument("default_value must be scalar"));
+    OP_REQUIRES(ctx, images.dims() == 5, errors::InvalidArgument("images must have rank 5"));
+    OP_REQUIRES(ctx, filters.dims() == 5, errors::InvalidArgument("filter must have rank 5"));
+    OP_REQUIRES(ctx, images.dim_size(4) == filters.dim_size(3), errors::InvalidArgument("images channel size wrong"));
+    chop_sc_desc d = {};
+    d.dtype = DtypeOf<T>::value;
+    d.dynamic_default = dynamic_default_;
+    d.B = images.dim_size(0); d.H = images.dim_size(1); d.W = images.dim_size(2); d.D = images.dim_size(3);
+    d.Cin = images.dim_size(4); d.Cout = filters.dim_size(4);
+    for (int i = 0; i < 3; ++i) {
+      d.filter[i] = filters.dim_size(i);
+      d.strides[i] = strides_[i];
+      d.dilations[i] = dilations_[i];
+    }
+    OP_REQUIRES(ctx, base_plane.dims() == 4 && base_plane.dim_size(0) == d.B && base_plane.dim_size(1) == d.H &&
+                         base_plane.dim_size(2) == d.W && base_plane.dim_size(3) == 1,
+                errors::InvalidArgument("base_plane must have rank 4, and must compate to ref_image"));
+    TensorShape out_shape({d.B, (d.H + strides_[0] - 1) / strides_[0], (d.W + strides_[1] - 1) / strides_[1],
+                           (d.D + strides_[2] - 1) / strides_[2], d.Cout});
+    int status;
+    if (!GRADIENT) {
+      Tensor* out = nullptr;
+      OP_REQUIRES_OK(ctx, ctx->allocate_output(0, out_shape, &out));
+      status = chop_sparse_conv3d_fwd(&d, In(ctx, 0), In(ctx, 1), In(ctx, 2), static_cast<const int32_t*>(In(ctx, 3)), Out(out),
+                                      StreamOf(ctx));
+    } else {
+      const Tensor& out_grad = ctx->input(4);
+      OP_REQUIRES(ctx, out_grad.shape() == out_shape, errors::InvalidArgument("out_grad must have rank 5, and must compate to ref_image"));
+      Tensor *ig = nullptr, *fg = nullptr, *dg = nullptr, ws;
+      OP_REQUIRES_OK(ctx, ctx->allocate_output(0, images.shape(), &ig));
+      OP_REQUIRES_OK(ctx, ctx->allocate_output(1, filters.shape(), &fg));
+      OP_REQUIRES_OK(ctx, ctx->allocate_output(2, defv.shape(), &dg));
+      const int64 ws_bytes = chop_sparse_conv3d_bwd_workspace_size(&d);
+      OP_REQUIRES_OK(ctx, ctx->allocate_temp(DT_UINT8, TensorShape({ws_bytes}), &ws));
+      status = chop_sparse_conv3d_bwd(&d, In(ctx, 0), In(ctx, 1), In(ctx, 2), static_cast<const int32_t*>(In(ctx, 3)), In(ctx, 4),
+                                      Out(ig), Out(fg), Out(dg), Out(&ws), ws_bytes, StreamOf(ctx));
+    }
+    OP_REQUIRES(ctx, status == 0, errors::Internal("libchop_b200: ", chop_status_string(status)));
+  }
+
+ private:
+  std::vector<int32> strides_, dilations_;
+  bool dynamic_default_ = false;
+};
+
+#define CHOP_REGISTER(T)                                                                                                   \
+  REGISTER_KERNEL_BUILDER(Name("CostVolume").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), CostOp<T, CHOP_COST_VOLUME, false>);      \
+  REGISTER_KERNEL_BUILDER(Name("CostVolumeGrad").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), CostOp<T, CHOP_COST_VOLUME, true>);   \
+  REGISTER_KERNEL_BUILDER(Name("CostVolumeV2").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), CostOp<T, CHOP_COST_VOLUME_V2, false>); \
+  REGISTER_KERNEL_BUILDER(Name("CostVolumeGradV2").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), CostOp<T, CHOP_COST_VOLUME_V2, true>); \
+  REGISTER_KERNEL_BUILDER(Name("CostAggregate").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), CostOp<T, CHOP_COST_AGGREGATE, false>); \
+  REGISTER_KERNEL_BUILDER(Name("CostAggregateGrad").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), CostOp<T, CHOP_COST_AGGREGATE, true>); \
+  REGISTER_KERNEL_BUILDER(Name("SparseConv3DFast").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), ManifoldConvOp<T, false>);          \
+  REGISTER_KERNEL_BUILDER(Name("SparseConv3DFastGrad").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), ManifoldConvOp<T, true>);
+
+CHOP_REGISTER(float)
+CHOP_REGISTER(double)
+#undef CHOP_REGISTER
+#endif  // GOOGLE_CUDA
+
+}  // namespace chop_b200
+}  // namespace tensorflow
