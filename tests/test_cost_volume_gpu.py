@@ -240,3 +240,40 @@ def test_host_pipeline_matches_device_ops():
         got = dict(cost=out["cost"].numpy(), mask=out["mask"].numpy(), ref_grad=out["ref_grad"].numpy(),
                    src_grad=out["src_grad"].numpy(), depth_grad=out["base_plane_grad"].numpy())
         check(got, want, np.float32, exact_cost=False)
+
+
+EDGE = [  # B, N, H, W, C, D : single plane, tiny images, many views, batch of odd sizes, wide channel counts
+    (1, 1, 2, 2, 4, 1), (1, 9, 6, 7, 32, 5), (3, 2, 5, 3, 8, 17), (1, 2, 4, 4, 128, 3), (2, 11, 4, 5, 16, 2), (1, 3, 3, 50, 1, 9),
+]
+
+
+@pytest.mark.parametrize("shape", EDGE)
+@pytest.mark.parametrize("kind", [1, 2, 3])
+def test_edge_shapes(shape, kind):
+    B, N, H, W, C, D = shape
+    groups = (C // 4 if C % 4 == 0 else 1) if kind == 2 else 1
+    c = helpers.make_case(kind, 900 + C + D, B, N, H, W, C, D, "random", np.float32)
+    for reduce in ("MEAN", "MIN"):
+        want = helpers.oracle_fwd_bwd(kind, c, reduce, groups, True, np.float32)
+        got = run_gpu(kind, c, reduce, groups, True, want["cost_grad"], strict=True)
+        check(got, want, np.float32, exact_cost=True)
+        if reduce == "MEAN":
+            got = run_gpu(kind, c, reduce, groups, True, want["cost_grad"], strict=False)
+            check(got, want, np.float32, exact_cost=False)
+
+
+def test_views_that_see_nothing():
+    """A camera looking away (z <= 0 everywhere) and one translated out of the image: no valid sample, the MEAN
+    cost stays 0 with mask 0, the MIN cost stays at the largest float with index -1, all gradients are zero."""
+    c = helpers.make_case(1, 31, 1, 2, 6, 8, 8, 5, "identity", np.float32)
+    c["Rs"][:, 0] = -np.eye(3, dtype=np.float32)      # z = -depth
+    c["Ts"][:, 1] = np.array([1e6, 1e6, 0], np.float32)
+    for reduce in ("MEAN", "MIN"):
+        want = helpers.oracle_fwd_bwd(1, c, reduce, 1, True, np.float32)
+        assert (want["mask"] <= 0).all()
+        got = run_gpu(1, c, reduce, 1, True, want["cost_grad"], strict=True)
+        check(got, want, np.float32, exact_cost=True)
+        got = run_gpu(1, c, reduce, 1, True, want["cost_grad"], strict=False)
+        assert helpers.bits_equal(got["mask"].reshape(want["mask"].shape), want["mask"])
+        assert np.array_equal(got["cost"].reshape(want["cost"].shape), want["cost"])
+        assert not got["ref_grad"].any() and not got["src_grad"].any() and not got["depth_grad"].any()
