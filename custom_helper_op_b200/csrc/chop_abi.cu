@@ -80,7 +80,7 @@ int validate(const chop_cv_desc* d, CvArgs* a, Typed* ty) {
 // cv_tuned.cuh, which use four channels per lane for float32 and bfloat16 features alike.
 bool tuned_eligible(const chop_cv_desc* d, const CvArgs& a) {
   if (!g_tuned.load() || d->reduce != CHOP_REDUCE_MEAN || !(d->dtype == CHOP_F32 || d->dtype == CHOP_BF16)) return false;
-  if (d->kind == CHOP_COST_VOLUME) return a.C == 8 || a.C == 16 || a.C == 32 || a.C == 64;
+  if (d->kind == CHOP_COST_VOLUME || d->kind == CHOP_COST_AGGREGATE) return a.C == 8 || a.C == 16 || a.C == 32 || a.C == 64;
   if (d->kind == CHOP_COST_VOLUME_V2) {
     const int sub = a.C / a.G;  // channels per group: a lane's four channels must cover whole groups
     return (a.C == 8 || a.C == 16 || a.C == 32) && (sub == 1 || sub == 2 || sub == 4);

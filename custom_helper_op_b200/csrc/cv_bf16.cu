@@ -5,6 +5,15 @@
 
 namespace chop {
 int cv_fwd_bf16(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
+  if (p.use_tuned && p.kind == 3 && p.mode == 0 && p.cpl == 4) {
+    switch (a.C) {
+      case 8: return fwd_tuned_go<__nv_bfloat16, 8, 4, true>(a, st);
+      case 16: return fwd_tuned_go<__nv_bfloat16, 16, 4, true>(a, st);
+      case 32: return fwd_tuned_go<__nv_bfloat16, 32, 4, true>(a, st);
+      case 64: return fwd_tuned_go<__nv_bfloat16, 64, 4, true>(a, st);
+      default: break;
+    }
+  }
   if (p.use_tuned && p.kind == 2 && p.mode == 0 && p.cpl == 4) {
     const int r = tuned2_dispatch<__nv_bfloat16>(false, a, st);
     if (r != -4) return r;  // -4: no compile-time-C kernel for this (C, groups): generic kernel below
@@ -21,6 +30,15 @@ int cv_fwd_bf16(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
   return p.cpl == 8 ? fwd_kind<__nv_bfloat16, float, 8>(a, p, st) : fwd_kind<__nv_bfloat16, float, 1>(a, p, st);
 }
 int cv_bwd_bf16(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
+  if (p.use_tuned && p.kind == 3 && !p.rmin && p.cpl == 4) {
+    switch (a.C) {
+      case 8: return bwd_tuned_go<__nv_bfloat16, 8, 4, true>(a, st);
+      case 16: return bwd_tuned_go<__nv_bfloat16, 16, 4, true>(a, st);
+      case 32: return bwd_tuned_go<__nv_bfloat16, 32, 4, true>(a, st);
+      case 64: return bwd_tuned_go<__nv_bfloat16, 64, 4, true>(a, st);
+      default: break;
+    }
+  }
   if (p.use_tuned && p.kind == 2 && !p.rmin && p.cpl == 4) {
     const int r = tuned2_dispatch<__nv_bfloat16>(true, a, st);
     if (r != -4) return r;

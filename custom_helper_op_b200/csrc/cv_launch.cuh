@@ -91,9 +91,9 @@ inline int tuned_warps(size_t smem_per_warp) {
   return w;
 }
 
-template <typename T, int C, int CPL>
+template <typename T, int C, int CPL, bool AGG = false>
 inline int fwd_tuned_go(const CvArgs& a, cudaStream_t st) {
-  auto k = cv_fwd_tuned<T, C, CPL>;
+  auto k = cv_fwd_tuned<T, C, CPL, AGG>;
   const size_t spw = tuned_fwd_smem_per_warp<T>(a.N, 32 / (C / CPL));
   const int warps = tuned_warps(spw);
   const size_t smem = spw * warps;
@@ -107,9 +107,9 @@ inline int fwd_tuned_go(const CvArgs& a, cudaStream_t st) {
   return (int)cudaGetLastError();
 }
 
-template <typename T, int C, int CPL>
+template <typename T, int C, int CPL, bool AGG = false>
 inline int bwd_tuned_go(const CvArgs& a, cudaStream_t st) {
-  auto k = cv_bwd_tuned<T, C, CPL>;
+  auto k = cv_bwd_tuned<T, C, CPL, AGG>;
   const size_t spw = tuned_bwd_smem_per_warp<C>(a.N, 32 / (C / CPL));
   const int warps = 4;
   const size_t smem = spw * warps;

@@ -30,7 +30,10 @@ __host__ __device__ inline size_t tuned_fwd_smem_per_warp(int N, int G) {
 #ifndef CHOP_FWD_MIN_BLOCKS
 #define CHOP_FWD_MIN_BLOCKS 3
 #endif
-template <typename T, int C, int CPL>
+// AGG = true is CostAggregate: the same sum of squared differences added over the channels and divided
+// by views*C (cost_aggregate_kernels_gpu.cu.cc:34-127); cost is one float per voxel, written coalesced
+// after a reduce-scatter over the pixel's lanes.
+template <typename T, int C, int CPL, bool AGG = false>
 __global__ void __launch_bounds__(256, CHOP_FWD_MIN_BLOCKS) cv_fwd_tuned(const CvArgs a, const int warps, const size_t smem_per_warp) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int LG = C / CPL;
@@ -68,9 +71,10 @@ __global__ void __launch_bounds__(256, CHOP_FWD_MIN_BLOCKS) cv_fwd_tuned(const C
   const float* offs = static_cast<const float*>(a.offsets) + (long long)b * D;
   const size_t row = (size_t)a.Ws * C;
   const ProjF<float>* myrec = proj + g * LG;
-  float* out = static_cast<float*>(a.cost) + (pix * D + dlo) * C + li * CPL;
+  float* out = AGG ? static_cast<float*>(a.cost) + pix * D + dlo + li
+                   : static_cast<float*>(a.cost) + (pix * D + dlo) * C + li * CPL;
 
-  for (int dblk = dlo; dblk < dhi; dblk += LG, out += LG * C) {
+  for (int dblk = dlo; dblk < dhi; dblk += LG, out += AGG ? LG : LG * C) {
     // ---- phase A: lane (g, li) projects plane dblk+li of pixel g into every view ---------------------
     float inv_mine;
     {
@@ -143,12 +147,34 @@ __global__ void __launch_bounds__(256, CHOP_FWD_MIN_BLOCKS) cv_fwd_tuned(const C
       }
     }
 
+    if constexpr (AGG) {
+      // channel sum per plane, then lane li collects plane li (reduce-scatter over the pixel's lanes)
+      float tot[LG];
 #pragma unroll
-    for (int j = 0; j < LG; ++j) {
-      const float inv = __shfl_sync(0xffffffffu, inv_mine, g * LG + j);
+      for (int j = 0; j < LG; ++j) {
+        tot[j] = acc[j][0];
 #pragma unroll
-      for (int k = 0; k < CPL; ++k) acc[j][k] *= inv;
-      if (pvalid && dblk + j < dhi) store_stream<float, CPL>(out + j * C, acc[j]);
+        for (int k = 1; k < CPL; ++k) tot[j] += acc[j][k];
+      }
+#pragma unroll
+      for (int s = LG / 2; s >= 1; s >>= 1) {
+#pragma unroll
+        for (int i = 0; i < s; ++i) {
+          const bool hi = (li & s) != 0;
+          const float keep = hi ? tot[i + s] : tot[i];
+          const float send = hi ? tot[i] : tot[i + s];
+          tot[i] = keep + __shfl_xor_sync(0xffffffffu, send, s);
+        }
+      }
+      if (pvalid && dblk + li < dhi) __stcs(out, tot[0] * inv_mine * (1.0f / (float)C));
+    } else {
+#pragma unroll
+      for (int j = 0; j < LG; ++j) {
+        const float inv = __shfl_sync(0xffffffffu, inv_mine, g * LG + j);
+#pragma unroll
+        for (int k = 0; k < CPL; ++k) acc[j][k] *= inv;
+        if (pvalid && dblk + j < dhi) store_stream<float, CPL>(out + j * C, acc[j]);
+      }
     }
     __syncwarp();
   }
@@ -194,7 +220,9 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
-template <typename T, int C, int CPL>
+// AGG = true is CostAggregateGrad: one upstream value per voxel, d(cost)/d(sample) = 2*diff*cost_grad/(views*C)
+// (cost_aggregate_kernels_gpu.cu.cc:385,431); the upstream value rides in the phase-A record, nothing is staged.
+template <typename T, int C, int CPL, bool AGG = false>
 __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const CvArgs a, const int warps, const size_t smem_per_warp) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int LG = C / CPL;
@@ -241,17 +269,19 @@ __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const C
   const float* cg_src = static_cast<const float*>(a.cost_grad) + (pix * D + dlo) * C + li * CPL;
 
   // stage the first block's upstream gradient
+  if constexpr (!AGG) {
 #pragma unroll
-  for (int j = 0; j < LG; ++j) {
-    if (dlo + j < dhi) cp_async16(cg_mine + j * C, cg_src + j * C);
-    else *reinterpret_cast<float4*>(cg_mine + j * C) = make_float4(0.f, 0.f, 0.f, 0.f);  // never left uninitialised
+    for (int j = 0; j < LG; ++j) {
+      if (dlo + j < dhi) cp_async16(cg_mine + j * C, cg_src + j * C);
+      else *reinterpret_cast<float4*>(cg_mine + j * C) = make_float4(0.f, 0.f, 0.f, 0.f);  // never left uninitialised
+    }
+    cp_async_commit();
   }
-  cp_async_commit();
   __syncwarp();
 
   int buf = 0;
   for (int dblk = dlo; dblk < dhi; dblk += LG, cg_src += LG * C, buf ^= (CG_BUFS - 1)) {
-    if (CG_BUFS == 2) {
+    if (!AGG && CG_BUFS == 2) {
       cp_async_wait_all();  // this block's slice has landed (each lane reads back only what it copied)
       __syncwarp();         // and every lane is done with the other buffer and with the records
       const int nxt = dblk + LG;
@@ -277,6 +307,8 @@ __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const C
         const int m0 = __ldg(a.mask + pix * D + d);
         live = m0 > 0;                       // cost_volume_kernels_gpu.cu.cc:367
         if (live) scale = 2.0f / (float)m0;  // :439
+        if (AGG && live)                     // one upstream value per voxel, divided by views*C
+          scale = 2.0f * __ldg(static_cast<const float*>(a.cost_grad) + pix * D + d) / (float)(m0 * C);
       }
       for (int n = 0; n < N; ++n) {
         ProjF<float> r;
@@ -290,7 +322,7 @@ __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const C
         recG[n * 32 + lane] = q;
       }
     }
-    if (CG_BUFS == 1) cp_async_wait_all();  // the slice requested at the end of the previous block
+    if (!AGG && CG_BUFS == 1) cp_async_wait_all();  // the slice requested at the end of the previous block
     __syncwarp();
 
     // ---- phase B ---------------------------------------------------------------------------------------
@@ -335,8 +367,13 @@ __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const C
             }
           }
           const RecG rq = rGp[j];
-          const float4 cg4 = *reinterpret_cast<const float4*>(cgb + j * C);
-          const float cgs[4] = {cg4.x * rc.aux, cg4.y * rc.aux, cg4.z * rc.aux, cg4.w * rc.aux};
+          float cgs[4];
+          if constexpr (AGG) {
+            cgs[0] = cgs[1] = cgs[2] = cgs[3] = rc.aux;
+          } else {
+            const float4 cg4 = *reinterpret_cast<const float4*>(cgb + j * C);
+            cgs[0] = cg4.x * rc.aux; cgs[1] = cg4.y * rc.aux; cgs[2] = cg4.z * rc.aux; cgs[3] = cg4.w * rc.aux;
+          }
           float w00, w01, w11, w10;
           bilinear_weights_fast(rc.dh, rc.dw, w00, w01, w11, w10);
           float hg = 0.0f, wg = 0.0f;
@@ -365,7 +402,7 @@ __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const C
         red_add<float, CPL>(gp + row + C, acc[3]);
       }
     }
-    if (CG_BUFS == 1) {
+    if (!AGG && CG_BUFS == 1) {
       // single buffer: each lane has finished reading its own slots, request the next block's slice now
       const int nxt = dblk + LG;
 #pragma unroll

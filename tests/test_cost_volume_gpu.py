@@ -83,7 +83,7 @@ def test_cost_volume_v2(cgs, reduce):
         check(got, want, np.float32, exact_cost=strict or reduce == "MIN")
 
 
-@pytest.mark.parametrize("C", [3, 8, 20, 32])
+@pytest.mark.parametrize("C", [3, 8, 16, 20, 32, 64])
 @pytest.mark.parametrize("reduce", ["MEAN", "MIN"])
 def test_cost_aggregate(C, reduce):
     c = helpers.make_case(3, 300 + C, 2, 3, 10, 14, C, 6, "random", np.float32)
@@ -110,7 +110,7 @@ def test_no_half_centor():
     check(got, want, np.float32, exact_cost=True)
 
 
-@pytest.mark.parametrize("kind,C,G", [(1, 32, 1), (1, 8, 1), (1, 64, 1), (2, 32, 8), (2, 16, 8), (2, 8, 8)])
+@pytest.mark.parametrize("kind,C,G", [(1, 32, 1), (1, 8, 1), (1, 64, 1), (2, 32, 8), (2, 16, 8), (2, 8, 8), (3, 32, 1), (3, 16, 1)])
 def test_bfloat16_features(kind, C, G):
     """bf16 features are an extension; the oracle is the float32 reference arithmetic on the
     bf16-rounded features."""
