@@ -222,6 +222,26 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 
 // AGG = true is CostAggregateGrad: one upstream value per voxel, d(cost)/d(sample) = 2*diff*cost_grad/(views*C)
 // (cost_aggregate_kernels_gpu.cu.cc:385,431); the upstream value rides in the phase-A record, nothing is staged.
+// Moments of the per-plane sample gradients over one 2x2 footprint -> the four corner gradients, added to
+// src_grad with vector reductions; the first moment is also what d(ref) loses.
+//   m0 = sum g, m1 = sum g*dw, m2 = sum g*dh, m3 = sum g*dh*dw
+//   corner (0,0): m0 - m1 - m2 + m3   (0,1): m1 - m3   (1,0): m2 - m3   (1,1): m3
+template <int CPL>
+__device__ __forceinline__ void flush_corners(float* gp, size_t row, int C, float (&m)[4][CPL], float (&rg)[CPL]) {
+  float c00[CPL], c01[CPL], c10[CPL];
+#pragma unroll
+  for (int k = 0; k < CPL; ++k) {
+    rg[k] -= m[0][k];
+    c01[k] = m[1][k] - m[3][k];
+    c10[k] = m[2][k] - m[3][k];
+    c00[k] = (m[0][k] - m[1][k]) - c10[k];
+  }
+  red_add<float, CPL>(gp, c00);
+  red_add<float, CPL>(gp + C, c01);
+  red_add<float, CPL>(gp + row, c10);
+  red_add<float, CPL>(gp + row + C, m[3]);
+}
+
 template <typename T, int C, int CPL, bool AGG = false>
 __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const CvArgs a, const int warps, const size_t smem_per_warp) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -342,13 +362,7 @@ __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const C
         const ProjF<float> rc = rA[j];
         if (rc.texel >= 0) {
           if (rc.texel != cur) {
-            if (cur >= 0) {
-              float* gp = sg_lane + (size_t)cur * C;
-              red_add<float, CPL>(gp, acc[0]);
-              red_add<float, CPL>(gp + C, acc[1]);
-              red_add<float, CPL>(gp + row, acc[2]);
-              red_add<float, CPL>(gp + row + C, acc[3]);
-            }
+            if (cur >= 0) flush_corners<CPL>(sg_lane + (size_t)cur * C, row, C, acc, rg);
             cur = rc.texel;
             const T* p00 = src_lane + (size_t)rc.texel * C;
             const T* p10 = p00 + row;
@@ -374,33 +388,29 @@ __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const C
             const float4 cg4 = *reinterpret_cast<const float4*>(cgb + j * C);
             cgs[0] = cg4.x * rc.aux; cgs[1] = cg4.y * rc.aux; cgs[2] = cg4.z * rc.aux; cgs[3] = cg4.w * rc.aux;
           }
-          float w00, w01, w11, w10;
-          bilinear_weights_fast(rc.dh, rc.dw, w00, w01, w11, w10);
-          float hg = 0.0f, wg = 0.0f;
+          // Per channel: gs = d(cost)/d(sample) (:439).  The four corner sums (:441-444) are kept as moments
+          // sum gs, sum gs*dw, sum gs*dh, sum gs*dh*dw and turned into corner values when the footprint is
+          // flushed; d(ref) (:440) is taken from the first moment at the same time.  The two coordinate
+          // derivatives (:448-449) are dw*P + Q and dh*P + R with P = sum gs*t1, Q = sum gs*u, R = sum gs*v.
+          const float hw = rc.dh * rc.dw;
+          float P = 0.0f, Q = 0.0f, R = 0.0f;
 #pragma unroll
           for (int k = 0; k < CPL; ++k) {
-            const float X = fmaf(t1[k], rc.dw, u[k]);  // d(sample)/dh
-            const float Y = fmaf(t1[k], rc.dh, v[k]);  // d(sample)/dw
+            const float X = fmaf(t1[k], rc.dw, u[k]);
             const float df = fmaf(rc.dh, X, fmaf(rc.dw, v[k], a0[k]));  // sample - ref
-            const float gs = df * cgs[k];                // :439
-            rg[k] -= gs;                                 // :440
-            acc[0][k] = fmaf(gs, w00, acc[0][k]);        // :441-444
-            acc[1][k] = fmaf(gs, w01, acc[1][k]);
-            acc[2][k] = fmaf(gs, w10, acc[2][k]);
-            acc[3][k] = fmaf(gs, w11, acc[3][k]);
-            hg = fmaf(gs, X, hg);                        // :448
-            wg = fmaf(gs, Y, wg);                        // :449
+            const float gs = df * cgs[k];
+            acc[0][k] += gs;
+            acc[1][k] = fmaf(gs, rc.dw, acc[1][k]);
+            acc[2][k] = fmaf(gs, rc.dh, acc[2][k]);
+            acc[3][k] = fmaf(gs, hw, acc[3][k]);
+            P = fmaf(gs, t1[k], P);
+            Q = fmaf(gs, u[k], Q);
+            R = fmaf(gs, v[k], R);
           }
-          dsum = fmaf(rq.gh, hg, fmaf(rq.gw, wg, dsum));  // :451
+          dsum = fmaf(rq.gh, fmaf(rc.dw, P, Q), fmaf(rq.gw, fmaf(rc.dh, P, R), dsum));  // :451
         }
       }
-      if (cur >= 0) {
-        float* gp = sg_lane + (size_t)cur * C;
-        red_add<float, CPL>(gp, acc[0]);
-        red_add<float, CPL>(gp + C, acc[1]);
-        red_add<float, CPL>(gp + row, acc[2]);
-        red_add<float, CPL>(gp + row + C, acc[3]);
-      }
+      if (cur >= 0) flush_corners<CPL>(sg_lane + (size_t)cur * C, row, C, acc, rg);
     }
     if (!AGG && CG_BUFS == 1) {
       // single buffer: each lane has finished reading its own slots, request the next block's slice now
