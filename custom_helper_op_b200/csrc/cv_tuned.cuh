@@ -441,8 +441,9 @@ __host__ __device__ inline size_t tuned2_bwd_smem_per_warp(int N, int G) {
   return (size_t)N * G * sizeof(Coef<float>) + (size_t)N * 32 * (sizeof(ProjF<float>) + sizeof(RecG));
 }
 
-// Forward: the corner differences are pre-multiplied by the reference pixel on a reload, so a plane costs
-// acc += a0' + dw*v' + dh*(u' + dw*t1')  =  sample*ref  per channel; groups are summed inside the lane.
+// Forward: on a reload the corner differences are multiplied by the reference pixel and summed over each
+// group's channels, so a plane costs  acc += a0' + dw*v' + dh*(u' + dw*t1')  per GROUP (not per channel):
+// the group's correlation  sum_c sample_c*ref_c  is bilinear in (dh, dw) with those four sums as coefficients.
 template <typename T, int C, int SUB>
 __global__ void __launch_bounds__(256, 3) cv2_fwd_tuned(const CvArgs a, const int warps, const size_t smem_per_warp) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -507,23 +508,25 @@ __global__ void __launch_bounds__(256, 3) cv2_fwd_tuned(const CvArgs a, const in
     }
     __syncwarp();
 
-    float acc[LG][CPL];
+    float acc[LG][NG];
 #pragma unroll
     for (int j = 0; j < LG; ++j)
 #pragma unroll
-      for (int k = 0; k < CPL; ++k) acc[j][k] = 0.0f;
+      for (int q = 0; q < NG; ++q) acc[j][q] = 0.0f;
 
     for (int n = 0; n < N; ++n) {
       const ProjF<float>* r = myrec + n * 32;
       int cur = -1;  // the empty footprint: all terms zero
-      float a0[CPL], u[CPL], v[CPL], t1[CPL];
+      float a0[NG], u[NG], v[NG], t1[NG];
 #pragma unroll
-      for (int k = 0; k < CPL; ++k) a0[k] = u[k] = v[k] = t1[k] = 0.0f;
+      for (int q = 0; q < NG; ++q) a0[q] = u[q] = v[q] = t1[q] = 0.0f;
 #pragma unroll
       for (int j = 0; j < LG; ++j) {
         const ProjF<float> rc = r[j];
         if (rc.texel != cur) {
           cur = rc.texel;
+#pragma unroll
+          for (int q = 0; q < NG; ++q) a0[q] = u[q] = v[q] = t1[q] = 0.0f;
           if (rc.texel >= 0) {
             const T* p00 = src_lane + (size_t)rc.texel * C;
             const T* p10 = p00 + row;
@@ -534,21 +537,19 @@ __global__ void __launch_bounds__(256, 3) cv2_fwd_tuned(const CvArgs a, const in
             Vec<T, float, CPL>::load(p10 + C, t11);
 #pragma unroll
             for (int k = 0; k < CPL; ++k) {
+              const int q = k / SUB;
               const float uu = t10[k] - t00[k];
-              a0[k] = t00[k] * refv[k];
-              u[k] = uu * refv[k];
-              v[k] = (t01[k] - t00[k]) * refv[k];
-              t1[k] = ((t11[k] - t01[k]) - uu) * refv[k];
+              a0[q] = fmaf(t00[k], refv[k], a0[q]);
+              u[q] = fmaf(uu, refv[k], u[q]);
+              v[q] = fmaf(t01[k] - t00[k], refv[k], v[q]);
+              t1[q] = fmaf((t11[k] - t01[k]) - uu, refv[k], t1[q]);
             }
-          } else {
-#pragma unroll
-            for (int k = 0; k < CPL; ++k) a0[k] = u[k] = v[k] = t1[k] = 0.0f;
           }
         }
 #pragma unroll
-        for (int k = 0; k < CPL; ++k) {
-          const float X = fmaf(t1[k], rc.dw, u[k]);
-          acc[j][k] = fmaf(rc.dh, X, fmaf(rc.dw, v[k], acc[j][k] + a0[k]));   // += sample*ref  (v2:118-120)
+        for (int q = 0; q < NG; ++q) {
+          const float X = fmaf(t1[q], rc.dw, u[q]);
+          acc[j][q] = fmaf(rc.dh, X, fmaf(rc.dw, v[q], acc[j][q] + a0[q]));   // += sum_c sample*ref  (v2:118-120)
         }
       }
     }
@@ -558,22 +559,23 @@ __global__ void __launch_bounds__(256, 3) cv2_fwd_tuned(const CvArgs a, const in
       const float inv = __shfl_sync(0xffffffffu, inv_mine, g * LG + j);
       float o[NG];
 #pragma unroll
-      for (int q = 0; q < NG; ++q) {
-        float sgrp = acc[j][q * SUB];
-#pragma unroll
-        for (int k = 1; k < SUB; ++k) sgrp += acc[j][q * SUB + k];
-        o[q] = sgrp * inv;   // v2:128-133
-      }
+      for (int q = 0; q < NG; ++q) o[q] = acc[j][q] * inv;   // v2:128-133
       if (pvalid && dblk + j < dhi) store_stream<float, NG>(out + j * GR, o);
     }
     __syncwarp();
   }
 }
 
-// Gradient.  d(ref) is a register sum; d(src) corner sums are flushed on a footprint change; the
-// depth-hypothesis gradient is per voxel: every lane keeps one partial per plane of the block, the
-// partials are reduce-scattered over the pixel's lanes (lane li ends up with plane li) and stored
-// coalesced (zero where no view saw the voxel, v2:375-378).
+// Gradient.  With bg = cost_grad[group]/views (v2:461) everything a plane contributes is linear in bg times
+// a function of (dh, dw), so per (plane, view, group) only the bilinear moments
+//   m0 += bg, m1 += bg*dw, m2 += bg*dh, m3 += bg*dh*dw
+// are accumulated while the 2x2 footprint stays; on a flush they give, per channel,
+//   d(ref)  += m0*p00 + m1*(p01-p00) + m2*(p10-p00) + m3*t1                    (v2:462)
+//   d(src corners) += ref * (m0-m1-m2+m3, m1-m3, m2-m3, m3)                     (v2:463-467)
+// The coordinate derivatives (v2:470-472) use per-group sums over channels of ref*t1, ref*(p10-p00),
+// ref*(p01-p00), formed once per footprint.  The depth-hypothesis gradient is per voxel: every lane keeps
+// one partial per plane of the block, the partials are reduce-scattered over the pixel's lanes (lane li
+// ends up with plane li) and stored coalesced (zero where no view saw the voxel, v2:375-378).
 template <typename T, int C, int SUB>
 __global__ void __launch_bounds__(128, 5) cv2_bwd_tuned(const CvArgs a, const int warps, const size_t smem_per_warp) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -655,24 +657,36 @@ __global__ void __launch_bounds__(128, 5) cv2_bwd_tuned(const CvArgs a, const in
       const ProjF<float>* rA = recA + n * 32 + g * LG;
       const RecG* rGp = recG + n * 32 + g * LG;
       int cur = -1;
-      float a0[CPL], u[CPL], v[CPL], t1[CPL], acc[4][CPL];
+      float a0[CPL], u[CPL], v[CPL], t1[CPL];   // p00 and the corner differences of the footprint
+      float T1R[NG], UR[NG], VR[NG], m[4][NG];
 #pragma unroll
-      for (int k = 0; k < CPL; ++k) {
-        a0[k] = u[k] = v[k] = t1[k] = 0.0f;
-        acc[0][k] = acc[1][k] = acc[2][k] = acc[3][k] = 0.0f;
-      }
+      for (int k = 0; k < CPL; ++k) a0[k] = u[k] = v[k] = t1[k] = 0.0f;
+#pragma unroll
+      for (int q = 0; q < NG; ++q) T1R[q] = UR[q] = VR[q] = m[0][q] = m[1][q] = m[2][q] = m[3][q] = 0.0f;
+      auto flush = [&]() {
+        float c00[CPL], c01[CPL], c10[CPL], c11[CPL];
+#pragma unroll
+        for (int k = 0; k < CPL; ++k) {
+          const int q = k / SUB;
+          rg[k] = fmaf(m[3][q], t1[k], fmaf(m[2][q], u[k], fmaf(m[1][q], v[k], fmaf(m[0][q], a0[k], rg[k]))));
+          const float w01 = m[1][q] - m[3][q], w10 = m[2][q] - m[3][q];
+          c00[k] = ((m[0][q] - m[1][q]) - w10) * refv[k];
+          c01[k] = w01 * refv[k];
+          c10[k] = w10 * refv[k];
+          c11[k] = m[3][q] * refv[k];
+        }
+        float* gp = sg_lane + (size_t)cur * C;
+        red_add<float, CPL>(gp, c00);
+        red_add<float, CPL>(gp + C, c01);
+        red_add<float, CPL>(gp + row, c10);
+        red_add<float, CPL>(gp + row + C, c11);
+      };
 #pragma unroll
       for (int j = 0; j < LG; ++j) {
         const ProjF<float> rc = rA[j];
         if (rc.texel >= 0) {
           if (rc.texel != cur) {
-            if (cur >= 0) {
-              float* gp = sg_lane + (size_t)cur * C;
-              red_add<float, CPL>(gp, acc[0]);
-              red_add<float, CPL>(gp + C, acc[1]);
-              red_add<float, CPL>(gp + row, acc[2]);
-              red_add<float, CPL>(gp + row + C, acc[3]);
-            }
+            if (cur >= 0) flush();
             cur = rc.texel;
             const T* p00 = src_lane + (size_t)rc.texel * C;
             const T* p10 = p00 + row;
@@ -682,45 +696,40 @@ __global__ void __launch_bounds__(128, 5) cv2_bwd_tuned(const CvArgs a, const in
             Vec<T, float, CPL>::load(p10, t10);
             Vec<T, float, CPL>::load(p10 + C, t11);
 #pragma unroll
+            for (int q = 0; q < NG; ++q) T1R[q] = UR[q] = VR[q] = m[0][q] = m[1][q] = m[2][q] = m[3][q] = 0.0f;
+#pragma unroll
             for (int k = 0; k < CPL; ++k) {
+              const int q = k / SUB;
               a0[k] = t00[k];
               u[k] = t10[k] - t00[k];
               v[k] = t01[k] - t00[k];
               t1[k] = (t11[k] - t01[k]) - u[k];
-              acc[0][k] = acc[1][k] = acc[2][k] = acc[3][k] = 0.0f;
+              T1R[q] = fmaf(t1[k], refv[k], T1R[q]);
+              UR[q] = fmaf(u[k], refv[k], UR[q]);
+              VR[q] = fmaf(v[k], refv[k], VR[q]);
             }
           }
           const RecG rq = rGp[j];
           float cgv[NG];
           Vec<float, float, NG>::load(cg_lane + j * GR, cgv);
-          float w00, w01, w11, w10;
-          bilinear_weights_fast(rc.dh, rc.dw, w00, w01, w11, w10);
-          float hg = 0.0f, wg = 0.0f;
+          const float hw = rc.dh * rc.dw;
+          float P = 0.0f, Q = 0.0f, R = 0.0f;
 #pragma unroll
-          for (int k = 0; k < CPL; ++k) {
-            const float bg = cgv[k / SUB] * rc.aux;                        // v2:461
-            const float X = fmaf(t1[k], rc.dw, u[k]);
-            const float Y = fmaf(t1[k], rc.dh, v[k]);
-            const float smp = fmaf(rc.dh, X, fmaf(rc.dw, v[k], a0[k]));   // bilinear sample
-            rg[k] = fmaf(bg, smp, rg[k]);                                   // v2:462
-            const float gs = bg * refv[k];                                  // v2:463
-            acc[0][k] = fmaf(gs, w00, acc[0][k]);                           // v2:464-467
-            acc[1][k] = fmaf(gs, w01, acc[1][k]);
-            acc[2][k] = fmaf(gs, w10, acc[2][k]);
-            acc[3][k] = fmaf(gs, w11, acc[3][k]);
-            hg = fmaf(gs, X, hg);                                           // v2:471
-            wg = fmaf(gs, Y, wg);                                           // v2:472
+          for (int q = 0; q < NG; ++q) {
+            const float bg = cgv[q] * rc.aux;                                // v2:461
+            m[0][q] += bg;
+            m[1][q] = fmaf(bg, rc.dw, m[1][q]);
+            m[2][q] = fmaf(bg, rc.dh, m[2][q]);
+            m[3][q] = fmaf(bg, hw, m[3][q]);
+            P = fmaf(bg, T1R[q], P);
+            Q = fmaf(bg, UR[q], Q);
+            R = fmaf(bg, VR[q], R);
           }
-          dv[j] = fmaf(rq.gh, hg, fmaf(rq.gw, wg, dv[j]));                  // v2:474
+          // d(sample)/dh summed = dw*P + Q, d(sample)/dw summed = dh*P + R           (v2:470-474)
+          dv[j] = fmaf(rq.gh, fmaf(rc.dw, P, Q), fmaf(rq.gw, fmaf(rc.dh, P, R), dv[j]));
         }
       }
-      if (cur >= 0) {
-        float* gp = sg_lane + (size_t)cur * C;
-        red_add<float, CPL>(gp, acc[0]);
-        red_add<float, CPL>(gp + C, acc[1]);
-        red_add<float, CPL>(gp + row, acc[2]);
-        red_add<float, CPL>(gp + row + C, acc[3]);
-      }
+      if (cur >= 0) flush();
     }
     // reduce-scatter the per-plane partials over the pixel's LG lanes: lane li keeps plane li
 #pragma unroll
