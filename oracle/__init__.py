@@ -21,7 +21,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _PORT = os.path.join(_HERE, "libchop_oracle.so")
 _REF = os.path.join(_HERE, "_ref", "libchop_ref.so")
 
-KIND_V1, KIND_V2, KIND_AGG = 1, 2, 3
+KIND_V1, KIND_V2, KIND_AGG, KIND_V3 = 1, 2, 3, 4
 _libs = {}
 
 
@@ -77,7 +77,8 @@ def _dims(ref, src, D):
 
 def cost_fwd(kind, ref, src, depth, offsets, Rs, Ts, reduce_method="MEAN", groups=1, half_centor=True,
              dtype=np.float32, impl="port", nthreads=None):
-    """Forward of CostVolume (kind 1), CostVolumeV2 (kind 2) or CostAggregate (kind 3).
+    """Forward of CostVolume (kind 1), CostVolumeV2 (kind 2), CostAggregate (kind 3) or CostVolumeV3
+    (kind 4: cost [B,H,W,D,1]; mask [B,H,W,D,1] for MEAN, [B,H,W,D,3] = (view, ref group, src group) for MIN).
 
     ``depth`` is base_plane [B,H,W,1] for kinds 1/3 and depth_grid [B,H,W,D] for kind 2 (offsets
     None).  Returns (cost, mask) shaped like the reference op's outputs."""
@@ -88,7 +89,7 @@ def cost_fwd(kind, ref, src, depth, offsets, Rs, Ts, reduce_method="MEAN", group
     rmin = int(reduce_method == "MIN")
     CO = C if kind == KIND_V1 else (groups if kind == KIND_V2 else 1)
     cost = np.empty((B, H, W, D, CO), dtype)
-    mask = np.empty((B, H, W, D, CO if rmin else 1), np.int32)
+    mask = np.empty((B, H, W, D, (3 if kind == KIND_V3 else CO) if rmin else 1), np.int32)
     nt = nthreads if nthreads is not None else max_threads()
     fn = _lib(impl).oracle_cost_fwd if impl == "port" else _lib(impl).ref_cost_fwd
     fn(ctypes.c_int(kind), ctypes.c_int(0 if dtype == np.float32 else 1), ctypes.c_int(rmin),
@@ -174,3 +175,92 @@ def sparse_conv3d_bwd(images, filters, default_value, base_plane, out_grad, stri
                                                _p(igrad), _p(fgrad), _p(dgrad), ctypes.c_int(nt))
     assert rc == 0
     return igrad, fgrad, dgrad.reshape(())
+
+
+def sparse_conv3d_transpose_fwd(images, filters, default_value, base_plane, output_size, strides=(1, 1, 1),
+                                dilations=(1, 1, 1), dtype=np.float32, nthreads=None):
+    """SparseConv3DTransposeFast forward: images [B,oH,oW,oD,Cout] (coarse), filters [fh,fw,fd,Cin,Cout],
+    base_plane [B,H,W,1] and output_size = (H,W,D) of the fine grid -> [B,H,W,D,Cin]."""
+    dtype = np.dtype(dtype)
+    images, filters = _prep(dtype, images, filters)
+    base_plane = np.ascontiguousarray(base_plane, np.int32)
+    defv = np.asarray(default_value, dtype).reshape(1)
+    B = images.shape[0]
+    H, W, D = [int(x) for x in output_size]
+    fh, fw, fd, Cin, Cout = filters.shape
+    p = (ctypes.c_int * 15)(B, H, W, D, Cin, Cout, fh, fw, fd, *[int(x) for x in strides], *[int(x) for x in dilations])
+    coarse = tuple((n + s - 1) // s for n, s in zip((H, W, D), strides))
+    assert tuple(images.shape) == (B, *coarse, Cout), (images.shape, coarse)
+    assert tuple(base_plane.shape[:3]) == (B, H, W)
+    out = np.empty((B, H, W, D, Cin), dtype)
+    nt = nthreads if nthreads is not None else max_threads()
+    rc = _lib("port").oracle_sparse_conv3d_transpose_fwd(ctypes.c_int(0 if dtype == np.float32 else 1), p, _p(images),
+                                                         _p(filters), _p(defv), _p(base_plane), _p(out), ctypes.c_int(nt))
+    assert rc == 0
+    return out
+
+
+def sparse_conv3d_transpose_bwd(images, filters, default_value, base_plane, output_size, out_grad, strides=(1, 1, 1),
+                                dilations=(1, 1, 1), reference_quirks=False, dtype=np.float32, nthreads=None):
+    """SparseConv3DTransposeFastGrad: returns (images_grad, filter_grad).  reference_quirks=True reproduces the
+    buffers the reference's grad op writes (see sparse_oracle.c); False gives the derivatives."""
+    dtype = np.dtype(dtype)
+    images, filters, out_grad = _prep(dtype, images, filters, out_grad)
+    base_plane = np.ascontiguousarray(base_plane, np.int32)
+    defv = np.asarray(default_value, dtype).reshape(1)
+    B = images.shape[0]
+    H, W, D = [int(x) for x in output_size]
+    fh, fw, fd, Cin, Cout = filters.shape
+    p = (ctypes.c_int * 15)(B, H, W, D, Cin, Cout, fh, fw, fd, *[int(x) for x in strides], *[int(x) for x in dilations])
+    assert tuple(out_grad.shape) == (B, H, W, D, Cin)
+    igrad = np.empty_like(images)
+    fgrad = np.empty_like(filters)
+    nt = nthreads if nthreads is not None else max_threads()
+    rc = _lib("port").oracle_sparse_conv3d_transpose_bwd(ctypes.c_int(0 if dtype == np.float32 else 1), p, _p(images),
+                                                         _p(filters), _p(defv), _p(base_plane), _p(out_grad),
+                                                         ctypes.c_int(int(reference_quirks)), _p(igrad), _p(fgrad),
+                                                         ctypes.c_int(nt))
+    assert rc == 0
+    return igrad, fgrad
+
+
+def _pad_params(images, strides):
+    B, h, w, d, C = images.shape
+    sr, sc, sd = [int(x) for x in strides]
+    p = (ctypes.c_int * 15)(B, h, w, d, C, 0, 0, 0, 0, sr, sc, sd, 1, 1, 1)
+    q = (ctypes.c_int * 11)(sr, sc, sd, B, h, w, d, C, h * sr, w * sc, d * sd)
+    return p, q, (B, h * sr, w * sc, d * sd, C)
+
+
+def sparse_pad_fwd(images, base_plane, strides, dtype=np.float32, impl="port"):
+    """SparsePad: images [B,h,w,d,C] (coarse band) -> [B,h*sr,w*sc,d*sd,C] with zeros between; base_plane
+    [B,h*sr,w*sc,1] is the fine band's first plane."""
+    dtype = np.dtype(dtype)
+    images, = _prep(dtype, images)
+    base_plane = np.ascontiguousarray(base_plane, np.int32)
+    p, q, oshape = _pad_params(images, strides)
+    assert tuple(base_plane.shape[:3]) == oshape[:3]
+    out = np.empty(oshape, dtype)
+    dt = ctypes.c_int(0 if dtype == np.float32 else 1)
+    if impl == "port":
+        _lib("port").oracle_sparse_pad_fwd(dt, p, _p(images), _p(base_plane), _p(out))
+    else:
+        _lib("ref").ref_sparse_pad_fwd(dt, q, _p(images), _p(base_plane), _p(out))
+    return out
+
+
+def sparse_pad_bwd(images, base_plane, out_grad, strides, reference_quirk=False, dtype=np.float32, impl="port"):
+    """SparsePadGrad.  impl="ref" runs the reference kernel, which reads the wrong pixel when a row/column
+    stride exceeds 1 (see sparse_oracle.c); impl="port" with reference_quirk=True reproduces that."""
+    dtype = np.dtype(dtype)
+    images, out_grad = _prep(dtype, images, out_grad)
+    base_plane = np.ascontiguousarray(base_plane, np.int32)
+    p, q, oshape = _pad_params(images, strides)
+    assert tuple(out_grad.shape) == oshape
+    igrad = np.empty_like(images)
+    dt = ctypes.c_int(0 if dtype == np.float32 else 1)
+    if impl == "port":
+        _lib("port").oracle_sparse_pad_bwd(dt, p, _p(base_plane), _p(out_grad), ctypes.c_int(int(reference_quirk)), _p(igrad))
+    else:
+        _lib("ref").ref_sparse_pad_bwd(dt, q, _p(images), _p(base_plane), _p(out_grad), _p(igrad))
+    return igrad

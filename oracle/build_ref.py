@@ -43,6 +43,12 @@ EXTRACTS = [
      ["SparseConv3DKernel"],
      ["SPARSE_CONV3D_KERNEL_BASE_ARG_DEF_LIST", "CHECK_PADDING"], "ref_sparse_conv3d.inc"),
     ("sparse_conv.h", [], ["SPARSE_CONV3D_FIX_PARAMETOR_DEF_LIST"], "ref_sparse_conv_macros.inc"),
+    ("cost_volume_v3.h", [], ["MAX_SUBCHANNELS_SIZE"], "ref_cost_volume_v3_macros.inc"),
+    ("cost_volume_kernels_gpu_v3.cu.cc",
+     ["CostMeanVolumeV3Kernel", "CostMinVolumeV3Kernel", "CostMeanVolumeGradV3Kernel", "CostMinVolumeGradV3Kernel"],
+     [], "ref_cost_volume_v3.inc"),
+    ("sparse_pad.h", [], ["SPARSE_PAD_BASE_ARG_DEF_LIST"], "ref_sparse_pad_macros.inc"),
+    ("sparse_pad_kernels_gpu.cu.cc", ["SparsePadKernel", "SparsePadGradKernel"], [], "ref_sparse_pad.inc"),
 ]
 
 

@@ -41,6 +41,11 @@ int oracle_cost_fwd(int kind, int dtype, int reduce_min, int half_centor, const 
                     int groups, const void *ref, const void *src, const void *depth,
                     const void *offsets, const void *Rs, const void *Ts, void *cost,
                     int32_t *mask, int nthreads) {
+  if (kind == 4) {
+    if (dtype == 0) cost3_fwd_f32(reduce_min, half_centor, dims, groups, ref, src, depth, offsets, Rs, Ts, cost, mask, nthreads);
+    else cost3_fwd_f64(reduce_min, half_centor, dims, groups, ref, src, depth, offsets, Rs, Ts, cost, mask, nthreads);
+    return 0;
+  }
   if (dtype == 0)
     cost_fwd_f32(kind, reduce_min, half_centor, dims, groups, ref, src, depth, offsets, Rs, Ts, cost, mask, nthreads);
   else
@@ -53,6 +58,11 @@ int oracle_cost_bwd(int kind, int dtype, int reduce_min, int half_centor, const 
                     const void *offsets, const void *Rs, const void *Ts, const void *cost_grad,
                     const int32_t *mask, void *ref_grad, void *src_grad, void *depth_grad,
                     int nthreads) {
+  if (kind == 4) {
+    if (dtype == 0) cost3_bwd_f32(reduce_min, half_centor, dims, groups, ref, src, depth, offsets, Rs, Ts, cost_grad, mask, ref_grad, src_grad, depth_grad, nthreads);
+    else cost3_bwd_f64(reduce_min, half_centor, dims, groups, ref, src, depth, offsets, Rs, Ts, cost_grad, mask, ref_grad, src_grad, depth_grad, nthreads);
+    return 0;
+  }
   if (dtype == 0)
     cost_bwd_f32(kind, reduce_min, half_centor, dims, groups, ref, src, depth, offsets, Rs, Ts, cost_grad, mask, ref_grad, src_grad, depth_grad, nthreads);
   else

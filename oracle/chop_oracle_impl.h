@@ -227,3 +227,138 @@ static void FN(cost_bwd)(int kind, int reduce_min, int half_centor, const int64_
     }
   }
 }
+
+/* ---- kind 4 = CostVolumeV3 (cost_volume_kernels_gpu_v3.cu.cc) ---------------------------------------
+ * cost [B,H,W,D,1]; depth = base_plane + offsets as in kind 1.  Per view the cost is the LARGEST dot
+ * product between any group of the sampled source feature and any group of the reference feature
+ * (groups are contiguous blocks of sub = C/groups <= 8 channels, :111-128); the running maximum starts
+ * at the smallest positive normal number, so a view whose dot products are all <= that contributes that
+ * number.  MEAN averages the per-view maxima over the valid views, mask = number of valid views
+ * (:130-141).  MIN keeps the maximum over views too, mask [..,3] = (view, reference group, source group)
+ * of the winner or -1,-1,-1 and cost 0 when nothing exceeded the start value (:190-193,237-257). */
+static REAL FN(v3_best)(const REAL *rc, const REAL *t00, const REAL *t01, const REAL *t10, const REAL *t11,
+                        const REAL wt[4], int64_t groups, int64_t sub, REAL start, int *best_gi, int *best_gs) {
+  REAL cur = start;
+  REAL buf[64];
+  for (int64_t gs = 0; gs < groups; ++gs) {
+    for (int64_t k = 0; k < sub; ++k) {
+      const int64_t c = gs * sub + k;
+      buf[k] = wt[0] * t00[c] + wt[1] * t01[c] + wt[2] * t11[c] + wt[3] * t10[c];   /* :114-115 */
+    }
+    for (int64_t gi = 0; gi < groups; ++gi) {
+      REAL tmp = (REAL)0;
+      for (int64_t k = 0; k < sub; ++k) tmp += buf[k] * rc[gi * sub + k];            /* :119-122 */
+      if (cur < tmp) { cur = tmp; *best_gi = (int)gi; *best_gs = (int)gs; }          /* :123-125 */
+    }
+  }
+  return cur;
+}
+
+static void FN(cost3_fwd)(int reduce_min, int half_centor, const int64_t *dims, int groups, const REAL *ref,
+                          const REAL *src, const REAL *base, const REAL *offsets, const REAL *Rs,
+                          const REAL *Ts, REAL *cost, int32_t *mask, int nthreads) {
+  const int64_t B = dims[0], H = dims[1], W = dims[2], C = dims[3], D = dims[4], N = dims[5],
+                Hs = dims[6], Ws = dims[7];
+  const int64_t sub = C / groups, npix = B * H * W;
+#pragma omp parallel for schedule(dynamic, 16) num_threads(nthreads > 0 ? nthreads : 1)
+  for (int64_t pix = 0; pix < npix; ++pix) {
+    const int64_t b = pix / (H * W), h = (pix / W) % H, w = pix % W;
+    REAL x = (REAL)w, y = (REAL)h;
+    if (half_centor) { x = x + (REAL)0.5; y = y + (REAL)0.5; }
+    const REAL *rc = ref + pix * C;
+    for (int64_t d = 0; d < D; ++d) {
+      const int64_t vox = pix * D + d;
+      const REAL depth = base[pix] + offsets[b * D + d];
+      int32_t used = 0;
+      int32_t win[3] = {-1, -1, -1};
+      REAL acc = reduce_min ? REAL_MIN_POS : (REAL)0;
+      for (int64_t n = 0; n < N; ++n) {
+        FN(proj) p;
+        FN(project)(x, y, depth, Rs + (b * N + n) * 9, Ts + (b * N + n) * 3, half_centor, Hs, Ws, &p);
+        if (!p.valid) continue;
+        REAL wt[4];
+        FN(weights)(p.dh, p.dw, wt);
+        const REAL *t00 = src + C * (p.fw + Ws * (p.fh + Hs * (n + N * b)));
+        const REAL *t01 = t00 + C, *t10 = t00 + Ws * C, *t11 = t10 + C;
+        int gi = -1, gs = -1;
+        if (reduce_min) {
+          const REAL best = FN(v3_best)(rc, t00, t01, t10, t11, wt, groups, sub, acc, &gi, &gs);
+          if (gi >= 0) { acc = best; win[0] = (int32_t)n; win[1] = gi; win[2] = gs; }
+        } else {
+          acc += FN(v3_best)(rc, t00, t01, t10, t11, wt, groups, sub, REAL_MIN_POS, &gi, &gs);  /* :130 */
+          used += 1;
+        }
+      }
+      if (reduce_min) {
+        mask[vox * 3] = win[0]; mask[vox * 3 + 1] = win[1]; mask[vox * 3 + 2] = win[2];
+        cost[vox] = win[0] >= 0 ? acc : (REAL)0;
+      } else {
+        mask[vox] = used;
+        cost[vox] = used > 0 ? acc / (REAL)used : (REAL)0;
+      }
+    }
+  }
+}
+
+/* Gradient (:376-520 MEAN, :522-639 MIN): only the winning pair of groups of each view receives a
+ * gradient.  MEAN recomputes the winner per view; a view in which no dot product exceeded the start
+ * value has no winner - the reference then indexes group -1 (out of bounds); here that view contributes
+ * nothing.  MIN reads the winner from the mask and does not re-test the sample position. */
+static void FN(cost3_bwd)(int reduce_min, int half_centor, const int64_t *dims, int groups, const REAL *ref,
+                          const REAL *src, const REAL *base, const REAL *offsets, const REAL *Rs,
+                          const REAL *Ts, const REAL *cost_grad, const int32_t *mask, REAL *ref_grad,
+                          REAL *src_grad, REAL *depth_grad, int nthreads) {
+  const int64_t B = dims[0], H = dims[1], W = dims[2], C = dims[3], D = dims[4], N = dims[5],
+                Hs = dims[6], Ws = dims[7];
+  const int64_t sub = C / groups, npix = B * H * W;
+  memset(ref_grad, 0, sizeof(REAL) * (size_t)(npix * C));
+  memset(src_grad, 0, sizeof(REAL) * (size_t)(B * N * Hs * Ws * C));
+  memset(depth_grad, 0, sizeof(REAL) * (size_t)npix);
+  const int par = nthreads > 1;
+#pragma omp parallel for schedule(dynamic, 16) num_threads(par ? nthreads : 1) if (par)
+  for (int64_t pix = 0; pix < npix; ++pix) {
+    const int64_t b = pix / (H * W), h = (pix / W) % H, w = pix % W;
+    REAL x = (REAL)w, y = (REAL)h;
+    if (half_centor) { x = x + (REAL)0.5; y = y + (REAL)0.5; }
+    const REAL *rc = ref + pix * C;
+    REAL *rg = ref_grad + pix * C;
+    for (int64_t d = 0; d < D; ++d) {
+      const int64_t vox = pix * D + d;
+      const int32_t *mo = mask + vox * (reduce_min ? 3 : 1);
+      if (reduce_min ? (mo[0] < 0) : (mo[0] <= 0)) continue;                       /* :393, :541 */
+      const REAL depth = base[pix] + offsets[b * D + d];
+      const REAL cg = reduce_min ? cost_grad[vox] : cost_grad[vox] / (REAL)mo[0];   /* :426 */
+      REAL dsum = (REAL)0;
+      for (int64_t n = reduce_min ? mo[0] : 0; n < (reduce_min ? mo[0] + 1 : N); ++n) {
+        FN(proj) p;
+        FN(project)(x, y, depth, Rs + (b * N + n) * 9, Ts + (b * N + n) * 3, half_centor, Hs, Ws, &p);
+        if (!p.valid) continue;
+        REAL wt[4];
+        FN(weights)(p.dh, p.dw, wt);
+        const int64_t off = C * (p.fw + Ws * (p.fh + Hs * (n + N * b)));
+        const REAL *t00 = src + off, *t01 = t00 + C, *t10 = t00 + Ws * C, *t11 = t10 + C;
+        REAL *g00 = src_grad + off, *g01 = g00 + C, *g10 = g00 + Ws * C, *g11 = g10 + C;
+        int gi = -1, gs = -1;
+        if (reduce_min) { gi = mo[1]; gs = mo[2]; }
+        else FN(v3_best)(rc, t00, t01, t10, t11, wt, groups, sub, REAL_MIN_POS, &gi, &gs);
+        if (gi < 0) continue;
+        REAL hg = (REAL)0, wg = (REAL)0;
+        for (int64_t k = 0; k < sub; ++k) {
+          const int64_t r = gi * sub + k, c = gs * sub + k;
+          REAL s = wt[0] * t00[c] + wt[1] * t01[c] + wt[2] * t11[c] + wt[3] * t10[c];
+          rg[r] += cg * s;                                                           /* :490 */
+          REAL bg = cg * rc[r];
+          SCATTER_ADD(&g00[c], bg * wt[0]);
+          SCATTER_ADD(&g01[c], bg * wt[1]);
+          SCATTER_ADD(&g11[c], bg * wt[2]);
+          SCATTER_ADD(&g10[c], bg * wt[3]);
+          REAL t1 = t11[c] - t10[c] - t01[c] + t00[c];                               /* :498 */
+          hg += bg * (t1 * p.dw + t10[c] - t00[c]);
+          wg += bg * (t1 * p.dh + t01[c] - t00[c]);
+        }
+        dsum += ((p.hc * p.z - p.zc * p.h3d) * hg + (p.wc * p.z - p.zc * p.w3d) * wg) / (p.z * p.z);
+      }
+      depth_grad[pix] += dsum;
+    }
+  }
+}

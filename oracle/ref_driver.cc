@@ -23,6 +23,10 @@ thread_local int64 hi = 0;
 #include "ref_cost_aggregate.inc"
 #include "ref_sparse_conv_macros.inc"
 #include "ref_sparse_conv3d.inc"
+#include "ref_cost_volume_v3_macros.inc"
+#include "ref_cost_volume_v3.inc"
+#include "ref_sparse_pad_macros.inc"
+#include "ref_sparse_pad.inc"
 
 namespace {
 
@@ -58,11 +62,14 @@ bool needs_int64(const Dims& s, int64 out_channels) {
 #define V1_ARGS(I)                                                                                 \
   (I) count, (I)s.B, (I)s.H, (I)s.W, (I)s.C, (I)s.D, (I)s.N, (I)s.Hs, (I)s.Ws, ref, src, depth, \
       offsets, Rs, Ts
+#define V3_ARGS(I)                                                                                 \
+  (I) count, (I)s.B, (I)s.H, (I)s.W, (I)s.C, (I)s.D, (I)s.N, (I)s.Hs, (I)s.Ws, (int32)groups,   \
+      ref, src, depth, offsets, Rs, Ts
 #define V2_ARGS(I)                                                                                 \
   (I) count, (I)s.B, (I)s.H, (I)s.W, (I)s.C, (I)s.D, (I)s.N, (I)s.Hs, (I)s.Ws, (int32)groups,   \
       ref, src, depth, Rs, Ts
 
-// kind: 1 = CostVolume, 2 = CostVolumeV2, 3 = CostAggregate
+// kind: 1 = CostVolume, 2 = CostVolumeV2, 3 = CostAggregate, 4 = CostVolumeV3
 template <typename T, typename I, bool HC>
 void fwd_t(int kind, int reduce_min, const Dims& s, int groups, const T* ref, const T* src,
            const T* depth, const T* offsets, const T* Rs, const T* Ts, T* cost, int32* mask,
@@ -78,6 +85,11 @@ void fwd_t(int kind, int reduce_min, const Dims& s, int groups, const T* ref, co
       sweep(count, nthreads, [&] { CostMeanVolumeV2Kernel<T, I, HC>(V2_ARGS(I), cost, mask); });
     else
       sweep(count, nthreads, [&] { CostMinVolumeV2Kernel<T, I, HC>(V2_ARGS(I), cost, mask); });
+  } else if (kind == 4) {
+    if (!reduce_min)
+      sweep(count, nthreads, [&] { CostMeanVolumeV3Kernel<T, I, HC>(V3_ARGS(I), cost, mask); });
+    else
+      sweep(count, nthreads, [&] { CostMinVolumeV3Kernel<T, I, HC>(V3_ARGS(I), cost, mask); });
   } else {
     if (!reduce_min)
       sweep(count, nthreads, [&] { CostMeanAggregateKernel<T, I, HC>(V1_ARGS(I), cost, mask); });
@@ -111,6 +123,15 @@ void bwd_t(int kind, int reduce_min, const Dims& s, int groups, const T* ref, co
     else
       sweep(count, nthreads, [&] {
         CostMinVolumeGradV2Kernel<T, I, HC>(V2_ARGS(I), cost_grad, mask, ref_grad, src_grad, depth_grad);
+      });
+  } else if (kind == 4) {
+    if (!reduce_min)
+      sweep(count, nthreads, [&] {
+        CostMeanVolumeGradV3Kernel<T, I, HC>(V3_ARGS(I), cost_grad, mask, ref_grad, src_grad, depth_grad);
+      });
+    else
+      sweep(count, nthreads, [&] {
+        CostMinVolumeGradV3Kernel<T, I, HC>(V3_ARGS(I), cost_grad, mask, ref_grad, src_grad, depth_grad);
       });
   } else {
     if (!reduce_min)
@@ -207,6 +228,34 @@ int ref_sparse_conv3d_fwd(int dtype, const int* p, const void* images, const voi
           (const double*)default_value, base_plane, (double*)out);
     });
 #undef SC_ARGS
+  return 0;
+}
+
+// SparsePad / SparsePadGrad (custom_helper_op/cc/kernels/sparse_pad_kernels_gpu.cu.cc:36-64, 82-104).
+// q = {stride h,w,d, B, coarse H,W,D, C, fine H,W,D}.
+int ref_sparse_pad_fwd(int dtype, const int* q, const void* images, const int32* base_plane, void* out) {
+  const int32 count = q[3] * q[8] * q[9] * q[10];
+#define PAD_ARGS q[0], q[1], q[2], q[3], q[4], q[5], q[6], q[7], q[8], q[9], q[10]
+  if (dtype == 0)
+    sweep(count, 1, [&] { SparsePadKernel<float, int32>(count, PAD_ARGS, (const float*)images, base_plane, (float*)out); });
+  else
+    sweep(count, 1, [&] { SparsePadKernel<double, int32>(count, PAD_ARGS, (const double*)images, base_plane, (double*)out); });
+  return 0;
+}
+int ref_sparse_pad_bwd(int dtype, const int* q, const void* images, const int32* base_plane, const void* out_grad,
+                       void* images_grad) {
+  const int32 count = q[3] * q[4] * q[5] * q[6];
+  if (dtype == 0)
+    sweep(count, 1, [&] {
+      SparsePadGradKernel<float, int32>(count, PAD_ARGS, (const float*)images, base_plane, (const float*)out_grad,
+                                        (float*)images_grad);
+    });
+  else
+    sweep(count, 1, [&] {
+      SparsePadGradKernel<double, int32>(count, PAD_ARGS, (const double*)images, base_plane, (const double*)out_grad,
+                                         (double*)images_grad);
+    });
+#undef PAD_ARGS
   return 0;
 }
 

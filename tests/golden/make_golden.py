@@ -34,7 +34,25 @@ CASES = {
     "v2_mean_f64_shift": (2, "MEAN", "float64", "shift", 1, 2, 12, 16, 8, 6, 2, True),
     "agg_mean_f32_random": (3, "MEAN", "float32", "random", 1, 2, 12, 16, 8, 6, 1, True),
     "agg_min_f32_random": (3, "MIN", "float32", "random", 1, 3, 12, 16, 5, 6, 1, True),
+    "v3_mean_f32_random": (4, "MEAN", "float32", "random", 1, 2, 12, 16, 8, 6, 4, True),
+    "v3_min_f32_shift": (4, "MIN", "float32", "shift", 1, 3, 12, 16, 6, 5, 2, True),
 }
+
+# SparsePad fixtures: name: (B, coarse h, w, d, C, strides).  The gradient fixture keeps the row/column
+# strides at 1, where the reference kernel reads the pixel it means to.
+PAD_CASES = {
+    "pad_f32_s223": (2, 5, 6, 4, 3, (2, 2, 3)),
+    "pad_f32_s112": (1, 6, 7, 5, 2, (1, 1, 2)),
+}
+
+
+def build_pad_case(name):
+    B, h, w, d, C, st = PAD_CASES[name]
+    rng = np.random.default_rng(2000 + sorted(PAD_CASES).index(name))
+    images = rng.standard_normal((B, h, w, d, C)).astype(np.float32)
+    base_plane = rng.integers(0, 10, (B, h * st[0], w * st[1], 1)).astype(np.int32)
+    out_grad = rng.standard_normal((B, h * st[0], w * st[1], d * st[2], C)).astype(np.float32)
+    return images, base_plane, out_grad, st
 
 
 def build_case(name):
@@ -73,7 +91,16 @@ def main():
         path = os.path.join(HERE, name + ".npz")
         np.savez_compressed(path, **arrays)
         print("%-24s %7d bytes  valid voxels %.2f" % (name, os.path.getsize(path),
-              float((out["mask"] > (-1 if c["reduce"] == "MIN" else 0)).mean())))
+              float((out["mask"][..., :1] > (-1 if c["reduce"] == "MIN" else 0)).mean())))
+    for name in sorted(PAD_CASES):
+        images, base_plane, out_grad, st = build_pad_case(name)
+        arrays = dict(in_images=images, in_base_plane=base_plane, in_out_grad=out_grad, in_strides=np.array(st),
+                      out_output=oracle.sparse_pad_fwd(images, base_plane, st, impl="ref"))
+        if st[0] == 1 and st[1] == 1:
+            arrays["out_images_grad"] = oracle.sparse_pad_bwd(images, base_plane, out_grad, st, impl="ref")
+        path = os.path.join(HERE, name + ".npz")
+        np.savez_compressed(path, **arrays)
+        print("%-24s %7d bytes" % (name, os.path.getsize(path)))
 
 
 if __name__ == "__main__":

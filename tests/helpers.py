@@ -11,11 +11,17 @@ GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
 def golden_names():
-    return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
+    """The cost-volume fixtures (v1_*, v2_*, v3_*, agg_*)."""
+    return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz"))
+                  if not os.path.basename(p).startswith("pad_"))
+
+
+def pad_golden_names():
+    return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN_DIR, "pad_*.npz")))
 
 
 def golden_meta(name):
-    kind = {"v1": 1, "v2": 2, "agg": 3}[name.split("_")[0]]
+    kind = {"v1": 1, "v2": 2, "agg": 3, "v3": 4}[name.split("_")[0]]
     reduce = name.split("_")[1].upper()
     return kind, reduce
 

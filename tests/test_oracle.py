@@ -24,13 +24,13 @@ def test_port_matches_golden_bit_for_bit(name):
 
 
 @pytest.mark.skipif(not oracle.have_ref(), reason="oracle/_ref not built (needs the reference checkout)")
-@pytest.mark.parametrize("kind", [1, 2, 3])
+@pytest.mark.parametrize("kind", [1, 2, 3, 4])
 @pytest.mark.parametrize("reduce", ["MEAN", "MIN"])
 @pytest.mark.parametrize("camera", ["identity", "shift", "rot_z", "rot_y", "random"])
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
 def test_port_matches_reference_kernels(kind, reduce, camera, dtype):
-    groups = 3 if kind == 2 else 1
-    c = helpers.make_case(kind, 11, 2, 3, 12, 18, 9 if kind == 2 else 5, 7, camera, dtype)
+    groups = 3 if kind in (2, 4) else 1
+    c = helpers.make_case(kind, 11, 2, 3, 12, 18, 9 if kind in (2, 4) else 5, 7, camera, dtype)
     a = helpers.oracle_fwd_bwd(kind, c, reduce, groups, True, dtype, impl="port")
     b = helpers.oracle_fwd_bwd(kind, c, reduce, groups, True, dtype, impl="ref")
     for k in ("mask", "cost", "ref_grad", "src_grad", "depth_grad"):
@@ -52,9 +52,9 @@ def test_reference_threads_agree():
         assert helpers.rel_err(x, a[k]) < 1e-5
 
 
-@pytest.mark.parametrize("kind", [1, 2, 3])
+@pytest.mark.parametrize("kind", [1, 2, 3, 4])
 def test_float32_tracks_float64(kind):
-    groups = 2 if kind == 2 else 1
+    groups = 2 if kind in (2, 4) else 1
     c64 = helpers.make_case(kind, 21, 1, 2, 12, 16, 8, 6, "random", np.float64)
     c32 = {k: (None if v is None else v.astype(np.float32)) for k, v in c64.items()}
     # evaluate the double oracle on the float32-rounded inputs so only the arithmetic differs
@@ -73,11 +73,11 @@ def _loss(kind, c, groups, dtype, w):
     return float((cost * w).sum()), mask
 
 
-@pytest.mark.parametrize("kind", [1, 2, 3])
+@pytest.mark.parametrize("kind", [1, 2, 3, 4])
 def test_gradient_is_the_derivative(kind):
     """The reference validates its gradient op against a numeric Jacobian in float64
     (cost_volume_op_test.py:422-463); same check for the oracle with central differences."""
-    groups = 2 if kind == 2 else 1
+    groups = 2 if kind in (2, 4) else 1
     c = helpers.make_case(kind, 31, 1, 2, 8, 10, 4, 4, "shift", np.float64)
     rng = np.random.default_rng(1)
     cost0, mask0 = oracle.cost_fwd(kind, c["ref"], c["src"], c["depth"], c["offsets"], c["Rs"], c["Ts"], "MEAN",
