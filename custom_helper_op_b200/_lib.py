@@ -62,6 +62,17 @@ def lib():
         L.chop_sparse_conv3d_bwd.argtypes = [ctypes.POINTER(ScDesc)] + [vp] * 9 + [ctypes.c_size_t, vp]
         L.chop_sparse_conv3d_bwd_noalloc.restype = ctypes.c_int
         L.chop_sparse_conv3d_bwd_noalloc.argtypes = [ctypes.POINTER(ScDesc)] + [vp] * 9
+        L.chop_sparse_conv3d_transpose_fwd.restype = ctypes.c_int
+        L.chop_sparse_conv3d_transpose_fwd.argtypes = [ctypes.POINTER(ScDesc)] + [vp] * 6
+        L.chop_sparse_conv3d_transpose_bwd_workspace_size.restype = ctypes.c_size_t
+        L.chop_sparse_conv3d_transpose_bwd_workspace_size.argtypes = [ctypes.POINTER(ScDesc)]
+        L.chop_sparse_conv3d_transpose_bwd.restype = ctypes.c_int
+        L.chop_sparse_conv3d_transpose_bwd.argtypes = [ctypes.POINTER(ScDesc)] + [vp] * 8 + [ctypes.c_size_t, vp]
+        i64, i3 = ctypes.c_int64, ctypes.POINTER(ctypes.c_int32)
+        L.chop_sparse_pad_fwd.restype = ctypes.c_int
+        L.chop_sparse_pad_fwd.argtypes = [ctypes.c_int32, i64, i64, i64, i64, i64, i3, vp, vp, vp, vp]
+        L.chop_sparse_pad_bwd.restype = ctypes.c_int
+        L.chop_sparse_pad_bwd.argtypes = [ctypes.c_int32, i64, i64, i64, i64, i64, i3, vp, vp, vp, vp]
         L.chop_copy_2d_async.restype = ctypes.c_int
         L.chop_copy_2d_async.argtypes = [vp, ctypes.c_size_t, vp, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, vp]
         L.chop_umma_timeouts.restype = ctypes.c_int

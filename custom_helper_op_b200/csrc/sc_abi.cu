@@ -32,7 +32,9 @@ int run_wgrad(int dtype, const ScArgs& a, int nparts, cudaStream_t st) {
   }
   return chop::sc_wgrad_simt_launch_parts(dtype, a, nparts, st);
 }
-int run_dgrad(int dtype, const ScArgs& a, cudaStream_t st) {
+int run_dgrad(int dtype, const ScArgs& in, cudaStream_t st) {
+  ScArgs a = in;
+  a.pad_zero = 1;  // a padded tap contributes nothing to the image gradient (sparse_conv3d_fast_op.cc:306,321)
   if (chop::g_use_umma.load() && chop::sc_umma_supported(dtype, a)) return chop::sc_umma_dgrad_launch(a, st);
   return chop::sc_dgrad_simt_launch(dtype, a, st);
 }
@@ -64,6 +66,14 @@ int fill(const chop_sc_desc* d, ScArgs* a) {
   // are int32 too, element offsets 64-bit
   if (d->B * d->H * d->W > INT32_MAX) return CHOP_ERR_SHAPE;
   if ((int64_t)a->fh * a->fw * a->fd * a->Cin > 1024) return CHOP_ERR_UNSUPPORTED;
+  return 0;
+}
+
+// The transposed op's filter gradient gathers the coarse tensor: taps * Cout accumulator rows.
+int fill_transpose(const chop_sc_desc* d, ScArgs* a) {
+  if (int e = fill(d, a)) return e;
+  if ((int64_t)a->fh * a->fw * a->fd * a->Cout > 1024) return CHOP_ERR_UNSUPPORTED;
+  a->dynamic_default = 0;
   return 0;
 }
 
@@ -138,6 +148,73 @@ int chop_sparse_conv3d_bwd_noalloc(const chop_sc_desc* d, const void* images, co
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (int e = run_wgrad(d->dtype, a, nparts, st)) return e;
   return run_dgrad(d->dtype, a, st);
+}
+
+int chop_sparse_conv3d_transpose_fwd(const chop_sc_desc* d, const void* images, const void* filters,
+                                     const void* default_value, const int32_t* base_plane, void* output, void* stream) {
+  ScArgs a;
+  if (int e = fill_transpose(d, &a)) return e;
+  if (!images || !filters || !default_value || !base_plane || !output) return CHOP_ERR_NULL;
+  // the gather-form kernels name their coarse tensor out_grad and their fine result images_grad
+  a.out_grad = images; a.images_grad = output;
+  a.filters = filters; a.default_value = default_value; a.base_plane = base_plane;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (chop::g_use_umma.load() && chop::sc_umma_supported(d->dtype, a)) return chop::sc_umma_dgrad_launch(a, st);
+  return chop::sc_tconv_simt_launch(d->dtype, a, st);
+}
+
+size_t chop_sparse_conv3d_transpose_bwd_workspace_size(const chop_sc_desc* d) {
+  ScArgs a;
+  if (fill_transpose(d, &a)) return 0;
+  return chop::sc_wgrad_workspace_bytes(d->dtype, a.fh * a.fw * a.fd, a.Cin, a.Cout, a.nvox_in);
+}
+
+int chop_sparse_conv3d_transpose_bwd(const chop_sc_desc* d, const void* images, const void* filters,
+                                     const void* default_value, const int32_t* base_plane, const void* out_grad,
+                                     void* images_grad, void* filter_grad, void* workspace, size_t workspace_bytes,
+                                     void* stream) {
+  ScArgs a;
+  if (int e = fill_transpose(d, &a)) return e;
+  if (!images || !filters || !default_value || !base_plane || !out_grad || !images_grad || !filter_grad)
+    return CHOP_ERR_NULL;
+  const size_t need = chop::sc_wgrad_workspace_bytes(d->dtype, a.fh * a.fw * a.fd, a.Cin, a.Cout, a.nvox_in);
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15)) return CHOP_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  a.filters = filters; a.default_value = default_value; a.base_plane = base_plane;
+  // filter gradient: gathers the coarse input under every tap of every fine voxel
+  a.images = images; a.out_grad = out_grad; a.filter_grad = filter_grad; a.workspace = workspace;
+  if (int e = chop::sc_twgrad_simt_launch(d->dtype, a, chop::sc_wgrad_parts(a.nvox_in), st)) return e;
+  // image gradient: the forward convolution of out_grad (fine, Cin channels) with the same filter, a padded tap
+  // contributing nothing
+  a.images = out_grad; a.output = images_grad; a.out_grad = nullptr; a.pad_zero = 1;
+  return run_fwd(d->dtype, a, st);
+}
+
+namespace {
+int pad_check(int32_t dtype, int64_t B, int64_t h, int64_t w, int64_t d, int64_t C, const int32_t* s) {
+  if (dtype < CHOP_F32 || dtype > CHOP_BF16) return CHOP_ERR_ATTR;
+  if (!s) return CHOP_ERR_NULL;
+  if (s[0] < 1 || s[1] < 1 || s[2] < 1) return CHOP_ERR_ATTR;
+  if (B < 1 || h < 1 || w < 1 || d < 1 || C < 1) return CHOP_ERR_SHAPE;
+  if (B * h * s[0] * w * s[1] > INT32_MAX || d * s[2] > INT32_MAX || C > INT32_MAX) return CHOP_ERR_SHAPE;
+  return 0;
+}
+}  // namespace
+
+int chop_sparse_pad_fwd(int32_t dtype, int64_t B, int64_t h, int64_t w, int64_t d, int64_t C, const int32_t strides[3],
+                        const void* images, const int32_t* base_plane, void* output, void* stream) {
+  if (int e = pad_check(dtype, B, h, w, d, C, strides)) return e;
+  if (!images || !base_plane || !output) return CHOP_ERR_NULL;
+  return chop::sc_pad_launch(dtype, false, images, base_plane, output, (int)B, (int)h, (int)w, (int)d, (int)C, strides[0],
+                             strides[1], strides[2], static_cast<cudaStream_t>(stream));
+}
+
+int chop_sparse_pad_bwd(int32_t dtype, int64_t B, int64_t h, int64_t w, int64_t d, int64_t C, const int32_t strides[3],
+                        const int32_t* base_plane, const void* out_grad, void* images_grad, void* stream) {
+  if (int e = pad_check(dtype, B, h, w, d, C, strides)) return e;
+  if (!out_grad || !base_plane || !images_grad) return CHOP_ERR_NULL;
+  return chop::sc_pad_launch(dtype, true, out_grad, base_plane, images_grad, (int)B, (int)h, (int)w, (int)d, (int)C,
+                             strides[0], strides[1], strides[2], static_cast<cudaStream_t>(stream));
 }
 
 int chop_umma_timeouts(void) { return chop::sc_umma_timeouts(); }

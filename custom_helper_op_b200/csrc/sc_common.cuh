@@ -27,6 +27,7 @@ struct ScArgs {
   int fh, fw, fd, sr, sc, sd, dr, dc, dd;
   int oH, oW, oD, pr, pc, pd;
   int dynamic_default;
+  int pad_zero;               // gathered taps that are padding read 0 instead of *default_value
   long long nvox_in, nvox_out;
 };
 
@@ -59,6 +60,22 @@ __device__ __forceinline__ long long sc_tap(const ScArgs& a, int b, int ro, int 
   const int ind = depth - a.pd + fz * a.dd - __ldg(a.base_plane + pix);
   if (oob(ind, a.D)) return -1;
   return (long long)pix * a.D + ind;
+}
+
+// Gather form used by the image gradient and by the transposed convolution: index (in voxels of the
+// COARSE grid [B,oH,oW,oD]) of the voxel that lies exactly under tap (fr,fc,fz) of FINE voxel (b,r,c,dz),
+// or -1 when the tap is padding - outside the image plane, not aligned with the strides, or outside the
+// coarse band (custom_helper_op/cc/kernels/sparse_conv3d_fast_op_gpu.cu.cc:201,233-247, with the right
+// padding of sparse_conv3d_fast_op.cc:314-316 / :395-397).
+__device__ __forceinline__ long long sc_tap_t(const ScArgs& a, int b, int r, int c, int dz, int fr, int fc, int fz) {
+  const int qr = (a.fh - 1) * a.dr - a.pr, qc = (a.fw - 1) * a.dc - a.pc, qd = (a.fd - 1) * a.dd - a.pd;
+  const int orow = r - qr + fr * a.dr, ocol = c - qc + fc * a.dc;
+  if (oob(orow, a.H) || oob(ocol, a.W)) return -1;
+  int od = dz + __ldg(a.base_plane + (b * a.H + r) * a.W + c) - qd + fz * a.dd;
+  if ((orow % a.sr) != 0 || (ocol % a.sc) != 0 || (od % a.sd) != 0) return -1;
+  od = od / a.sd - (__ldg(a.base_plane + (b * a.H + orow) * a.W + ocol) + a.sd - 1) / a.sd;
+  if (oob(od, a.oD)) return -1;
+  return (((long long)b * a.oH + orow / a.sr) * a.oW + ocol / a.sc) * a.oD + od;
 }
 
 }  // namespace chop

@@ -8,6 +8,10 @@ struct ScArgs;
 int sc_fwd_simt_launch(int dtype, const ScArgs& a, cudaStream_t st);
 int sc_dgrad_simt_launch(int dtype, const ScArgs& a, cudaStream_t st);
 int sc_wgrad_simt_launch(int dtype, const ScArgs& a, cudaStream_t st);
+int sc_tconv_simt_launch(int dtype, const ScArgs& a, cudaStream_t st);
+int sc_twgrad_simt_launch(int dtype, const ScArgs& a, int nparts, cudaStream_t st);
+int sc_pad_launch(int dtype, bool grad, const void* src, const int* base_plane, void* dst, int B, int h, int w, int d,
+                  int C, int sr, int sc, int sd, cudaStream_t st);
 int sc_wgrad_parts(long long nvox_out);
 int sc_wgrad_simt_launch_parts(int dtype, const ScArgs& a, int nparts, cudaStream_t st);
 int sc_static_scratch(void** ptr, size_t* bytes);

@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(256) sc_fwd_simt(const ScArgs a) {
   const int b = (int)(v / a.oH);
   const T* img = static_cast<const T*>(a.images);
   const T* flt = static_cast<const T*>(a.filters);
-  const ACC defv = (ACC)ScIo<T>::ld(static_cast<const T*>(a.default_value));
+  const ACC defv = a.pad_zero ? (ACC)0 : (ACC)ScIo<T>::ld(static_cast<const T*>(a.default_value));
   ACC acc = 0;
   for (int fr = 0; fr < a.fh; ++fr)
     for (int fc = 0; fc < a.fw; ++fc)
@@ -53,10 +53,29 @@ __global__ void __launch_bounds__(256) sc_fwd_simt(const ScArgs a) {
   ScIo<T>::st(static_cast<T*>(a.output) + idx, acc);
 }
 
-// images_grad in gather form: the forward run over out_grad with the flipped, channel-swapped filter,
-// zero padding value and right padding (custom_helper_op/cc/kernels/sparse_conv3d_fast_op.cc:298-323).
-template <typename T, typename ACC>
+// Gather form: every voxel of the fine grid [B,H,W,D] sums, over the taps of the flipped, channel-swapped
+// filter, the coarse voxel under the tap.  Two users:
+//   * images_grad of the convolution: coarse tensor = out_grad, padded taps contribute nothing
+//     (custom_helper_op/cc/kernels/sparse_conv3d_fast_op.cc:298-323);
+//   * the transposed convolution itself: coarse tensor = its input, padded taps contribute default_value
+//     (sparse_conv3d_fast_op.cc:383-407) - PADDED: per-(tap, channel) sums of the filter over the coarse
+//     channels are formed once per CTA in shared memory, a padded tap then costs one add.
+template <typename T, typename ACC, bool PADDED>
 __global__ void __launch_bounds__(256) sc_dgrad_simt(const ScArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  ACC* wsum = reinterpret_cast<ACC*>(smem_raw);   // [taps][Cin], PADDED only
+  const T* flt = static_cast<const T*>(a.filters);
+  const int taps = a.fh * a.fw * a.fd;
+  if (PADDED) {
+    for (int e = threadIdx.x; e < taps * a.Cin; e += blockDim.x) {
+      const int t = e / a.Cin, ci = e - t * a.Cin;
+      const T* w = flt + ((long long)(taps - 1 - t) * a.Cin + ci) * a.Cout;   // flipped in all three dimensions
+      ACC sum = 0;
+      for (int o = 0; o < a.Cout; ++o) sum += (ACC)ScIo<T>::ld(w + o);
+      wsum[e] = sum;
+    }
+    __syncthreads();
+  }
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= a.nvox_in * a.Cin) return;
   const int ci = (int)(idx % a.Cin);
@@ -66,24 +85,21 @@ __global__ void __launch_bounds__(256) sc_dgrad_simt(const ScArgs a) {
   const int r = (int)(v % a.H);
   const int b = (int)(v / a.H);
   const T* og = static_cast<const T*>(a.out_grad);
-  const T* flt = static_cast<const T*>(a.filters);
-  const int qr = (a.fh - 1) * a.dr - a.pr, qc = (a.fw - 1) * a.dc - a.pc, qd = (a.fd - 1) * a.dd - a.pd;
-  const int depth = dz + __ldg(a.base_plane + (b * a.H + r) * a.W + c);
-  ACC acc = 0;
+  ACC acc = 0, pad = 0;
+  int t = 0;
   for (int fr = 0; fr < a.fh; ++fr)
     for (int fc = 0; fc < a.fw; ++fc)
-      for (int fz = 0; fz < a.fd; ++fz) {
-        const int orow = r - qr + fr * a.dr, ocol = c - qc + fc * a.dc;
-        if (oob(orow, a.H) || oob(ocol, a.W)) continue;
-        int od = depth - qd + fz * a.dd;
-        if ((orow % a.sr) != 0 || (ocol % a.sc) != 0 || (od % a.sd) != 0) continue;
-        od = od / a.sd - (__ldg(a.base_plane + (b * a.H + orow) * a.W + ocol) + a.sd - 1) / a.sd;
-        if (oob(od, a.oD)) continue;
-        const T* g = og + ((((long long)b * a.oH + orow / a.sr) * a.oW + ocol / a.sc) * a.oD + od) * a.Cout;
-        const T* w = flt + (((long long)(a.fh - 1 - fr) * a.fw + (a.fw - 1 - fc)) * a.fd + (a.fd - 1 - fz)) * a.Cin * a.Cout +
-                     (long long)ci * a.Cout;
+      for (int fz = 0; fz < a.fd; ++fz, ++t) {
+        const long long at = sc_tap_t(a, b, r, c, dz, fr, fc, fz);
+        if (at < 0) {
+          if (PADDED) pad += wsum[t * a.Cin + ci];
+          continue;
+        }
+        const T* g = og + at * a.Cout;
+        const T* w = flt + ((long long)(taps - 1 - t) * a.Cin + ci) * a.Cout;
         for (int o = 0; o < a.Cout; ++o) acc += (ACC)ScIo<T>::ld(w + o) * (ACC)ScIo<T>::ld(g + o);
       }
+  if (PADDED) acc += pad * (ACC)ScIo<T>::ld(static_cast<const T*>(a.default_value));
   ScIo<T>::st(static_cast<T*>(a.images_grad) + idx, acc);
 }
 
@@ -92,12 +108,22 @@ constexpr int WG_TM = 32;   // voxels staged per step
 constexpr int WG_NC = 16;   // output channels per sweep
 constexpr int WG_KPT = 4;   // k values per thread -> K <= 1024
 
-// partial[cta][k][n] (+ partial default gradient at the end of every CTA's slab)
-template <typename T, typename ACC>
+// partial[cta][k][n] (+ partial default gradient at the end of every CTA's slab).
+// TR = false: filter gradient of the convolution; the CTA's voxels are output voxels, k = (tap, input
+//   channel) of the gathered image value, n = output channel of out_grad.
+// TR = true: filter gradient of the TRANSPOSED convolution (sparse_conv3d_fast_op.cc:477-488); the CTA's
+//   voxels are voxels of the fine grid, k = (tap, coarse channel) of the gathered coarse input (default_value
+//   where the tap is padding), n = fine channel of out_grad; the reduce kernel moves element [tap][co][ci]
+//   to filter_grad[flipped tap][ci][co].
+template <typename T, typename ACC, bool TR>
 __global__ void __launch_bounds__(WG_THREADS) sc_wgrad_partial(const ScArgs a, const int vox_per_cta) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int taps = a.fh * a.fw * a.fd;
-  const int K = taps * a.Cin;
+  const int KC = TR ? a.Cout : a.Cin;   // channels of the gathered tensor
+  const int NC = TR ? a.Cin : a.Cout;   // channels of the upstream gradient
+  const int K = taps * KC;
+  const long long nvox = TR ? a.nvox_in : a.nvox_out;
+  const int d1 = TR ? a.D : a.oD, d2 = TR ? a.W : a.oW, d3 = TR ? a.H : a.oH;
   long long* tapidx = reinterpret_cast<long long*>(smem_raw);             // [WG_TM][taps]
   ACC* gt = reinterpret_cast<ACC*>(tapidx + (size_t)WG_TM * taps);         // [WG_TM][WG_NC]
   ACC* red = gt + WG_TM * WG_NC;                                           // [WG_THREADS]
@@ -106,12 +132,12 @@ __global__ void __launch_bounds__(WG_THREADS) sc_wgrad_partial(const ScArgs a, c
   const T* og = static_cast<const T*>(a.out_grad);
   const ACC defv = (ACC)ScIo<T>::ld(static_cast<const T*>(a.default_value));
   const long long v0 = (long long)blockIdx.x * vox_per_cta;
-  const long long v1 = min(a.nvox_out, v0 + vox_per_cta);
-  ACC* part = static_cast<ACC*>(a.workspace) + (size_t)blockIdx.x * ((size_t)K * a.Cout + 1);
+  const long long v1 = min(nvox, v0 + vox_per_cta);
+  ACC* part = static_cast<ACC*>(a.workspace) + (size_t)blockIdx.x * ((size_t)K * NC + 1);
   ACC dacc = 0;
 
-  for (int n0 = 0; n0 < a.Cout; n0 += WG_NC) {
-    const int nn = min(WG_NC, a.Cout - n0);
+  for (int n0 = 0; n0 < NC; n0 += WG_NC) {
+    const int nn = min(WG_NC, NC - n0);
     ACC acc[WG_KPT][WG_NC];
 #pragma unroll
     for (int i = 0; i < WG_KPT; ++i)
@@ -124,30 +150,30 @@ __global__ void __launch_bounds__(WG_THREADS) sc_wgrad_partial(const ScArgs a, c
       for (int e = threadIdx.x; e < tm * taps; e += WG_THREADS) {
         const int m = e / taps, t = e - m * taps;
         long long v = vt + m;
-        const int dz = (int)(v % a.oD); v /= a.oD;
-        const int co = (int)(v % a.oW); v /= a.oW;
-        const int ro = (int)(v % a.oH);
-        const int b = (int)(v / a.oH);
+        const int dz = (int)(v % d1); v /= d1;
+        const int co = (int)(v % d2); v /= d2;
+        const int ro = (int)(v % d3);
+        const int b = (int)(v / d3);
         const int fz = t % a.fd, fc = (t / a.fd) % a.fw, fr = t / a.fd / a.fw;
-        tapidx[m * taps + t] = sc_tap(a, b, ro, co, dz, fr, fc, fz);
+        tapidx[m * taps + t] = TR ? sc_tap_t(a, b, ro, co, dz, fr, fc, fz) : sc_tap(a, b, ro, co, dz, fr, fc, fz);
       }
       for (int e = threadIdx.x; e < tm * WG_NC; e += WG_THREADS) {
         const int m = e / WG_NC, n = e - m * WG_NC;
-        gt[e] = n < nn ? (ACC)ScIo<T>::ld(og + (vt + m) * a.Cout + n0 + n) : (ACC)0;
+        gt[e] = n < nn ? (ACC)ScIo<T>::ld(og + (vt + m) * NC + n0 + n) : (ACC)0;
       }
       __syncthreads();
 #pragma unroll
       for (int i = 0; i < WG_KPT; ++i) {
         const int k = threadIdx.x + i * WG_THREADS;
         if (k >= K) break;
-        const int t = k / a.Cin, ci = k - t * a.Cin;
+        const int t = k / KC, ci = k - t * KC;
         for (int m = 0; m < tm; ++m) {
           const long long at = tapidx[m * taps + t];
-          const ACC x = at < 0 ? defv : (ACC)ScIo<T>::ld(img + at * a.Cin + ci);
+          const ACC x = at < 0 ? defv : (ACC)ScIo<T>::ld(img + at * KC + ci);
           const ACC* g = gt + m * WG_NC;
 #pragma unroll
           for (int n = 0; n < WG_NC; ++n) acc[i][n] += x * g[n];
-          if (at < 0 && a.dynamic_default) {
+          if (!TR && at < 0 && a.dynamic_default) {
             // fixed_param_op_gpu.cu.cc:273-277: d(default) collects filter*out_grad over the padded taps
             const T* w = flt + (long long)k * a.Cout + n0;
             for (int n = 0; n < nn; ++n) dacc += (ACC)ScIo<T>::ld(w + n) * g[n];
@@ -161,7 +187,7 @@ __global__ void __launch_bounds__(WG_THREADS) sc_wgrad_partial(const ScArgs a, c
       if (k >= K) break;
 #pragma unroll
       for (int n = 0; n < WG_NC; ++n)
-        if (n < nn) part[(size_t)k * a.Cout + n0 + n] = acc[i][n];
+        if (n < nn) part[(size_t)k * NC + n0 + n] = acc[i][n];
     }
   }
   // block sum of the default-value gradient
@@ -172,7 +198,7 @@ __global__ void __launch_bounds__(WG_THREADS) sc_wgrad_partial(const ScArgs a, c
     if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
     __syncthreads();
   }
-  if (threadIdx.x == 0) part[(size_t)K * a.Cout] = red[0];
+  if (threadIdx.x == 0) part[(size_t)K * NC] = red[0];
 }
 
 // filter_grad[e] = sum over CTAs of partial[cta][e]; element K*Cout is the default-value gradient.
@@ -186,6 +212,87 @@ __global__ void sc_wgrad_reduce(const ACC* part, int nparts, long long n_el, OUT
   else *default_grad = (OUT)s;
 }
 
+// Transposed convolution: partial element [tap][co][ci] -> filter_grad[taps-1-tap][ci][co].
+template <typename ACC, typename OUT>
+__global__ void sc_wgrad_reduce_t(const ACC* part, int nparts, int taps, int Cin, int Cout, OUT* filter_grad) {
+  const long long n_el = (long long)taps * Cin * Cout;
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= n_el) return;
+  ACC s = 0;
+  for (int p = 0; p < nparts; ++p) s += part[(size_t)p * (n_el + 1) + e];
+  const int ci = (int)(e % Cin), co = (int)((e / Cin) % Cout), t = (int)(e / ((long long)Cin * Cout));
+  filter_grad[((long long)(taps - 1 - t) * Cin + ci) * Cout + co] = (OUT)s;
+}
+
+// SparsePad (custom_helper_op/cc/kernels/sparse_pad_kernels_gpu.cu.cc:36-64): the coarse band [B,h,w,d,C]
+// placed into the fine band [B,h*sr,w*sc,d*sd,C] whose first plane per pixel is base_plane; a fine voxel
+// receives a coarse value iff its row, column and absolute depth are multiples of the strides, else zero.
+// One thread per 16-byte piece of a fine voxel's channel vector (E elements).
+template <typename T, int E>
+__global__ void __launch_bounds__(256) sc_pad_fwd(const T* img, const int* bp, T* out, int B, int h, int w, int d, int C,
+                                                   int sr, int sc, int sd) {
+  const int cv = C / E;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int oh = h * sr, ow = w * sc, od = d * sd;
+  if (idx >= (long long)B * oh * ow * od * cv) return;
+  const int q = (int)(idx % cv);
+  long long v = idx / cv;
+  int z = (int)(v % od);
+  const long long pos = v / od;
+  const int x = (int)(pos % ow), y = (int)((pos / ow) % oh), b = (int)(pos / ow / oh);
+  const int p0 = __ldg(bp + pos);
+  z = z + p0 - ((p0 + sd - 1) / sd) * sd;
+  struct alignas(sizeof(T) * E) Vec { T e[E]; };
+  Vec val;
+#pragma unroll
+  for (int i = 0; i < E; ++i) val.e[i] = T(0);
+  if ((y % sr) == 0 && (x % sc) == 0 && (z % sd) == 0)   // z > -sd, so a negative z is never a multiple
+    val = *reinterpret_cast<const Vec*>(img + ((((long long)b * h + y / sr) * w + x / sc) * d + z / sd) * C + q * E);
+  *reinterpret_cast<Vec*>(out + v * C + q * E) = val;
+}
+
+// SparsePadGrad: every coarse voxel reads the fine voxel it was copied to - pixel (y*sr, x*sc), plane
+// z*sd + ceil(bp/sd)*sd - bp.  (The reference kernel, :82-104, forms the fine pixel index from the coarse
+// row and column before scaling them and so reads another pixel when sr or sc exceeds 1.)
+template <typename T, int E>
+__global__ void __launch_bounds__(256) sc_pad_bwd(const T* og, const int* bp, T* igrad, int B, int h, int w, int d, int C,
+                                                   int sr, int sc, int sd) {
+  const int cv = C / E;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)B * h * w * d * cv) return;
+  const int q = (int)(idx % cv);
+  long long v = idx / cv;
+  const int z = (int)(v % d);
+  const long long pc = v / d;
+  const int x = (int)(pc % w), y = (int)((pc / w) % h), b = (int)(pc / w / h);
+  const long long pos = ((long long)b * h * sr + (long long)y * sr) * ((long long)w * sc) + (long long)x * sc;
+  const int p0 = __ldg(bp + pos);
+  const int zf = z * sd + ((p0 + sd - 1) / sd) * sd - p0;
+  struct alignas(sizeof(T) * E) Vec { T e[E]; };
+  *reinterpret_cast<Vec*>(igrad + v * C + q * E) =
+      *reinterpret_cast<const Vec*>(og + (pos * ((long long)d * sd) + zf) * C + q * E);
+}
+
+template <typename T>
+int pad_t(bool grad, const void* src, const int* bp, void* dst, int B, int h, int w, int d, int C, int sr, int sc, int sd,
+          cudaStream_t st) {
+  constexpr int EV = 16 / (int)sizeof(T);
+  const bool vec = (C % EV) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+  const long long nv = grad ? (long long)B * h * w * d : (long long)B * h * sr * w * sc * d * sd;
+  const long long n = nv * (vec ? C / EV : C);
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  const T* s = static_cast<const T*>(src);
+  T* o = static_cast<T*>(dst);
+  if (grad) {
+    if (vec) sc_pad_bwd<T, EV><<<grid, 256, 0, st>>>(s, bp, o, B, h, w, d, C, sr, sc, sd);
+    else sc_pad_bwd<T, 1><<<grid, 256, 0, st>>>(s, bp, o, B, h, w, d, C, sr, sc, sd);
+  } else {
+    if (vec) sc_pad_fwd<T, EV><<<grid, 256, 0, st>>>(s, bp, o, B, h, w, d, C, sr, sc, sd);
+    else sc_pad_fwd<T, 1><<<grid, 256, 0, st>>>(s, bp, o, B, h, w, d, C, sr, sc, sd);
+  }
+  return (int)cudaGetLastError();
+}
+
 template <typename T, typename ACC>
 int fwd_t(const ScArgs& a, cudaStream_t st) {
   const long long n = a.nvox_out * a.Cout;
@@ -193,18 +300,24 @@ int fwd_t(const ScArgs& a, cudaStream_t st) {
   return (int)cudaGetLastError();
 }
 template <typename T, typename ACC>
-int dgrad_t(const ScArgs& a, cudaStream_t st) {
+int dgrad_t(const ScArgs& a, bool padded, cudaStream_t st) {
   const long long n = a.nvox_in * a.Cin;
-  sc_dgrad_simt<T, ACC><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a);
+  if (padded) {
+    const size_t smem = (size_t)a.fh * a.fw * a.fd * a.Cin * sizeof(ACC);
+    sc_dgrad_simt<T, ACC, true><<<(unsigned)((n + 255) / 256), 256, smem, st>>>(a);
+  } else {
+    sc_dgrad_simt<T, ACC, false><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a);
+  }
   return (int)cudaGetLastError();
 }
-template <typename T, typename ACC, typename OUT>
+template <typename T, typename ACC, typename OUT, bool TR>
 int wgrad_t(const ScArgs& a, int nparts, cudaStream_t st) {
   const int taps = a.fh * a.fw * a.fd;
   const long long n_el = (long long)taps * a.Cin * a.Cout;
-  const int vox_per_cta = (int)((a.nvox_out + nparts - 1) / nparts);
+  const long long nvox = TR ? a.nvox_in : a.nvox_out;
+  const int vox_per_cta = (int)((nvox + nparts - 1) / nparts);
   const size_t smem = (size_t)WG_TM * taps * sizeof(long long) + (size_t)(WG_TM * WG_NC + WG_THREADS) * sizeof(ACC);
-  auto k = sc_wgrad_partial<T, ACC>;
+  auto k = sc_wgrad_partial<T, ACC, TR>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -212,9 +325,13 @@ int wgrad_t(const ScArgs& a, int nparts, cudaStream_t st) {
   k<<<nparts, WG_THREADS, smem, st>>>(a, vox_per_cta);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
-  sc_wgrad_reduce<ACC, OUT><<<(unsigned)((n_el + 1 + 255) / 256), 256, 0, st>>>(
-      static_cast<const ACC*>(a.workspace), nparts, n_el, static_cast<OUT*>(a.filter_grad),
-      static_cast<OUT*>(a.default_grad));
+  if (TR)
+    sc_wgrad_reduce_t<ACC, OUT><<<(unsigned)((n_el + 255) / 256), 256, 0, st>>>(
+        static_cast<const ACC*>(a.workspace), nparts, taps, a.Cin, a.Cout, static_cast<OUT*>(a.filter_grad));
+  else
+    sc_wgrad_reduce<ACC, OUT><<<(unsigned)((n_el + 1 + 255) / 256), 256, 0, st>>>(
+        static_cast<const ACC*>(a.workspace), nparts, n_el, static_cast<OUT*>(a.filter_grad),
+        static_cast<OUT*>(a.default_grad));
   return (int)cudaGetLastError();
 }
 
@@ -245,9 +362,9 @@ int sc_static_scratch(void** ptr, size_t* bytes) {
 // Filter gradient with a caller-chosen number of partial slabs (the workspace holds nparts slabs).
 int sc_wgrad_simt_launch_parts(int dtype, const ScArgs& a, int nparts, cudaStream_t st) {
   switch (dtype) {
-    case 0: return wgrad_t<float, float, float>(a, nparts, st);
-    case 1: return wgrad_t<double, double, double>(a, nparts, st);
-    default: return wgrad_t<__nv_bfloat16, float, float>(a, nparts, st);
+    case 0: return wgrad_t<float, float, float, false>(a, nparts, st);
+    case 1: return wgrad_t<double, double, double, false>(a, nparts, st);
+    default: return wgrad_t<__nv_bfloat16, float, float, false>(a, nparts, st);
   }
 }
 
@@ -272,17 +389,42 @@ int sc_fwd_simt_launch(int dtype, const ScArgs& a, cudaStream_t st) {
 }
 int sc_dgrad_simt_launch(int dtype, const ScArgs& a, cudaStream_t st) {
   switch (dtype) {
-    case 0: return dgrad_t<float, float>(a, st);
-    case 1: return dgrad_t<double, double>(a, st);
-    default: return dgrad_t<__nv_bfloat16, float>(a, st);
+    case 0: return dgrad_t<float, float>(a, false, st);
+    case 1: return dgrad_t<double, double>(a, false, st);
+    default: return dgrad_t<__nv_bfloat16, float>(a, false, st);
+  }
+}
+// Transposed convolution forward: a.out_grad = the coarse input, a.images_grad = the fine output.
+int sc_tconv_simt_launch(int dtype, const ScArgs& a, cudaStream_t st) {
+  switch (dtype) {
+    case 0: return dgrad_t<float, float>(a, true, st);
+    case 1: return dgrad_t<double, double>(a, true, st);
+    default: return dgrad_t<__nv_bfloat16, float>(a, true, st);
+  }
+}
+// Filter gradient of the transposed convolution: a.images = the coarse input, a.out_grad = the fine gradient.
+int sc_twgrad_simt_launch(int dtype, const ScArgs& a, int nparts, cudaStream_t st) {
+  switch (dtype) {
+    case 0: return wgrad_t<float, float, float, true>(a, nparts, st);
+    case 1: return wgrad_t<double, double, double, true>(a, nparts, st);
+    default: return wgrad_t<__nv_bfloat16, float, float, true>(a, nparts, st);
   }
 }
 int sc_wgrad_simt_launch(int dtype, const ScArgs& a, cudaStream_t st) {
   const int nparts = sc_wgrad_parts(a.nvox_out);
   switch (dtype) {
-    case 0: return wgrad_t<float, float, float>(a, nparts, st);
-    case 1: return wgrad_t<double, double, double>(a, nparts, st);
-    default: return wgrad_t<__nv_bfloat16, float, float>(a, nparts, st);
+    case 0: return wgrad_t<float, float, float, false>(a, nparts, st);
+    case 1: return wgrad_t<double, double, double, false>(a, nparts, st);
+    default: return wgrad_t<__nv_bfloat16, float, float, false>(a, nparts, st);
+  }
+}
+
+int sc_pad_launch(int dtype, bool grad, const void* src, const int* base_plane, void* dst, int B, int h, int w, int d,
+                  int C, int sr, int sc, int sd, cudaStream_t st) {
+  switch (dtype) {
+    case 0: return pad_t<float>(grad, src, base_plane, dst, B, h, w, d, C, sr, sc, sd, st);
+    case 1: return pad_t<double>(grad, src, base_plane, dst, B, h, w, d, C, sr, sc, sd, st);
+    default: return pad_t<unsigned short>(grad, src, base_plane, dst, B, h, w, d, C, sr, sc, sd, st);
   }
 }
 

@@ -126,9 +126,9 @@ __global__ void __launch_bounds__(128) sc_umma_kernel(const ScArgs a, const long
   // instruction descriptor: D f32, A/B bf16, both K-major, N = COUT, M = 128
   constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(COUT >> 3) << 17) | ((128u >> 4) << 24);
 
-  // padding value of the gathered tensor, replicated over 8 bf16 (zero for the image gradient)
+  // padding value of the gathered tensor, replicated over 8 bf16 (zero for gradients with respect to images)
   uint4 padv = make_uint4(0, 0, 0, 0);
-  if (!DGRAD) {
+  if (!a.pad_zero) {
     const unsigned d16 = __ldg(static_cast<const unsigned short*>(a.default_value));
     const unsigned d32 = d16 | (d16 << 16);
     padv = make_uint4(d32, d32, d32, d32);

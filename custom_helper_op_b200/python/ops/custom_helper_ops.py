@@ -288,3 +288,157 @@ def sparse_conv3d_fast(images, filters, default_value, base_plane, data_format='
     _require(data_format == 'NDHWC', "data_format must be NDHWC")
     default_value = _scalar(default_value, images)
     return _SparseConvFn.apply(images, filters, default_value, base_plane, strides, dilations, dynamic_default)
+
+
+# ---- transposed manifold convolution ------------------------------------------------------------------
+def _sct_desc(images, filters, output_size, strides, dilations):
+    """Descriptor of the forward convolution whose transpose is taken, derived as the reference op derives it
+    (sparse_conv3d_fast_op.cc:78-146): output_size is the fine grid, images the coarse one."""
+    _require(images.is_cuda, "sparse_conv3d_transpose_fast runs on CUDA tensors only (no CPU kernel is registered)")
+    _require(images.dtype in _DT, "dtype must be float32, float64 or bfloat16")
+    _require(images.dim() == 5, "images must have rank 5")
+    _require(filters.dim() == 5, "filter must have rank 5")
+    _require(len(strides) == 3, "strides must be a vector have 3 element")
+    _require(len(dilations) == 3, "dilations must be a vector have 3 element")
+    output_size = [int(x) for x in (output_size.tolist() if torch.is_tensor(output_size) else output_size)]
+    _require(len(output_size) == 3, "output_shape must be an 1-D vector of (height, width, depth)")
+    _require(images.shape[4] == filters.shape[4], "images channel size wrong")
+    d = _lib.ScDesc()
+    d.dtype = _DT[images.dtype]
+    d.dynamic_default = 0
+    d.B = images.shape[0]
+    d.H, d.W, d.D = output_size
+    d.Cin, d.Cout = filters.shape[3], filters.shape[4]
+    for i in range(3):
+        d.filter[i] = int(filters.shape[i])
+        d.strides[i] = int(strides[i])
+        d.dilations[i] = int(dilations[i])
+    coarse = tuple((n + s - 1) // s for n, s in zip(output_size, d.strides))
+    _require(tuple(images.shape[1:4]) == coarse, "images shape and output_shape does not compate")
+    return d, (d.B, d.H, d.W, d.D, d.Cin)
+
+
+def sparse_conv3d_transpose_forward(images, filters, default_value, base_plane, output_size, strides=(1, 1, 1),
+                                    dilations=(1, 1, 1)):
+    """Raw op SparseConv3DTransposeFast: images [B,oH,oW,oD,Cout] -> [B,H,W,D,Cin]."""
+    images = images.contiguous()
+    filters = filters.to(images.dtype).contiguous()
+    default_value = _scalar(default_value, images)
+    base_plane = base_plane.contiguous()
+    d, out_shape = _sct_desc(images, filters, output_size, strides, dilations)
+    _require(base_plane.dtype == torch.int32 and tuple(base_plane.shape) == (d.B, d.H, d.W, 1),
+             "base_plane must have rank 4, and must compate to ref_image")
+    out = torch.empty(out_shape, dtype=images.dtype, device=images.device)
+    st = _lib.lib().chop_sparse_conv3d_transpose_fwd(ctypes.byref(d), _ptr(images), _ptr(filters), _ptr(default_value),
+                                                     _ptr(base_plane), _ptr(out), _stream())
+    _lib.check(st, "chop_sparse_conv3d_transpose_fwd")
+    return out
+
+
+def sparse_conv3d_transpose_backward(images, filters, default_value, base_plane, output_size, out_grad,
+                                     strides=(1, 1, 1), dilations=(1, 1, 1)):
+    """Raw op SparseConv3DTransposeFastGrad: (images_grad, filter_grad), both the derivatives of the forward op."""
+    images = images.contiguous()
+    filters = filters.to(images.dtype).contiguous()
+    default_value = _scalar(default_value, images)
+    base_plane = base_plane.contiguous()
+    out_grad = out_grad.to(images.dtype).contiguous()
+    d, out_shape = _sct_desc(images, filters, output_size, strides, dilations)
+    _require(tuple(out_grad.shape) == out_shape, "out_grad must have rank 5, and must compate to ref_image")
+    wdt = torch.float32 if images.dtype == torch.bfloat16 else images.dtype
+    images_grad = torch.empty_like(images)
+    filter_grad = torch.empty(filters.shape, dtype=wdt, device=images.device)
+    nbytes = _lib.lib().chop_sparse_conv3d_transpose_bwd_workspace_size(ctypes.byref(d))
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=images.device)
+    st = _lib.lib().chop_sparse_conv3d_transpose_bwd(ctypes.byref(d), _ptr(images), _ptr(filters), _ptr(default_value),
+                                                     _ptr(base_plane), _ptr(out_grad), _ptr(images_grad),
+                                                     _ptr(filter_grad), _ptr(ws), ctypes.c_size_t(ws.numel()), _stream())
+    _lib.check(st, "chop_sparse_conv3d_transpose_bwd")
+    return images_grad, filter_grad
+
+
+class _SparseConvTransposeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, images, filters, default_value, base_plane, output_size, strides, dilations):
+        out = sparse_conv3d_transpose_forward(images, filters, default_value, base_plane, output_size, strides, dilations)
+        ctx.save_for_backward(images, filters, default_value, base_plane)
+        ctx.conf = (tuple(int(x) for x in output_size), tuple(strides), tuple(dilations))
+        return out
+
+    @staticmethod
+    def backward(ctx, out_grad):
+        images, filters, default_value, base_plane = ctx.saved_tensors
+        output_size, strides, dilations = ctx.conf
+        ig, fg = sparse_conv3d_transpose_backward(images, filters, default_value, base_plane, output_size, out_grad,
+                                                  strides, dilations)
+        # gradients for images and filters only (reference: custom_helper_ops.py:313)
+        return ig, fg.to(filters.dtype), None, None, None, None, None
+
+
+def sparse_conv3d_transpose_fast(images, filters, default_value, base_plane, output_size, data_format='NDHWC',
+                                 strides=(1, 1, 1), dilations=(1, 1, 1), dynamic_default=False, name=None):
+    """output [B,*output_size,Cin] for filters [fh,fw,fd,Cin,Cout] (reference: custom_helper_ops.py:290-294)."""
+    _require(data_format == 'NDHWC', "data_format must be NDHWC")
+    default_value = _scalar(default_value, images)
+    output_size = [int(x) for x in (output_size.tolist() if torch.is_tensor(output_size) else output_size)]
+    return _SparseConvTransposeFn.apply(images, filters, default_value, base_plane, output_size, strides, dilations)
+
+
+# ---- SparsePad ----------------------------------------------------------------------------------------
+def _pad_args(images, base_plane, strides):
+    _require(images.is_cuda, "sparse_pad runs on CUDA tensors only")
+    _require(images.dtype in _DT, "dtype must be float32, float64 or bfloat16")
+    _require(images.dim() == 5, "images must have rank 5")
+    _require(len(strides) == 3, "strides must be a vector have 3 element")
+    B, h, w, d, C = images.shape
+    st = (ctypes.c_int32 * 3)(*[int(x) for x in strides])
+    fine = (B, h * st[0], w * st[1], d * st[2], C)
+    _require(base_plane.dtype == torch.int32 and tuple(base_plane.shape) == (B, fine[1], fine[2], 1),
+             "base_plane must have rank 4, and must compate to ref_image")
+    return st, fine
+
+
+def sparse_pad_forward(images, base_plane, strides=(1, 1, 1)):
+    """Raw op SparsePad."""
+    images = images.contiguous()
+    base_plane = base_plane.contiguous()
+    st, fine = _pad_args(images, base_plane, strides)
+    out = torch.empty(fine, dtype=images.dtype, device=images.device)
+    B, h, w, d, C = images.shape
+    rc = _lib.lib().chop_sparse_pad_fwd(_DT[images.dtype], B, h, w, d, C, st, _ptr(images), _ptr(base_plane), _ptr(out),
+                                        _stream())
+    _lib.check(rc, "chop_sparse_pad_fwd")
+    return out
+
+
+def sparse_pad_backward(images, base_plane, out_grad, strides=(1, 1, 1)):
+    """Raw op SparsePadGrad (images is used for its shape only, as in the reference)."""
+    base_plane = base_plane.contiguous()
+    st, fine = _pad_args(images, base_plane, strides)
+    out_grad = out_grad.to(images.dtype).contiguous()
+    _require(tuple(out_grad.shape) == fine, "out_grad must compate to the padded shape")
+    images_grad = torch.empty(images.shape, dtype=images.dtype, device=images.device)
+    B, h, w, d, C = images.shape
+    rc = _lib.lib().chop_sparse_pad_bwd(_DT[images.dtype], B, h, w, d, C, st, _ptr(base_plane), _ptr(out_grad),
+                                        _ptr(images_grad), _stream())
+    _lib.check(rc, "chop_sparse_pad_bwd")
+    return images_grad
+
+
+class _SparsePadFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, images, base_plane, strides):
+        ctx.save_for_backward(images, base_plane)
+        ctx.strides = tuple(strides)
+        return sparse_pad_forward(images, base_plane, strides)
+
+    @staticmethod
+    def backward(ctx, out_grad):
+        images, base_plane = ctx.saved_tensors
+        return sparse_pad_backward(images, base_plane, out_grad, ctx.strides), None, None
+
+
+def sparse_pad(images, base_plane, strides=(1, 1, 1), dilations=(1, 1, 1), name=None):
+    """Zero insertion of a coarse band into the fine band (reference: custom_helper_ops.py:220-234)."""
+    _require(len(dilations) == 3, "dilations must be a vector have 3 element")
+    return _SparsePadFn.apply(images, base_plane, strides)

@@ -151,6 +151,44 @@ CHOP_API int chop_sparse_conv3d_bwd_noalloc(const chop_sc_desc *desc, const void
                                             const void *out_grad, void *images_grad, void *filter_grad,
                                             void *default_value_grad, void *stream);
 
+/* ---- transposed manifold convolution -------------------------------------------------------------------
+ * SparseConv3DTransposeFast / SparseConv3DTransposeFastGrad (custom_helper_op/cc/kernels/
+ * sparse_conv3d_fast_op.cc:346-411, 427-505; schema cc/ops/custom_helper_ops.cc:644-715).  desc describes the
+ * forward convolution whose transpose is taken, exactly as the reference derives it from its inputs
+ * (sparse_conv3d_fast_op.cc:78-146): (H,W,D) = the op's output_size, the FINE grid that base_plane
+ * [B,H,W,1] describes; the op's input `images` is the COARSE grid [B,ceil(H/sr),ceil(W/sc),ceil(D/sd),Cout];
+ * filters [fh,fw,fd,Cin,Cout]; output [B,H,W,D,Cin].  Every fine voxel sums, over the taps of the flipped
+ * filter, the coarse voxel lying exactly under the tap, or default_value where there is none.
+ * desc->dynamic_default is ignored (the reference produces no default-value gradient for this op). */
+CHOP_API int chop_sparse_conv3d_transpose_fwd(const chop_sc_desc *desc, const void *images, const void *filters,
+                                              const void *default_value, const int32_t *base_plane, void *output,
+                                              void *stream);
+
+CHOP_API size_t chop_sparse_conv3d_transpose_bwd_workspace_size(const chop_sc_desc *desc);
+
+/* Gradient of the transposed convolution: images_grad [B,oH,oW,oD,Cout], filter_grad [fh,fw,fd,Cin,Cout]
+ * (float32 for bfloat16 data).  Both are the derivatives of the forward entry point.  The reference's grad
+ * op differs from them in two places, neither reachable from its own layer (which fixes default_value to a
+ * non-trainable 0 and Cin/Cout by construction): it adds default_value times the filter at padded taps to
+ * images_grad (sparse_conv3d_fast_op.cc:495-500), and it leaves the two channel axes of filter_grad in the
+ * order [Cout, Cin] (:477-488 only reverses the spatial axes of the swapped problem's result). */
+CHOP_API int chop_sparse_conv3d_transpose_bwd(const chop_sc_desc *desc, const void *images, const void *filters,
+                                              const void *default_value, const int32_t *base_plane,
+                                              const void *out_grad, void *images_grad, void *filter_grad,
+                                              void *workspace, size_t workspace_bytes, void *stream);
+
+/* SparsePad / SparsePadGrad (custom_helper_op/cc/kernels/sparse_pad_kernels.cc:76-130, 150-210; kernels
+ * sparse_pad_kernels_gpu.cu.cc:36-64, 82-104).  images [B,h,w,d,C] (coarse band) -> output
+ * [B,h*sr,w*sc,d*sd,C]; base_plane [B,h*sr,w*sc,1] is the fine band's first plane per pixel.  The gradient
+ * entry reads, for every coarse voxel, the fine voxel the forward wrote it to (the reference's kernel
+ * addresses the fine pixel by the unscaled coarse row/column and is only right for sr = sc = 1). */
+CHOP_API int chop_sparse_pad_fwd(int32_t dtype, int64_t B, int64_t h, int64_t w, int64_t d, int64_t C,
+                                 const int32_t strides[3], const void *images, const int32_t *base_plane,
+                                 void *output, void *stream);
+CHOP_API int chop_sparse_pad_bwd(int32_t dtype, int64_t B, int64_t h, int64_t w, int64_t d, int64_t C,
+                                 const int32_t strides[3], const int32_t *base_plane, const void *out_grad,
+                                 void *images_grad, void *stream);
+
 /* Diagnostic: how many times a tensor-core convolution kernel gave up waiting for its MMAs since the
  * library was loaded (0 in a healthy run; the affected call's output is then incomplete).  Copies one
  * int from the device, so it synchronises with the current device; -1 if that copy fails. */
