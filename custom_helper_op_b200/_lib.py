@@ -8,7 +8,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libchop_b200.so")
 
 F32, F64, BF16 = 0, 1, 2
-KIND_V1, KIND_V2, KIND_AGG = 1, 2, 3
+KIND_V1, KIND_V2, KIND_AGG, KIND_V3 = 1, 2, 3, 4
 REDUCE_MEAN, REDUCE_MIN = 0, 1
 FLAG_STRICT, FLAG_ACCUMULATE = 1, 2
 

@@ -9,6 +9,7 @@
 #include "../../include/chop.h"
 #include "cv_entry.h"
 #include "cv_launch.cuh"
+#include "cv_v3_entry.h"
 
 namespace chop {
 extern std::atomic<int> g_use_umma;
@@ -46,7 +47,7 @@ int typed_of(int dtype, Typed* t) {
 // Shape / attribute checks shared by forward and backward.  Fills the narrowed CvArgs dims.
 int validate(const chop_cv_desc* d, CvArgs* a, Typed* ty) {
   if (!d) return CHOP_ERR_NULL;
-  if (d->kind < CHOP_COST_VOLUME || d->kind > CHOP_COST_AGGREGATE) return CHOP_ERR_ATTR;
+  if (d->kind < CHOP_COST_VOLUME || d->kind > CHOP_COST_VOLUME_V3) return CHOP_ERR_ATTR;
   if (d->reduce != CHOP_REDUCE_MEAN && d->reduce != CHOP_REDUCE_MIN) return CHOP_ERR_ATTR;
   if (int e = typed_of(d->dtype, ty)) return e;
   const int64_t dims[] = {d->B, d->H, d->W, d->C, d->D, d->N, d->Hs, d->Ws};
@@ -59,6 +60,13 @@ int validate(const chop_cv_desc* d, CvArgs* a, Typed* ty) {
   int G = 1;
   if (d->kind == CHOP_COST_VOLUME_V2) {
     if (d->groups < 1 || d->C % d->groups != 0) return CHOP_ERR_ATTR;  // cost_volume_kernels_v2.cc:107-108
+    G = d->groups;
+  }
+  if (d->kind == CHOP_COST_VOLUME_V3) {
+    // cost_volume_kernels_v3.cc:107-111: groups divides C, at most 8 channels per group
+    if (d->groups < 1 || d->C % d->groups != 0) return CHOP_ERR_ATTR;
+    if (d->C / d->groups > 8) return CHOP_ERR_ATTR;
+    if (d->groups > 32) return CHOP_ERR_UNSUPPORTED;  // one lane per group
     G = d->groups;
   }
   // texel and pixel indices are 32-bit inside the kernels; voxel and element offsets are 64-bit
@@ -158,6 +166,16 @@ int chop_cost_volume_fwd(const chop_cv_desc* d, const void* ref, const void* src
   if (!ref || !src || !depth || !Rs || !Ts || !cost || !mask) return CHOP_ERR_NULL;
   if (d->kind != CHOP_COST_VOLUME_V2 && !offsets) return CHOP_ERR_NULL;
   if (a.d_begin == a.d_end) return CHOP_OK;
+  if (d->kind == CHOP_COST_VOLUME_V3) {
+    if (!aligned(ref, ty.feat_size) || !aligned(src, ty.feat_size) || !aligned(depth, ty.real_size) ||
+        !aligned(cost, ty.real_size) || !aligned(mask, 4))
+      return CHOP_ERR_ALIGN;
+    a.lg_log2 = pow2ceil_log2(a.G);
+    plan_chunks(&a, 1 << a.lg_log2, 148 * 64, 16, g_fwd_chunk.load());
+    a.ref = ref; a.src = src; a.depth = depth; a.offsets = offsets; a.Rs = Rs; a.Ts = Ts;
+    a.cost = cost; a.mask = mask;
+    return chop::cv3_fwd_launch(d->dtype, d->reduce == CHOP_REDUCE_MIN, a, static_cast<cudaStream_t>(stream));
+  }
   int cpl, lgl;
   if (int e = plan_lanes(d, a, &cpl, &lgl, (d->flags & CHOP_FLAG_STRICT) != 0)) return e;
   const int mode = d->reduce == CHOP_REDUCE_MIN ? 2 : ((d->flags & CHOP_FLAG_STRICT) ? 1 : 0);
@@ -232,6 +250,26 @@ int chop_cost_volume_bwd(const chop_cv_desc* d, const void* ref, const void* src
   if (!ref || !src || !depth || !Rs || !Ts || !cost_grad || !mask || !ref_grad || !src_grad || !depth_grad)
     return CHOP_ERR_NULL;
   if (d->kind != CHOP_COST_VOLUME_V2 && !offsets) return CHOP_ERR_NULL;
+  if (d->kind == CHOP_COST_VOLUME_V3) {
+    if (!aligned(ref, ty.feat_size) || !aligned(src, ty.feat_size) || !aligned(depth, ty.real_size) ||
+        !aligned(cost_grad, ty.real_size) || !aligned(mask, 4) || !aligned(ref_grad, ty.real_size) ||
+        !aligned(src_grad, ty.real_size) || !aligned(depth_grad, ty.real_size))
+      return CHOP_ERR_ALIGN;
+    cudaStream_t st3 = static_cast<cudaStream_t>(stream);
+    if (!(d->flags & CHOP_FLAG_ACCUMULATE)) {   // zero fill: cost_volume_kernels_gpu_v3.cu.cc:667-672
+      cudaError_t e = cudaMemsetAsync(ref_grad, 0, (size_t)a.npix * a.C * ty.real_size, st3);
+      if (e == cudaSuccess) e = cudaMemsetAsync(src_grad, 0, (size_t)a.B * a.N * a.Hs * a.Ws * a.C * ty.real_size, st3);
+      if (e == cudaSuccess) e = cudaMemsetAsync(depth_grad, 0, (size_t)a.npix * ty.real_size, st3);
+      if (e != cudaSuccess) return (int)e;
+    }
+    if (a.d_begin == a.d_end) return CHOP_OK;
+    a.lg_log2 = pow2ceil_log2(a.G);
+    plan_chunks(&a, 1 << a.lg_log2, 148 * 64, 16, g_bwd_chunk.load());
+    a.ref = ref; a.src = src; a.depth = depth; a.offsets = offsets; a.Rs = Rs; a.Ts = Ts;
+    a.cost_grad = cost_grad; a.mask = const_cast<int32_t*>(mask);
+    a.ref_grad = ref_grad; a.src_grad = src_grad; a.depth_grad = depth_grad;
+    return chop::cv3_bwd_launch(d->dtype, d->reduce == CHOP_REDUCE_MIN, a, st3);
+  }
   int cpl, lgl;
   if (int e = plan_lanes(d, a, &cpl, &lgl, false)) return e;
   a.lg_log2 = lgl;

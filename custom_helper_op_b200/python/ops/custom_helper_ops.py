@@ -83,16 +83,28 @@ def _out_channels(kind, C, groups):
     return C if kind == _lib.KIND_V1 else (groups if kind == _lib.KIND_V2 else 1)
 
 
+def _mask_channels(kind, CO, reduce_method):
+    if reduce_method != "MIN":
+        return 1
+    return 3 if kind == _lib.KIND_V3 else CO   # v3 MIN: (view, reference group, source group)
+
+
+def _check_groups(kind, C, groups):
+    if kind in (_lib.KIND_V2, _lib.KIND_V3):
+        _require(groups is not None and groups >= 1 and C % groups == 0, "channels must be divisible by groups")
+    if kind == _lib.KIND_V3:   # cost_volume_kernels_v3.cc:110-111
+        _require(C // groups <= 8, "image_channels / groups_ less than MAX_SUBCHANNELS_SIZE(8)")
+
+
 def cost_forward(kind, ref_image, src_images, depth, offsets, Rs, Ts, reduce_method="MEAN", groups=None,
                  half_centor=True, strict=False, d_range=None, out=None):
     """Raw forward op (CostVolume / CostVolumeV2 / CostAggregate).  Returns (cost, cost_mask).
     ``d_range=(d0,d1)`` computes only those depth planes (into ``out=(cost, mask)`` if given)."""
     ref_image, src_images, depth, offsets, Rs, Ts, dims, real = _prep(ref_image, src_images, depth, offsets, Rs, Ts, kind)
     B, H, W, C, D, N = dims
-    if kind == _lib.KIND_V2:
-        _require(groups is not None and groups >= 1 and C % groups == 0, "channels must be divisible by groups")
+    _check_groups(kind, C, groups)
     CO = _out_channels(kind, C, groups)
-    MC = CO if reduce_method == "MIN" else 1
+    MC = _mask_channels(kind, CO, reduce_method)
     if out is None:
         alloc = torch.empty if d_range is None else torch.zeros
         cost = alloc((B, H, W, D, CO), dtype=real, device=ref_image.device)
@@ -116,8 +128,9 @@ def cost_backward(kind, ref_image, src_images, depth, offsets, Rs, Ts, cost_grad
     Returns (ref_image_grad, src_images_grad, depth_grad)."""
     ref_image, src_images, depth, offsets, Rs, Ts, dims, real = _prep(ref_image, src_images, depth, offsets, Rs, Ts, kind)
     B, H, W, C, D, N = dims
+    _check_groups(kind, C, groups)
     CO = _out_channels(kind, C, groups)
-    MC = CO if reduce_method == "MIN" else 1
+    MC = _mask_channels(kind, CO, reduce_method)
     cost_grad = cost_grad.to(real).contiguous()
     cost_mask = cost_mask.contiguous()
     _require(cost_grad.numel() == B * H * W * D * CO, "cost_grad must have rank 5, and must compate to ref_image")
@@ -181,6 +194,16 @@ def cost_volume_v2(ref_image, src_images, depth_grid, Rs, Ts, reduce_method="MEA
     dev = ref_image.device
     return _CostFn.apply(_lib.KIND_V2, reduce_method, groups, half_centor, ref_image, src_images,
                          torch.as_tensor(depth_grid, device=dev), None, torch.as_tensor(Rs, device=dev),
+                         torch.as_tensor(Ts, device=dev))
+
+
+def cost_volume_v3(ref_image, src_images, base_plane, offsets, Rs, Ts, reduce_method="MEAN", groups=None,
+                   half_centor=True, name=None):
+    """cost [B,H,W,D,1], cost_mask [B,H,W,D,1|3]: the largest correlation between any group of the sampled
+    source feature and any group of the reference feature (reference: custom_helper_ops.py:98-104)."""
+    dev = ref_image.device
+    return _CostFn.apply(_lib.KIND_V3, reduce_method, groups, half_centor, ref_image, src_images, base_plane,
+                         torch.as_tensor(offsets, device=dev), torch.as_tensor(Rs, device=dev),
                          torch.as_tensor(Ts, device=dev))
 
 

@@ -16,7 +16,9 @@
  *   CostVolume   : base_plane [B,H,W,1], offsets [B,D]   -> cost [B,H,W,D,C], mask [B,H,W,D,1|C]
  *   CostVolumeV2 : depth_grid [B,H,W,D]                  -> cost [B,H,W,D,G], mask [B,H,W,D,1|G]
  *   CostAggregate: base_plane, offsets                   -> cost [B,H,W,D],   mask [B,H,W,D]
- * (mask is int32; its last dimension is 1 for MEAN and C|G for MIN).
+ *   CostVolumeV3 : base_plane, offsets                   -> cost [B,H,W,D,1], mask [B,H,W,D,1|3]
+ * (mask is int32; its last dimension is 1 for MEAN and C|G for MIN; for CostVolumeV3 MIN it holds the
+ * winning (view, reference group, source group)).
  */
 #ifndef CHOP_H_
 #define CHOP_H_
@@ -56,7 +58,11 @@ typedef enum chop_dtype {
 typedef enum chop_kind {
   CHOP_COST_VOLUME = 1,    /* op CostVolume / CostVolumeGrad */
   CHOP_COST_VOLUME_V2 = 2, /* op CostVolumeV2 / CostVolumeGradV2 */
-  CHOP_COST_AGGREGATE = 3  /* op CostAggregate / CostAggregateGrad */
+  CHOP_COST_AGGREGATE = 3, /* op CostAggregate / CostAggregateGrad */
+  CHOP_COST_VOLUME_V3 = 4  /* op CostVolumeV3 / CostVolumeGradV3 (cost_volume_kernels_v3.cc:57-150,
+                              cost_volume_kernels_gpu_v3.cu.cc): largest group-pair correlation; needs
+                              C % groups == 0 and C / groups <= 8.  Depth-range fields are honoured;
+                              CHOP_FLAG_STRICT is implied (the arithmetic is always the unfused one). */
 } chop_kind;
 
 typedef enum chop_reduce { CHOP_REDUCE_MEAN = 0, CHOP_REDUCE_MIN = 1 } chop_reduce;
@@ -78,7 +84,7 @@ typedef struct chop_cv_desc {
   int32_t dtype;       /* chop_dtype */
   int32_t reduce;      /* chop_reduce; attr reduce_method */
   int32_t half_centor; /* attr half_centor (pixel centres at +0.5) */
-  int32_t groups;      /* attr groups (CostVolumeV2 only; must divide C) */
+  int32_t groups;      /* attr groups (CostVolumeV2 / CostVolumeV3; must divide C) */
   uint32_t flags;
   int64_t B, H, W, C;  /* ref image */
   int64_t D;           /* depth hypotheses = extent of every D-indexed tensor passed in */

@@ -277,3 +277,69 @@ def test_views_that_see_nothing():
         assert helpers.bits_equal(got["mask"].reshape(want["mask"].shape), want["mask"])
         assert np.array_equal(got["cost"].reshape(want["cost"].shape), want["cost"])
         assert not got["ref_grad"].any() and not got["src_grad"].any() and not got["depth_grad"].any()
+
+
+# ---- CostVolumeV3 -------------------------------------------------------------------------------------
+@pytest.mark.parametrize("cgs", [(9, 3), (8, 8), (8, 2), (8, 4), (32, 8), (32, 4), (16, 2), (12, 3), (6, 1), (7, 1), (5, 5),
+                                 (24, 3), (64, 8), (40, 5), (32, 32)])
+@pytest.mark.parametrize("reduce", ["MEAN", "MIN"])
+def test_cost_volume_v3(cgs, reduce):
+    """Cost, validity count and the MIN winner (view, reference group, source group) are bit-exact."""
+    C, G = cgs
+    c = helpers.make_case(4, 600 + C, 2, 3, 10, 14, C, 7, "random", np.float32)
+    want = helpers.oracle_fwd_bwd(4, c, reduce, G, True, np.float32)
+    got = run_gpu(4, c, reduce, G, True, want["cost_grad"])
+    check(got, want, np.float32, exact_cost=True)
+
+
+@pytest.mark.parametrize("camera", ["identity", "shift", "rot_z", "rot_y", "random"])
+@pytest.mark.parametrize("shape", [(1, 1, 12, 16, 6, 5, 3), (2, 2, 9, 11, 8, 33, 4), (1, 5, 7, 13, 16, 3, 2)])
+def test_cost_volume_v3_cameras_and_ragged_shapes(camera, shape):
+    B, N, H, W, C, D, G = shape
+    c = helpers.make_case(4, 620 + D, B, N, H, W, C, D, camera, np.float32)
+    for reduce in ("MEAN", "MIN"):
+        want = helpers.oracle_fwd_bwd(4, c, reduce, G, True, np.float32)
+        got = run_gpu(4, c, reduce, G, True, want["cost_grad"])
+        check(got, want, np.float32, exact_cost=True)
+
+
+def test_cost_volume_v3_signed_features_and_float64():
+    """Zero-mean features: with one group about half of the views have no dot product above the start value
+    (the smallest positive normal), which then is that view's cost and carries no gradient."""
+    for dtype in (np.float32, np.float64):
+        c = helpers.make_case(4, 640, 1, 3, 10, 12, 8, 6, "random", dtype)
+        c["ref"] = (c["ref"] - 5).astype(dtype)
+        c["src"] = (c["src"] - 5).astype(dtype)
+        for G in (1, 4):
+            for reduce in ("MEAN", "MIN"):
+                want = helpers.oracle_fwd_bwd(4, c, reduce, G, True, dtype)
+                got = run_gpu(4, c, reduce, G, True, want["cost_grad"])
+                check(got, want, dtype, exact_cost=True)
+
+
+def test_cost_volume_v3_bfloat16_depth_range_and_autograd():
+    c = helpers.make_case(4, 660, 1, 3, 10, 12, 16, 12, "random", np.float32)
+    for k in ("ref", "src"):
+        c[k] = torch.from_numpy(c[k]).to(torch.bfloat16).to(torch.float32).numpy()
+    want = helpers.oracle_fwd_bwd(4, c, "MEAN", 4, True, np.float32)
+    got = run_gpu(4, c, "MEAN", 4, True, want["cost_grad"], bf16=True)
+    check(got, want, np.float32, exact_cost=True)
+    # two depth ranges compose to the full call
+    dev = "cuda:0"
+    t = {k: (None if v is None else torch.from_numpy(v).to(dev)) for k, v in c.items()}
+    cost, mask = ops.cost_forward(4, t["ref"], t["src"], t["depth"], t["offsets"], t["Rs"], t["Ts"], "MEAN", 4,
+                                  d_range=(0, 5))
+    ops.cost_forward(4, t["ref"], t["src"], t["depth"], t["offsets"], t["Rs"], t["Ts"], "MEAN", 4, d_range=(5, 12),
+                     out=(cost, mask))
+    assert helpers.bits_equal(cost.cpu().numpy(), want["cost"]) and helpers.bits_equal(mask.cpu().numpy(), want["mask"])
+    # the public function under autograd
+    ref = t["ref"].clone().requires_grad_()
+    src = t["src"].clone().requires_grad_()
+    base = t["depth"].clone().requires_grad_()
+    cost, mask = ops.cost_volume_v3(ref, src, base, t["offsets"], t["Rs"], t["Ts"], "MEAN", 4)
+    (cost * torch.from_numpy(want["cost_grad"]).to(dev)).sum().backward()
+    assert helpers.rel_err(ref.grad.cpu().numpy(), want["ref_grad"]) <= 1e-4
+    assert helpers.rel_err(src.grad.cpu().numpy(), want["src_grad"]) <= 1e-4
+    assert helpers.rel_err(base.grad.cpu().numpy(), want["depth_grad"]) <= 1e-4
+    with pytest.raises(ValueError):   # more than 8 channels per group
+        ops.cost_volume_v3(ref, src, base, t["offsets"], t["Rs"], t["Ts"], "MEAN", 1)
