@@ -424,6 +424,96 @@ def sparse_conv_main(args):
     print(json.dumps(out), flush=True)
 
 
+def secondary_main(args):
+    """Secondary workloads, one JSON line each (not the headline): device-timed ops that sit either side of the
+    hot path.  c4_updown: the strided manifold convolution (2,2,2) that halves the c4 band, the transposed
+    convolution that brings it back and SparsePad, bf16, forward + gradient each.  c1_v3: CostVolumeV3 (8 groups,
+    MEAN) forward + gradient on the c1 shapes, fp32.  Single GPU, L2 flushed between steps."""
+    import torch
+
+    from custom_helper_op_b200 import synth
+    from custom_helper_op_b200.python.ops import custom_helper_ops as ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    K, Wm = args.steps, max(args.warmup, 3)
+    peak, peak_kind = measured_peak()
+
+    def timed(fns):
+        """Mean milliseconds of every callable in fns, K steps, L2 flushed before each step."""
+        for _ in range(Wm):
+            for f in fns:
+                f()
+        torch.cuda.synchronize()
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(fns) + 1)] for _ in range(K)]
+        for i in range(K):
+            flush.zero_()
+            ev[i][0].record()
+            for j, f in enumerate(fns):
+                f()
+                ev[i][j + 1].record()
+        torch.cuda.synchronize()
+        return [float(np.mean([e[j].elapsed_time(e[j + 1]) for e in ev])) for j in range(len(fns))]
+
+    if args.workload == "c4_updown":
+        w = synth.manifold_conv(20246)
+        bf = torch.bfloat16
+        fine = torch.from_numpy(w["images"]).to(dev).to(bf)
+        flt = torch.from_numpy(w["filters"]).to(dev).to(bf)
+        bp = torch.from_numpy(w["base_plane"]).to(dev)
+        B, H, W_, D, C = fine.shape
+        st = (2, 2, 2)
+        coarse = ops.sparse_conv3d_forward(fine, flt, 0.0, bp, st)
+        og_c, og_f = torch.randn_like(coarse), torch.randn_like(fine)
+        size = (H, W_, D)
+        padded_bp = bp[:, :coarse.shape[1] * 2, :coarse.shape[2] * 2].contiguous()
+        padded = ops.sparse_pad_forward(coarse, padded_bp, st)
+        og_p = torch.randn_like(padded)
+        names = ["down_fwd", "down_bwd", "up_fwd", "up_bwd", "pad_fwd", "pad_bwd"]
+        ms = timed([lambda: ops.sparse_conv3d_forward(fine, flt, 0.0, bp, st),
+                    lambda: ops.sparse_conv3d_backward(fine, flt, 0.0, bp, og_c, st),
+                    lambda: ops.sparse_conv3d_transpose_forward(coarse, flt, 0.0, bp, size, st),
+                    lambda: ops.sparse_conv3d_transpose_backward(coarse, flt, 0.0, bp, size, og_f, st),
+                    lambda: ops.sparse_pad_forward(coarse, padded_bp, st),
+                    lambda: ops.sparse_pad_backward(coarse, padded_bp, og_p, st)])
+        nf, nc, npad = fine.numel() * 2, coarse.numel() * 2, padded.numel() * 2
+        wb, bpb = flt.numel() * 2, bp.numel() * 4
+        alg = [nf + nc + wb + bpb, 2 * (nf + nc) + nf + 3 * wb + 2 * bpb, nc + nf + wb + bpb,
+               2 * (nf + nc) + nc + 3 * wb + 2 * bpb, nc + npad + bpb, npad // 8 + nc + bpb]
+        units, unit = fine.numel() // C, "fine voxels/s"
+        desc = "c4_updown: SparseConv3DFast strides (2,2,2) + SparseConv3DTransposeFast + SparsePad, fine band %dx%dx%d, " \
+               "3x3x3, %d->%d, bf16/fp32-acc" % (H, W_, D, C, C)
+        launches = 10
+    else:
+        wl = synth.make("c1_mvsnet", with_grad=False)
+        t = {k: torch.from_numpy(v).to(dev) for k, v in wl.items()}
+        B, H, W_, C = t["ref"].shape
+        D, N, G = t["offsets"].shape[1], t["src"].shape[1], 8
+        a = (t["ref"], t["src"], t["base_plane"], t["offsets"], t["Rs"], t["Ts"])
+        cost, mask = ops.cost_forward(4, *a, "MEAN", G)
+        cg = torch.randn_like(cost)
+        names = ["v3_fwd", "v3_bwd"]
+        ms = timed([lambda: ops.cost_forward(4, *a, "MEAN", G, out=(cost, mask)),
+                    lambda: ops.cost_backward(4, *a, cg, mask, "MEAN", G)])
+        feats = (1 + N) * B * H * W_ * C * 4
+        vox = B * H * W_ * D
+        alg = [feats + 8 * vox + 4 * B * H * W_, 2 * feats + 8 * vox + 8 * B * H * W_]
+        units, unit = vox * N, UNIT
+        desc = "c1_v3: CostVolumeV3 fwd+bwd fp32, B=%d, V=%d, C=%d, groups=%d, %dx%d, D=%d, MEAN" % (B, N + 1, C, G, H, W_, D)
+        launches = 5
+    total = float(sum(ms))
+    out = {"metric": args.workload + "_fwd_bwd", "value": units / (total * 1e-3), "unit": unit, "n_gpus": 1, "steps": K,
+           "warmup": Wm, "ms_per_step": total, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+           "dtype": "bf16" if args.workload == "c4_updown" else "f32", "data": "synthetic",
+           "config": {"workload": desc, "l2": "flushed between steps (256 MB write)"}, "gpu_launches": launches * K,
+           "roofline": {"bound": "hbm", "peak": peak, "peak_source": peak_kind, "unit": "GB/s", "traffic": None,
+                        "ops": {n: {"ms": m, "algorithmic_bytes": b, "achieved": b / (m * 1e-3) / 1e9,
+                                    "frac": b / (m * 1e-3) / 1e9 / peak} for n, m, b in zip(names, ms, alg)}},
+           "cpu_baseline": None, "e2e": None}
+    print(json.dumps(out), flush=True)
+
+
 def reference_main(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -460,7 +550,12 @@ def main():
     ap.add_argument("--profile", action="store_true",
                     help="device-timed loop only (no clock probe loop, e2e leg or CPU baseline): the command to run under ncu")
     args = ap.parse_args()
-    if args.workload == "c4_sparse_conv":
+    if args.workload in ("c4_updown", "c1_v3"):
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "secondary workload: timed on the GPU only"}))
+        else:
+            secondary_main(args)
+    elif args.workload == "c4_sparse_conv":
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the reference has no CPU kernel for SparseConv3DFast and its "
                                                                   "GPU kernels are warp-cooperative (not compilable for the host)"}))

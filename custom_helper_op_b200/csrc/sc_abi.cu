@@ -183,7 +183,12 @@ int chop_sparse_conv3d_transpose_bwd(const chop_sc_desc* d, const void* images, 
   a.filters = filters; a.default_value = default_value; a.base_plane = base_plane;
   // filter gradient: gathers the coarse input under every tap of every fine voxel
   a.images = images; a.out_grad = out_grad; a.filter_grad = filter_grad; a.workspace = workspace;
-  if (int e = chop::sc_twgrad_simt_launch(d->dtype, a, chop::sc_wgrad_parts(a.nvox_in), st)) return e;
+  const int nparts = chop::sc_wgrad_parts(a.nvox_in);
+  if (chop::g_use_umma.load() && chop::sc_umma_supported(d->dtype, a)) {
+    if (int e = chop::sc_umma_twgrad_launch(a, nparts, st)) return e;
+  } else {
+    if (int e = chop::sc_twgrad_simt_launch(d->dtype, a, nparts, st)) return e;
+  }
   // image gradient: the forward convolution of out_grad (fine, Cin channels) with the same filter, a padded tap
   // contributing nothing
   a.images = out_grad; a.output = images_grad; a.out_grad = nullptr; a.pad_zero = 1;

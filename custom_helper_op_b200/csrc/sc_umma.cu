@@ -80,8 +80,66 @@ __device__ __forceinline__ void tmem_ld<32>(uint32_t taddr, uint32_t* r) {
   tmem_ld<16>(taddr + 16, r + 16);
 }
 
+// ---- tap geometry (3x3x3, dilation 1, any strides) -------------------------------------------------------
+// TG = false, "forward form": the tile's voxels are OUTPUT voxels of the (strided) convolution, grid
+//   [B,oH,oW,oD]; a tap reads the input grid [B,H,W,D] (sc_tap in sc_common.cuh).
+// TG = true, "transposed form": the tile's voxels are voxels of the fine grid [B,H,W,D]; a tap reads the
+//   coarse grid [B,oH,oW,oD] and exists only where row, column and absolute depth are multiples of the
+//   strides (sc_tap_t).  At stride 1 the two forms coincide.
+struct VoxPos {
+  int b, r, c;      // batch, row and column in the fine grid (forward form: of the voxel's centre tap)
+  int depth_abs;    // absolute fine depth plane of the voxel
+};
+
+// S1 = all strides are 1 (known at compile time: no divisions in the gather).
+template <bool TG, bool S1>
+__device__ __forceinline__ VoxPos vox_pos(const ScArgs& a, long long v) {
+  VoxPos p;
+  const int d1 = (TG || S1) ? a.D : a.oD, d2 = (TG || S1) ? a.W : a.oW, d3 = (TG || S1) ? a.H : a.oH;
+  const int dz = (int)(v % d1); v /= d1;
+  const int cc = (int)(v % d2); v /= d2;
+  const int rr = (int)(v % d3);
+  p.b = (int)(v / d3);
+  p.r = (TG || S1) ? rr : rr * a.sr;
+  p.c = (TG || S1) ? cc : cc * a.sc;
+  const int bp = __ldg(a.base_plane + (p.b * a.H + p.r) * a.W + p.c);
+  p.depth_abs = (TG || S1) ? dz + bp : (dz + (bp + a.sd - 1) / a.sd) * a.sd;
+  return p;
+}
+
+// One (fr, fc) column of taps: false if the whole column is padding; otherwise base = index of the source
+// pixel's first voxel and shift = what to subtract from the tap's absolute depth.
+template <bool TG, bool S1>
+__device__ __forceinline__ bool tap_column(const ScArgs& a, const VoxPos& p, int fr, int fc, long long& base, int& shift) {
+  const int orow = p.r - 1 + fr, ocol = p.c - 1 + fc;
+  if (oob(orow, a.H) || oob(ocol, a.W)) return false;
+  const int bp = __ldg(a.base_plane + (p.b * a.H + orow) * a.W + ocol);
+  if (TG && !S1) {
+    if ((orow % a.sr) != 0 || (ocol % a.sc) != 0) return false;
+    base = (((long long)p.b * a.oH + orow / a.sr) * a.oW + ocol / a.sc) * a.oD;
+    shift = (bp + a.sd - 1) / a.sd;
+  } else {
+    base = ((long long)(p.b * a.H + orow) * a.W + ocol) * a.D;
+    shift = bp;
+  }
+  return true;
+}
+
+// Source voxel of tap fz in a column, or -1.
+template <bool TG, bool S1>
+__device__ __forceinline__ long long tap_voxel(const ScArgs& a, const VoxPos& p, long long base, int shift, int fz) {
+  const int od = p.depth_abs - 1 + fz;
+  if (TG && !S1) {
+    if ((od % a.sd) != 0) return -1;
+    const int cd = od / a.sd - shift;
+    return oob(cd, a.oD) ? -1 : base + cd;
+  }
+  const int ind = od - shift;
+  return oob(ind, a.D) ? -1 : base + ind;
+}
+
 // CIN: channels of the gathered tensor (K per tap), COUT: channels produced (N).
-template <int CIN, int COUT, bool DGRAD>
+template <int CIN, int COUT, bool DGRAD, bool S1>
 __global__ void __launch_bounds__(128) sc_umma_kernel(const ScArgs a, const long long nvox, const int ntiles) {
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t mbar_s;
@@ -136,38 +194,25 @@ __global__ void __launch_bounds__(128) sc_umma_kernel(const ScArgs a, const long
 
   uint32_t phase = 0;
   bool alive = true;
-  const int H = a.H, W = a.W, D = a.D;
   for (int tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
     const long long v = (long long)tile * 128 + tid;
     const bool vvalid = v < nvox;
-    int d = 0, c = 0, r = 0, b = 0, depth_abs = 0;
-    if (vvalid) {
-      long long t = v;
-      d = (int)(t % D); t /= D;
-      c = (int)(t % W); t /= W;
-      r = (int)(t % H);
-      b = (int)(t / H);
-      depth_abs = d + __ldg(a.base_plane + (b * H + r) * W + c);
-    }
+    VoxPos pos = {0, 0, 0, 0};
+    if (vvalid) pos = vox_pos<DGRAD, S1>(a, v);
     unsigned char* a_row = sA + (tid / 8) * SBO + (tid % 8) * 16;
 
     for (int fr = 0; fr < 3; ++fr) {
       // ---- gather nine taps (filter row fr) into the staging buffer ---------------------------------------
-      const int orow = r - 1 + fr;
 #pragma unroll
       for (int fc = 0; fc < 3; ++fc) {
-        const int ocol = c - 1 + fc;
-        const bool inb = vvalid && !oob(orow, H) && !oob(ocol, W);
-        int pix = 0, ind0 = 0;
-        if (inb) {
-          pix = (b * H + orow) * W + ocol;
-          ind0 = depth_abs - 1 - __ldg(a.base_plane + pix);  // band-local depth of tap fz = 0
-        }
+        long long base = 0;
+        int shift = 0;
+        const bool inb = vvalid && tap_column<DGRAD, S1>(a, pos, fr, fc, base, shift);
 #pragma unroll
         for (int fz = 0; fz < 3; ++fz) {
-          const int ind = ind0 + fz;
-          const bool ok = inb && !oob(ind, D);
-          const uint4* p = reinterpret_cast<const uint4*>(src + ((size_t)pix * D + (ok ? ind : 0)) * CIN);
+          const long long sv = inb ? tap_voxel<DGRAD, S1>(a, pos, base, shift, fz) : -1;
+          const bool ok = sv >= 0;
+          const uint4* p = reinterpret_cast<const uint4*>(src + (size_t)(ok ? sv : 0) * CIN);
           unsigned char* dstA = a_row + (fc * 3 + fz) * A_TAP_BYTES;
 #pragma unroll
           for (int kc = 0; kc < KC; ++kc) {
@@ -246,8 +291,12 @@ __global__ void __launch_bounds__(128) sc_umma_kernel(const ScArgs a, const long
 // fixed-order reduction kernel as the generic path sums over the CTAs.
 // d(default_value) (dynamic_default only) is accumulated on the CUDA cores while gathering.
 // ---------------------------------------------------------------------------------------------------------
-template <int CIN, int COUT>
-__global__ void __launch_bounds__(128) sc_umma_wgrad_kernel(const ScArgs a, const int ntiles) {
+// TG = true is the filter gradient of the TRANSPOSED convolution: the voxels are those of the fine grid, the
+// gathered tensor (CIN channels) is the op's coarse input under every tap (default_value where there is
+// none) and G (COUT channels) its upstream gradient; the slab is written [tap][coarse ch][fine ch] and the
+// reduction kernel moves it to filter_grad[flipped tap][fine ch][coarse ch].
+template <int CIN, int COUT, bool TG, bool S1>
+__global__ void __launch_bounds__(128) sc_umma_wgrad_kernel(const ScArgs a, const long long nvox, const int ntiles) {
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t mbar_s;
   __shared__ uint32_t tmem_base_s;
@@ -266,7 +315,8 @@ __global__ void __launch_bounds__(128) sc_umma_wgrad_kernel(const ScArgs a, cons
   const __nv_bfloat16* img = static_cast<const __nv_bfloat16*>(a.images);
   const __nv_bfloat16* og = static_cast<const __nv_bfloat16*>(a.out_grad);
 
-  if (a.dynamic_default) {
+  const bool dyn = !TG && a.dynamic_default;
+  if (dyn) {
     const __nv_bfloat16* flt = static_cast<const __nv_bfloat16*>(a.filters);
     for (int e = tid; e < 27 * COUT; e += 128) {
       const int t = e / COUT, n = e % COUT;
@@ -301,32 +351,24 @@ __global__ void __launch_bounds__(128) sc_umma_wgrad_kernel(const ScArgs a, cons
   bool alive = true;
   bool first = true;
   float dacc = 0.f;
-  const int H = a.H, W = a.W, D = a.D;
   unsigned char* a_row = sA + (tid / 8) * LBO_A + (tid % 8) * 16;
   unsigned char* g_row = sG + (tid / 8) * LBO_G + (tid % 8) * 16;
 
   for (int tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
     const long long v = (long long)tile * 128 + tid;
-    const bool vvalid = v < a.nvox_out;
-    int d = 0, c = 0, r = 0, b = 0, depth_abs = 0;
+    const bool vvalid = v < nvox;
+    VoxPos pos = {0, 0, 0, 0};
     float gf[COUT];
 #pragma unroll
     for (int n = 0; n < COUT; ++n) gf[n] = 0.f;
-    if (vvalid) {
-      long long t = v;
-      d = (int)(t % D); t /= D;
-      c = (int)(t % W); t /= W;
-      r = (int)(t % H);
-      b = (int)(t / H);
-      depth_abs = d + __ldg(a.base_plane + (b * H + r) * W + c);
-    }
+    if (vvalid) pos = vox_pos<TG, S1>(a, v);
     // out_grad row of this voxel -> G tile (previous tile's MMAs have completed: every round waits)
 #pragma unroll
     for (int nc = 0; nc < COUT / 8; ++nc) {
       uint4 x = zero4;
       if (vvalid) x = __ldg(reinterpret_cast<const uint4*>(og + (size_t)v * COUT) + nc);
       *reinterpret_cast<uint4*>(g_row + nc * SBO) = x;
-      if (a.dynamic_default) {
+      if (dyn) {
         const unsigned w4[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -346,16 +388,16 @@ __global__ void __launch_bounds__(128) sc_umma_wgrad_kernel(const ScArgs a, cons
         size_t off = 0;
         if (real_tap && vvalid) {
           const int fz = t % 3, fc = (t / 3) % 3, fr = t / 9;
-          const int orow = r - 1 + fr, ocol = c - 1 + fc;
-          if (!oob(orow, H) && !oob(ocol, W)) {
-            const int pix = (b * H + orow) * W + ocol;
-            const int ind = depth_abs - 1 + fz - __ldg(a.base_plane + pix);
-            if (!oob(ind, D)) {
+          long long base = 0;
+          int shift = 0;
+          if (tap_column<TG, S1>(a, pos, fr, fc, base, shift)) {
+            const long long sv = tap_voxel<TG, S1>(a, pos, base, shift, fz);
+            if (sv >= 0) {
               ok = true;
-              off = ((size_t)pix * D + ind) * CIN;
+              off = (size_t)sv * CIN;
             }
           }
-          if (!ok && a.dynamic_default) {
+          if (!ok && dyn) {
             // fixed_param_op_gpu.cu.cc:273-277: d(default) += sum_n (sum_ci filter[t][ci][n]) * out_grad[m][n]
             const float* ws = wsum + t * COUT;
 #pragma unroll
@@ -450,36 +492,61 @@ __global__ void __launch_bounds__(256) sc_umma_wgrad_reduce(const float* part, i
   }
 }
 
-template <int CIN, int COUT>
+// Transposed convolution: slab element [tap][kc][n] (kc: coarse channel of KC, n: fine channel of NC) ->
+// filter_grad[26 - tap][n][kc]; same fixed summation order.
+__global__ void __launch_bounds__(256) sc_umma_wgrad_reduce_t(const float* part, int nparts, int KC, int NC, float* filter_grad) {
+  __shared__ float sm[8][32];
+  const long long n_el = (long long)27 * KC * NC;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long e = (long long)blockIdx.x * 32 + lane;
+  float s = 0.f;
+  if (e < n_el)
+    for (int p = warp; p < nparts; p += 8) s += part[(size_t)p * (n_el + 1) + e];
+  sm[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0 && e < n_el) {
+    float t = sm[0][lane];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) t += sm[w][lane];
+    const int n = (int)(e % NC), kc = (int)((e / NC) % KC), tap = (int)(e / ((long long)NC * KC));
+    filter_grad[((long long)(26 - tap) * NC + n) * KC + kc] = t;
+  }
+}
+
+template <int CIN, int COUT, bool TG>
 int launch_wgrad(const ScArgs& a, int nparts, cudaStream_t st) {
-  auto k = sc_umma_wgrad_kernel<CIN, COUT>;
+  const bool s1 = a.sr == 1 && a.sc == 1 && a.sd == 1;
+  auto k = s1 ? sc_umma_wgrad_kernel<CIN, COUT, TG, true> : sc_umma_wgrad_kernel<CIN, COUT, TG, false>;
   const size_t smem = (size_t)16 * 2048 + (size_t)16 * (COUT / 8) * 128 + (size_t)27 * COUT * 4 + 1024;
-  static bool attr_set = false;
-  if (smem > 48 * 1024 && !attr_set) {
+  if (smem > 48 * 1024) {  // per device and per kernel: set on every call (a cheap host-side call)
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
   }
-  const int ntiles = (int)((a.nvox_out + 127) / 128);
-  k<<<nparts, 128, smem, st>>>(a, ntiles);
+  const long long nvox = TG ? a.nvox_in : a.nvox_out;
+  const int ntiles = (int)((nvox + 127) / 128);
+  if (nparts > ntiles) nparts = ntiles;  // a persistent CTA per slab: more CTAs than tiles would leave slabs unwritten
+  k<<<nparts, 128, smem, st>>>(a, nvox, ntiles);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   const long long n_el = (long long)27 * CIN * COUT;
-  sc_umma_wgrad_reduce<<<(unsigned)((n_el + 1 + 31) / 32), 256, 0, st>>>(static_cast<const float*>(a.workspace), nparts, n_el,
-                                                                           static_cast<float*>(a.filter_grad),
-                                                                           static_cast<float*>(a.default_grad));
+  if (TG)
+    sc_umma_wgrad_reduce_t<<<(unsigned)((n_el + 31) / 32), 256, 0, st>>>(static_cast<const float*>(a.workspace), nparts, CIN,
+                                                                          COUT, static_cast<float*>(a.filter_grad));
+  else
+    sc_umma_wgrad_reduce<<<(unsigned)((n_el + 1 + 31) / 32), 256, 0, st>>>(static_cast<const float*>(a.workspace), nparts, n_el,
+                                                                             static_cast<float*>(a.filter_grad),
+                                                                             static_cast<float*>(a.default_grad));
   return (int)cudaGetLastError();
 }
 
 template <int CIN, int COUT, bool DGRAD>
 int launch(const ScArgs& a, long long nvox, cudaStream_t st) {
-  auto k = sc_umma_kernel<CIN, COUT, DGRAD>;
+  const bool s1 = a.sr == 1 && a.sc == 1 && a.sd == 1;
+  auto k = s1 ? sc_umma_kernel<CIN, COUT, DGRAD, true> : sc_umma_kernel<CIN, COUT, DGRAD, false>;
   const size_t smem = (size_t)27 * COUT * CIN * 2 + (size_t)9 * 128 * CIN * 2 + 1024;
-  static bool attr_set = false;  // per instantiation; setting it again is harmless
-  if (smem > 48 * 1024 && !attr_set) {
+  if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
   }
   const int ntiles = (int)((nvox + 127) / 128);
   int per_sm = (int)((size_t)220 * 1024 / (smem + 2048));
@@ -494,9 +561,8 @@ int launch(const ScArgs& a, long long nvox, cudaStream_t st) {
 }  // namespace
 
 bool sc_umma_supported(int dtype, const ScArgs& a) {
-  return dtype == 2 && a.fh == 3 && a.fw == 3 && a.fd == 3 && a.sr == 1 && a.sc == 1 && a.sd == 1 && a.dr == 1 && a.dc == 1 &&
-         a.dd == 1 && (a.Cin == 16 || a.Cin == 32) && (a.Cout == 16 || a.Cout == 32) &&
-         a.nvox_in < ((long long)1 << 31) - 128;
+  return dtype == 2 && a.fh == 3 && a.fw == 3 && a.fd == 3 && a.dr == 1 && a.dc == 1 && a.dd == 1 &&
+         (a.Cin == 16 || a.Cin == 32) && (a.Cout == 16 || a.Cout == 32) && a.nvox_in < ((long long)1 << 31) - 128;
 }
 
 int sc_umma_fwd_launch(const ScArgs& a, cudaStream_t st) {
@@ -516,10 +582,19 @@ int sc_umma_dgrad_launch(const ScArgs& a, cudaStream_t st) {
 
 // nparts partial slabs of (27*Cin*Cout + 1) floats must fit in the workspace; every CTA writes one.
 int sc_umma_wgrad_launch(const ScArgs& a, int nparts, cudaStream_t st) {
-  if (a.Cin == 16 && a.Cout == 16) return launch_wgrad<16, 16>(a, nparts, st);
-  if (a.Cin == 16 && a.Cout == 32) return launch_wgrad<16, 32>(a, nparts, st);
-  if (a.Cin == 32 && a.Cout == 16) return launch_wgrad<32, 16>(a, nparts, st);
-  return launch_wgrad<32, 32>(a, nparts, st);
+  if (a.Cin == 16 && a.Cout == 16) return launch_wgrad<16, 16, false>(a, nparts, st);
+  if (a.Cin == 16 && a.Cout == 32) return launch_wgrad<16, 32, false>(a, nparts, st);
+  if (a.Cin == 32 && a.Cout == 16) return launch_wgrad<32, 16, false>(a, nparts, st);
+  return launch_wgrad<32, 32, false>(a, nparts, st);
+}
+
+// Filter gradient of the transposed convolution: gathers a.images (coarse, Cout channels) under the taps of
+// every fine voxel, G = a.out_grad (fine, Cin channels).
+int sc_umma_twgrad_launch(const ScArgs& a, int nparts, cudaStream_t st) {
+  if (a.Cin == 16 && a.Cout == 16) return launch_wgrad<16, 16, true>(a, nparts, st);
+  if (a.Cin == 16 && a.Cout == 32) return launch_wgrad<32, 16, true>(a, nparts, st);
+  if (a.Cin == 32 && a.Cout == 16) return launch_wgrad<16, 32, true>(a, nparts, st);
+  return launch_wgrad<32, 32, true>(a, nparts, st);
 }
 
 int sc_umma_timeouts() {

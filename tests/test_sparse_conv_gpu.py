@@ -84,6 +84,36 @@ def test_tensor_core_kernel_matches_generic_kernel(shape):
         assert helpers.rel_err(x, y) <= 2.0 ** -7
 
 
+@pytest.mark.parametrize("strides", [(2, 2, 2), (2, 2, 1), (1, 1, 2), (3, 2, 2)])
+@pytest.mark.parametrize("chans", [(16, 16), (32, 16), (16, 32)])
+def test_bfloat16_strided(strides, chans):
+    """Strided 3x3x3 bf16 convolutions (the down-sampling step of a coarse-to-fine network) run on the tensor
+    cores too; oracle on the bf16-rounded inputs, and the generic kernels on the same inputs."""
+    from custom_helper_op_b200 import _lib
+    Cin, Cout = chans
+    B, H, W, D = 2, 11, 13, 9
+    images, filters, defv, bp, _ = make_case(15, B, H, W, D, Cin, Cout, (3, 3, 3), 2 * D + 8, np.float32)
+    r = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(torch.bfloat16).float().numpy()
+    images, filters = r(images - 0.5), r(filters * 0.3)
+    defv = float(r(np.array([defv]))[0])
+    want = oracle.sparse_conv3d_fwd(images, filters, defv, bp, strides, dtype=np.float32)
+    og = r(np.random.default_rng(16).uniform(-1, 1, want.shape))
+    ig_w, fg_w, dg_w = oracle.sparse_conv3d_bwd(images, filters, defv, bp, og, strides, dynamic_default=True, dtype=np.float32)
+    res = {}
+    for umma in (1, 0):
+        try:
+            _lib.set_tuning("umma", umma)
+            res[umma] = run_gpu(images, filters, defv, bp, og, strides, (1, 1, 1), True, torch.bfloat16)
+        finally:
+            _lib.set_tuning("umma", 1)
+    assert _lib.lib().chop_umma_timeouts() == 0
+    for out, ig, fg, dg in res.values():
+        assert helpers.rel_err(out, want) <= 1e-2
+        assert helpers.rel_err(ig, ig_w) <= 1e-2
+        assert helpers.rel_err(fg, fg_w) <= 2e-3
+        assert abs(float(dg) - float(dg_w)) <= 2e-3 * max(1.0, abs(float(dg_w)))
+
+
 def test_autograd_wrapper():
     images, filters, defv, bp, _ = make_case(11, 1, 6, 7, 5, 4, 3, (3, 3, 3), 12, np.float32)
     want = oracle.sparse_conv3d_fwd(images, filters, defv, bp, dtype=np.float32)

@@ -44,7 +44,7 @@ def test_transpose_forward_and_gradient(case, dtype, default):
 @pytest.mark.parametrize("strides", [(1, 1, 1), (2, 2, 2), (2, 2, 1)])
 @pytest.mark.parametrize("chans", [(16, 16), (32, 16), (16, 32)])
 def test_transpose_bfloat16(strides, chans):
-    """bf16 storage, float32 accumulation; the stride-1 16/32-channel 3x3x3 case runs on the tensor cores."""
+    """bf16 storage, float32 accumulation; 16/32-channel 3x3x3 filters run on the tensor cores."""
     Cin, Cout = chans
     B, H, W, D = 1, 10, 12, 8
     images, filters, defv, bp = make_transpose_case(33, B, H, W, D, Cin, Cout, (3, 3, 3), strides, dtype=np.float32)
@@ -55,14 +55,21 @@ def test_transpose_bfloat16(strides, chans):
     og = r(np.random.default_rng(34).uniform(-1, 1, want.shape))
     ig_w, fg_w = oracle.sparse_conv3d_transpose_bwd(images, filters, defv, bp, (H, W, D), og, strides, (1, 1, 1), False,
                                                     np.float32)
+    from custom_helper_op_b200 import _lib
     bf = torch.bfloat16
-    out = ops.sparse_conv3d_transpose_forward(_t(images, bf), _t(filters, bf), defv, _t(bp), (H, W, D), strides)
-    ig, fg = ops.sparse_conv3d_transpose_backward(_t(images, bf), _t(filters, bf), defv, _t(bp), (H, W, D), _t(og, bf),
-                                                  strides)
-    torch.cuda.synchronize()
-    assert helpers.rel_err(_np(out), want) <= 1e-2
-    assert helpers.rel_err(_np(ig), ig_w) <= 1e-2
-    assert fg.dtype == torch.float32 and helpers.rel_err(_np(fg), fg_w) <= 2e-3
+    for umma in (1, 0):   # tensor-core kernels, then the generic ones
+        try:
+            _lib.set_tuning("umma", umma)
+            out = ops.sparse_conv3d_transpose_forward(_t(images, bf), _t(filters, bf), defv, _t(bp), (H, W, D), strides)
+            ig, fg = ops.sparse_conv3d_transpose_backward(_t(images, bf), _t(filters, bf), defv, _t(bp), (H, W, D),
+                                                          _t(og, bf), strides)
+            torch.cuda.synchronize()
+        finally:
+            _lib.set_tuning("umma", 1)
+        assert helpers.rel_err(_np(out), want) <= 1e-2
+        assert helpers.rel_err(_np(ig), ig_w) <= 1e-2
+        assert fg.dtype == torch.float32 and helpers.rel_err(_np(fg), fg_w) <= 2e-3
+    assert _lib.lib().chop_umma_timeouts() == 0
 
 
 def test_transpose_autograd_and_up_down_round_trip():
