@@ -31,6 +31,9 @@ if ROOT not in sys.path:
 
 import numpy as np  # noqa: E402
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, ncu capture of `bench.py --profile` on this workload
+NCU_DRAM_BYTES = {("c1_mvsnet", "fwd"): 475.9e6, ("c1_mvsnet", "bwd"): 581.3e6}
+
 METRIC = "cost_volume_fwd_bwd_voxel_views_per_s"
 UNIT = "voxel*views/s"
 
@@ -328,10 +331,14 @@ def gpu_main(args):
     if rank == 0:
         fwd_b, bwd_b = algorithmic_bytes(dict(dims, D=(d_hi - d_lo)))
         peak, peak_kind = measured_peak()
-        dom = ("cv_bwd_kernel", bwd_b, bwd_ms) if bwd_ms >= fwd_ms else ("cv_fwd_kernel", fwd_b, fwd_ms)
+        dom = ("cv_bwd_tuned (+ 3 zero-fill memsets)", bwd_b, bwd_ms, "bwd") if bwd_ms >= fwd_ms else \
+              ("cv_fwd_tuned", fwd_b, fwd_ms, "fwd")
         ach = dom[1] / (dom[2] * 1e-3) / 1e9
+        # DRAM bytes per launch of the dominant kernel from the committed ncu capture of this workload
+        # (profiles/cost_volume_c1_mvsnet_ncu.md: dram__bytes_read.sum + dram__bytes_write.sum); null elsewhere
+        traffic = NCU_DRAM_BYTES.get((args.workload, dom[3])) if (args.shard == "batch" and d_lo == 0 and d_hi == D) else None
         roof = {"bound": "hbm", "kernel": dom[0], "achieved": ach, "peak": peak, "peak_source": peak_kind,
-                "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                "unit": "GB/s", "frac": ach / peak, "traffic": traffic,
                 "fwd": {"ms": fwd_ms, "algorithmic_bytes": fwd_b, "gbs": fwd_b / (fwd_ms * 1e-3) / 1e9},
                 "bwd": {"ms": bwd_ms, "algorithmic_bytes": bwd_b, "gbs": bwd_b / (bwd_ms * 1e-3) / 1e9,
                         "note": "includes the three zero-fill memsets of the gradient outputs"},
