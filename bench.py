@@ -32,7 +32,7 @@ if ROOT not in sys.path:
 import numpy as np  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, ncu capture of `bench.py --profile` on this workload
-NCU_DRAM_BYTES = {("c1_mvsnet", "fwd"): 475.9e6, ("c1_mvsnet", "bwd"): 581.3e6}
+NCU_DRAM_BYTES = {("c1_mvsnet", "fwd"): 471.7e6, ("c1_mvsnet", "bwd"): 575.9e6}
 
 METRIC = "cost_volume_fwd_bwd_voxel_views_per_s"
 UNIT = "voxel*views/s"
