@@ -167,7 +167,9 @@ int chop_cost_volume_fwd(const chop_cv_desc* d, const void* ref, const void* src
   if (d->kind != CHOP_COST_VOLUME_V2 && !offsets) return CHOP_ERR_NULL;
   if (a.d_begin == a.d_end) return CHOP_OK;
   if (d->kind == CHOP_COST_VOLUME_V3) {
-    if (!aligned(ref, ty.feat_size) || !aligned(src, ty.feat_size) || !aligned(depth, ty.real_size) ||
+    // groups of 4 or 8 channels are fetched with vector loads
+    const size_t fa = ((a.C / a.G) % 4 == 0 ? 4 : 1) * ty.feat_size;
+    if (!aligned(ref, ty.feat_size) || !aligned(src, fa) || !aligned(depth, ty.real_size) ||
         !aligned(cost, ty.real_size) || !aligned(mask, 4))
       return CHOP_ERR_ALIGN;
     a.lg_log2 = pow2ceil_log2(a.G);
@@ -251,9 +253,10 @@ int chop_cost_volume_bwd(const chop_cv_desc* d, const void* ref, const void* src
     return CHOP_ERR_NULL;
   if (d->kind != CHOP_COST_VOLUME_V2 && !offsets) return CHOP_ERR_NULL;
   if (d->kind == CHOP_COST_VOLUME_V3) {
-    if (!aligned(ref, ty.feat_size) || !aligned(src, ty.feat_size) || !aligned(depth, ty.real_size) ||
+    const size_t fa = ((a.C / a.G) % 4 == 0 ? 4 : 1) * ty.feat_size;
+    if (!aligned(ref, ty.feat_size) || !aligned(src, fa) || !aligned(depth, ty.real_size) ||
         !aligned(cost_grad, ty.real_size) || !aligned(mask, 4) || !aligned(ref_grad, ty.real_size) ||
-        !aligned(src_grad, ty.real_size) || !aligned(depth_grad, ty.real_size))
+        !aligned(src_grad, ((a.C / a.G) % 4 == 0 ? 4 : 1) * ty.real_size) || !aligned(depth_grad, ty.real_size))
       return CHOP_ERR_ALIGN;
     cudaStream_t st3 = static_cast<cudaStream_t>(stream);
     if (!(d->flags & CHOP_FLAG_ACCUMULATE)) {   // zero fill: cost_volume_kernels_gpu_v3.cu.cc:667-672

@@ -35,29 +35,61 @@ __device__ __forceinline__ R ld1(const T* p) {
 
 // Sample group gs at the four corners (unfused, the reference's operand order :114-115) and take the dot
 // product with every reference group (:118-126).  Returns the lane's best value above `start`.
-template <typename T, typename R>
+// SUBT = 4 or 8 (float arithmetic only): channels per group known at compile time - 16-byte loads of the
+// corners and of the reference groups (shared memory), fully unrolled dot products.  SUBT = 0: any sub <= 8.
+template <typename T, typename R, int SUBT>
 __device__ __forceinline__ R lane_best(const T* t00, int C, size_t row, const R* refp, int groups, int sub, int gs,
                                        R dh, R dw, R start, int& best_gi, R* smp) {
   R w00, w01, w11, w10;
   bilinear_weights(dh, dw, w00, w01, w11, w10);
-  const T* p = t00 + gs * sub;
-#pragma unroll
-  for (int k = 0; k < V3_MAX_SUB; ++k) {
-    if (k < sub) {
-      const R a = ld1<T, R>(p + k), b = ld1<T, R>(p + C + k), c = ld1<T, R>(p + row + C + k), d = ld1<T, R>(p + row + k);
-      smp[k] = xadd(xadd(xadd(xmul(w00, a), xmul(w01, b)), xmul(w11, c)), xmul(w10, d));
-    }
-  }
   R cur = start;
   best_gi = -1;
-  for (int gi = 0; gi < groups; ++gi) {
-    R tmp = (R)0;
+  if constexpr (SUBT > 0) {
+    const T* p = t00 + gs * SUBT;
+    R a[SUBT], b[SUBT], c[SUBT], d[SUBT];
 #pragma unroll
-    for (int k = 0; k < V3_MAX_SUB; ++k)
-      if (k < sub) tmp = xadd(tmp, xmul(smp[k], refp[gi * sub + k]));
-    if (cur < tmp) {
-      cur = tmp;
-      best_gi = gi;
+    for (int q = 0; q < SUBT; q += 4) {
+      Vec<T, R, 4>::load(p + q, a + q);
+      Vec<T, R, 4>::load(p + C + q, b + q);
+      Vec<T, R, 4>::load(p + row + C + q, c + q);
+      Vec<T, R, 4>::load(p + row + q, d + q);
+    }
+#pragma unroll
+    for (int k = 0; k < SUBT; ++k)
+      smp[k] = xadd(xadd(xadd(xmul(w00, a[k]), xmul(w01, b[k])), xmul(w11, c[k])), xmul(w10, d[k]));
+    for (int gi = 0; gi < groups; ++gi) {
+      R rv[SUBT];
+#pragma unroll
+      for (int q = 0; q < SUBT; q += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(refp + gi * SUBT + q);
+        rv[q] = t.x; rv[q + 1] = t.y; rv[q + 2] = t.z; rv[q + 3] = t.w;
+      }
+      R tmp = (R)0;
+#pragma unroll
+      for (int k = 0; k < SUBT; ++k) tmp = xadd(tmp, xmul(smp[k], rv[k]));
+      if (cur < tmp) {
+        cur = tmp;
+        best_gi = gi;
+      }
+    }
+  } else {
+    const T* p = t00 + gs * sub;
+#pragma unroll
+    for (int k = 0; k < V3_MAX_SUB; ++k) {
+      if (k < sub) {
+        const R a = ld1<T, R>(p + k), b = ld1<T, R>(p + C + k), c = ld1<T, R>(p + row + C + k), d = ld1<T, R>(p + row + k);
+        smp[k] = xadd(xadd(xadd(xmul(w00, a), xmul(w01, b)), xmul(w11, c)), xmul(w10, d));
+      }
+    }
+    for (int gi = 0; gi < groups; ++gi) {
+      R tmp = (R)0;
+#pragma unroll
+      for (int k = 0; k < V3_MAX_SUB; ++k)
+        if (k < sub) tmp = xadd(tmp, xmul(smp[k], refp[gi * sub + k]));
+      if (cur < tmp) {
+        cur = tmp;
+        best_gi = gi;
+      }
     }
   }
   return cur;
@@ -95,7 +127,7 @@ size_t v3_smem_per_warp(int N, int G, int C, bool bwd) {
   return (s + 15) & ~(size_t)15;
 }
 
-template <typename T, typename R, bool RMIN>
+template <typename T, typename R, bool RMIN, int SUBT>
 __global__ void __launch_bounds__(256) cv3_fwd_kernel(const CvArgs a, const int warps, const size_t smem_per_warp) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int LG = 1 << a.lg_log2;
@@ -163,7 +195,7 @@ __global__ void __launch_bounds__(256) cv3_fwd_kernel(const CvArgs a, const int 
         int gi = -1, gs = li;
         if (valid && lane_on) {
           R smp[V3_MAX_SUB];
-          cur = lane_best<T, R>(src + (size_t)r.texel * C, C, row, refp, groups, sub, li, r.dh, r.dw, start, gi, smp);
+          cur = lane_best<T, R, SUBT>(src + (size_t)r.texel * C, C, row, refp, groups, sub, li, r.dh, r.dw, start, gi, smp);
         }
         group_best<R>(cur, gi, gs, LG);
         if (valid) {
@@ -198,7 +230,7 @@ __global__ void __launch_bounds__(256) cv3_fwd_kernel(const CvArgs a, const int 
   }
 }
 
-template <typename T, typename R, bool RMIN>
+template <typename T, typename R, bool RMIN, int SUBT>
 __global__ void __launch_bounds__(256) cv3_bwd_kernel(const CvArgs a, const int warps, const size_t smem_per_warp) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int LG = 1 << a.lg_log2;
@@ -288,7 +320,7 @@ __global__ void __launch_bounds__(256) cv3_bwd_kernel(const CvArgs a, const int 
         } else {
           // recompute this view's winner exactly as the forward pass did (:470-489)
           R cur = Lim<R>::min_pos();
-          if (valid && lane_on) cur = lane_best<T, R>(t00, C, row, refp, groups, sub, li, r.dh, r.dw, cur, gi, smp);
+          if (valid && lane_on) cur = lane_best<T, R, SUBT>(t00, C, row, refp, groups, sub, li, r.dh, r.dw, cur, gi, smp);
           group_best<R>(cur, gi, gs, LG);
         }
         // the lane that holds the winning source group scatters the gradient of its `sub` channels; a view
@@ -299,20 +331,47 @@ __global__ void __launch_bounds__(256) cv3_bwd_kernel(const CvArgs a, const int 
           R hg = (R)0, wg = (R)0;
           R* g00 = sgrad + (size_t)r.texel * C + gs * sub;
           const T* p = t00 + gs * sub;
-          for (int k = 0; k < sub; ++k) {
-            const R v00 = ld1<T, R>(p + k), v01 = ld1<T, R>(p + C + k), v11 = ld1<T, R>(p + row + C + k),
-                    v10 = ld1<T, R>(p + row + k);
-            const R s = w00 * v00 + w01 * v01 + w11 * v11 + w10 * v10;
-            const int rc = gi * sub + k;
-            rgp[rc] += r.cg * s;                          // :490 (one lane per pixel is here at a time)
-            const R bg = r.cg * refp[rc];                 // :491
-            atomicAdd(g00 + k, bg * w00);                 // :492-495
-            atomicAdd(g00 + C + k, bg * w01);
-            atomicAdd(g00 + row + C + k, bg * w11);
-            atomicAdd(g00 + row + k, bg * w10);
-            const R t1 = v11 - v10 - v01 + v00;           // :498
-            hg += bg * (t1 * r.dw + v10 - v00);
-            wg += bg * (t1 * r.dh + v01 - v00);
+          if constexpr (SUBT > 0) {
+            // whole group at once: 16-byte corner loads, 16-byte vector reductions into src_grad
+            R v00[SUBT], v01[SUBT], v11[SUBT], v10[SUBT], c00[SUBT], c01[SUBT], c11[SUBT], c10[SUBT];
+#pragma unroll
+            for (int q = 0; q < SUBT; q += 4) {
+              Vec<T, R, 4>::load(p + q, v00 + q);
+              Vec<T, R, 4>::load(p + C + q, v01 + q);
+              Vec<T, R, 4>::load(p + row + C + q, v11 + q);
+              Vec<T, R, 4>::load(p + row + q, v10 + q);
+            }
+#pragma unroll
+            for (int k = 0; k < SUBT; ++k) {
+              const R s = w00 * v00[k] + w01 * v01[k] + w11 * v11[k] + w10 * v10[k];
+              const int rc = gi * SUBT + k;
+              rgp[rc] += r.cg * s;                        // :490 (one lane per pixel is here at a time)
+              const R bg = r.cg * refp[rc];               // :491
+              c00[k] = bg * w00; c01[k] = bg * w01; c11[k] = bg * w11; c10[k] = bg * w10;   // :492-495
+              const R t1 = v11[k] - v10[k] - v01[k] + v00[k];   // :498
+              hg += bg * (t1 * r.dw + v10[k] - v00[k]);
+              wg += bg * (t1 * r.dh + v01[k] - v00[k]);
+            }
+            red_add<R, SUBT>(g00, c00);
+            red_add<R, SUBT>(g00 + C, c01);
+            red_add<R, SUBT>(g00 + row + C, c11);
+            red_add<R, SUBT>(g00 + row, c10);
+          } else {
+            for (int k = 0; k < sub; ++k) {
+              const R v00 = ld1<T, R>(p + k), v01 = ld1<T, R>(p + C + k), v11 = ld1<T, R>(p + row + C + k),
+                      v10 = ld1<T, R>(p + row + k);
+              const R s = w00 * v00 + w01 * v01 + w11 * v11 + w10 * v10;
+              const int rc = gi * sub + k;
+              rgp[rc] += r.cg * s;                          // :490 (one lane per pixel is here at a time)
+              const R bg = r.cg * refp[rc];                 // :491
+              atomicAdd(g00 + k, bg * w00);                 // :492-495
+              atomicAdd(g00 + C + k, bg * w01);
+              atomicAdd(g00 + row + C + k, bg * w11);
+              atomicAdd(g00 + row + k, bg * w10);
+              const R t1 = v11 - v10 - v01 + v00;           // :498
+              hg += bg * (t1 * r.dw + v10 - v00);
+              wg += bg * (t1 * r.dh + v01 - v00);
+            }
           }
           dsum += r.gh * hg + r.gw * wg;                  // :502
         }
@@ -330,8 +389,8 @@ __global__ void __launch_bounds__(256) cv3_bwd_kernel(const CvArgs a, const int 
   if (pvalid && li == 0) atomicAdd(static_cast<R*>(a.depth_grad) + pix, dsum);   // :505
 }
 
-template <typename T, typename R, bool BWD, bool RMIN>
-int launch(const CvArgs& a, cudaStream_t st) {
+template <typename T, typename R, bool BWD, bool RMIN, int SUBT>
+int launch_sub(const CvArgs& a, cudaStream_t st) {
   const int LG = 1 << a.lg_log2, G = 32 / LG;
   const size_t spw = v3_smem_per_warp<R>(a.N, G, a.C, BWD);
   int warps = 8;
@@ -341,13 +400,23 @@ int launch(const CvArgs& a, cudaStream_t st) {
   const long long items = (long long)a.npb * a.nchunks;
   const long long blocks = (items + warps - 1) / warps;
   if (blocks > 0x7fffffffLL) return -2;     // CHOP_ERR_SHAPE
-  auto k = BWD ? cv3_bwd_kernel<T, R, RMIN> : cv3_fwd_kernel<T, R, RMIN>;
+  auto k = BWD ? cv3_bwd_kernel<T, R, RMIN, SUBT> : cv3_fwd_kernel<T, R, RMIN, SUBT>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   k<<<(unsigned)blocks, warps * 32, smem, st>>>(a, warps, spw);
   return (int)cudaGetLastError();
+}
+
+template <typename T, typename R, bool BWD, bool RMIN>
+int launch(const CvArgs& a, cudaStream_t st) {
+  if constexpr (sizeof(R) == 4) {
+    const int sub = a.C / a.G;
+    if (sub == 4) return launch_sub<T, R, BWD, RMIN, 4>(a, st);
+    if (sub == 8) return launch_sub<T, R, BWD, RMIN, 8>(a, st);
+  }
+  return launch_sub<T, R, BWD, RMIN, 0>(a, st);
 }
 
 template <bool BWD>
