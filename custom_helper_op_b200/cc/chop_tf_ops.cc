@@ -6,8 +6,9 @@
 //       -I<repo>/include -L<repo>/custom_helper_op_b200 -lchop_b200 -DGOOGLE_CUDA=1
 //
 // Op names, input order, attrs and output shapes are those of the reference project
-// (custom_helper_op/cc/ops/custom_helper_ops.cc:190-307 CostVolume*, :374-411 CostAggregate*, :590-641
-// SparseConv3DFast*), so its Python wrapper and its tf.RegisterGradient functions work unchanged.  The
+// (custom_helper_op/cc/ops/custom_helper_ops.cc:190-307 CostVolume*, :311-371 CostVolumeV3*, :374-411
+// CostAggregate*, :498-535 SparsePad*, :590-641 SparseConv3DFast*, :644-715 SparseConv3DTransposeFast*), so its
+// Python wrapper and its tf.RegisterGradient functions work unchanged.  The
 // dtype list additionally admits bfloat16.  As in the reference only DEVICE_GPU kernels are registered.
 #include <string>
 #include <vector>
@@ -111,6 +112,89 @@ REGISTER_OP("CostAggregateGrad")
     .Attr("dtype: " CHOP_FLOAT_TYPES).Attr("reduce_method: {'MEAN', 'MIN'}").Attr("half_centor: bool = true")
     .SetShapeFn(GradLikeInputs);
 
+REGISTER_OP("CostVolumeV3")
+    .Input("ref_image: dtype").Input("src_images: dtype").Input("base_plane: dtype").Input("offsets: dtype")
+    .Input("rs: dtype").Input("ts: dtype")
+    .Output("cost: dtype").Output("cost_mask: int32")
+    .Attr("dtype: " CHOP_FLOAT_TYPES).Attr("reduce_method: {'MEAN', 'MIN'}").Attr("groups: int")
+    .Attr("half_centor: bool = true")
+    .SetShapeFn([](InferenceContext* c) {
+      // cost [B,H,W,D,1]; mask [B,H,W,D,1] (MEAN) or [B,H,W,D,3] (MIN): custom_helper_ops.cc:311-371 of the reference
+      std::string reduce;
+      TF_RETURN_IF_ERROR(c->GetAttr("reduce_method", &reduce));
+      ShapeHandle ref, offs;
+      TF_RETURN_IF_ERROR(c->WithRank(c->input(0), 4, &ref));
+      TF_RETURN_IF_ERROR(c->WithRank(c->input(3), 2, &offs));
+      c->set_output(0, c->MakeShape({c->Dim(ref, 0), c->Dim(ref, 1), c->Dim(ref, 2), c->Dim(offs, 1), c->MakeDim(1)}));
+      c->set_output(1, c->MakeShape({c->Dim(ref, 0), c->Dim(ref, 1), c->Dim(ref, 2), c->Dim(offs, 1),
+                                     c->MakeDim(reduce == "MIN" ? 3 : 1)}));
+      return Status::OK();
+    });
+
+REGISTER_OP("CostVolumeGradV3")
+    .Input("ref_image: dtype").Input("src_images: dtype").Input("base_plane: dtype").Input("offsets: dtype")
+    .Input("rs: dtype").Input("ts: dtype").Input("cost_grad: dtype").Input("cost_mask: int32")
+    .Output("ref_image_grad: dtype").Output("src_images_grad: dtype").Output("base_plane_grad: dtype")
+    .Attr("dtype: " CHOP_FLOAT_TYPES).Attr("reduce_method: {'MEAN', 'MIN'}").Attr("groups: int")
+    .Attr("half_centor: bool = true")
+    .SetShapeFn(GradLikeInputs);
+
+REGISTER_OP("SparseConv3DTransposeFast")
+    .Input("images: dtype").Input("filters: dtype").Input("default_value: dtype").Input("base_plane: int32")
+    .Input("output_size: int32")
+    .Output("output: dtype")
+    .Attr("dtype: " CHOP_FLOAT_TYPES).Attr("strides: list(int)").Attr("dilations: list(int)")
+    .Attr("dynamic_default: bool").Attr("data_format: { 'NDHWC' }")
+    .SetShapeFn([](InferenceContext* c) {
+      ShapeHandle img, flt, size;
+      TF_RETURN_IF_ERROR(c->WithRank(c->input(0), 5, &img));
+      TF_RETURN_IF_ERROR(c->WithRank(c->input(1), 5, &flt));
+      TF_RETURN_IF_ERROR(c->MakeShapeFromShapeTensor(4, &size));
+      TF_RETURN_IF_ERROR(c->WithRank(size, 3, &size));
+      c->set_output(0, c->MakeShape({c->Dim(img, 0), c->Dim(size, 0), c->Dim(size, 1), c->Dim(size, 2), c->Dim(flt, 3)}));
+      return Status::OK();
+    });
+
+REGISTER_OP("SparseConv3DTransposeFastGrad")
+    .Input("images: dtype").Input("filters: dtype").Input("default_value: dtype").Input("base_plane: int32")
+    .Input("output_size: int32").Input("out_grad: dtype")
+    .Output("images_grad: dtype").Output("filter_grad: dtype")
+    .Attr("dtype: " CHOP_FLOAT_TYPES).Attr("strides: list(int)").Attr("dilations: list(int)")
+    .Attr("dynamic_default: bool").Attr("data_format: { 'NDHWC' }")
+    .SetShapeFn([](InferenceContext* c) {
+      c->set_output(0, c->input(0));
+      c->set_output(1, c->input(1));
+      return Status::OK();
+    });
+
+REGISTER_OP("SparsePad")
+    .Input("images: dtype").Input("base_plane: int32")
+    .Output("output: dtype")
+    .Attr("dtype: " CHOP_FLOAT_TYPES).Attr("strides: list(int)").Attr("dilations: list(int)")
+    .SetShapeFn([](InferenceContext* c) {
+      std::vector<int32> s;
+      TF_RETURN_IF_ERROR(c->GetAttr("strides", &s));
+      ShapeHandle img;
+      TF_RETURN_IF_ERROR(c->WithRank(c->input(0), 5, &img));
+      std::vector<shape_inference::DimensionHandle> out = {c->Dim(img, 0)};
+      for (int i = 0; i < 3; ++i) {
+        const int64 n = c->Value(c->Dim(img, 1 + i));
+        out.push_back(n < 0 ? c->UnknownDim() : c->MakeDim(n * s[i]));
+      }
+      out.push_back(c->Dim(img, 4));
+      c->set_output(0, c->MakeShape(out));
+      return Status::OK();
+    });
+
+REGISTER_OP("SparsePadGrad")
+    .Input("images: dtype").Input("base_plane: int32").Input("out_grad: dtype")
+    .Output("images_grad: dtype")
+    .Attr("dtype: " CHOP_FLOAT_TYPES).Attr("strides: list(int)").Attr("dilations: list(int)")
+    .SetShapeFn([](InferenceContext* c) {
+      c->set_output(0, c->input(0));
+      return Status::OK();
+    });
+
 REGISTER_OP("SparseConv3DFast")
     .Input("images: dtype").Input("filters: dtype").Input("default_value: dtype").Input("base_plane: int32")
     .Output("output: dtype")
@@ -157,7 +241,7 @@ inline void* StreamOf(OpKernelContext* ctx) { return ctx->eigen_device<Eigen::Gp
 
 }  // namespace
 
-// kind: CHOP_COST_VOLUME / _V2 / _AGGREGATE;  gradient: the *Grad op
+// kind: CHOP_COST_VOLUME / _V2 / _AGGREGATE / _V3;  gradient: the *Grad op
 template <typename T, int KIND, bool GRADIENT>
 class CostOp : public OpKernel {
  public:
@@ -168,7 +252,7 @@ class CostOp : public OpKernel {
                 errors::InvalidArgument("Invalid reduce method ", reduce, ". Supported types: MEAN, MIN"));
     min_ = reduce == "MIN";
     OP_REQUIRES_OK(ctx, ctx->GetAttr("half_centor", &half_centor_));
-    if (KIND == CHOP_COST_VOLUME_V2) OP_REQUIRES_OK(ctx, ctx->GetAttr("groups", &groups_));
+    if (KIND == CHOP_COST_VOLUME_V2 || KIND == CHOP_COST_VOLUME_V3) OP_REQUIRES_OK(ctx, ctx->GetAttr("groups", &groups_));
   }
 
   void Compute(OpKernelContext* ctx) override {
@@ -197,6 +281,10 @@ class CostOp : public OpKernel {
       OP_REQUIRES(ctx, offsets.dims() == 2 && offsets.dim_size(0) == B,
                   errors::InvalidArgument("offsets must have rank 2, and must compate to ref_image"));
       D = offsets.dim_size(1);
+      if (KIND == CHOP_COST_VOLUME_V3) {   // cost_volume_kernels_v3.cc:107-111
+        OP_REQUIRES(ctx, groups_ > 0 && C % groups_ == 0, errors::InvalidArgument("image_channels and groups_ must match"));
+        OP_REQUIRES(ctx, C / groups_ <= 8, errors::InvalidArgument("image_channels / groups_ less than MAX_SUBCHANNELS_SIZE(8)"));
+      }
     }
     const Tensor& Rs = ctx->input(cam0);
     const Tensor& Ts = ctx->input(cam0 + 1);
@@ -213,13 +301,14 @@ class CostOp : public OpKernel {
     d.groups = groups_;
     d.B = B; d.H = H; d.W = W; d.C = C; d.D = D; d.N = N; d.Hs = src.dim_size(2); d.Ws = src.dim_size(3);
     const int64 last = KIND == CHOP_COST_VOLUME ? C : (V2 ? groups_ : 1);
+    const int64 mask_last = !min_ ? 1 : (KIND == CHOP_COST_VOLUME_V3 ? 3 : last);
     const void* offsets = V2 ? nullptr : In(ctx, 3);
     int status;
     if (!GRADIENT) {
       TensorShape cs({B, H, W, D}), ms({B, H, W, D});
       if (KIND != CHOP_COST_AGGREGATE) {
         cs.AddDim(last);
-        ms.AddDim(min_ ? last : 1);
+        ms.AddDim(mask_last);
       }
       Tensor *cost = nullptr, *mask = nullptr;
       OP_REQUIRES_OK(ctx, ctx->allocate_output(0, cs, &cost));
@@ -231,7 +320,7 @@ class CostOp : public OpKernel {
       const Tensor& cost_mask = ctx->input(cam0 + 3);
       OP_REQUIRES(ctx, cost_grad.NumElements() == B * H * W * D * last,
                   errors::InvalidArgument("cost_grad must have rank 5, and must compate to ref_image"));
-      OP_REQUIRES(ctx, cost_mask.NumElements() == B * H * W * D * (min_ ? last : 1),
+      OP_REQUIRES(ctx, cost_mask.NumElements() == B * H * W * D * mask_last,
                   errors::InvalidArgument("cost_mask must be the mask returned by the forward op"));
       Tensor *rg = nullptr, *sg = nullptr, *dg = nullptr;
       OP_REQUIRES_OK(ctx, ctx->allocate_output(0, ref.shape(), &rg));
@@ -311,6 +400,112 @@ class ManifoldConvOp : public OpKernel {
   bool dynamic_default_ = false;
 };
 
+// SparseConv3DTransposeFast / ...Grad (reference: sparse_conv3d_fast_op.cc:346-411, 427-505).  The descriptor is that of
+// the forward convolution whose transpose is taken: its input grid is output_size, its output grid the op's images.
+template <typename T, bool GRADIENT>
+class ManifoldConvTransposeOp : public OpKernel {
+ public:
+  explicit ManifoldConvTransposeOp(OpKernelConstruction* ctx) : OpKernel(ctx) {
+    OP_REQUIRES_OK(ctx, ctx->GetAttr("strides", &strides_));
+    OP_REQUIRES_OK(ctx, ctx->GetAttr("dilations", &dilations_));
+    OP_REQUIRES(ctx, strides_.size() == 3, errors::InvalidArgument("strides must be a vector have 3 element"));
+    OP_REQUIRES(ctx, dilations_.size() == 3, errors::InvalidArgument("dilations must be a vector have 3 element"));
+  }
+
+  void Compute(OpKernelContext* ctx) override {
+    const Tensor& images = ctx->input(0);
+    const Tensor& filters = ctx->input(1);
+    const Tensor& defv = ctx->input(2);
+    const Tensor& base_plane = ctx->input(3);
+    const Tensor& size = ctx->input(4);   // host memory
+    OP_REQUIRES(ctx, TensorShapeUtils::IsScalar(defv.shape()), errors::InvalidArgument("default_value must be scalar"));
+    OP_REQUIRES(ctx, images.dims() == 5, errors::InvalidArgument("images must have rank 5"));
+    OP_REQUIRES(ctx, filters.dims() == 5, errors::InvalidArgument("filter must have rank 5"));
+    OP_REQUIRES(ctx, size.dims() == 1 && size.dim_size(0) == 3,
+                errors::InvalidArgument("output_shape must be an 1-D vector of (height, width, depth)"));
+    OP_REQUIRES(ctx, images.dim_size(4) == filters.dim_size(4), errors::InvalidArgument("images channel size wrong"));
+    const auto sv = size.vec<int32>();
+    chop_sc_desc d = {};
+    d.dtype = DtypeOf<T>::value;
+    d.B = images.dim_size(0); d.H = sv(0); d.W = sv(1); d.D = sv(2);
+    d.Cin = filters.dim_size(3); d.Cout = filters.dim_size(4);
+    for (int i = 0; i < 3; ++i) {
+      d.filter[i] = filters.dim_size(i);
+      d.strides[i] = strides_[i];
+      d.dilations[i] = dilations_[i];
+    }
+    OP_REQUIRES(ctx, base_plane.dims() == 4 && base_plane.dim_size(0) == d.B && base_plane.dim_size(1) == d.H &&
+                         base_plane.dim_size(2) == d.W && base_plane.dim_size(3) == 1,
+                errors::InvalidArgument("base_plane must have rank 4, and must compate to ref_image"));
+    OP_REQUIRES(ctx, images.dim_size(1) == (d.H + strides_[0] - 1) / strides_[0] &&
+                         images.dim_size(2) == (d.W + strides_[1] - 1) / strides_[1] &&
+                         images.dim_size(3) == (d.D + strides_[2] - 1) / strides_[2],
+                errors::InvalidArgument("images shape and output_shape does not compate"));
+    const TensorShape fine({d.B, d.H, d.W, d.D, d.Cin});
+    int status;
+    if (!GRADIENT) {
+      Tensor* out = nullptr;
+      OP_REQUIRES_OK(ctx, ctx->allocate_output(0, fine, &out));
+      status = chop_sparse_conv3d_transpose_fwd(&d, In(ctx, 0), In(ctx, 1), In(ctx, 2), static_cast<const int32_t*>(In(ctx, 3)),
+                                                Out(out), StreamOf(ctx));
+    } else {
+      const Tensor& out_grad = ctx->input(5);
+      OP_REQUIRES(ctx, out_grad.shape() == fine, errors::InvalidArgument("out_grad must have rank 5, and must compate to ref_image"));
+      Tensor *ig = nullptr, *fg = nullptr, ws;
+      OP_REQUIRES_OK(ctx, ctx->allocate_output(0, images.shape(), &ig));
+      OP_REQUIRES_OK(ctx, ctx->allocate_output(1, filters.shape(), &fg));
+      const int64 ws_bytes = chop_sparse_conv3d_transpose_bwd_workspace_size(&d);
+      OP_REQUIRES_OK(ctx, ctx->allocate_temp(DT_UINT8, TensorShape({ws_bytes}), &ws));
+      status = chop_sparse_conv3d_transpose_bwd(&d, In(ctx, 0), In(ctx, 1), In(ctx, 2), static_cast<const int32_t*>(In(ctx, 3)),
+                                                In(ctx, 5), Out(ig), Out(fg), Out(&ws), ws_bytes, StreamOf(ctx));
+    }
+    OP_REQUIRES(ctx, status == 0, errors::Internal("libchop_b200: ", chop_status_string(status)));
+  }
+
+ private:
+  std::vector<int32> strides_, dilations_;
+};
+
+// SparsePad / SparsePadGrad (reference: sparse_pad_kernels.cc:76-130, 150-210).
+template <typename T, bool GRADIENT>
+class ManifoldPadOp : public OpKernel {
+ public:
+  explicit ManifoldPadOp(OpKernelConstruction* ctx) : OpKernel(ctx) {
+    OP_REQUIRES_OK(ctx, ctx->GetAttr("strides", &strides_));
+    OP_REQUIRES(ctx, strides_.size() == 3, errors::InvalidArgument("strides must be a vector have 3 element"));
+  }
+
+  void Compute(OpKernelContext* ctx) override {
+    const Tensor& images = ctx->input(0);
+    const Tensor& base_plane = ctx->input(1);
+    OP_REQUIRES(ctx, images.dims() == 5, errors::InvalidArgument("images must have rank 5"));
+    const int64 B = images.dim_size(0), h = images.dim_size(1), w = images.dim_size(2), dd = images.dim_size(3),
+                C = images.dim_size(4);
+    const int32_t s[3] = {strides_[0], strides_[1], strides_[2]};
+    OP_REQUIRES(ctx, base_plane.dims() == 4 && base_plane.dim_size(0) == B && base_plane.dim_size(1) == h * s[0] &&
+                         base_plane.dim_size(2) == w * s[1] && base_plane.dim_size(3) == 1,
+                errors::InvalidArgument("base_plane must have rank 4, and must compate to ref_image"));
+    const TensorShape fine({B, h * s[0], w * s[1], dd * s[2], C});
+    int status;
+    if (!GRADIENT) {
+      Tensor* out = nullptr;
+      OP_REQUIRES_OK(ctx, ctx->allocate_output(0, fine, &out));
+      status = chop_sparse_pad_fwd(DtypeOf<T>::value, B, h, w, dd, C, s, In(ctx, 0), static_cast<const int32_t*>(In(ctx, 1)),
+                                   Out(out), StreamOf(ctx));
+    } else {
+      OP_REQUIRES(ctx, ctx->input(2).shape() == fine, errors::InvalidArgument("out_grad must compate to the padded shape"));
+      Tensor* ig = nullptr;
+      OP_REQUIRES_OK(ctx, ctx->allocate_output(0, images.shape(), &ig));
+      status = chop_sparse_pad_bwd(DtypeOf<T>::value, B, h, w, dd, C, s, static_cast<const int32_t*>(In(ctx, 1)), In(ctx, 2),
+                                   Out(ig), StreamOf(ctx));
+    }
+    OP_REQUIRES(ctx, status == 0, errors::Internal("libchop_b200: ", chop_status_string(status)));
+  }
+
+ private:
+  std::vector<int32> strides_;
+};
+
 #define CHOP_REGISTER(T)                                                                                                   \
   REGISTER_KERNEL_BUILDER(Name("CostVolume").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), CostOp<T, CHOP_COST_VOLUME, false>);      \
   REGISTER_KERNEL_BUILDER(Name("CostVolumeGrad").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), CostOp<T, CHOP_COST_VOLUME, true>);   \
@@ -319,7 +514,15 @@ class ManifoldConvOp : public OpKernel {
   REGISTER_KERNEL_BUILDER(Name("CostAggregate").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), CostOp<T, CHOP_COST_AGGREGATE, false>); \
   REGISTER_KERNEL_BUILDER(Name("CostAggregateGrad").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), CostOp<T, CHOP_COST_AGGREGATE, true>); \
   REGISTER_KERNEL_BUILDER(Name("SparseConv3DFast").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), ManifoldConvOp<T, false>);          \
-  REGISTER_KERNEL_BUILDER(Name("SparseConv3DFastGrad").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), ManifoldConvOp<T, true>);
+  REGISTER_KERNEL_BUILDER(Name("SparseConv3DFastGrad").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), ManifoldConvOp<T, true>);         \
+  REGISTER_KERNEL_BUILDER(Name("CostVolumeV3").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), CostOp<T, CHOP_COST_VOLUME_V3, false>); \
+  REGISTER_KERNEL_BUILDER(Name("CostVolumeGradV3").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), CostOp<T, CHOP_COST_VOLUME_V3, true>); \
+  REGISTER_KERNEL_BUILDER(Name("SparseConv3DTransposeFast").Device(DEVICE_GPU).TypeConstraint<T>("dtype").HostMemory("output_size"), \
+                          ManifoldConvTransposeOp<T, false>);                                                                         \
+  REGISTER_KERNEL_BUILDER(Name("SparseConv3DTransposeFastGrad").Device(DEVICE_GPU).TypeConstraint<T>("dtype").HostMemory("output_size"), \
+                          ManifoldConvTransposeOp<T, true>);                                                                          \
+  REGISTER_KERNEL_BUILDER(Name("SparsePad").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), ManifoldPadOp<T, false>);                  \
+  REGISTER_KERNEL_BUILDER(Name("SparsePadGrad").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), ManifoldPadOp<T, true>);
 
 CHOP_REGISTER(float)
 CHOP_REGISTER(double)
