@@ -435,7 +435,8 @@ def secondary_main(args):
     """Secondary workloads, one JSON line each (not the headline): device-timed ops that sit either side of the
     hot path.  c4_updown: the strided manifold convolution (2,2,2) that halves the c4 band, the transposed
     convolution that brings it back and SparsePad, bf16, forward + gradient each.  c1_v3: CostVolumeV3 (8 groups,
-    MEAN) forward + gradient on the c1 shapes, fp32.  Single GPU, L2 flushed between steps."""
+    MEAN) forward + gradient on the c1 shapes, fp32.  c1_fa: FeatureAggregate forward + gradient on the c1 shapes
+    (the forward allocates its 1 GB output every step, as the op does).  Single GPU, L2 flushed between steps."""
     import torch
 
     from custom_helper_op_b200 import synth
@@ -492,6 +493,22 @@ def secondary_main(args):
         desc = "c4_updown: SparseConv3DFast strides (2,2,2) + SparseConv3DTransposeFast + SparsePad, fine band %dx%dx%d, " \
                "3x3x3, %d->%d, bf16/fp32-acc" % (H, W_, D, C, C)
         launches = 10
+    elif args.workload == "c1_fa":
+        wl = synth.make("c1_mvsnet", with_grad=False)
+        t = {k: torch.from_numpy(v).to(dev) for k, v in wl.items()}
+        B, H, W_, C = t["ref"].shape
+        D, N = t["offsets"].shape[1], t["src"].shape[1]
+        a = (t["src"], t["base_plane"], t["offsets"], t["Rs"], t["Ts"])
+        mapped, mask = ops.feature_aggregate_forward(*a)
+        mg = torch.randn_like(mapped)
+        names = ["fa_fwd", "fa_bwd"]
+        ms = timed([lambda: ops.feature_aggregate_forward(*a), lambda: ops.feature_aggregate_backward(*a, mg, mask)])
+        feats = N * B * H * W_ * C * 4
+        vox = B * H * W_ * D
+        alg = [feats + vox * N * (C * 4 + 4) + 4 * B * H * W_, 2 * feats + vox * N * (C * 4 + 4) + 8 * B * H * W_]
+        units, unit = vox * N, UNIT
+        desc = "c1_fa: FeatureAggregate fwd+bwd fp32, B=%d, N=%d, C=%d, %dx%d, D=%d" % (B, N, C, H, W_, D)
+        launches = 4
     else:
         wl = synth.make("c1_mvsnet", with_grad=False)
         t = {k: torch.from_numpy(v).to(dev) for k, v in wl.items()}
@@ -557,7 +574,7 @@ def main():
     ap.add_argument("--profile", action="store_true",
                     help="device-timed loop only (no clock probe loop, e2e leg or CPU baseline): the command to run under ncu")
     args = ap.parse_args()
-    if args.workload in ("c4_updown", "c1_v3"):
+    if args.workload in ("c4_updown", "c1_v3", "c1_fa"):
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "secondary workload: timed on the GPU only"}))
         else:

@@ -11,6 +11,7 @@ F32, F64, BF16 = 0, 1, 2
 KIND_V1, KIND_V2, KIND_AGG, KIND_V3 = 1, 2, 3, 4
 REDUCE_MEAN, REDUCE_MIN = 0, 1
 FLAG_STRICT, FLAG_ACCUMULATE = 1, 2
+ERR_FORMAT = -8
 
 
 class CvDesc(ctypes.Structure):
@@ -73,6 +74,15 @@ def lib():
         L.chop_sparse_pad_fwd.argtypes = [ctypes.c_int32, i64, i64, i64, i64, i64, i3, vp, vp, vp, vp]
         L.chop_sparse_pad_bwd.restype = ctypes.c_int
         L.chop_sparse_pad_bwd.argtypes = [ctypes.c_int32, i64, i64, i64, i64, i64, i3, vp, vp, vp, vp]
+        L.chop_feature_aggregate_fwd.restype = ctypes.c_int
+        L.chop_feature_aggregate_fwd.argtypes = [ctypes.POINTER(CvDesc)] + [vp] * 8
+        L.chop_feature_aggregate_bwd.restype = ctypes.c_int
+        L.chop_feature_aggregate_bwd.argtypes = [ctypes.POINTER(CvDesc)] + [vp] * 10
+        L.chop_index_initializer.restype = ctypes.c_int
+        L.chop_index_initializer.argtypes = [ctypes.c_int32, ctypes.c_int32, i64, i64, vp, vp]
+        L.chop_decode_pfm.restype = ctypes.c_int
+        L.chop_decode_pfm.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(i64), ctypes.POINTER(i64),
+                                      ctypes.POINTER(i64), vp, ctypes.c_size_t, ctypes.c_char_p, ctypes.c_size_t]
         L.chop_copy_2d_async.restype = ctypes.c_int
         L.chop_copy_2d_async.argtypes = [vp, ctypes.c_size_t, vp, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, vp]
         L.chop_umma_timeouts.restype = ctypes.c_int

@@ -10,6 +10,7 @@
 #include "cv_entry.h"
 #include "cv_launch.cuh"
 #include "cv_v3_entry.h"
+#include "fa_entry.h"
 
 namespace chop {
 extern std::atomic<int> g_use_umma;
@@ -330,6 +331,87 @@ int chop_cost_volume_bwd(const chop_cv_desc* d, const void* ref, const void* src
   return dispatch_bwd(d->dtype, a, p, st);
 }
 
+namespace {
+// Shared checks of the two FeatureAggregate entry points; fills the kernel arguments and the lane split.
+int fa_prepare(const chop_cv_desc* d, CvArgs* a, Typed* ty, int* cpl) {
+  if (!d) return CHOP_ERR_NULL;
+  if (int e = typed_of(d->dtype, ty)) return e;
+  const int64_t dims[] = {d->B, d->H, d->W, d->C, d->D, d->N, d->Hs, d->Ws};
+  for (int64_t v : dims)
+    if (v < 1 || v > INT32_MAX) return CHOP_ERR_SHAPE;
+  if (d->Hs < 2 || d->Ws < 2) return CHOP_ERR_SHAPE;
+  if (d->B * d->N * d->Hs * d->Ws > INT32_MAX || d->B * d->H * d->W > INT32_MAX || d->B * d->D > INT32_MAX)
+    return CHOP_ERR_SHAPE;
+  const int64_t d_end = d->d_end == 0 ? d->D : d->d_end;
+  if (d->d_begin < 0 || d_end > d->D || d->d_begin > d_end) return CHOP_ERR_RANGE;
+  std::memset(a, 0, sizeof(*a));
+  a->B = (int)d->B; a->H = (int)d->H; a->W = (int)d->W; a->C = (int)d->C; a->D = (int)d->D;
+  a->N = (int)d->N; a->Hs = (int)d->Hs; a->Ws = (int)d->Ws; a->G = 1;
+  a->d_begin = (int)d->d_begin; a->d_end = (int)d_end;
+  a->half_centor = d->half_centor ? 1 : 0;
+  a->npix = d->B * d->H * d->W;
+  int c = 1;
+  if (d->dtype == CHOP_F64) { if (a->C % 2 == 0) c = 2; }
+  else if (a->C % 4 == 0) c = 4;
+  const int lanes = (a->C + c - 1) / c;
+  if (lanes > 32) return CHOP_ERR_UNSUPPORTED;
+  *cpl = c;
+  a->lg_log2 = pow2ceil_log2(lanes);
+  return 0;
+}
+}  // namespace
+
+int chop_feature_aggregate_fwd(const chop_cv_desc* d, const void* src, const void* base_plane, const void* offsets,
+                               const void* Rs, const void* Ts, void* mapped_feature, int32_t* mapped_mask, void* stream) {
+  CvArgs a;
+  Typed ty;
+  int cpl;
+  if (int e = fa_prepare(d, &a, &ty, &cpl)) return e;
+  if (!src || !base_plane || !offsets || !Rs || !Ts || !mapped_feature || !mapped_mask) return CHOP_ERR_NULL;
+  if (!aligned(src, cpl * ty.feat_size) || !aligned(base_plane, ty.real_size) || !aligned(mapped_feature, cpl * ty.real_size) ||
+      !aligned(mapped_mask, 4))
+    return CHOP_ERR_ALIGN;
+  if (a.d_begin == a.d_end) return CHOP_OK;
+  plan_chunks(&a, 1 << a.lg_log2, 148 * 128, 16, g_fwd_chunk.load());
+  a.src = src; a.depth = base_plane; a.offsets = offsets; a.Rs = Rs; a.Ts = Ts;
+  a.cost = mapped_feature; a.mask = mapped_mask;
+  return chop::fa_fwd_launch(d->dtype, cpl, a, static_cast<cudaStream_t>(stream));
+}
+
+int chop_feature_aggregate_bwd(const chop_cv_desc* d, const void* src, const void* base_plane, const void* offsets,
+                               const void* Rs, const void* Ts, const void* mapped_feature_grad, const int32_t* mapped_mask,
+                               void* src_grad, void* base_plane_grad, void* stream) {
+  CvArgs a;
+  Typed ty;
+  int cpl;
+  if (int e = fa_prepare(d, &a, &ty, &cpl)) return e;
+  if (!src || !base_plane || !offsets || !Rs || !Ts || !mapped_feature_grad || !mapped_mask || !src_grad || !base_plane_grad)
+    return CHOP_ERR_NULL;
+  if (!aligned(src, cpl * ty.feat_size) || !aligned(base_plane, ty.real_size) ||
+      !aligned(mapped_feature_grad, cpl * ty.real_size) || !aligned(mapped_mask, 4) || !aligned(src_grad, cpl * ty.real_size) ||
+      !aligned(base_plane_grad, ty.real_size))
+    return CHOP_ERR_ALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!(d->flags & CHOP_FLAG_ACCUMULATE)) {
+    cudaError_t e = cudaMemsetAsync(src_grad, 0, (size_t)a.B * a.N * a.Hs * a.Ws * a.C * ty.real_size, st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(base_plane_grad, 0, (size_t)a.npix * ty.real_size, st);
+    if (e != cudaSuccess) return (int)e;
+  }
+  if (a.d_begin == a.d_end) return CHOP_OK;
+  plan_chunks(&a, 1 << a.lg_log2, 148 * 128, 16, g_bwd_chunk.load());
+  a.src = src; a.depth = base_plane; a.offsets = offsets; a.Rs = Rs; a.Ts = Ts;
+  a.cost_grad = mapped_feature_grad; a.mask = const_cast<int32_t*>(mapped_mask);
+  a.src_grad = src_grad; a.depth_grad = base_plane_grad;
+  return chop::fa_bwd_launch(d->dtype, cpl, a, st);
+}
+
+int chop_index_initializer(int32_t dtype, int32_t half_centor, int64_t H, int64_t W, void* out, void* stream) {
+  if (dtype != CHOP_F32 && dtype != CHOP_F64) return CHOP_ERR_ATTR;
+  if (H < 1 || W < 1 || H * W > INT32_MAX / 3) return CHOP_ERR_SHAPE;
+  if (!out) return CHOP_ERR_NULL;
+  return chop::index_init_launch(dtype, half_centor ? 1 : 0, (int)H, (int)W, out, static_cast<cudaStream_t>(stream));
+}
+
 int chop_copy_2d_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t rows,
                        void* stream) {
   if (!dst || !src) return CHOP_ERR_NULL;
@@ -349,6 +431,7 @@ const char* chop_status_string(int status) {
     case CHOP_ERR_ALIGN: return "pointer not aligned for its element type";
     case CHOP_ERR_WORKSPACE: return "workspace missing or too small";
     case CHOP_ERR_RANGE: return "depth range outside [0, D]";
+    case CHOP_ERR_FORMAT: return "malformed or unsupported file contents";
     default: break;
   }
   if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));

@@ -465,3 +465,129 @@ def sparse_pad(images, base_plane, strides=(1, 1, 1), dilations=(1, 1, 1), name=
     """Zero insertion of a coarse band into the fine band (reference: custom_helper_ops.py:220-234)."""
     _require(len(dilations) == 3, "dilations must be a vector have 3 element")
     return _SparsePadFn.apply(images, base_plane, strides)
+
+
+# ---- FeatureAggregate ---------------------------------------------------------------------------------
+def _fa_prep(src_images, base_plane, offsets, Rs, Ts):
+    _require(src_images.is_cuda, "feature_aggregate runs on CUDA tensors only (no CPU kernel is registered)")
+    _require(src_images.dtype in _DT, "dtype must be float32, float64 or bfloat16")
+    _require(src_images.dim() == 5, "src image must have rank 5")
+    real = torch.float32 if src_images.dtype == torch.bfloat16 else src_images.dtype
+    dev = src_images.device
+    src_images = src_images.contiguous()
+    base_plane = base_plane.to(real).contiguous()
+    offsets = torch.as_tensor(offsets, device=dev).to(real).contiguous()
+    Rs = torch.as_tensor(Rs, device=dev).to(real).contiguous()
+    Ts = torch.as_tensor(Ts, device=dev).to(real).contiguous()
+    B, N, Hs, Ws, C = src_images.shape
+    _require(base_plane.dim() == 4 and base_plane.shape[0] == B and base_plane.shape[3] == 1,
+             "base_plane must have rank 4, and must compate to src_images")
+    H, W = base_plane.shape[1], base_plane.shape[2]
+    _require(offsets.dim() == 2 and offsets.shape[0] == B, "offsets must have rank 2, and must compate to src_images")
+    D = offsets.shape[1]
+    _require(tuple(Rs.shape) == (B, N, 3, 3), "Rs must have rank 4, and must compate to src_images")
+    _require(tuple(Ts.shape) == (B, N, 3), "Ts must have rank 3, and must compate to src_images")
+    d = _lib.CvDesc()
+    d.kind, d.dtype, d.reduce, d.groups, d.flags = 0, _DT[src_images.dtype], 0, 1, 0
+    d.B, d.H, d.W, d.C, d.D, d.N, d.Hs, d.Ws = B, H, W, C, D, N, Hs, Ws
+    d.d_begin, d.d_end = 0, 0
+    return src_images, base_plane, offsets, Rs, Ts, d, real
+
+
+def feature_aggregate_forward(src_images, base_plane, offsets, Rs, Ts, half_centor=True):
+    """Raw op FeatureAggregate: (mapped_feature [B,H,W,D,N,C], mapped_mask int32 [B,H,W,D,N,1])."""
+    src_images, base_plane, offsets, Rs, Ts, d, real = _fa_prep(src_images, base_plane, offsets, Rs, Ts)
+    d.half_centor = int(bool(half_centor))
+    shape = (d.B, d.H, d.W, d.D, d.N)
+    mapped = torch.empty(shape + (d.C,), dtype=real, device=src_images.device)
+    mask = torch.empty(shape + (1,), dtype=torch.int32, device=src_images.device)
+    st = _lib.lib().chop_feature_aggregate_fwd(ctypes.byref(d), _ptr(src_images), _ptr(base_plane), _ptr(offsets), _ptr(Rs),
+                                               _ptr(Ts), _ptr(mapped), _ptr(mask), _stream())
+    _lib.check(st, "chop_feature_aggregate_fwd")
+    return mapped, mask
+
+
+def feature_aggregate_backward(src_images, base_plane, offsets, Rs, Ts, mapped_feature_grad, mapped_mask, half_centor=True):
+    """Raw op FeatureAggregateGrad: (src_images_grad, base_plane_grad)."""
+    src_images, base_plane, offsets, Rs, Ts, d, real = _fa_prep(src_images, base_plane, offsets, Rs, Ts)
+    d.half_centor = int(bool(half_centor))
+    n = d.B * d.H * d.W * d.D * d.N
+    mapped_feature_grad = mapped_feature_grad.to(real).contiguous()
+    mapped_mask = mapped_mask.contiguous()
+    _require(mapped_feature_grad.numel() == n * d.C, "mapped_feature_grad must compate to the forward output")
+    _require(mapped_mask.dtype == torch.int32 and mapped_mask.numel() == n,
+             "mapped_mask must be the int32 mask returned by the forward op")
+    src_grad = torch.empty(src_images.shape, dtype=real, device=src_images.device)
+    base_grad = torch.empty_like(base_plane)
+    st = _lib.lib().chop_feature_aggregate_bwd(ctypes.byref(d), _ptr(src_images), _ptr(base_plane), _ptr(offsets), _ptr(Rs),
+                                               _ptr(Ts), _ptr(mapped_feature_grad), _ptr(mapped_mask), _ptr(src_grad),
+                                               _ptr(base_grad), _stream())
+    _lib.check(st, "chop_feature_aggregate_bwd")
+    return src_grad, base_grad
+
+
+class _FeatureAggregateFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, half_centor, src_images, base_plane, offsets, Rs, Ts):
+        mapped, mask = feature_aggregate_forward(src_images, base_plane, offsets, Rs, Ts, half_centor)
+        ctx.save_for_backward(src_images, base_plane, offsets, Rs, Ts, mask)
+        ctx.half_centor = half_centor
+        ctx.mark_non_differentiable(mask)
+        return mapped, mask
+
+    @staticmethod
+    def backward(ctx, grad_out, grad_mask):
+        src_images, base_plane, offsets, Rs, Ts, mask = ctx.saved_tensors
+        sg, bg = feature_aggregate_backward(src_images, base_plane, offsets, Rs, Ts, grad_out, mask, ctx.half_centor)
+        # gradients for src_images and base_plane only (reference: custom_helper_ops.py:192)
+        return None, sg.to(src_images.dtype), bg.to(base_plane.dtype), None, None, None
+
+
+def feature_aggregate(src_images, base_plane, offsets, Rs, Ts, half_centor=True, name=None):
+    """Warped source features of every view at every voxel (reference: custom_helper_ops.py:166-171)."""
+    dev = src_images.device
+    return _FeatureAggregateFn.apply(half_centor, src_images, base_plane, torch.as_tensor(offsets, device=dev),
+                                     torch.as_tensor(Rs, device=dev), torch.as_tensor(Ts, device=dev))
+
+
+# ---- IndexInitializer, DecodePfm ----------------------------------------------------------------------
+def index_initializer(output_shape, half_centor=True, dtype=torch.float32, device="cuda"):
+    """[H,W,3] = (column, row, 1) per pixel, +0.5 on the first two when half_centor (reference:
+    custom_helper_ops.py:329-330; output_shape = (H, W, 3))."""
+    output_shape = [int(x) for x in (output_shape.tolist() if torch.is_tensor(output_shape) else output_shape)]
+    _require(len(output_shape) == 3, "output shape must have 3 elements")
+    _require(output_shape[2] == 3, "last dimsion must be 3")
+    _require(dtype in (torch.float32, torch.float64), "dtype must be float32 or float64")
+    out = torch.empty(output_shape, dtype=dtype, device=device)
+    _require(out.is_cuda, "index_initializer fills a CUDA tensor")
+    with torch.cuda.device(out.device):
+        st = _lib.lib().chop_index_initializer(_DT[dtype], int(bool(half_centor)), output_shape[0], output_shape[1], _ptr(out),
+                                               _stream())
+    _lib.check(st, "chop_index_initializer")
+    return out
+
+
+class IndexInitializer:
+    """Initializer object form of index_initializer (reference: custom_helper_ops.py:332-344)."""
+
+    def __call__(self, output_shape, half_centor=True, dtype=torch.float32, device="cuda"):
+        return index_initializer(output_shape, half_centor, dtype, device)
+
+
+def decode_pfm(contents, name=None):
+    """Decode an in-memory single-channel PFM file to a float32 CPU tensor [height, width, 1] (reference:
+    custom_helper_ops.py:317-326; a host op there too).  Raises ValueError with the reference's message for
+    contents it rejects."""
+    contents = bytes(contents)
+    h, w, c = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()
+    msg = ctypes.create_string_buffer(256)
+    L = _lib.lib()
+    st = L.chop_decode_pfm(contents, len(contents), ctypes.byref(h), ctypes.byref(w), ctypes.byref(c), None, 0, msg, 256)
+    if st == _lib.ERR_FORMAT:
+        raise ValueError(msg.value.decode(errors="replace"))
+    _lib.check(st, "chop_decode_pfm")
+    out = torch.empty((h.value, w.value, c.value), dtype=torch.float32)
+    st = L.chop_decode_pfm(contents, len(contents), ctypes.byref(h), ctypes.byref(w), ctypes.byref(c),
+                           ctypes.c_void_p(out.data_ptr()), out.numel(), msg, 256)
+    _lib.check(st, "chop_decode_pfm")
+    return out

@@ -44,7 +44,8 @@ typedef enum chop_status {
   CHOP_ERR_UNSUPPORTED = -4,  /* valid for the reference but not implemented here */
   CHOP_ERR_ALIGN = -5,        /* a pointer is not aligned for the element type */
   CHOP_ERR_WORKSPACE = -6,    /* workspace missing or too small */
-  CHOP_ERR_RANGE = -7         /* depth range outside [0, D] */
+  CHOP_ERR_RANGE = -7,        /* depth range outside [0, D] */
+  CHOP_ERR_FORMAT = -8        /* chop_decode_pfm: malformed or unsupported file contents */
 } chop_status;
 
 typedef enum chop_dtype {
@@ -194,6 +195,34 @@ CHOP_API int chop_sparse_pad_fwd(int32_t dtype, int64_t B, int64_t h, int64_t w,
 CHOP_API int chop_sparse_pad_bwd(int32_t dtype, int64_t B, int64_t h, int64_t w, int64_t d, int64_t C,
                                  const int32_t strides[3], const int32_t *base_plane, const void *out_grad,
                                  void *images_grad, void *stream);
+
+/* ---- FeatureAggregate / IndexInitializer / DecodePfm -----------------------------------------------------
+ * FeatureAggregate(Grad) (custom_helper_op/cc/kernels/feature_aggregate_kernels.cc:60-130,170-250; kernels
+ * feature_aggregate_kernels_gpu.cu.cc:33-121,219-317): the plane-sweep warp without a reduction.
+ *   src [B,N,Hs,Ws,C], base_plane [B,H,W,1], offsets [B,D], Rs, Ts ->
+ *   mapped_feature [B,H,W,D,N,C] (zeros where a view does not see the voxel), mapped_mask int32 [B,H,W,D,N,1].
+ * desc: kind is ignored; (H,W) is the output grid and may differ from (Hs,Ws); reduce/groups unused; the depth
+ * range fields and CHOP_FLAG_ACCUMULATE (gradient) are honoured.  Gradient outputs: src_grad like src,
+ * base_plane_grad like base_plane, zero-filled first as the reference functor does (:337-383). */
+CHOP_API int chop_feature_aggregate_fwd(const chop_cv_desc *desc, const void *src, const void *base_plane,
+                                        const void *offsets, const void *Rs, const void *Ts, void *mapped_feature,
+                                        int32_t *mapped_mask, void *stream);
+CHOP_API int chop_feature_aggregate_bwd(const chop_cv_desc *desc, const void *src, const void *base_plane,
+                                        const void *offsets, const void *Rs, const void *Ts,
+                                        const void *mapped_feature_grad, const int32_t *mapped_mask, void *src_grad,
+                                        void *base_plane_grad, void *stream);
+
+/* IndexInitializer (index_initializer_kernels.cc:60-100, index_initializer_kernels_gpu.cu.cc:21-29):
+ * out [H,W,3] = (column, row, 1), the first two plus 0.5 when half_centor.  dtype CHOP_F32 or CHOP_F64. */
+CHOP_API int chop_index_initializer(int32_t dtype, int32_t half_centor, int64_t H, int64_t W, void *out, void *stream);
+
+/* DecodePfm (pfm_decoder_kernels.cc:38-116), a HOST function: parses the header of a PFM file held in memory and,
+ * when image != NULL, copies the single-channel little-endian payload into image [height,width,1] (host memory,
+ * image_capacity floats) with the rows flipped.  Call once with image == NULL to learn the shape.  Errors are those
+ * of the reference (magic other than Pf/PF, missing field, big-endian scale, colour format "PF" not implemented,
+ * too little data, a comment line after the magic): CHOP_ERR_FORMAT with the reference's message in msg. */
+CHOP_API int chop_decode_pfm(const void *contents, size_t size, int64_t *height, int64_t *width, int64_t *channels,
+                             float *image, size_t image_capacity, char *msg, size_t msg_capacity);
 
 /* Diagnostic: how many times a tensor-core convolution kernel gave up waiting for its MMAs since the
  * library was loaded (0 in a healthy run; the affected call's output is then incomplete).  Copies one

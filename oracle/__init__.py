@@ -264,3 +264,118 @@ def sparse_pad_bwd(images, base_plane, out_grad, strides, reference_quirk=False,
     else:
         _lib("ref").ref_sparse_pad_bwd(dt, q, _p(images), _p(base_plane), _p(out_grad), _p(igrad))
     return igrad
+
+
+# ---- FeatureAggregate, IndexInitializer, DecodePfm ----------------------------------------------------
+def feature_aggregate_fwd(src, base_plane, offsets, Rs, Ts, half_centor=True, dtype=np.float32, impl="port",
+                          nthreads=None):
+    """FeatureAggregate: src [B,N,Hs,Ws,C], base_plane [B,H,W,1], offsets [B,D] ->
+    (mapped_feature [B,H,W,D,N,C], mapped_mask int32 [B,H,W,D,N,1])."""
+    dtype = np.dtype(dtype)
+    src, base_plane, offsets, Rs, Ts = _prep(dtype, src, base_plane, offsets, Rs, Ts)
+    B, N, Hs, Ws, C = src.shape
+    H, W, D = base_plane.shape[1], base_plane.shape[2], offsets.shape[1]
+    dims = (ctypes.c_int64 * 8)(B, H, W, C, D, N, Hs, Ws)
+    mapped = np.empty((B, H, W, D, N, C), dtype)
+    mask = np.empty((B, H, W, D, N, 1), np.int32)
+    nt = nthreads if nthreads is not None else max_threads()
+    fn = _lib("port").oracle_feature_aggregate_fwd if impl == "port" else _lib("ref").ref_feature_aggregate_fwd
+    fn(ctypes.c_int(0 if dtype == np.float32 else 1), ctypes.c_int(int(half_centor)), dims, _p(src), _p(base_plane),
+       _p(offsets), _p(Rs), _p(Ts), _p(mapped), _p(mask), ctypes.c_int(nt))
+    return mapped, mask
+
+
+def feature_aggregate_bwd(src, base_plane, offsets, Rs, Ts, mapped_grad, mask, half_centor=True, dtype=np.float32,
+                          impl="port", nthreads=1):
+    """FeatureAggregateGrad: returns (src_grad, base_plane_grad)."""
+    dtype = np.dtype(dtype)
+    src, base_plane, offsets, Rs, Ts, mapped_grad = _prep(dtype, src, base_plane, offsets, Rs, Ts, mapped_grad)
+    mask = np.ascontiguousarray(mask, np.int32)
+    B, N, Hs, Ws, C = src.shape
+    H, W, D = base_plane.shape[1], base_plane.shape[2], offsets.shape[1]
+    dims = (ctypes.c_int64 * 8)(B, H, W, C, D, N, Hs, Ws)
+    src_grad = np.empty_like(src)
+    base_grad = np.empty_like(base_plane)
+    fn = _lib("port").oracle_feature_aggregate_bwd if impl == "port" else _lib("ref").ref_feature_aggregate_bwd
+    fn(ctypes.c_int(0 if dtype == np.float32 else 1), ctypes.c_int(int(half_centor)), dims, _p(src), _p(base_plane),
+       _p(offsets), _p(Rs), _p(Ts), _p(mapped_grad), _p(mask), _p(src_grad), _p(base_grad), ctypes.c_int(nthreads))
+    return src_grad, base_grad
+
+
+def index_initializer(H, W, half_centor=True, dtype=np.float32, impl="port"):
+    """IndexInitializer: [H,W,3] = (column, row, 1), +0.5 on the first two when half_centor
+    (index_initializer_kernels_gpu.cu.cc:21-29)."""
+    dtype = np.dtype(dtype)
+    if impl == "ref":
+        out = np.empty((H, W, 3), dtype)
+        _lib("ref").ref_index_initializer(ctypes.c_int(0 if dtype == np.float32 else 1), ctypes.c_int(int(half_centor)),
+                                          ctypes.c_int(H), ctypes.c_int(W), _p(out))
+        return out
+    out = np.ones((H, W, 3), dtype)
+    out[..., 0] = np.arange(W, dtype=dtype)[None, :] + (0.5 if half_centor else 0.0)
+    out[..., 1] = np.arange(H, dtype=dtype)[:, None] + (0.5 if half_centor else 0.0)
+    return out
+
+
+def decode_pfm(contents):
+    """DecodePfm (pfm_decoder_kernels.cc:38-116), statement by statement: a little-endian single-channel "Pf"
+    image -> float32 [H,W,1] with the rows flipped (PFM stores the bottom row first).  Raises ValueError where the
+    reference reports InvalidArgument: a magic other than Pf/PF, a missing field, a positive (big-endian) scale on
+    a little-endian host, the unimplemented colour format "PF", too little data - and a comment line after the
+    magic, which the reference skips up to (not past) its newline and then fails to parse as the width."""
+    ws = b" \t\r\n"
+    n = len(contents)
+
+    def first_of(pos):
+        while pos < n and contents[pos] not in ws:
+            pos += 1
+        return pos if pos < n else -1
+
+    def first_not_of(pos):
+        while pos < n and contents[pos] in ws:
+            pos += 1
+        return pos if pos < n else -1
+
+    def number(tok, conv, what):
+        try:
+            return conv(tok.decode("ascii"))
+        except (ValueError, UnicodeDecodeError):
+            raise ValueError("unable to parse %s: %r" % (what, tok))
+
+    off = first_of(0)
+    if off < 0:
+        raise ValueError("no magic")
+    magic = contents[:off]
+    if magic not in (b"Pf", b"PF"):
+        raise ValueError("invalid format: %r" % magic)
+    off = first_not_of(off)
+    if off < 0:
+        raise ValueError("no width")
+    if contents[off:off + 1] == b"#":
+        while off < n and contents[off:off + 1] != b"\n":
+            off += 1
+    pos = off
+    off = first_of(pos)
+    if off < 0:
+        raise ValueError("no width")
+    width = number(contents[pos:off], int, "width")
+    fields = []
+    for what, conv in (("height", int), ("scaling_factor", float)):
+        off = first_not_of(off)
+        if off < 0:
+            raise ValueError("no " + what)
+        pos = off
+        off = first_of(pos)
+        if off < 0:
+            raise ValueError("no " + what)
+        fields.append(number(contents[pos:off], conv, what))
+    height, scale = fields
+    if scale > 0.0:     # big-endian data on a little-endian host
+        raise ValueError("invalid scaling_factor value: mismatched endian type")
+    off += 1
+    if magic != b"Pf":
+        raise ValueError("no implement")
+    if off + 4 * width * height > n:
+        raise ValueError("not enough data")
+    img = np.frombuffer(contents, dtype="<f4", count=width * height, offset=off).reshape(height, width)
+    return np.ascontiguousarray(img[::-1])[..., None]

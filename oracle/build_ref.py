@@ -47,6 +47,9 @@ EXTRACTS = [
     ("cost_volume_kernels_gpu_v3.cu.cc",
      ["CostMeanVolumeV3Kernel", "CostMinVolumeV3Kernel", "CostMeanVolumeGradV3Kernel", "CostMinVolumeGradV3Kernel"],
      [], "ref_cost_volume_v3.inc"),
+    ("feature_aggregate_kernels_gpu.cu.cc", ["FeatureAggregateKernel", "FeatureAggregateGradKernel"], [],
+     "ref_feature_aggregate.inc"),
+    ("index_initializer_kernels_gpu.cu.cc", ["SetToIndex"], [], "ref_index_initializer.inc"),
     ("sparse_pad.h", [], ["SPARSE_PAD_BASE_ARG_DEF_LIST"], "ref_sparse_pad_macros.inc"),
     ("sparse_pad_kernels_gpu.cu.cc", ["SparsePadKernel", "SparsePadGradKernel"], [], "ref_sparse_pad.inc"),
 ]

@@ -69,3 +69,20 @@ int oracle_cost_bwd(int kind, int dtype, int reduce_min, int half_centor, const 
     cost_bwd_f64(kind, reduce_min, half_centor, dims, groups, ref, src, depth, offsets, Rs, Ts, cost_grad, mask, ref_grad, src_grad, depth_grad, nthreads);
   return 0;
 }
+
+/* dims = {B, H, W, C, D, N, Hs, Ws}: (H, W) the output grid, (Hs, Ws) the source images. */
+int oracle_feature_aggregate_fwd(int dtype, int half_centor, const int64_t *dims, const void *src, const void *base,
+                                 const void *offsets, const void *Rs, const void *Ts, void *mapped, int32_t *mask,
+                                 int nthreads) {
+  if (dtype == 0) fa_fwd_f32(half_centor, dims, src, base, offsets, Rs, Ts, mapped, mask, nthreads);
+  else fa_fwd_f64(half_centor, dims, src, base, offsets, Rs, Ts, mapped, mask, nthreads);
+  return 0;
+}
+
+int oracle_feature_aggregate_bwd(int dtype, int half_centor, const int64_t *dims, const void *src, const void *base,
+                                 const void *offsets, const void *Rs, const void *Ts, const void *mapped_grad,
+                                 const int32_t *mask, void *src_grad, void *base_grad, int nthreads) {
+  if (dtype == 0) fa_bwd_f32(half_centor, dims, src, base, offsets, Rs, Ts, mapped_grad, mask, src_grad, base_grad, nthreads);
+  else fa_bwd_f64(half_centor, dims, src, base, offsets, Rs, Ts, mapped_grad, mask, src_grad, base_grad, nthreads);
+  return 0;
+}

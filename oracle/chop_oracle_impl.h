@@ -362,3 +362,92 @@ static void FN(cost3_bwd)(int reduce_min, int half_centor, const int64_t *dims, 
     }
   }
 }
+
+/* ---- FeatureAggregate (feature_aggregate_kernels_gpu.cu.cc:33-121, gradient :219-317) -----------------
+ * The plane-sweep warp without a reduction: mapped [B,H,W,D,N,C] holds the bilinear sample of every source
+ * view at every voxel (zeros where the view does not see it), mask [B,H,W,D,N,1] is 1/0.  (H,W) is the
+ * output grid (that of base_plane) and may differ from the source size (Hs,Ws). */
+static void FN(fa_fwd)(int half_centor, const int64_t *dims, const REAL *src, const REAL *base,
+                       const REAL *offsets, const REAL *Rs, const REAL *Ts, REAL *mapped, int32_t *mask,
+                       int nthreads) {
+  const int64_t B = dims[0], H = dims[1], W = dims[2], C = dims[3], D = dims[4], N = dims[5],
+                Hs = dims[6], Ws = dims[7];
+  const int64_t npix = B * H * W;
+#pragma omp parallel for schedule(dynamic, 16) num_threads(nthreads > 0 ? nthreads : 1)
+  for (int64_t pix = 0; pix < npix; ++pix) {
+    const int64_t b = pix / (H * W), h = (pix / W) % H, w = pix % W;
+    REAL x = (REAL)w, y = (REAL)h;
+    if (half_centor) { x = x + (REAL)0.5; y = y + (REAL)0.5; }
+    for (int64_t d = 0; d < D; ++d) {
+      const int64_t vox = pix * D + d;
+      const REAL depth = base[pix] + offsets[b * D + d];
+      for (int64_t n = 0; n < N; ++n) {
+        REAL *out = mapped + (vox * N + n) * C;
+        FN(proj) p;
+        FN(project)(x, y, depth, Rs + (b * N + n) * 9, Ts + (b * N + n) * 3, half_centor, Hs, Ws, &p);
+        mask[vox * N + n] = p.valid;
+        if (!p.valid) {
+          for (int64_t c = 0; c < C; ++c) out[c] = (REAL)0;   /* :113-117 */
+          continue;
+        }
+        REAL wt[4];
+        FN(weights)(p.dh, p.dw, wt);
+        const REAL *t00 = src + C * (p.fw + Ws * (p.fh + Hs * (n + N * b)));
+        const REAL *t01 = t00 + C, *t10 = t00 + Ws * C, *t11 = t10 + C;
+        for (int64_t c = 0; c < C; ++c)
+          out[c] = wt[0] * t00[c] + wt[1] * t01[c] + wt[2] * t11[c] + wt[3] * t10[c];   /* :104-105 */
+      }
+    }
+  }
+}
+
+static void FN(fa_bwd)(int half_centor, const int64_t *dims, const REAL *src, const REAL *base,
+                       const REAL *offsets, const REAL *Rs, const REAL *Ts, const REAL *mapped_grad,
+                       const int32_t *mask, REAL *src_grad, REAL *base_grad, int nthreads) {
+  const int64_t B = dims[0], H = dims[1], W = dims[2], C = dims[3], D = dims[4], N = dims[5],
+                Hs = dims[6], Ws = dims[7];
+  const int64_t npix = B * H * W;
+  memset(src_grad, 0, sizeof(REAL) * (size_t)(B * N * Hs * Ws * C));
+  memset(base_grad, 0, sizeof(REAL) * (size_t)npix);
+  const int par = nthreads > 1;
+#pragma omp parallel for schedule(dynamic, 16) num_threads(par ? nthreads : 1) if (par)
+  for (int64_t pix = 0; pix < npix; ++pix) {
+    const int64_t b = pix / (H * W), h = (pix / W) % H, w = pix % W;
+    REAL x = (REAL)w, y = (REAL)h;
+    if (half_centor) { x = x + (REAL)0.5; y = y + (REAL)0.5; }
+    for (int64_t d = 0; d < D; ++d) {
+      const int64_t vox = pix * D + d;
+      const REAL depth = base[pix] + offsets[b * D + d];
+      REAL dsum = (REAL)0;
+      for (int64_t n = 0; n < N; ++n) {
+        if (mask[vox * N + n] == 0) continue;   /* :262-264; the position is not re-tested */
+        FN(proj) p;
+        FN(project)(x, y, depth, Rs + (b * N + n) * 9, Ts + (b * N + n) * 3, half_centor, Hs, Ws, &p);
+        if (!p.valid) continue;                 /* (a mask that did not come from the forward pass) */
+        REAL wt[4];
+        FN(weights)(p.dh, p.dw, wt);
+        const int64_t off = C * (p.fw + Ws * (p.fh + Hs * (n + N * b)));
+        const REAL *t00 = src + off, *t01 = t00 + C, *t10 = t00 + Ws * C, *t11 = t10 + C;
+        REAL *g00 = src_grad + off, *g01 = g00 + C, *g10 = g00 + Ws * C, *g11 = g10 + C;
+        const REAL *g = mapped_grad + (vox * N + n) * C;
+        REAL hg = (REAL)0, wg = (REAL)0;
+        for (int64_t c = 0; c < C; ++c) {
+          SCATTER_ADD(&g00[c], g[c] * wt[0]);   /* :303-306 */
+          SCATTER_ADD(&g01[c], g[c] * wt[1]);
+          SCATTER_ADD(&g11[c], g[c] * wt[2]);
+          SCATTER_ADD(&g10[c], g[c] * wt[3]);
+          REAL t1 = t11[c] - t10[c] - t01[c] + t00[c];
+          hg += g[c] * (t1 * p.dw + t10[c] - t00[c]);
+          wg += g[c] * (t1 * p.dh + t01[c] - t00[c]);
+        }
+        dsum += ((p.hc * p.z - p.zc * p.h3d) * hg + (p.wc * p.z - p.zc * p.w3d) * wg) / (p.z * p.z);
+      }
+      if (par) {
+#pragma omp atomic
+        base_grad[pix] += dsum;
+      } else {
+        base_grad[pix] += dsum;
+      }
+    }
+  }
+}

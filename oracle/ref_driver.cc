@@ -25,6 +25,8 @@ thread_local int64 hi = 0;
 #include "ref_sparse_conv3d.inc"
 #include "ref_cost_volume_v3_macros.inc"
 #include "ref_cost_volume_v3.inc"
+#include "ref_feature_aggregate.inc"
+#include "ref_index_initializer.inc"
 #include "ref_sparse_pad_macros.inc"
 #include "ref_sparse_pad.inc"
 
@@ -256,6 +258,61 @@ int ref_sparse_pad_bwd(int dtype, const int* q, const void* images, const int32*
                                          (double*)images_grad);
     });
 #undef PAD_ARGS
+  return 0;
+}
+
+// FeatureAggregate / FeatureAggregateGrad (custom_helper_op/cc/kernels/feature_aggregate_kernels_gpu.cu.cc:33-121,
+// 219-317), with the int32/int64 choice and the zero fill of the gradient functor (:337-383).
+// dims = {B, H, W, C, D, N, Hs, Ws}: (H, W) is the output grid (base_plane), (Hs, Ws) the source images.
+int ref_feature_aggregate_fwd(int dtype, int half_centor, const int64* dims, const void* src, const void* base,
+                              const void* offsets, const void* Rs, const void* Ts, void* mapped, int32* mask, int nthreads) {
+  Dims s{dims[0], dims[1], dims[2], dims[3], dims[4], dims[5], dims[6], dims[7]};
+  const int64 count = s.B * s.H * s.W * s.D;
+  const bool big = s.B * s.H * s.W * s.C > INT32_MAX || s.B * s.N * s.Hs * s.Ws * s.C > INT32_MAX || count > INT32_MAX;
+#define FA_ARGS(I, T) (I) count, (I)s.B, (I)s.H, (I)s.W, (I)s.C, (I)s.D, (I)s.N, (I)s.Hs, (I)s.Ws, (const T*)src, (const T*)base, \
+                      (const T*)offsets, (const T*)Rs, (const T*)Ts
+#define FA_FWD(T, I, HC) sweep(count, nthreads, [&] { FeatureAggregateKernel<T, I, HC>(FA_ARGS(I, T), (T*)mapped, mask); })
+#define FA_PICK(M, T)                                                                  \
+  do {                                                                                 \
+    if (big) { if (half_centor) M(T, int64, true); else M(T, int64, false); }          \
+    else     { if (half_centor) M(T, int32, true); else M(T, int32, false); }          \
+  } while (0)
+  if (dtype == 0) FA_PICK(FA_FWD, float); else FA_PICK(FA_FWD, double);
+  return 0;
+}
+
+int ref_feature_aggregate_bwd(int dtype, int half_centor, const int64* dims, const void* src, const void* base,
+                              const void* offsets, const void* Rs, const void* Ts, const void* mapped_grad,
+                              const int32* mask, void* src_grad, void* base_grad, int nthreads) {
+  Dims s{dims[0], dims[1], dims[2], dims[3], dims[4], dims[5], dims[6], dims[7]};
+  const int64 count = s.B * s.H * s.W * s.D;
+  const bool big = s.B * s.H * s.W * s.C > INT32_MAX || s.B * s.N * s.Hs * s.Ws * s.C > INT32_MAX || count > INT32_MAX;
+  const size_t el = dtype == 0 ? 4 : 8;
+  std::memset(src_grad, 0, el * s.B * s.N * s.Hs * s.Ws * s.C);
+  std::memset(base_grad, 0, el * s.B * s.H * s.W);
+#define FA_BWD(T, I, HC)                                                                                            \
+  sweep(count, nthreads, [&] {                                                                                      \
+    FeatureAggregateGradKernel<T, I, HC>(FA_ARGS(I, T), (const T*)mapped_grad, mask, (T*)src_grad, (T*)base_grad);  \
+  })
+  if (dtype == 0) FA_PICK(FA_BWD, float); else FA_PICK(FA_BWD, double);
+#undef FA_BWD
+#undef FA_FWD
+#undef FA_PICK
+#undef FA_ARGS
+  return 0;
+}
+
+// IndexInitializer (custom_helper_op/cc/kernels/index_initializer_kernels_gpu.cu.cc:21-29): out [H,W,3] = (column, row, 1),
+// plus 0.5 on the first two when half_centor.
+int ref_index_initializer(int dtype, int half_centor, int H, int W, void* out) {
+  const int32 count = H * W;
+  if (dtype == 0) {
+    if (half_centor) sweep(count, 1, [&] { SetToIndex<float, true>(count, (float*)out, W); });
+    else sweep(count, 1, [&] { SetToIndex<float, false>(count, (float*)out, W); });
+  } else {
+    if (half_centor) sweep(count, 1, [&] { SetToIndex<double, true>(count, (double*)out, W); });
+    else sweep(count, 1, [&] { SetToIndex<double, false>(count, (double*)out, W); });
+  }
   return 0;
 }
 
