@@ -189,7 +189,17 @@ __global__ void __launch_bounds__(256) fa_bwd_kernel(const CvArgs a, const int w
       int cur = -1;
       R t00[CPL], u[CPL], v[CPL], t1[CPL], m[4][CPL];
       const int jn = min(LG, dhi - dblk);
+      // the upstream gradient of plane j+1 is requested before plane j is processed (each value is read once, so
+      // nothing else hides its latency)
+      const R* mgp = mg + ((pix * D + dblk) * N + n) * C + li * CPL;
+      const size_t mstep = (size_t)N * C;
+      R gnext[CPL];
+      load_stream<R, CPL>(mgp, gnext);
       for (int j = 0; j < jn; ++j) {
+        R gv[CPL];
+#pragma unroll
+        for (int k = 0; k < CPL; ++k) gv[k] = gnext[k];
+        if (j + 1 < jn) load_stream<R, CPL>(mgp + (size_t)(j + 1) * mstep, gnext);
         const ProjF<R> rc = r[j];
         if (rc.texel < 0) continue;
         if (rc.texel != cur) {
@@ -209,8 +219,6 @@ __global__ void __launch_bounds__(256) fa_bwd_kernel(const CvArgs a, const int w
             m[0][k] = m[1][k] = m[2][k] = m[3][k] = (R)0;
           }
         }
-        R gv[CPL];
-        load_stream<R, CPL>(mg + ((pix * D + dblk + j) * N + n) * C + li * CPL, gv);
         const R hw = rc.dh * rc.dw;
         R P = (R)0, Q = (R)0, S = (R)0;
 #pragma unroll
