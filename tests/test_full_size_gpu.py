@@ -142,3 +142,94 @@ def test_manifold_conv_full_size():
         assert float((a - b).abs().max()) <= 2.0 ** -7 * float(b.abs().max())
     want = oracle.sparse_conv3d_fwd(r(w["images"]).float().numpy(), r(w["filters"]).float().numpy(), 0.0, w["base_plane"])
     assert helpers.rel_err(res[1][0].float().cpu().numpy(), want) <= 1e-2
+
+
+def test_feature_aggregate_and_v3_full_size():
+    """c1 shapes.  FeatureAggregate: the mean over the seen views of (mapped - ref)^2 is the CostVolume cost and the mask
+    sums to its view count; a band of rows against the oracle bit for bit; the gradient checksum sum(d src) = sum over
+    seen samples of the upstream gradient.  CostVolumeV3: deterministic, MIN cost >= MEAN cost where every view sees the
+    voxel, a band of rows against the oracle bit for bit (cost, mask and winner indices)."""
+    w = synth.make("c1_mvsnet", with_grad=False)
+    t = {k: torch.from_numpy(v).to(DEV) for k, v in w.items()}
+    args = (t["ref"], t["src"], t["base_plane"], t["offsets"], t["Rs"], t["Ts"])
+    fa_args = args[1:]
+    mapped, fmask = ops.feature_aggregate_forward(*fa_args)
+    cost, used = ops.cost_forward(1, *args)
+    assert torch.equal(fmask.sum(dim=4), used)
+    sq = ((mapped - t["ref"][:, :, :, None, None, :]) ** 2 * fmask).sum(dim=4)
+    want = torch.where(used > 0, sq / used.clamp(min=1), torch.zeros_like(sq))
+    assert float((want - cost).abs().max() / cost.abs().max()) <= 1e-5
+    rows = 3
+    m_o, k_o = oracle.feature_aggregate_fwd(w["src"], np.ascontiguousarray(w["base_plane"][:, :rows]), w["offsets"], w["Rs"], w["Ts"])
+    assert helpers.bits_equal(mapped[:, :rows].cpu().numpy(), m_o) and helpers.bits_equal(fmask[:, :rows].cpu().numpy(), k_o)
+    g = torch.Generator(device=DEV)
+    g.manual_seed(6)
+    mg = torch.randn(mapped.shape, device=DEV, generator=g)
+    sg, bg = ops.feature_aggregate_backward(*fa_args, mg, fmask)
+    lhs = sg.double().sum(dim=(0, 2, 3))                                # [N, C]
+    rhs = (mg.double() * fmask).sum(dim=(0, 1, 2, 3))                   # [N, C]
+    assert float((lhs - rhs).abs().max()) <= 1e-4 * float(rhs.abs().max())
+    del mapped, mg, sq, want
+    torch.cuda.empty_cache()
+
+    G = 8
+    c_mean, m_mean = ops.cost_forward(4, *args, "MEAN", G)
+    c_mean2, m_mean2 = ops.cost_forward(4, *args, "MEAN", G)
+    assert torch.equal(c_mean, c_mean2) and torch.equal(m_mean, m_mean2)
+    assert torch.equal(m_mean, used)                                     # the same validity count as CostVolume
+    c_min, m_min = ops.cost_forward(4, *args, "MIN", G)
+    full = (used == t["src"].shape[1]).squeeze(-1)
+    assert bool((c_min.squeeze(-1)[full] >= c_mean.squeeze(-1)[full]).all())
+    ref_b = np.ascontiguousarray(w["ref"][:, :rows])
+    base_b = np.ascontiguousarray(w["base_plane"][:, :rows])
+    for red, c_gpu, m_gpu in (("MEAN", c_mean, m_mean), ("MIN", c_min, m_min)):
+        c_o, m_o = oracle.cost_fwd(4, ref_b, w["src"], base_b, w["offsets"], w["Rs"], w["Ts"], red, G)
+        assert helpers.bits_equal(m_gpu[:, :rows].cpu().numpy(), m_o)
+        assert helpers.bits_equal(c_gpu[:, :rows].cpu().numpy(), c_o)
+    cg = torch.randn(c_mean.shape, device=DEV, generator=g)
+    rg, sg3, bg3 = ops.cost_backward(4, *args, cg, m_mean, "MEAN", G)
+    rg_o, _, bg_o = oracle.cost_bwd(4, ref_b, w["src"], base_b, w["offsets"], w["Rs"], w["Ts"], cg[:, :rows].cpu().numpy(),
+                                    m_mean[:, :rows].cpu().numpy(), "MEAN", G)
+    assert helpers.rel_err(rg[:, :rows].cpu().numpy(), rg_o) <= 1e-4
+    assert helpers.rel_err(bg3[:, :rows].cpu().numpy(), bg_o) <= 1e-4
+
+
+def test_up_down_convolution_full_size():
+    """c4 band, bf16, strides (2,2,2) on the tensor cores.  The transposed convolution is the adjoint of the strided one
+    (default_value 0): <conv(x), z> = <x, convT(z)>; both gradients of a pair agree with that; SparsePad followed by its
+    gradient is the identity; tensor-core and generic kernels agree."""
+    w = synth.manifold_conv(20247)
+    bf = torch.bfloat16
+    x = torch.from_numpy(w["images"]).to(DEV).to(bf)
+    flt = torch.from_numpy(w["filters"]).to(DEV).to(bf)
+    bp = torch.from_numpy(w["base_plane"]).to(DEV)
+    B, H, W, D, C = x.shape
+    st = (2, 2, 2)
+    y = ops.sparse_conv3d_forward(x, flt, 0.0, bp, st)
+    g = torch.Generator(device=DEV)
+    g.manual_seed(7)
+    z = (torch.randn(y.shape, device=DEV, generator=g) * 0.1).to(bf)
+    xt = ops.sparse_conv3d_transpose_forward(z, flt, 0.0, bp, (H, W, D), st)
+    assert _lib.lib().chop_umma_timeouts() == 0
+    lhs = float((y.double() * z.double()).sum())
+    rhs = float((x.double() * xt.double()).sum())
+    scale = float((y.double().abs() * z.double().abs()).sum())
+    assert abs(lhs - rhs) <= 2e-3 * scale                                 # bf16-rounded outputs on both sides
+    # the image gradient of the strided convolution IS the transposed convolution of the upstream gradient
+    ig, fg, _ = ops.sparse_conv3d_backward(x, flt, 0.0, bp, z, st)
+    assert torch.equal(ig, xt)
+    # and the two filter gradients of the pair agree: d<conv(x), z>/dW = d<x, convT(z)>/dW
+    _, fg_t = ops.sparse_conv3d_transpose_backward(z, flt, 0.0, bp, (H, W, D), x, st)
+    assert float((fg - fg_t).abs().max()) <= 2e-3 * float(fg.abs().max())
+    try:
+        _lib.set_tuning("umma", 0)
+        xt_g = ops.sparse_conv3d_transpose_forward(z, flt, 0.0, bp, (H, W, D), st)
+        _, fg_g = ops.sparse_conv3d_transpose_backward(z, flt, 0.0, bp, (H, W, D), x, st)
+    finally:
+        _lib.set_tuning("umma", 1)
+    assert float((xt.float() - xt_g.float()).abs().max()) <= 2.0 ** -7 * float(xt_g.float().abs().max())
+    assert float((fg_t - fg_g).abs().max()) <= 2e-3 * float(fg_g.abs().max())
+    pbp = bp[:, :y.shape[1] * 2, :y.shape[2] * 2].contiguous()
+    padded = ops.sparse_pad_forward(y, pbp, st)
+    assert torch.equal(ops.sparse_pad_backward(y, pbp, padded, st), y)
+    assert int((padded != 0).sum()) == int((y != 0).sum())
