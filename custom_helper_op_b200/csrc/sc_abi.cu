@@ -60,6 +60,11 @@ int fill(const chop_sc_desc* d, ScArgs* a) {
   a->pc = a->fw / 2 * a->dc;
   a->pd = a->fd / 2 * a->dd;
   a->dynamic_default = d->dynamic_default ? 1 : 0;
+  {
+    auto lg = [](int v) { int l = 0; while ((1 << l) < v) ++l; return (1 << l) == v ? l : -1; };
+    a->ls_r = lg(a->sr); a->ls_c = lg(a->sc); a->ls_d = lg(a->sd);
+    if (a->ls_r < 0 || a->ls_c < 0 || a->ls_d < 0) a->ls_r = a->ls_c = a->ls_d = -1;
+  }
   a->nvox_in = d->B * d->H * d->W * d->D;
   a->nvox_out = (long long)a->B * a->oH * a->oW * a->oD;
   // the reference indexes these tensors with int32 (fixed_param_op_gpu.cu.cc:171-174); pixel indices here

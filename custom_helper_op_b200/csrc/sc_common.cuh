@@ -28,6 +28,7 @@ struct ScArgs {
   int oH, oW, oD, pr, pc, pd;
   int dynamic_default;
   int pad_zero;               // gathered taps that are padding read 0 instead of *default_value
+  int ls_r, ls_c, ls_d;       // log2 of the strides when all three are powers of two, else -1
   long long nvox_in, nvox_out;
 };
 

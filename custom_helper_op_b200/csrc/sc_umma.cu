@@ -91,10 +91,15 @@ struct VoxPos {
   int depth_abs;    // absolute fine depth plane of the voxel
 };
 
-// S1 = all strides are 1 (known at compile time: no divisions in the gather).
-template <bool TG, bool S1>
+// SM (stride mode): 0 = any strides (runtime divisions), 1 = all strides are 1 (no divisions in the gather),
+// 2 = all strides are powers of two (the transposed form tests and divides with masks and shifts; it performs
+// about a hundred such operations per voxel, which otherwise dominate the kernel).
+__device__ __forceinline__ int div_pow2_trunc(int t, int l) { return t >= 0 ? (t >> l) : -((-t) >> l); }
+
+template <bool TG, int SM>
 __device__ __forceinline__ VoxPos vox_pos(const ScArgs& a, long long v) {
   VoxPos p;
+  constexpr bool S1 = SM == 1;
   const int d1 = (TG || S1) ? a.D : a.oD, d2 = (TG || S1) ? a.W : a.oW, d3 = (TG || S1) ? a.H : a.oH;
   const int dz = (int)(v % d1); v /= d1;
   const int cc = (int)(v % d2); v /= d2;
@@ -109,12 +114,16 @@ __device__ __forceinline__ VoxPos vox_pos(const ScArgs& a, long long v) {
 
 // One (fr, fc) column of taps: false if the whole column is padding; otherwise base = index of the source
 // pixel's first voxel and shift = what to subtract from the tap's absolute depth.
-template <bool TG, bool S1>
+template <bool TG, int SM>
 __device__ __forceinline__ bool tap_column(const ScArgs& a, const VoxPos& p, int fr, int fc, long long& base, int& shift) {
   const int orow = p.r - 1 + fr, ocol = p.c - 1 + fc;
   if (oob(orow, a.H) || oob(ocol, a.W)) return false;
   const int bp = __ldg(a.base_plane + (p.b * a.H + orow) * a.W + ocol);
-  if (TG && !S1) {
+  if (TG && SM == 2) {
+    if ((orow & (a.sr - 1)) != 0 || (ocol & (a.sc - 1)) != 0) return false;   // orow, ocol >= 0 here
+    base = (((long long)p.b * a.oH + (orow >> a.ls_r)) * a.oW + (ocol >> a.ls_c)) * a.oD;
+    shift = div_pow2_trunc(bp + a.sd - 1, a.ls_d);
+  } else if (TG && SM == 0) {
     if ((orow % a.sr) != 0 || (ocol % a.sc) != 0) return false;
     base = (((long long)p.b * a.oH + orow / a.sr) * a.oW + ocol / a.sc) * a.oD;
     shift = (bp + a.sd - 1) / a.sd;
@@ -126,10 +135,15 @@ __device__ __forceinline__ bool tap_column(const ScArgs& a, const VoxPos& p, int
 }
 
 // Source voxel of tap fz in a column, or -1.
-template <bool TG, bool S1>
+template <bool TG, int SM>
 __device__ __forceinline__ long long tap_voxel(const ScArgs& a, const VoxPos& p, long long base, int shift, int fz) {
   const int od = p.depth_abs - 1 + fz;
-  if (TG && !S1) {
+  if (TG && SM == 2) {
+    if ((od & (a.sd - 1)) != 0) return -1;           // two's complement: also right for negative od
+    const int cd = (od >> a.ls_d) - shift;            // od is a multiple of sd: the shift divides exactly
+    return oob(cd, a.oD) ? -1 : base + cd;
+  }
+  if (TG && SM == 0) {
     if ((od % a.sd) != 0) return -1;
     const int cd = od / a.sd - shift;
     return oob(cd, a.oD) ? -1 : base + cd;
@@ -139,7 +153,7 @@ __device__ __forceinline__ long long tap_voxel(const ScArgs& a, const VoxPos& p,
 }
 
 // CIN: channels of the gathered tensor (K per tap), COUT: channels produced (N).
-template <int CIN, int COUT, bool DGRAD, bool S1>
+template <int CIN, int COUT, bool DGRAD, int SM>
 __global__ void __launch_bounds__(128) sc_umma_kernel(const ScArgs a, const long long nvox, const int ntiles) {
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t mbar_s;
@@ -198,7 +212,7 @@ __global__ void __launch_bounds__(128) sc_umma_kernel(const ScArgs a, const long
     const long long v = (long long)tile * 128 + tid;
     const bool vvalid = v < nvox;
     VoxPos pos = {0, 0, 0, 0};
-    if (vvalid) pos = vox_pos<DGRAD, S1>(a, v);
+    if (vvalid) pos = vox_pos<DGRAD, SM>(a, v);
     unsigned char* a_row = sA + (tid / 8) * SBO + (tid % 8) * 16;
 
     for (int fr = 0; fr < 3; ++fr) {
@@ -207,10 +221,10 @@ __global__ void __launch_bounds__(128) sc_umma_kernel(const ScArgs a, const long
       for (int fc = 0; fc < 3; ++fc) {
         long long base = 0;
         int shift = 0;
-        const bool inb = vvalid && tap_column<DGRAD, S1>(a, pos, fr, fc, base, shift);
+        const bool inb = vvalid && tap_column<DGRAD, SM>(a, pos, fr, fc, base, shift);
 #pragma unroll
         for (int fz = 0; fz < 3; ++fz) {
-          const long long sv = inb ? tap_voxel<DGRAD, S1>(a, pos, base, shift, fz) : -1;
+          const long long sv = inb ? tap_voxel<DGRAD, SM>(a, pos, base, shift, fz) : -1;
           const bool ok = sv >= 0;
           const uint4* p = reinterpret_cast<const uint4*>(src + (size_t)(ok ? sv : 0) * CIN);
           unsigned char* dstA = a_row + (fc * 3 + fz) * A_TAP_BYTES;
@@ -295,7 +309,7 @@ __global__ void __launch_bounds__(128) sc_umma_kernel(const ScArgs a, const long
 // gathered tensor (CIN channels) is the op's coarse input under every tap (default_value where there is
 // none) and G (COUT channels) its upstream gradient; the slab is written [tap][coarse ch][fine ch] and the
 // reduction kernel moves it to filter_grad[flipped tap][fine ch][coarse ch].
-template <int CIN, int COUT, bool TG, bool S1>
+template <int CIN, int COUT, bool TG, int SM>
 __global__ void __launch_bounds__(128) sc_umma_wgrad_kernel(const ScArgs a, const long long nvox, const int ntiles) {
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t mbar_s;
@@ -361,7 +375,7 @@ __global__ void __launch_bounds__(128) sc_umma_wgrad_kernel(const ScArgs a, cons
     float gf[COUT];
 #pragma unroll
     for (int n = 0; n < COUT; ++n) gf[n] = 0.f;
-    if (vvalid) pos = vox_pos<TG, S1>(a, v);
+    if (vvalid) pos = vox_pos<TG, SM>(a, v);
     // out_grad row of this voxel -> G tile (previous tile's MMAs have completed: every round waits)
 #pragma unroll
     for (int nc = 0; nc < COUT / 8; ++nc) {
@@ -390,8 +404,8 @@ __global__ void __launch_bounds__(128) sc_umma_wgrad_kernel(const ScArgs a, cons
           const int fz = t % 3, fc = (t / 3) % 3, fr = t / 9;
           long long base = 0;
           int shift = 0;
-          if (tap_column<TG, S1>(a, pos, fr, fc, base, shift)) {
-            const long long sv = tap_voxel<TG, S1>(a, pos, base, shift, fz);
+          if (tap_column<TG, SM>(a, pos, fr, fc, base, shift)) {
+            const long long sv = tap_voxel<TG, SM>(a, pos, base, shift, fz);
             if (sv >= 0) {
               ok = true;
               off = (size_t)sv * CIN;
@@ -516,7 +530,8 @@ __global__ void __launch_bounds__(256) sc_umma_wgrad_reduce_t(const float* part,
 template <int CIN, int COUT, bool TG>
 int launch_wgrad(const ScArgs& a, int nparts, cudaStream_t st) {
   const bool s1 = a.sr == 1 && a.sc == 1 && a.sd == 1;
-  auto k = s1 ? sc_umma_wgrad_kernel<CIN, COUT, TG, true> : sc_umma_wgrad_kernel<CIN, COUT, TG, false>;
+  auto k = s1 ? sc_umma_wgrad_kernel<CIN, COUT, TG, 1>
+              : ((TG && a.ls_r >= 0) ? sc_umma_wgrad_kernel<CIN, COUT, TG, TG ? 2 : 0> : sc_umma_wgrad_kernel<CIN, COUT, TG, 0>);
   const size_t smem = (size_t)16 * 2048 + (size_t)16 * (COUT / 8) * 128 + (size_t)27 * COUT * 4 + 1024;
   if (smem > 48 * 1024) {  // per device and per kernel: set on every call (a cheap host-side call)
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -542,7 +557,8 @@ int launch_wgrad(const ScArgs& a, int nparts, cudaStream_t st) {
 template <int CIN, int COUT, bool DGRAD>
 int launch(const ScArgs& a, long long nvox, cudaStream_t st) {
   const bool s1 = a.sr == 1 && a.sc == 1 && a.sd == 1;
-  auto k = s1 ? sc_umma_kernel<CIN, COUT, DGRAD, true> : sc_umma_kernel<CIN, COUT, DGRAD, false>;
+  auto k = s1 ? sc_umma_kernel<CIN, COUT, DGRAD, 1>
+              : ((DGRAD && a.ls_r >= 0) ? sc_umma_kernel<CIN, COUT, DGRAD, DGRAD ? 2 : 0> : sc_umma_kernel<CIN, COUT, DGRAD, 0>);
   const size_t smem = (size_t)27 * COUT * CIN * 2 + (size_t)9 * 128 * CIN * 2 + 1024;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
