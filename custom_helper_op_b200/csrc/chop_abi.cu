@@ -14,6 +14,7 @@
 
 namespace chop {
 extern std::atomic<int> g_use_umma;
+void sc_umma_set_rows(int on);
 }
 
 namespace {
@@ -447,6 +448,7 @@ int chop_set_tuning(const char* name, int value) {
   if (!std::strcmp(name, "bwd_views")) { g_bwd_views = value; return CHOP_OK; }
   if (!std::strcmp(name, "tuned")) { g_tuned = value; return CHOP_OK; }
   if (!std::strcmp(name, "umma")) { chop::g_use_umma = value; return CHOP_OK; }
+  if (!std::strcmp(name, "umma_rows")) { chop::sc_umma_set_rows(value); return CHOP_OK; }
   return CHOP_ERR_ATTR;
 }
 

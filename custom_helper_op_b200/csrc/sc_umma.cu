@@ -24,6 +24,8 @@
 // (readable through sc_umma_timeouts()), stops issuing work, frees its tensor memory and returns.
 #include <cuda_bf16.h>
 
+#include <atomic>
+
 #include "sc_common.cuh"
 #include "sc_entry.h"
 
@@ -271,6 +273,174 @@ __global__ void __launch_bounds__(128) sc_umma_kernel(const ScArgs a, const long
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
     if (vvalid) {
       uint4* o = reinterpret_cast<uint4*>(dst + (size_t)v * COUT);
+#pragma unroll
+      for (int q = 0; q < COUT / 8; ++q) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(acc[q * 8 + 2 * i]), __uint_as_float(acc[q * 8 + 2 * i + 1]));
+          w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        o[q] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    uint32_t ncols = 32;
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(ncols) : "memory");
+  }
+}
+
+
+// ---------------------------------------------------------------------------------------------------------
+// Stride-1 variant with ONE staged copy per neighbour pixel instead of one per tap.
+//
+// The three depth taps of a filter column (fr, fc) read the same neighbour pixel at consecutive planes, so
+// their A operands are the same rows shifted by one.  With SBO = 128 bytes the canonical K-major layout
+// stores row r of a 16-byte K-chunk at r*16 bytes, i.e. rows are linear, and a tap's operand is simply the
+// column buffer's address plus fz*16 bytes.  A tile therefore holds PT = 128 / (D + 2) pixels, every pixel
+// owning D + 2 rows: row (p, j) of column (fr, fc) holds plane j - 1 + base_plane[p] - base_plane[nbr] of
+// the neighbour pixel (default_value outside its band or outside the image), and MMA row m = p*(D+2) + d,
+// d < D, is output voxel (p, d); the two remaining rows per pixel produce values that are discarded.
+// Against the per-tap gather this stages 9 instead of 27 rows per voxel, issues all 27 taps of a tile
+// behind one barrier (one commit, one wait) and reads every neighbour plane once.
+// ---------------------------------------------------------------------------------------------------------
+template <int CIN, int COUT, bool DGRAD>
+__global__ void __launch_bounds__(128) sc_umma_rows_kernel(const ScArgs a, const int ntiles, const int PT) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t mbar_s;
+  __shared__ uint32_t tmem_base_s;
+  constexpr int KC = CIN / 8;
+  constexpr int NRB = 136;                              // rows per column buffer: 128 + the two shifted reads, padded to 8
+  constexpr uint32_t B_LBO = 128, B_SBO = KC * 128;     // filter tiles: K-chunks adjacent, then 8-row groups
+  constexpr uint32_t A_LBO = NRB * 16, A_SBO = 128;     // column buffers: rows linear, K-chunks NRB rows apart
+  constexpr int B_TAP_BYTES = COUT * CIN * 2;
+  constexpr int COL_BYTES = KC * NRB * 16;
+  unsigned char* sB = smem;                             // 27 taps
+  unsigned char* sX = smem + 27 * B_TAP_BYTES;          // 9 filter columns
+  const int tid = threadIdx.x, warp = tid >> 5;
+
+  const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(DGRAD ? a.out_grad : a.images);
+  __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(DGRAD ? a.images_grad : a.output);
+
+  {
+    const unsigned short* flt = static_cast<const unsigned short*>(a.filters);  // [27][Cin_f][Cout_f]
+    for (int e = tid; e < 27 * COUT * CIN; e += 128) {
+      const int k = e % CIN, n = (e / CIN) % COUT, t = e / (CIN * COUT);
+      unsigned short w;
+      if (!DGRAD) w = __ldg(flt + ((size_t)t * CIN + k) * COUT + n);         // B[n=oc][k=ci] = f[t][ci][oc]
+      else w = __ldg(flt + ((size_t)(26 - t) * COUT + n) * CIN + k);          // B[n=ci][k=oc] = f[flip t][ci][oc]
+      *reinterpret_cast<unsigned short*>(sB + t * B_TAP_BYTES + (n / 8) * B_SBO + (k / 8) * B_LBO + (n % 8) * 16 + (k % 8) * 2) = w;
+    }
+    // rows 128..135 of every column buffer are only ever read into discarded output rows; keep them defined
+    for (int e = tid; e < 9 * KC * (NRB - 128); e += 128) {
+      const int rr = e % (NRB - 128), kc = (e / (NRB - 128)) % KC, col = e / ((NRB - 128) * KC);
+      *reinterpret_cast<uint4*>(sX + col * COL_BYTES + kc * A_LBO + (128 + rr) * 16) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  if (warp == 0) {
+    uint32_t slot = smem_u32(&tmem_base_s), ncols = 32;
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&mbar_s)), "r"(1) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t mbar = smem_u32(&mbar_s);
+  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(COUT >> 3) << 17) | ((128u >> 4) << 24);
+
+  uint4 padv = make_uint4(0, 0, 0, 0);
+  if (!a.pad_zero) {
+    const unsigned d16 = __ldg(static_cast<const unsigned short*>(a.default_value));
+    const unsigned d32 = d16 | (d16 << 16);
+    padv = make_uint4(d32, d32, d32, d32);
+  }
+
+  const int H = a.H, W = a.W, D = a.D, RP = D + 2;
+  const long long npix = (long long)a.B * H * W;
+  const int p_in_tile = tid / RP, j = tid - p_in_tile * RP;   // this thread's row: pixel of the tile, row of the pixel
+  const bool row_used = p_in_tile < PT;
+  uint32_t phase = 0;
+  bool alive = true;
+  for (int tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
+    const long long pix = (long long)tile * PT + p_in_tile;
+    const bool rvalid = row_used && pix < npix;
+    int b = 0, r = 0, c = 0, bp_out = 0;
+    if (rvalid) {
+      c = (int)(pix % W);
+      const long long t = pix / W;
+      r = (int)(t % H);
+      b = (int)(t / H);
+      bp_out = __ldg(a.base_plane + pix);
+    }
+    // ---- stage the nine filter columns: one row per thread and column --------------------------------------
+#pragma unroll
+    for (int fr = 0; fr < 3; ++fr) {
+#pragma unroll
+      for (int fc = 0; fc < 3; ++fc) {
+        const int orow = r - 1 + fr, ocol = c - 1 + fc;
+        bool ok = rvalid && !oob(orow, H) && !oob(ocol, W);
+        long long sv = 0;
+        if (ok) {
+          const int np = (b * H + orow) * W + ocol;
+          const int plane = j - 1 + bp_out - __ldg(a.base_plane + np);
+          ok = !oob(plane, D);
+          sv = (long long)np * D + plane;
+        }
+        const uint4* p = reinterpret_cast<const uint4*>(src + (size_t)(ok ? sv : 0) * CIN);
+        unsigned char* dx = sX + (fr * 3 + fc) * COL_BYTES + tid * 16;
+#pragma unroll
+        for (int kc = 0; kc < KC; ++kc) {
+          uint4 x = rvalid ? padv : make_uint4(0, 0, 0, 0);
+          if (ok) x = __ldg(p + kc);
+          *reinterpret_cast<uint4*>(dx + kc * A_LBO) = x;
+        }
+      }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int col = 0; col < 9; ++col) {
+#pragma unroll
+        for (int fz = 0; fz < 3; ++fz) {
+#pragma unroll
+          for (int k16 = 0; k16 < CIN / 16; ++k16) {
+            const uint64_t da = umma_desc(smem_u32(sX + col * COL_BYTES + k16 * 2 * A_LBO + fz * 16), A_LBO, A_SBO);
+            const uint64_t db = umma_desc(smem_u32(sB + (col * 3 + fz) * B_TAP_BYTES + k16 * 2 * B_LBO), B_LBO, B_SBO);
+            umma_bf16(tmem, da, db, IDESC, (col | fz | k16) != 0 ? 1u : 0u);
+          }
+        }
+      }
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
+    }
+    const bool done = mbar_wait(mbar, phase);
+    phase ^= 1;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (!__syncthreads_and(done)) {
+      if (tid == 0) atomicAdd(&g_umma_timeouts, 1);
+      alive = false;
+      break;
+    }
+
+    // ---- epilogue: MMA row m = this thread's row; it is output voxel (pixel, j) when j < D -----------------------
+    uint32_t acc[COUT];
+    tmem_ld<COUT>(tmem + ((uint32_t)(warp * 32) << 16), acc);
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    if (rvalid && j < D) {
+      uint4* o = reinterpret_cast<uint4*>(dst + ((size_t)pix * D + j) * COUT);
 #pragma unroll
       for (int q = 0; q < COUT / 8; ++q) {
         uint32_t w[4];
@@ -555,7 +725,31 @@ int launch_wgrad(const ScArgs& a, int nparts, cudaStream_t st) {
 }
 
 template <int CIN, int COUT, bool DGRAD>
+int launch_rows(const ScArgs& a, cudaStream_t st) {
+  auto k = sc_umma_rows_kernel<CIN, COUT, DGRAD>;
+  const size_t smem = (size_t)27 * COUT * CIN * 2 + (size_t)9 * (CIN / 8) * 136 * 16 + 1024;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int PT = 128 / (a.D + 2);
+  const long long npix = (long long)a.B * a.H * a.W;
+  const long long ntiles = (npix + PT - 1) / PT;
+  int per_sm = (int)((size_t)220 * 1024 / (smem + 2048));
+  if (per_sm > 8) per_sm = 8;
+  if (per_sm < 1) per_sm = 1;
+  long long grid = 148LL * per_sm;
+  if (grid > ntiles) grid = ntiles;
+  k<<<(unsigned)grid, 128, smem, st>>>(a, (int)ntiles, PT);
+  return (int)cudaGetLastError();
+}
+
+std::atomic<int> g_umma_rows{1};   // tuning knob "umma_rows": 0 = always the per-tap gather
+
+template <int CIN, int COUT, bool DGRAD>
 int launch(const ScArgs& a, long long nvox, cudaStream_t st) {
+  // stride 1 and a band of at most 126 planes: the shifted-row kernel
+  if (a.sr == 1 && a.sc == 1 && a.sd == 1 && a.D + 2 <= 128 && g_umma_rows.load()) return launch_rows<CIN, COUT, DGRAD>(a, st);
   const bool s1 = a.sr == 1 && a.sc == 1 && a.sd == 1;
   auto k = s1 ? sc_umma_kernel<CIN, COUT, DGRAD, 1>
               : ((DGRAD && a.ls_r >= 0) ? sc_umma_kernel<CIN, COUT, DGRAD, DGRAD ? 2 : 0> : sc_umma_kernel<CIN, COUT, DGRAD, 0>);
@@ -612,6 +806,8 @@ int sc_umma_twgrad_launch(const ScArgs& a, int nparts, cudaStream_t st) {
   if (a.Cin == 32 && a.Cout == 16) return launch_wgrad<16, 32, true>(a, nparts, st);
   return launch_wgrad<32, 32, true>(a, nparts, st);
 }
+
+void sc_umma_set_rows(int on) { g_umma_rows = on; }
 
 int sc_umma_timeouts() {
   int v = -1;

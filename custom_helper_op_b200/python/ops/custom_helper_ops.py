@@ -244,7 +244,8 @@ def _scalar(value, like):
     """default_value as a device scalar of the images' dtype (python floats keep full precision)."""
     if torch.is_tensor(value):
         return value.to(device=like.device, dtype=like.dtype).reshape(())
-    return torch.tensor(value, dtype=like.dtype, device=like.device)
+    # a fill kernel on the current stream, not a synchronous host-to-device copy; float64 keeps the python float exactly
+    return torch.full((), float(value), dtype=like.dtype, device=like.device)
 
 
 def sparse_conv3d_forward(images, filters, default_value, base_plane, strides=(1, 1, 1), dilations=(1, 1, 1)):

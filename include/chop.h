@@ -245,8 +245,9 @@ CHOP_API int chop_version(void);
 /* Tuning knobs for experiments: "fwd_chunk", "bwd_chunk" (depth planes per warp work item, 0 =
  * heuristic), "bwd_views" (source views per backward pass, 0 = heuristic), "tuned" (1 = use the compile-time-C
  * kernels where one exists, 0 = always the generic kernels), "umma" (1 = tensor-core manifold convolution
- * where supported, 0 = always the generic kernels).  Returns CHOP_ERR_ATTR
- * for an unknown name.  Process-wide; not part of the reference surface. */
+ * where supported, 0 = always the generic kernels), "umma_rows" (1 = the stride-1 tensor-core forward / image
+ * gradient stages one copy per neighbour pixel, 0 = one per tap).  Returns CHOP_ERR_ATTR for an unknown name.
+ * Process-wide; not part of the reference surface. */
 CHOP_API int chop_set_tuning(const char *name, int value);
 
 #ifdef __cplusplus

@@ -114,6 +114,31 @@ def test_bfloat16_strided(strides, chans):
         assert abs(float(dg) - float(dg_w)) <= 2e-3 * max(1.0, abs(float(dg_w)))
 
 
+@pytest.mark.parametrize("D", [1, 2, 30, 62, 63, 126, 127])
+def test_tensor_core_kernel_band_depths(D):
+    """The stride-1 tensor-core forward / image gradient packs 128 // (D + 2) pixels into a tile (D <= 126) and falls
+    back to one voxel per row above that; both against the oracle on bf16-rounded inputs."""
+    from custom_helper_op_b200 import _lib
+    B, H, W, Cin, Cout = 1, 5, 7, 16, 16
+    images, filters, defv, bp, _ = make_case(17, B, H, W, D, Cin, Cout, (3, 3, 3), 2 * D + 6, np.float32)
+    r = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(torch.bfloat16).float().numpy()
+    images, filters = r(images - 0.5), r(filters * 0.3)
+    defv = float(r(np.array([defv]))[0])
+    want = oracle.sparse_conv3d_fwd(images, filters, defv, bp, dtype=np.float32)
+    og = r(np.random.default_rng(18).uniform(-1, 1, want.shape))
+    ig_w, fg_w, dg_w = oracle.sparse_conv3d_bwd(images, filters, defv, bp, og, dynamic_default=True, dtype=np.float32)
+    for rows in (1, 0):
+        try:
+            _lib.set_tuning("umma_rows", rows)
+            out, ig, fg, dg = run_gpu(images, filters, defv, bp, og, (1, 1, 1), (1, 1, 1), True, torch.bfloat16)
+        finally:
+            _lib.set_tuning("umma_rows", 1)
+        assert helpers.rel_err(out, want) <= 1e-2
+        assert helpers.rel_err(ig, ig_w) <= 1e-2
+        assert helpers.rel_err(fg, fg_w) <= 2e-3
+    assert _lib.lib().chop_umma_timeouts() == 0
+
+
 def test_autograd_wrapper():
     images, filters, defv, bp, _ = make_case(11, 1, 6, 7, 5, 4, 3, (3, 3, 3), 12, np.float32)
     want = oracle.sparse_conv3d_fwd(images, filters, defv, bp, dtype=np.float32)
