@@ -33,6 +33,7 @@ namespace chop {
 namespace {
 
 __device__ int g_umma_timeouts = 0;
+std::atomic<int> g_umma_rows{1};   // tuning knob "umma_rows": 0 = always the per-tap gather
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -384,28 +385,31 @@ __global__ void __launch_bounds__(128) sc_umma_rows_kernel(const ScArgs a, const
       bp_out = __ldg(a.base_plane + pix);
     }
     // ---- stage the nine filter columns: one row per thread and column --------------------------------------
+    // three passes so that the nine base-plane lookups, then the nine neighbour rows, are all in flight together
+    long long sv[9];
 #pragma unroll
-    for (int fr = 0; fr < 3; ++fr) {
+    for (int col = 0; col < 9; ++col) {
+      const int orow = r - 1 + col / 3, ocol = c - 1 + col % 3;
+      const bool inb = rvalid && !oob(orow, H) && !oob(ocol, W);
+      const int np = inb ? (b * H + orow) * W + ocol : 0;
+      const int plane = j - 1 + bp_out - __ldg(a.base_plane + np);
+      sv[col] = (inb && !oob(plane, D)) ? (long long)np * D + plane : -1;
+    }
+    uint4 val[9][KC];
 #pragma unroll
-      for (int fc = 0; fc < 3; ++fc) {
-        const int orow = r - 1 + fr, ocol = c - 1 + fc;
-        bool ok = rvalid && !oob(orow, H) && !oob(ocol, W);
-        long long sv = 0;
-        if (ok) {
-          const int np = (b * H + orow) * W + ocol;
-          const int plane = j - 1 + bp_out - __ldg(a.base_plane + np);
-          ok = !oob(plane, D);
-          sv = (long long)np * D + plane;
-        }
-        const uint4* p = reinterpret_cast<const uint4*>(src + (size_t)(ok ? sv : 0) * CIN);
-        unsigned char* dx = sX + (fr * 3 + fc) * COL_BYTES + tid * 16;
+    for (int col = 0; col < 9; ++col) {
+      const uint4* p = reinterpret_cast<const uint4*>(src + (size_t)(sv[col] >= 0 ? sv[col] : 0) * CIN);
 #pragma unroll
-        for (int kc = 0; kc < KC; ++kc) {
-          uint4 x = rvalid ? padv : make_uint4(0, 0, 0, 0);
-          if (ok) x = __ldg(p + kc);
-          *reinterpret_cast<uint4*>(dx + kc * A_LBO) = x;
-        }
+      for (int kc = 0; kc < KC; ++kc) {
+        val[col][kc] = rvalid ? padv : make_uint4(0, 0, 0, 0);
+        if (sv[col] >= 0) val[col][kc] = __ldg(p + kc);
       }
+    }
+#pragma unroll
+    for (int col = 0; col < 9; ++col) {
+      unsigned char* dx = sX + col * COL_BYTES + tid * 16;
+#pragma unroll
+      for (int kc = 0; kc < KC; ++kc) *reinterpret_cast<uint4*>(dx + kc * A_LBO) = val[col][kc];
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -654,6 +658,226 @@ __global__ void __launch_bounds__(128) sc_umma_wgrad_kernel(const ScArgs a, cons
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Stride-1 filter gradient with the column buffers of sc_umma_rows_kernel (16 gathered channels).
+//
+// The buffers hold, per 16-byte chunk q = (filter column, channel chunk), the rows of a tile at 16 bytes each -
+// which is also the MN-major layout with the voxels as the reduction dimension (LBO = 128: eight voxels per core
+// matrix, linear beyond; SBO = the chunk stride).  For a depth tap fz the operand is again the buffer address plus
+// fz*16 bytes; out_grad (the other operand) is not shifted and carries zeros in the rows that are not voxels.
+// One MMA block of M = 128 covers chunks 0..15 = filter columns 0..7; the ninth column is taken from a second
+// block that starts at chunk 2 (columns 1..8, only its last 16 rows are kept) - the tensor pipe is idle anyway
+// and no dummy shared memory is needed.  3 depth taps x 2 blocks x COUT tensor-memory columns accumulate over
+// all tiles of the CTA.  One barrier per tile instead of four, 9 staged rows per voxel instead of 27.
+// TG (transposed convolution) only changes the operand roles, exactly as in sc_umma_wgrad_kernel.
+// ---------------------------------------------------------------------------------------------------------
+template <int COUT, bool TG>
+__global__ void __launch_bounds__(128) sc_umma_wgrad_rows_kernel(const ScArgs a, const int ntiles, const int PT) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t mbar_s;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ float red_s[128];
+  constexpr int CIN = 16, KC = 2;
+  constexpr int NRB = 136;
+  constexpr uint32_t X_SBO = NRB * 16;             // chunk stride (M direction)
+  constexpr uint32_t X_LBO = 128;                  // eight voxels further (reduction direction): rows are linear
+  constexpr uint32_t G_SBO = 128, G_LBO = (COUT / 8) * 128;
+  constexpr int TMEM_COLS = 6 * COUT <= 128 ? 128 : 256;
+  unsigned char* sX = smem;                        // 18 chunks x NRB rows x 16 B
+  unsigned char* sG = smem + 18 * X_SBO;           // 16 voxel groups x G_LBO
+  float* wsum = reinterpret_cast<float*>(sG + 16 * G_LBO);   // [27][COUT], dynamic_default only
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const __nv_bfloat16* img = static_cast<const __nv_bfloat16*>(a.images);
+  const __nv_bfloat16* og = static_cast<const __nv_bfloat16*>(a.out_grad);
+
+  const bool dyn = !TG && a.dynamic_default;
+  if (dyn) {
+    const __nv_bfloat16* flt = static_cast<const __nv_bfloat16*>(a.filters);
+    for (int e = tid; e < 27 * COUT; e += 128) {
+      const int t = e / COUT, n = e % COUT;
+      float sum = 0.f;
+      for (int ci = 0; ci < CIN; ++ci) sum += __bfloat162float(flt[((size_t)t * CIN + ci) * COUT + n]);
+      wsum[e] = sum;
+    }
+  }
+  for (int e = tid; e < 18 * (NRB - 128); e += 128)   // rows 128..135: only multiplied by zero rows of out_grad, but
+    *reinterpret_cast<uint4*>(sX + (e / (NRB - 128)) * X_SBO + (128 + e % (NRB - 128)) * 16) = make_uint4(0, 0, 0, 0);  // must be finite
+  if (warp == 0) {
+    uint32_t slot = smem_u32(&tmem_base_s), ncols = TMEM_COLS;
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&mbar_s)), "r"(1) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t mbar = smem_u32(&mbar_s);
+  // D f32, A/B bf16, both operands MN-major (bits 15, 16), N = COUT, M = 128
+  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(COUT >> 3) << 17) |
+                             ((128u >> 4) << 24);
+  const unsigned d16 = __ldg(static_cast<const unsigned short*>(a.default_value));
+  const unsigned d32 = d16 | (d16 << 16);
+  const uint4 padv = make_uint4(d32, d32, d32, d32);
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+
+  const int H = a.H, W = a.W, D = a.D, RP = D + 2;
+  const long long npix = (long long)a.B * H * W;
+  const int p_in_tile = tid / RP, j = tid - p_in_tile * RP;
+  const bool row_used = p_in_tile < PT;
+  unsigned char* g_row = sG + (tid / 8) * G_LBO + (tid % 8) * 16;
+  uint32_t phase = 0;
+  bool alive = true, first = true;
+  float dacc = 0.f;
+
+  for (int tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
+    const long long pix = (long long)tile * PT + p_in_tile;
+    const bool rvalid = row_used && pix < npix;
+    const bool is_voxel = rvalid && j < D;          // rows j = D, D+1 of a pixel are halo rows, not output voxels
+    int b = 0, r = 0, c = 0, bp_out = 0;
+    if (rvalid) {
+      c = (int)(pix % W);
+      const long long t = pix / W;
+      r = (int)(t % H);
+      b = (int)(t / H);
+      bp_out = __ldg(a.base_plane + pix);
+    }
+    // out_grad row of this voxel -> G tile (zeros for rows that are not voxels)
+#pragma unroll
+    for (int nc = 0; nc < COUT / 8; ++nc) {
+      uint4 x = zero4;
+      if (is_voxel) x = __ldg(reinterpret_cast<const uint4*>(og + ((size_t)pix * D + j) * COUT) + nc);
+      *reinterpret_cast<uint4*>(g_row + nc * G_SBO) = x;
+    }
+    // the nine filter columns, one row per thread and column (as in sc_umma_rows_kernel)
+    long long sv[9];
+    unsigned padmask = 0;                            // bit col: this row of column col is padding
+#pragma unroll
+    for (int col = 0; col < 9; ++col) {
+      const int orow = r - 1 + col / 3, ocol = c - 1 + col % 3;
+      const bool inb = rvalid && !oob(orow, H) && !oob(ocol, W);
+      const int np = inb ? (b * H + orow) * W + ocol : 0;
+      const int plane = j - 1 + bp_out - __ldg(a.base_plane + np);
+      const bool ok = inb && !oob(plane, D);
+      sv[col] = ok ? (long long)np * D + plane : -1;
+      if (!ok) padmask |= 1u << col;
+    }
+    uint4 val[9][KC];
+#pragma unroll
+    for (int col = 0; col < 9; ++col) {
+      const uint4* p = reinterpret_cast<const uint4*>(img + (size_t)(sv[col] >= 0 ? sv[col] : 0) * CIN);
+#pragma unroll
+      for (int kc = 0; kc < KC; ++kc) {
+        val[col][kc] = rvalid ? padv : zero4;
+        if (sv[col] >= 0) val[col][kc] = __ldg(p + kc);
+      }
+    }
+#pragma unroll
+    for (int col = 0; col < 9; ++col)
+#pragma unroll
+      for (int kc = 0; kc < KC; ++kc) *reinterpret_cast<uint4*>(sX + (col * KC + kc) * X_SBO + tid * 16) = val[col][kc];
+
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int fz = 0; fz < 3; ++fz) {
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {   // 16 tile rows (two 8-row groups) per MMA
+            const uint64_t da = umma_desc(smem_u32(sX + blk * 2 * X_SBO + fz * 16 + ks * 2 * X_LBO), X_LBO, X_SBO);
+            const uint64_t db = umma_desc(smem_u32(sG + ks * 2 * G_LBO), G_LBO, G_SBO);
+            umma_bf16(tmem + (fz * 2 + blk) * COUT, da, db, IDESC, (first && ks == 0) ? 0u : 1u);
+          }
+        }
+      }
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
+    }
+    if (dyn) {
+      // fixed_param_op_gpu.cu.cc:273-277: d(default) += sum_n (sum_ci filter[tap][ci][n]) * out_grad[voxel][n] over the
+      // padded taps.  This thread's row j of column col is tap (col, fz) of voxel d = j - fz of the same pixel; the
+      // G tile (read here, behind the barrier above) holds that voxel's out_grad row at tile row tid - fz.
+      for (int fz = 0; fz < 3; ++fz) {
+        const int dv = j - fz;
+        if (!rvalid || dv < 0 || dv >= D || padmask == 0) continue;
+        const unsigned char* grow = sG + ((tid - fz) / 8) * G_LBO + ((tid - fz) % 8) * 16;
+        float gf[COUT];
+#pragma unroll
+        for (int nc = 0; nc < COUT / 8; ++nc) {
+          const uint4 x = *reinterpret_cast<const uint4*>(grow + nc * G_SBO);
+          const unsigned w4[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            gf[nc * 8 + 2 * i] = __uint_as_float(w4[i] << 16);
+            gf[nc * 8 + 2 * i + 1] = __uint_as_float(w4[i] & 0xffff0000u);
+          }
+        }
+        for (int col = 0; col < 9; ++col) {
+          if (!((padmask >> col) & 1u)) continue;
+          const float* ws = wsum + (col * 3 + fz) * COUT;
+#pragma unroll
+          for (int n = 0; n < COUT; ++n) dacc = fmaf(ws[n], gf[n], dacc);
+        }
+      }
+    }
+    const bool done = mbar_wait(mbar, phase);
+    phase ^= 1;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (!__syncthreads_and(done)) {
+      if (tid == 0) atomicAdd(&g_umma_timeouts, 1);
+      alive = false;
+      break;
+    }
+    first = false;
+  }
+
+  // ---- accumulators -> this CTA's partial slab [27*CIN][COUT] (+ default-value gradient) -------------------
+  constexpr int K = 27 * CIN;
+  float* part = static_cast<float*>(a.workspace) + (size_t)blockIdx.x * ((size_t)K * COUT + 1);
+  if (alive) {
+#pragma unroll
+    for (int fz = 0; fz < 3; ++fz) {
+#pragma unroll
+      for (int blk = 0; blk < 2; ++blk) {
+        uint32_t acc[COUT];
+        if (!first) {
+          tmem_ld<COUT>(tmem + ((uint32_t)(warp * 32) << 16) + (fz * 2 + blk) * COUT, acc);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        }
+        // MMA row tid of block blk is chunk q = 2*blk + tid/8, element tid%8: column q/2, channel (q%2)*8 + tid%8.
+        // Block 0 supplies columns 0..7, block 1 only column 8 (its rows 112..127).
+        const int q = 2 * blk + tid / 8;
+        const int col = q / KC, ci = (q % KC) * 8 + (tid % 8);
+        if (blk == 0 || col == 8) {
+          const int k = (col * 3 + fz) * CIN + ci;
+#pragma unroll
+          for (int n = 0; n < COUT; ++n) part[(size_t)k * COUT + n] = first ? 0.f : __uint_as_float(acc[n]);
+        }
+      }
+    }
+  }
+  red_s[tid] = dacc;
+  __syncthreads();
+  for (int o = 64; o > 0; o >>= 1) {
+    if (tid < o) red_s[tid] += red_s[tid + o];
+    __syncthreads();
+  }
+  if (tid == 0) part[(size_t)K * COUT] = red_s[0];
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    uint32_t ncols = TMEM_COLS;
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(ncols) : "memory");
+  }
+}
+
 // Sum of the per-CTA partial slabs in a fixed order (deterministic).  A block owns 32 consecutive
 // elements; its 8 warps each add every 8th slab with coalesced 128-byte reads, then the 8 warp sums are
 // added in warp order.  Element n_el is the default-value gradient.
@@ -697,9 +921,38 @@ __global__ void __launch_bounds__(256) sc_umma_wgrad_reduce_t(const float* part,
   }
 }
 
+template <int COUT, bool TG>
+int launch_wgrad_rows(const ScArgs& a, int nparts, cudaStream_t st) {
+  auto k = sc_umma_wgrad_rows_kernel<COUT, TG>;
+  const size_t smem = (size_t)18 * 136 * 16 + (size_t)16 * (COUT / 8) * 128 + (size_t)27 * COUT * 4 + 1024;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int PT = 128 / (a.D + 2);
+  const long long npix = (long long)a.B * a.H * a.W;
+  const long long ntiles = (npix + PT - 1) / PT;
+  if (nparts > ntiles) nparts = (int)ntiles;
+  k<<<nparts, 128, smem, st>>>(a, (int)ntiles, PT);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  const long long n_el = (long long)27 * 16 * COUT;
+  if (TG)
+    sc_umma_wgrad_reduce_t<<<(unsigned)((n_el + 31) / 32), 256, 0, st>>>(static_cast<const float*>(a.workspace), nparts, 16, COUT,
+                                                                          static_cast<float*>(a.filter_grad));
+  else
+    sc_umma_wgrad_reduce<<<(unsigned)((n_el + 1 + 31) / 32), 256, 0, st>>>(static_cast<const float*>(a.workspace), nparts, n_el,
+                                                                             static_cast<float*>(a.filter_grad),
+                                                                             static_cast<float*>(a.default_grad));
+  return (int)cudaGetLastError();
+}
+
 template <int CIN, int COUT, bool TG>
 int launch_wgrad(const ScArgs& a, int nparts, cudaStream_t st) {
   const bool s1 = a.sr == 1 && a.sc == 1 && a.sd == 1;
+  if constexpr (CIN == 16) {
+    if (s1 && a.D + 2 <= 128 && g_umma_rows.load()) return launch_wgrad_rows<COUT, TG>(a, nparts, st);
+  }
   auto k = s1 ? sc_umma_wgrad_kernel<CIN, COUT, TG, 1>
               : ((TG && a.ls_r >= 0) ? sc_umma_wgrad_kernel<CIN, COUT, TG, TG ? 2 : 0> : sc_umma_wgrad_kernel<CIN, COUT, TG, 0>);
   const size_t smem = (size_t)16 * 2048 + (size_t)16 * (COUT / 8) * 128 + (size_t)27 * COUT * 4 + 1024;
@@ -744,7 +997,6 @@ int launch_rows(const ScArgs& a, cudaStream_t st) {
   return (int)cudaGetLastError();
 }
 
-std::atomic<int> g_umma_rows{1};   // tuning knob "umma_rows": 0 = always the per-tap gather
 
 template <int CIN, int COUT, bool DGRAD>
 int launch(const ScArgs& a, long long nvox, cudaStream_t st) {
