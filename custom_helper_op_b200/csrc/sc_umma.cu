@@ -878,6 +878,20 @@ __global__ void __launch_bounds__(128) sc_umma_wgrad_rows_kernel(const ScArgs a,
   }
 }
 
+// Sum of element e over the slabs warp, warp + 8, warp + 16, ... in a fixed order, four loads in flight (the
+// slabs are 27*CIN*COUT*4 bytes apart, so every load is a separate DRAM/L2 access and one at a time is latency-bound).
+__device__ __forceinline__ float slab_column_sum(const float* col, size_t stride, int first, int nparts) {
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  int p = first;
+  for (; p + 24 < nparts; p += 32) {
+    const float a0 = col[(size_t)p * stride], a1 = col[(size_t)(p + 8) * stride], a2 = col[(size_t)(p + 16) * stride],
+                a3 = col[(size_t)(p + 24) * stride];
+    s0 += a0; s1 += a1; s2 += a2; s3 += a3;
+  }
+  for (; p < nparts; p += 8) s0 += col[(size_t)p * stride];
+  return (s0 + s1) + (s2 + s3);
+}
+
 // Sum of the per-CTA partial slabs in a fixed order (deterministic).  A block owns 32 consecutive
 // elements; its 8 warps each add every 8th slab with coalesced 128-byte reads, then the 8 warp sums are
 // added in warp order.  Element n_el is the default-value gradient.
@@ -887,8 +901,7 @@ __global__ void __launch_bounds__(256) sc_umma_wgrad_reduce(const float* part, i
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long e = (long long)blockIdx.x * 32 + lane;
   float s = 0.f;
-  if (e <= n_el)
-    for (int p = warp; p < nparts; p += 8) s += part[(size_t)p * (n_el + 1) + e];
+  if (e <= n_el) s = slab_column_sum(part + e, (size_t)(n_el + 1), warp, nparts);
   sm[warp][lane] = s;
   __syncthreads();
   if (warp == 0 && e <= n_el) {
@@ -908,8 +921,7 @@ __global__ void __launch_bounds__(256) sc_umma_wgrad_reduce_t(const float* part,
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long e = (long long)blockIdx.x * 32 + lane;
   float s = 0.f;
-  if (e < n_el)
-    for (int p = warp; p < nparts; p += 8) s += part[(size_t)p * (n_el + 1) + e];
+  if (e < n_el) s = slab_column_sum(part + e, (size_t)(n_el + 1), warp, nparts);
   sm[warp][lane] = s;
   __syncthreads();
   if (warp == 0 && e < n_el) {
