@@ -570,7 +570,7 @@ def main():
     ap.add_argument("--workload", default="c1_mvsnet")
     ap.add_argument("--shard", default="batch", choices=["batch", "depth"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--e2e-chunks", type=int, default=8, help="depth chunks of the host-buffer pipeline")
+    ap.add_argument("--e2e-chunks", type=int, default=2, help="depth chunks of the host-buffer pipeline")
     ap.add_argument("--profile", action="store_true",
                     help="device-timed loop only (no clock probe loop, e2e leg or CPU baseline): the command to run under ncu")
     args = ap.parse_args()
