@@ -14,7 +14,7 @@ Floating-point contract: ``-ffp-contract=off`` - every ``*``, ``+``, ``/`` in th
 is one correctly-rounded IEEE operation, evaluated in source order.  That is the arithmetic the
 CUDA kernels reproduce bit-for-bit for the projection (and, in strict mode, for everything).
 
-Usage: python oracle/build_ref.py [--reference /root/reference] [--quiet]
+Usage: python oracle/build_ref.py [--reference PATH_OF_THE_REFERENCE_CHECKOUT] [--quiet]
 Exit code 0 with the library built, 3 if the reference checkout is absent (nothing to do).
 """
 import argparse
