@@ -14,6 +14,7 @@
 
 namespace chop {
 extern std::atomic<int> g_use_umma;
+extern std::atomic<int> g_use_tile;
 void sc_umma_set_rows(int on);
 }
 
@@ -449,6 +450,7 @@ int chop_set_tuning(const char* name, int value) {
   if (!std::strcmp(name, "tuned")) { g_tuned = value; return CHOP_OK; }
   if (!std::strcmp(name, "umma")) { chop::g_use_umma = value; return CHOP_OK; }
   if (!std::strcmp(name, "umma_rows")) { chop::sc_umma_set_rows(value); return CHOP_OK; }
+  if (!std::strcmp(name, "tile")) { chop::g_use_tile = value; return CHOP_OK; }
   return CHOP_ERR_ATTR;
 }
 

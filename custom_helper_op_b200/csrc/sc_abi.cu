@@ -13,14 +13,19 @@
 
 namespace chop {
 std::atomic<int> g_use_umma{1};  // tuning knob "umma": 0 forces the generic kernels
+std::atomic<int> g_use_tile{1};  // tuning knob "tile": 0 = never the register-tiled float32 kernels
 }
 
 namespace {
 
 using chop::ScArgs;
 
+inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 int run_fwd(int dtype, const ScArgs& a, cudaStream_t st) {
   if (chop::g_use_umma.load() && chop::sc_umma_supported(dtype, a)) return chop::sc_umma_fwd_launch(a, st);
+  if (chop::g_use_tile.load() && chop::sc_tile_supported(dtype, a) && al16(a.images) && al16(a.output) && al16(a.filters))
+    return chop::sc_tile_fwd_launch(a, st);
   return chop::sc_fwd_simt_launch(dtype, a, st);
 }
 int run_wgrad(int dtype, const ScArgs& a, int nparts, cudaStream_t st) {
@@ -36,6 +41,8 @@ int run_dgrad(int dtype, const ScArgs& in, cudaStream_t st) {
   ScArgs a = in;
   a.pad_zero = 1;  // a padded tap contributes nothing to the image gradient (sparse_conv3d_fast_op.cc:306,321)
   if (chop::g_use_umma.load() && chop::sc_umma_supported(dtype, a)) return chop::sc_umma_dgrad_launch(a, st);
+  if (chop::g_use_tile.load() && chop::sc_tile_supported(dtype, a) && al16(a.out_grad) && al16(a.images_grad) && al16(a.filters))
+    return chop::sc_tile_gather_launch(a, st);
   return chop::sc_dgrad_simt_launch(dtype, a, st);
 }
 
@@ -165,6 +172,8 @@ int chop_sparse_conv3d_transpose_fwd(const chop_sc_desc* d, const void* images, 
   a.filters = filters; a.default_value = default_value; a.base_plane = base_plane;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (chop::g_use_umma.load() && chop::sc_umma_supported(d->dtype, a)) return chop::sc_umma_dgrad_launch(a, st);
+  if (chop::g_use_tile.load() && chop::sc_tile_supported(d->dtype, a) && al16(a.out_grad) && al16(a.images_grad) && al16(a.filters))
+    return chop::sc_tile_gather_launch(a, st);
   return chop::sc_tconv_simt_launch(d->dtype, a, st);
 }
 

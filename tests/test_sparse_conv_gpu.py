@@ -139,6 +139,41 @@ def test_tensor_core_kernel_band_depths(D):
     assert _lib.lib().chop_umma_timeouts() == 0
 
 
+TILE_CASES = [  # B, H, W, D, Cin, Cout, ksize, strides, dilations, virtual depth
+    (1, 7, 9, 9, 16, 16, (3, 3, 3), (1, 1, 1), (1, 1, 1), 20),
+    (2, 6, 8, 5, 8, 16, (3, 3, 3), (2, 2, 2), (1, 1, 1), 14),
+    (1, 8, 7, 6, 16, 8, (3, 3, 3), (2, 2, 1), (1, 1, 1), 14),
+    (1, 6, 6, 7, 32, 16, (3, 3, 3), (1, 1, 1), (2, 2, 2), 18),
+    (1, 5, 6, 4, 16, 32, (5, 3, 3), (1, 1, 1), (1, 1, 1), 12),
+    (1, 6, 5, 3, 32, 32, (2, 2, 1), (2, 2, 1), (1, 1, 1), 10),
+    (1, 5, 5, 1, 8, 8, (1, 1, 1), (1, 1, 1), (1, 1, 1), 6),
+]
+
+
+@pytest.mark.parametrize("case", TILE_CASES)
+def test_float32_register_tiled_kernels(case):
+    """float32 with 8/16/32 channels runs the register-tiled kernels (forward, image gradient); against the oracle and
+    against the one-thread-per-element kernels on the same inputs."""
+    from custom_helper_op_b200 import _lib
+    B, H, W, D, Cin, Cout, ks, st, dl, vd = case
+    images, filters, defv, bp, _ = make_case(19, B, H, W, D, Cin, Cout, ks, vd, np.float32)
+    want = oracle.sparse_conv3d_fwd(images, filters, defv, bp, st, dl, np.float32)
+    og = np.random.default_rng(20).uniform(-1, 1, want.shape).astype(np.float32)
+    ig_w, fg_w, dg_w = oracle.sparse_conv3d_bwd(images, filters, defv, bp, og, st, dl, True, np.float32)
+    res = {}
+    for tile in (1, 0):
+        try:
+            _lib.set_tuning("tile", tile)
+            res[tile] = run_gpu(images, filters, defv, bp, og, st, dl, True, torch.float32)
+        finally:
+            _lib.set_tuning("tile", 1)
+        out, ig, fg, dg = res[tile]
+        assert helpers.rel_err(out, want) <= 1e-5
+        assert helpers.rel_err(ig, ig_w) <= 1e-5
+        assert helpers.rel_err(fg, fg_w) <= 1e-5
+    assert helpers.rel_err(res[1][0], res[0][0]) <= 1e-6 and helpers.rel_err(res[1][1], res[0][1]) <= 1e-6
+
+
 def test_autograd_wrapper():
     images, filters, defv, bp, _ = make_case(11, 1, 6, 7, 5, 4, 3, (3, 3, 3), 12, np.float32)
     want = oracle.sparse_conv3d_fwd(images, filters, defv, bp, dtype=np.float32)

@@ -72,6 +72,27 @@ def test_transpose_bfloat16(strides, chans):
     assert _lib.lib().chop_umma_timeouts() == 0
 
 
+@pytest.mark.parametrize("strides", [(1, 1, 1), (2, 2, 2), (2, 2, 1)])
+@pytest.mark.parametrize("chans", [(16, 16), (8, 16), (32, 16)])
+@pytest.mark.parametrize("default", [0.0, None])
+def test_transpose_float32_register_tiled(strides, chans, default):
+    """float32 with 8/16/32 channels: the transposed forward and the image gradient run the register-tiled kernels."""
+    Cin, Cout = chans
+    B, H, W, D = 1, 9, 10, 6
+    images, filters, defv, bp = make_transpose_case(36, B, H, W, D, Cin, Cout, (3, 3, 3), strides, dtype=np.float32,
+                                                    default=default)
+    want = oracle.sparse_conv3d_transpose_fwd(images, filters, defv, bp, (H, W, D), strides, (1, 1, 1), np.float32)
+    og = np.random.default_rng(37).uniform(-1, 1, want.shape).astype(np.float32)
+    ig_w, fg_w = oracle.sparse_conv3d_transpose_bwd(images, filters, defv, bp, (H, W, D), og, strides, (1, 1, 1), False,
+                                                    np.float32)
+    out = ops.sparse_conv3d_transpose_forward(_t(images), _t(filters), float(defv), _t(bp), (H, W, D), strides)
+    ig, fg = ops.sparse_conv3d_transpose_backward(_t(images), _t(filters), float(defv), _t(bp), (H, W, D), _t(og), strides)
+    torch.cuda.synchronize()
+    assert helpers.rel_err(_np(out), want) <= 1e-5
+    assert helpers.rel_err(_np(ig), ig_w) <= 1e-5
+    assert helpers.rel_err(_np(fg), fg_w) <= 1e-5
+
+
 def test_transpose_autograd_and_up_down_round_trip():
     """The public function under autograd, and the shapes of a down-sampling convolution followed by the
     transposed one on the same base plane (the pair a coarse-to-fine network uses)."""
