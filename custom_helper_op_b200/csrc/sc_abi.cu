@@ -35,6 +35,9 @@ int run_wgrad(int dtype, const ScArgs& a, int nparts, cudaStream_t st) {
     if (nparts > ntiles) nparts = (int)ntiles;
     return chop::sc_umma_wgrad_launch(a, nparts, st);
   }
+  if (chop::g_use_tile.load() && chop::sc_tile_wgrad_supported(dtype, a, false) && al16(a.images) && al16(a.out_grad) &&
+      al16(a.workspace))
+    return chop::sc_tile_wgrad_launch(a, nparts, st);
   return chop::sc_wgrad_simt_launch_parts(dtype, a, nparts, st);
 }
 int run_dgrad(int dtype, const ScArgs& in, cudaStream_t st) {
@@ -200,6 +203,9 @@ int chop_sparse_conv3d_transpose_bwd(const chop_sc_desc* d, const void* images, 
   const int nparts = chop::sc_wgrad_parts(a.nvox_in);
   if (chop::g_use_umma.load() && chop::sc_umma_supported(d->dtype, a)) {
     if (int e = chop::sc_umma_twgrad_launch(a, nparts, st)) return e;
+  } else if (chop::g_use_tile.load() && chop::sc_tile_wgrad_supported(d->dtype, a, true) && al16(a.images) && al16(a.out_grad) &&
+             al16(a.workspace)) {
+    if (int e = chop::sc_tile_twgrad_launch(a, nparts, st)) return e;
   } else {
     if (int e = chop::sc_twgrad_simt_launch(d->dtype, a, nparts, st)) return e;
   }

@@ -127,6 +127,7 @@ __global__ void __launch_bounds__(WG_THREADS) sc_wgrad_partial(const ScArgs a, c
   long long* tapidx = reinterpret_cast<long long*>(smem_raw);             // [WG_TM][taps]
   ACC* gt = reinterpret_cast<ACC*>(tapidx + (size_t)WG_TM * taps);         // [WG_TM][WG_NC]
   ACC* red = gt + WG_TM * WG_NC;                                           // [WG_THREADS]
+  __shared__ int4 vox[WG_TM];                                              // b, row, column, depth of a staged voxel
   const T* img = static_cast<const T*>(a.images);
   const T* flt = static_cast<const T*>(a.filters);
   const T* og = static_cast<const T*>(a.out_grad);
@@ -147,19 +148,23 @@ __global__ void __launch_bounds__(WG_THREADS) sc_wgrad_partial(const ScArgs a, c
     for (long long vt = v0; vt < v1; vt += WG_TM) {
       const int tm = (int)min((long long)WG_TM, v1 - vt);
       __syncthreads();
-      for (int e = threadIdx.x; e < tm * taps; e += WG_THREADS) {
-        const int m = e / taps, t = e - m * taps;
-        long long v = vt + m;
+      // voxel coordinates once per voxel (64-bit divisions), then the tap table with 32-bit arithmetic
+      if (threadIdx.x < tm) {
+        long long v = vt + threadIdx.x;
         const int dz = (int)(v % d1); v /= d1;
         const int co = (int)(v % d2); v /= d2;
-        const int ro = (int)(v % d3);
-        const int b = (int)(v / d3);
-        const int fz = t % a.fd, fc = (t / a.fd) % a.fw, fr = t / a.fd / a.fw;
-        tapidx[m * taps + t] = TR ? sc_tap_t(a, b, ro, co, dz, fr, fc, fz) : sc_tap(a, b, ro, co, dz, fr, fc, fz);
+        vox[threadIdx.x] = make_int4((int)(v / d3), (int)(v % d3), co, dz);
       }
       for (int e = threadIdx.x; e < tm * WG_NC; e += WG_THREADS) {
         const int m = e / WG_NC, n = e - m * WG_NC;
         gt[e] = n < nn ? (ACC)ScIo<T>::ld(og + (vt + m) * NC + n0 + n) : (ACC)0;
+      }
+      __syncthreads();
+      for (int e = threadIdx.x; e < tm * taps; e += WG_THREADS) {
+        const int m = e / taps, t = e - m * taps;
+        const int4 c4 = vox[m];
+        const int fz = t % a.fd, fc = (t / a.fd) % a.fw, fr = t / a.fd / a.fw;
+        tapidx[e] = TR ? sc_tap_t(a, c4.x, c4.y, c4.z, c4.w, fr, fc, fz) : sc_tap(a, c4.x, c4.y, c4.z, c4.w, fr, fc, fz);
       }
       __syncthreads();
 #pragma unroll

@@ -246,7 +246,8 @@ CHOP_API int chop_version(void);
  * heuristic), "bwd_views" (source views per backward pass, 0 = heuristic), "tuned" (1 = use the compile-time-C
  * kernels where one exists, 0 = always the generic kernels), "umma" (1 = tensor-core manifold convolution
  * where supported, 0 = always the generic kernels), "umma_rows" (1 = the stride-1 tensor-core forward / image
- * gradient stages one copy per neighbour pixel, 0 = one per tap).  Returns CHOP_ERR_ATTR for an unknown name.
+ * gradient stages one copy per neighbour pixel, 0 = one per tap), "tile" (1 = register-tiled float32 manifold
+ * convolution kernels where supported, 0 = the one-thread-per-element kernels).  Returns CHOP_ERR_ATTR for an unknown name.
  * Process-wide; not part of the reference surface. */
 CHOP_API int chop_set_tuning(const char *name, int value);
 
