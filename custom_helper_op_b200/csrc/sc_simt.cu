@@ -233,17 +233,19 @@ __global__ void sc_wgrad_reduce_t(const ACC* part, int nparts, int taps, int Cin
 // placed into the fine band [B,h*sr,w*sc,d*sd,C] whose first plane per pixel is base_plane; a fine voxel
 // receives a coarse value iff its row, column and absolute depth are multiples of the strides, else zero.
 // One thread per 16-byte piece of a fine voxel's channel vector (E elements).
-template <typename T, int E>
+// I: index type of the flattened thread index - unsigned where the element count allows it (64-bit divisions cost
+// several times the copy itself)
+template <typename T, int E, typename I>
 __global__ void __launch_bounds__(256) sc_pad_fwd(const T* img, const int* bp, T* out, int B, int h, int w, int d, int C,
                                                    int sr, int sc, int sd) {
   const int cv = C / E;
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const I idx = (I)blockIdx.x * blockDim.x + threadIdx.x;
   const int oh = h * sr, ow = w * sc, od = d * sd;
-  if (idx >= (long long)B * oh * ow * od * cv) return;
+  if ((long long)idx >= (long long)B * oh * ow * od * cv) return;
   const int q = (int)(idx % cv);
-  long long v = idx / cv;
+  I v = idx / cv;
   int z = (int)(v % od);
-  const long long pos = v / od;
+  const I pos = v / od;
   const int x = (int)(pos % ow), y = (int)((pos / ow) % oh), b = (int)(pos / ow / oh);
   const int p0 = __ldg(bp + pos);
   z = z + p0 - ((p0 + sd - 1) / sd) * sd;
@@ -253,28 +255,28 @@ __global__ void __launch_bounds__(256) sc_pad_fwd(const T* img, const int* bp, T
   for (int i = 0; i < E; ++i) val.e[i] = T(0);
   if ((y % sr) == 0 && (x % sc) == 0 && (z % sd) == 0)   // z > -sd, so a negative z is never a multiple
     val = *reinterpret_cast<const Vec*>(img + ((((long long)b * h + y / sr) * w + x / sc) * d + z / sd) * C + q * E);
-  *reinterpret_cast<Vec*>(out + v * C + q * E) = val;
+  *reinterpret_cast<Vec*>(out + (long long)v * C + q * E) = val;
 }
 
 // SparsePadGrad: every coarse voxel reads the fine voxel it was copied to - pixel (y*sr, x*sc), plane
 // z*sd + ceil(bp/sd)*sd - bp.  (The reference kernel, :82-104, forms the fine pixel index from the coarse
 // row and column before scaling them and so reads another pixel when sr or sc exceeds 1.)
-template <typename T, int E>
+template <typename T, int E, typename I>
 __global__ void __launch_bounds__(256) sc_pad_bwd(const T* og, const int* bp, T* igrad, int B, int h, int w, int d, int C,
                                                    int sr, int sc, int sd) {
   const int cv = C / E;
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (long long)B * h * w * d * cv) return;
+  const I idx = (I)blockIdx.x * blockDim.x + threadIdx.x;
+  if ((long long)idx >= (long long)B * h * w * d * cv) return;
   const int q = (int)(idx % cv);
-  long long v = idx / cv;
+  I v = idx / cv;
   const int z = (int)(v % d);
-  const long long pc = v / d;
+  const I pc = v / d;
   const int x = (int)(pc % w), y = (int)((pc / w) % h), b = (int)(pc / w / h);
   const long long pos = ((long long)b * h * sr + (long long)y * sr) * ((long long)w * sc) + (long long)x * sc;
   const int p0 = __ldg(bp + pos);
   const int zf = z * sd + ((p0 + sd - 1) / sd) * sd - p0;
   struct alignas(sizeof(T) * E) Vec { T e[E]; };
-  *reinterpret_cast<Vec*>(igrad + v * C + q * E) =
+  *reinterpret_cast<Vec*>(igrad + (long long)v * C + q * E) =
       *reinterpret_cast<const Vec*>(og + (pos * ((long long)d * sd) + zf) * C + q * E);
 }
 
@@ -288,13 +290,18 @@ int pad_t(bool grad, const void* src, const int* bp, void* dst, int B, int h, in
   const unsigned grid = (unsigned)((n + 255) / 256);
   const T* s = static_cast<const T*>(src);
   T* o = static_cast<T*>(dst);
+  const bool small = n + 256 < 0xffffffffLL;   // the thread index (rounded up to the grid) fits 32 bits
+#define CHOP_PAD_GO(K, EE)                                                                              \
+  do {                                                                                                  \
+    if (small) K<T, EE, unsigned><<<grid, 256, 0, st>>>(s, bp, o, B, h, w, d, C, sr, sc, sd);           \
+    else K<T, EE, long long><<<grid, 256, 0, st>>>(s, bp, o, B, h, w, d, C, sr, sc, sd);                \
+  } while (0)
   if (grad) {
-    if (vec) sc_pad_bwd<T, EV><<<grid, 256, 0, st>>>(s, bp, o, B, h, w, d, C, sr, sc, sd);
-    else sc_pad_bwd<T, 1><<<grid, 256, 0, st>>>(s, bp, o, B, h, w, d, C, sr, sc, sd);
+    if (vec) CHOP_PAD_GO(sc_pad_bwd, EV); else CHOP_PAD_GO(sc_pad_bwd, 1);
   } else {
-    if (vec) sc_pad_fwd<T, EV><<<grid, 256, 0, st>>>(s, bp, o, B, h, w, d, C, sr, sc, sd);
-    else sc_pad_fwd<T, 1><<<grid, 256, 0, st>>>(s, bp, o, B, h, w, d, C, sr, sc, sd);
+    if (vec) CHOP_PAD_GO(sc_pad_fwd, EV); else CHOP_PAD_GO(sc_pad_fwd, 1);
   }
+#undef CHOP_PAD_GO
   return (int)cudaGetLastError();
 }
 
