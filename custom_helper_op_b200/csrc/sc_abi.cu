@@ -25,7 +25,7 @@ inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) =
 int run_fwd(int dtype, const ScArgs& a, cudaStream_t st) {
   if (chop::g_use_umma.load() && chop::sc_umma_supported(dtype, a)) return chop::sc_umma_fwd_launch(a, st);
   if (chop::g_use_tile.load() && chop::sc_tile_supported(dtype, a) && al16(a.images) && al16(a.output) && al16(a.filters))
-    return chop::sc_tile_fwd_launch(a, st);
+    return chop::sc_tile_fwd_launch(dtype, a, st);
   return chop::sc_fwd_simt_launch(dtype, a, st);
 }
 int run_wgrad(int dtype, const ScArgs& a, int nparts, cudaStream_t st) {
@@ -37,7 +37,7 @@ int run_wgrad(int dtype, const ScArgs& a, int nparts, cudaStream_t st) {
   }
   if (chop::g_use_tile.load() && chop::sc_tile_wgrad_supported(dtype, a, false) && al16(a.images) && al16(a.out_grad) &&
       al16(a.workspace))
-    return chop::sc_tile_wgrad_launch(a, nparts, st);
+    return chop::sc_tile_wgrad_launch(dtype, a, nparts, st);
   return chop::sc_wgrad_simt_launch_parts(dtype, a, nparts, st);
 }
 int run_dgrad(int dtype, const ScArgs& in, cudaStream_t st) {
@@ -45,7 +45,7 @@ int run_dgrad(int dtype, const ScArgs& in, cudaStream_t st) {
   a.pad_zero = 1;  // a padded tap contributes nothing to the image gradient (sparse_conv3d_fast_op.cc:306,321)
   if (chop::g_use_umma.load() && chop::sc_umma_supported(dtype, a)) return chop::sc_umma_dgrad_launch(a, st);
   if (chop::g_use_tile.load() && chop::sc_tile_supported(dtype, a) && al16(a.out_grad) && al16(a.images_grad) && al16(a.filters))
-    return chop::sc_tile_gather_launch(a, st);
+    return chop::sc_tile_gather_launch(dtype, a, st);
   return chop::sc_dgrad_simt_launch(dtype, a, st);
 }
 
@@ -176,7 +176,7 @@ int chop_sparse_conv3d_transpose_fwd(const chop_sc_desc* d, const void* images, 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (chop::g_use_umma.load() && chop::sc_umma_supported(d->dtype, a)) return chop::sc_umma_dgrad_launch(a, st);
   if (chop::g_use_tile.load() && chop::sc_tile_supported(d->dtype, a) && al16(a.out_grad) && al16(a.images_grad) && al16(a.filters))
-    return chop::sc_tile_gather_launch(a, st);
+    return chop::sc_tile_gather_launch(d->dtype, a, st);
   return chop::sc_tconv_simt_launch(d->dtype, a, st);
 }
 
@@ -205,7 +205,7 @@ int chop_sparse_conv3d_transpose_bwd(const chop_sc_desc* d, const void* images, 
     if (int e = chop::sc_umma_twgrad_launch(a, nparts, st)) return e;
   } else if (chop::g_use_tile.load() && chop::sc_tile_wgrad_supported(d->dtype, a, true) && al16(a.images) && al16(a.out_grad) &&
              al16(a.workspace)) {
-    if (int e = chop::sc_tile_twgrad_launch(a, nparts, st)) return e;
+    if (int e = chop::sc_tile_twgrad_launch(d->dtype, a, nparts, st)) return e;
   } else {
     if (int e = chop::sc_twgrad_simt_launch(d->dtype, a, nparts, st)) return e;
   }

@@ -21,11 +21,11 @@ int sc_umma_dgrad_launch(const ScArgs& a, cudaStream_t st);
 int sc_umma_wgrad_launch(const ScArgs& a, int nparts, cudaStream_t st);
 int sc_umma_twgrad_launch(const ScArgs& a, int nparts, cudaStream_t st);
 bool sc_tile_supported(int dtype, const ScArgs& a);
-int sc_tile_fwd_launch(const ScArgs& a, cudaStream_t st);
+int sc_tile_fwd_launch(int dtype, const ScArgs& a, cudaStream_t st);
 bool sc_tile_wgrad_supported(int dtype, const ScArgs& a, bool transposed);
-int sc_tile_wgrad_launch(const ScArgs& a, int nparts, cudaStream_t st);
-int sc_tile_twgrad_launch(const ScArgs& a, int nparts, cudaStream_t st);
-int sc_tile_gather_launch(const ScArgs& a, cudaStream_t st);
+int sc_tile_wgrad_launch(int dtype, const ScArgs& a, int nparts, cudaStream_t st);
+int sc_tile_twgrad_launch(int dtype, const ScArgs& a, int nparts, cudaStream_t st);
+int sc_tile_gather_launch(int dtype, const ScArgs& a, cudaStream_t st);
 int sc_umma_timeouts();
 void sc_umma_set_rows(int on);
 size_t sc_wgrad_workspace_bytes(int dtype, int taps, int Cin, int Cout, long long nvox_out);

@@ -1,5 +1,7 @@
-// Register-tiled CUDA-core manifold convolution for float32 data (the reference's own dtype): forward, gather-form
-// image gradient and transposed forward, any filter size / stride / dilation, 8, 16 or 32 channels on either side.
+// Register-tiled CUDA-core manifold convolution for float32 data (the reference's own dtype) and for bfloat16 storage
+// with float32 accumulation where the tensor-core kernels do not apply (8 channels, other filter sizes, dilation):
+// forward, gather-form image gradient, transposed forward and filter gradient, any filter size / stride / dilation,
+// 8, 16 or 32 channels on either side.
 //
 // One thread owns four consecutive voxels (two for 32 output channels) and all output channels: per tap it loads
 // their gathered channel vectors once (16-byte loads) and multiplies them with the tap's [gathered x produced] weight block, which the CTA
@@ -13,6 +15,28 @@
 namespace chop {
 namespace {
 
+// Storage type T: float, or bfloat16 widened to float on load and rounded on store (float32 accumulation).
+template <typename T> struct TileIo;
+template <> struct TileIo<float> {
+  static __device__ __forceinline__ float ld1(const float* p) { return __ldg(p); }
+  static __device__ __forceinline__ float4 ld4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+  static __device__ __forceinline__ void st4(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+  }
+};
+template <> struct TileIo<__nv_bfloat16> {
+  static __device__ __forceinline__ float ld1(const __nv_bfloat16* p) { return ScIo<__nv_bfloat16>::ld(p); }
+  static __device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
+    const uint2 u = __ldg(reinterpret_cast<const uint2*>(p));
+    return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16),
+                       __uint_as_float(u.y & 0xffff0000u));
+  }
+  static __device__ __forceinline__ void st4(__nv_bfloat16* p, float a, float b, float c, float d) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const unsigned*>(&lo), *reinterpret_cast<const unsigned*>(&hi));
+  }
+};
+
 // FORM 0: forward - voxels of the output grid gather the input grid (sc_tap); weights w[t][ci][co].
 // FORM 1: gather form - voxels of the fine grid gather the coarse grid (sc_tap_t); the gathered tensor has Cout
 //         channels, the produced one Cin, weights flipped: w'[t][co][ci] = filter[taps-1-t][ci][co].
@@ -21,17 +45,17 @@ namespace {
 template <int NCH>
 struct TileVpt { static constexpr int v = NCH <= 16 ? 4 : 2; };   // 4*NCH accumulators beyond 16 channels would spill
 
-template <int KCH, int NCH, int FORM>
+template <typename T, int KCH, int NCH, int FORM>
 __global__ void __launch_bounds__(128, 3) sc_tile_kernel(const ScArgs a, const long long nvox) {
   constexpr int VPT = TileVpt<NCH>::v;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int taps = a.fh * a.fw * a.fd;
   float* ws = reinterpret_cast<float*>(smem_raw);          // [taps][KCH][NCH]
   float* wsum = ws + (size_t)taps * KCH * NCH;              // [taps][NCH]
-  const float* flt = static_cast<const float*>(a.filters);
+  const T* flt = static_cast<const T*>(a.filters);
   for (int e = threadIdx.x; e < taps * KCH * NCH; e += blockDim.x) {
     const int n = e % NCH, k = (e / NCH) % KCH, t = e / (NCH * KCH);
-    ws[e] = FORM == 0 ? __ldg(flt + e) : __ldg(flt + ((size_t)(taps - 1 - t) * NCH + n) * KCH + k);
+    ws[e] = FORM == 0 ? TileIo<T>::ld1(flt + e) : TileIo<T>::ld1(flt + ((size_t)(taps - 1 - t) * NCH + n) * KCH + k);
   }
   __syncthreads();
   for (int e = threadIdx.x; e < taps * NCH; e += blockDim.x) {
@@ -42,9 +66,9 @@ __global__ void __launch_bounds__(128, 3) sc_tile_kernel(const ScArgs a, const l
   }
   __syncthreads();
 
-  const float* src = static_cast<const float*>(FORM == 0 ? a.images : a.out_grad);
-  float* dst = static_cast<float*>(FORM == 0 ? a.output : a.images_grad);
-  const float pad = a.pad_zero ? 0.f : __ldg(static_cast<const float*>(a.default_value));
+  const T* src = static_cast<const T*>(FORM == 0 ? a.images : a.out_grad);
+  T* dst = static_cast<T*>(FORM == 0 ? a.output : a.images_grad);
+  const float pad = a.pad_zero ? 0.f : TileIo<T>::ld1(static_cast<const T*>(a.default_value));
   const int d1 = FORM == 0 ? a.oD : a.D, d2 = FORM == 0 ? a.oW : a.W, d3 = FORM == 0 ? a.oH : a.H;
   const long long ngroups = (nvox + VPT - 1) / VPT;
 
@@ -99,7 +123,7 @@ __global__ void __launch_bounds__(128, 3) sc_tile_kernel(const ScArgs a, const l
             for (int u = 0; u < VPT; ++u) {
               // a voxel whose tap is padding got its share above: it adds zero here
               float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (at[u] >= 0) x = __ldg(reinterpret_cast<const float4*>(src + at[u] * KCH) + k4);
+              if (at[u] >= 0) x = TileIo<T>::ld4(src + at[u] * KCH + k4 * 4);
               xs[u][0] = x.x; xs[u][1] = x.y; xs[u][2] = x.z; xs[u][3] = x.w;
             }
 #pragma unroll
@@ -122,9 +146,10 @@ __global__ void __launch_bounds__(128, 3) sc_tile_kernel(const ScArgs a, const l
 #pragma unroll
     for (int u = 0; u < VPT; ++u) {
       if (!live[u]) continue;
-      float4* o = reinterpret_cast<float4*>(dst + (vbase + u) * NCH);
+      T* o = dst + (vbase + u) * NCH;
 #pragma unroll
-      for (int n4 = 0; n4 < NCH / 4; ++n4) o[n4] = make_float4(acc[u][n4 * 4], acc[u][n4 * 4 + 1], acc[u][n4 * 4 + 2], acc[u][n4 * 4 + 3]);
+      for (int n4 = 0; n4 < NCH / 4; ++n4)
+        TileIo<T>::st4(o + n4 * 4, acc[u][n4 * 4], acc[u][n4 * 4 + 1], acc[u][n4 * 4 + 2], acc[u][n4 * 4 + 3]);
     }
   }
 }
@@ -139,7 +164,7 @@ __global__ void __launch_bounds__(128, 3) sc_tile_kernel(const ScArgs a, const l
 // writes element [tap][co][ci] to filter_grad[taps-1-tap][ci][co].
 constexpr int WT = 32;   // voxels per staging step
 
-template <int KCH, int NCH, bool TR>
+template <typename T, int KCH, int NCH, bool TR>
 __global__ void __launch_bounds__(256) sc_wgrad_tile_kernel(const ScArgs a, const int vox_per_cta) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int NT = NCH < 16 ? NCH : 16;                   // upstream channels per sweep
@@ -152,19 +177,19 @@ __global__ void __launch_bounds__(256) sc_wgrad_tile_kernel(const ScArgs a, cons
   int4* vox = reinterpret_cast<int4*>(red + blockDim.x);                  // [WT]: b, row, column, depth of a staged voxel
   int3* tapf = reinterpret_cast<int3*>(vox + WT);                         // [taps]: fr, fc, fz
   for (int t = threadIdx.x; t < taps; t += blockDim.x) tapf[t] = make_int3(t / a.fd / a.fw, (t / a.fd) % a.fw, t % a.fd);
-  const float* img = static_cast<const float*>(a.images);
-  const float* og = static_cast<const float*>(a.out_grad);
+  const T* img = static_cast<const T*>(a.images);
+  const T* og = static_cast<const T*>(a.out_grad);
   const bool dyn = !TR && a.dynamic_default;
   if (dyn) {
-    const float* flt = static_cast<const float*>(a.filters);
+    const T* flt = static_cast<const T*>(a.filters);
     for (int e = threadIdx.x; e < taps * NCH; e += blockDim.x) {
       const int n = e % NCH, t = e / NCH;
       float s = 0.f;
-      for (int k = 0; k < KCH; ++k) s += __ldg(flt + ((size_t)t * KCH + k) * NCH + n);
+      for (int k = 0; k < KCH; ++k) s += TileIo<T>::ld1(flt + ((size_t)t * KCH + k) * NCH + n);
       wsum[e] = s;
     }
   }
-  const float defv = __ldg(static_cast<const float*>(a.default_value));
+  const float defv = TileIo<T>::ld1(static_cast<const T*>(a.default_value));
   const float4 pad4 = make_float4(defv, defv, defv, defv);
   const long long nvox = TR ? a.nvox_in : a.nvox_out;
   const int d1 = TR ? a.D : a.oD, d2 = TR ? a.W : a.oW, d3 = TR ? a.H : a.oH;
@@ -194,7 +219,7 @@ __global__ void __launch_bounds__(256) sc_wgrad_tile_kernel(const ScArgs a, cons
         const int cc = (int)(v % d2); v /= d2;
         vox[threadIdx.x] = make_int4((int)(v / d3), (int)(v % d3), cc, dz);
       }
-      for (int e = threadIdx.x; e < tm * NCH; e += blockDim.x) gt[e] = __ldg(og + vt * NCH + e);
+      for (int e = threadIdx.x; e < tm * NCH; e += blockDim.x) gt[e] = TileIo<T>::ld1(og + vt * NCH + e);
       __syncthreads();
       for (int e = threadIdx.x; e < tm * taps; e += blockDim.x) {
         const int m = e / taps, t = e - m * taps;
@@ -212,7 +237,7 @@ __global__ void __launch_bounds__(256) sc_wgrad_tile_kernel(const ScArgs a, cons
           for (int u = 0; u < 4; ++u) at[u] = m0 + u < tm ? tapidx[(m0 + u) * taps + my_tap] : -2;   // -2: no voxel
 #pragma unroll
           for (int u = 0; u < 4; ++u)
-            x[u] = at[u] >= 0 ? __ldg(reinterpret_cast<const float4*>(img + at[u] * KCH + my_k))
+            x[u] = at[u] >= 0 ? TileIo<T>::ld4(img + at[u] * KCH + my_k)
                               : (at[u] == -1 ? pad4 : make_float4(0.f, 0.f, 0.f, 0.f));
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
@@ -285,12 +310,12 @@ __global__ void __launch_bounds__(256) wgrad_tile_reduce(const float* part, int 
   filter_grad[((long long)(taps - 1 - t) * NCH + n) * KCH + k] = s;
 }
 
-template <int KCH, int NCH, bool TR>
+template <typename T, int KCH, int NCH, bool TR>
 int launch_wgrad(const ScArgs& a, int nparts, cudaStream_t st) {
   const int taps = a.fh * a.fw * a.fd;
   const int K4 = taps * KCH / 4;
-  int threads = (K4 + 31) / 32 * 32;
-  if (threads < 64) threads = 64;
+  int threads = 64;   // a power of two (the block sum of the default-value gradient halves the block repeatedly)
+  while (threads < K4) threads <<= 1;
   if (threads > 256) return -4;
   const long long nvox = TR ? a.nvox_in : a.nvox_out;
   if (nparts > (nvox + WT - 1) / WT) nparts = (int)((nvox + WT - 1) / WT);
@@ -298,7 +323,7 @@ int launch_wgrad(const ScArgs& a, int nparts, cudaStream_t st) {
   nparts = (int)((nvox + vox_per_cta - 1) / vox_per_cta);   // every launched CTA owns at least one voxel and writes its slab
   const size_t smem = (size_t)WT * taps * sizeof(long long) + ((size_t)WT * NCH + (size_t)taps * NCH + threads) * sizeof(float) +
                       WT * sizeof(int4) + (size_t)taps * sizeof(int3);
-  auto k = sc_wgrad_tile_kernel<KCH, NCH, TR>;
+  auto k = sc_wgrad_tile_kernel<T, KCH, NCH, TR>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -313,22 +338,22 @@ int launch_wgrad(const ScArgs& a, int nparts, cudaStream_t st) {
   return (int)cudaGetLastError();
 }
 
-template <bool TR>
+template <typename T, bool TR>
 int dispatch_wgrad(const ScArgs& a, int nparts, cudaStream_t st) {
   const int kch = TR ? a.Cout : a.Cin, nch = TR ? a.Cin : a.Cout;
 #define CHOP_TILE_CASE(K, N) \
-  if (kch == K && nch == N) return launch_wgrad<K, N, TR>(a, nparts, st);
+  if (kch == K && nch == N) return launch_wgrad<T, K, N, TR>(a, nparts, st);
   CHOP_TILE_CASE(8, 8) CHOP_TILE_CASE(8, 16) CHOP_TILE_CASE(16, 8) CHOP_TILE_CASE(16, 16) CHOP_TILE_CASE(16, 32)
   CHOP_TILE_CASE(32, 16) CHOP_TILE_CASE(32, 32)
 #undef CHOP_TILE_CASE
   return -4;
 }
 
-template <int KCH, int NCH, int FORM>
+template <typename T, int KCH, int NCH, int FORM>
 int launch(const ScArgs& a, cudaStream_t st) {
   const int taps = a.fh * a.fw * a.fd;
   const size_t smem = ((size_t)taps * KCH * NCH + (size_t)taps * NCH) * sizeof(float);
-  auto k = sc_tile_kernel<KCH, NCH, FORM>;
+  auto k = sc_tile_kernel<T, KCH, NCH, FORM>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -342,11 +367,11 @@ int launch(const ScArgs& a, cudaStream_t st) {
   return (int)cudaGetLastError();
 }
 
-template <int FORM>
+template <typename T, int FORM>
 int dispatch(const ScArgs& a, cudaStream_t st) {
   const int kch = FORM == 0 ? a.Cin : a.Cout, nch = FORM == 0 ? a.Cout : a.Cin;
 #define CHOP_TILE_CASE(K, N) \
-  if (kch == K && nch == N) return launch<K, N, FORM>(a, st);
+  if (kch == K && nch == N) return launch<T, K, N, FORM>(a, st);
   CHOP_TILE_CASE(8, 8) CHOP_TILE_CASE(8, 16) CHOP_TILE_CASE(16, 8) CHOP_TILE_CASE(16, 16) CHOP_TILE_CASE(16, 32)
   CHOP_TILE_CASE(32, 16) CHOP_TILE_CASE(32, 32)
 #undef CHOP_TILE_CASE
@@ -355,10 +380,10 @@ int dispatch(const ScArgs& a, cudaStream_t st) {
 
 }  // namespace
 
-// float32 data, both channel counts in {8,16,32} (one of the instantiated pairs), weights + sums within 160 KB of
-// shared memory, 16-byte aligned tensors (checked by the caller)
+// float32 or bfloat16 data, both channel counts in {8,16,32} (one of the instantiated pairs), weights + sums within
+// 160 KB of shared memory, 16-byte aligned tensors (checked by the caller)
 bool sc_tile_supported(int dtype, const ScArgs& a) {
-  if (dtype != 0) return false;
+  if (dtype != 0 && dtype != 2) return false;
   const int taps = a.fh * a.fw * a.fd;
   if (((size_t)taps * a.Cin * a.Cout + (size_t)taps * (a.Cin > a.Cout ? a.Cin : a.Cout)) * 4 > 160 * 1024) return false;
   const int c[2] = {a.Cin, a.Cout};
@@ -372,12 +397,20 @@ bool sc_tile_wgrad_supported(int dtype, const ScArgs& a, bool transposed) {
   if (!sc_tile_supported(dtype, a)) return false;
   return (long long)a.fh * a.fw * a.fd * (transposed ? a.Cout : a.Cin) / 4 <= 256;
 }
-int sc_tile_wgrad_launch(const ScArgs& a, int nparts, cudaStream_t st) { return dispatch_wgrad<false>(a, nparts, st); }
-int sc_tile_twgrad_launch(const ScArgs& a, int nparts, cudaStream_t st) { return dispatch_wgrad<true>(a, nparts, st); }
+int sc_tile_wgrad_launch(int dtype, const ScArgs& a, int nparts, cudaStream_t st) {
+  return dtype == 0 ? dispatch_wgrad<float, false>(a, nparts, st) : dispatch_wgrad<__nv_bfloat16, false>(a, nparts, st);
+}
+int sc_tile_twgrad_launch(int dtype, const ScArgs& a, int nparts, cudaStream_t st) {
+  return dtype == 0 ? dispatch_wgrad<float, true>(a, nparts, st) : dispatch_wgrad<__nv_bfloat16, true>(a, nparts, st);
+}
 
-int sc_tile_fwd_launch(const ScArgs& a, cudaStream_t st) { return dispatch<0>(a, st); }
+int sc_tile_fwd_launch(int dtype, const ScArgs& a, cudaStream_t st) {
+  return dtype == 0 ? dispatch<float, 0>(a, st) : dispatch<__nv_bfloat16, 0>(a, st);
+}
 // gather form: a.out_grad = the coarse tensor (Cout channels), a.images_grad = the fine result (Cin channels);
 // a.pad_zero selects the image gradient (1) or the transposed forward (0)
-int sc_tile_gather_launch(const ScArgs& a, cudaStream_t st) { return dispatch<1>(a, st); }
+int sc_tile_gather_launch(int dtype, const ScArgs& a, cudaStream_t st) {
+  return dtype == 0 ? dispatch<float, 1>(a, st) : dispatch<__nv_bfloat16, 1>(a, st);
+}
 
 }  // namespace chop

@@ -171,7 +171,32 @@ def test_float32_register_tiled_kernels(case):
         assert helpers.rel_err(out, want) <= 1e-5
         assert helpers.rel_err(ig, ig_w) <= 1e-5
         assert helpers.rel_err(fg, fg_w) <= 1e-5
+        assert abs(float(dg) - float(dg_w)) <= 1e-5 * max(1.0, abs(float(dg_w)))
     assert helpers.rel_err(res[1][0], res[0][0]) <= 1e-6 and helpers.rel_err(res[1][1], res[0][1]) <= 1e-6
+
+
+@pytest.mark.parametrize("case", TILE_CASES[1:])
+def test_bfloat16_register_tiled_kernels(case):
+    """bf16 storage where the tensor-core kernels do not apply (8 channels, dilation, other filter sizes): the
+    register-tiled kernels with float32 accumulation against the oracle on the bf16-rounded inputs."""
+    from custom_helper_op_b200 import _lib
+    B, H, W, D, Cin, Cout, ks, st, dl, vd = case
+    images, filters, defv, bp, _ = make_case(21, B, H, W, D, Cin, Cout, ks, vd, np.float32)
+    r = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(torch.bfloat16).float().numpy()
+    images, filters = r(images - 0.5), r(filters * 0.3)
+    defv = float(r(np.array([defv]))[0])
+    want = oracle.sparse_conv3d_fwd(images, filters, defv, bp, st, dl, np.float32)
+    og = r(np.random.default_rng(22).uniform(-1, 1, want.shape))
+    ig_w, fg_w, dg_w = oracle.sparse_conv3d_bwd(images, filters, defv, bp, og, st, dl, True, np.float32)
+    try:
+        _lib.set_tuning("umma", 0)     # the (16|32)-channel 3x3x3 cases would otherwise take the tensor-core path
+        out, ig, fg, dg = run_gpu(images, filters, defv, bp, og, st, dl, True, torch.bfloat16)
+    finally:
+        _lib.set_tuning("umma", 1)
+    assert helpers.rel_err(out, want) <= 1e-2
+    assert helpers.rel_err(ig, ig_w) <= 1e-2
+    assert helpers.rel_err(fg, fg_w) <= 2e-3
+    assert abs(float(dg) - float(dg_w)) <= 2e-3 * max(1.0, abs(float(dg_w)))
 
 
 def test_autograd_wrapper():

@@ -42,9 +42,10 @@ def test_transpose_forward_and_gradient(case, dtype, default):
 
 
 @pytest.mark.parametrize("strides", [(1, 1, 1), (2, 2, 2), (2, 2, 1)])
-@pytest.mark.parametrize("chans", [(16, 16), (32, 16), (16, 32)])
+@pytest.mark.parametrize("chans", [(16, 16), (32, 16), (16, 32), (8, 16), (8, 8)])
 def test_transpose_bfloat16(strides, chans):
-    """bf16 storage, float32 accumulation; 16/32-channel 3x3x3 filters run on the tensor cores."""
+    """bf16 storage, float32 accumulation; 16/32-channel 3x3x3 filters run on the tensor cores, 8 channels on the
+    register-tiled kernels."""
     Cin, Cout = chans
     B, H, W, D = 1, 10, 12, 8
     images, filters, defv, bp = make_transpose_case(33, B, H, W, D, Cin, Cout, (3, 3, 3), strides, dtype=np.float32)
