@@ -89,8 +89,11 @@ int validate(const chop_cv_desc* d, CvArgs* a, Typed* ty) {
 
 // CostVolume MEAN (fused arithmetic) with a common channel count runs the compile-time-C kernels of
 // cv_tuned.cuh, which use four channels per lane for float32 and bfloat16 features alike.
-bool tuned_eligible(const chop_cv_desc* d, const CvArgs& a) {
-  if (!g_tuned.load() || d->reduce != CHOP_REDUCE_MEAN || !(d->dtype == CHOP_F32 || d->dtype == CHOP_BF16)) return false;
+// The backward kernels also exist for MIN.
+bool tuned_eligible(const chop_cv_desc* d, const CvArgs& a, bool backward) {
+  if (!g_tuned.load() || !(d->dtype == CHOP_F32 || d->dtype == CHOP_BF16)) return false;
+  const bool min_ok = backward;
+  if (d->reduce != CHOP_REDUCE_MEAN && !min_ok) return false;
   if (d->kind == CHOP_COST_VOLUME || d->kind == CHOP_COST_AGGREGATE) return a.C == 8 || a.C == 16 || a.C == 32 || a.C == 64;
   if (d->kind == CHOP_COST_VOLUME_V2) {
     const int sub = a.C / a.G;  // channels per group: a lane's four channels must cover whole groups
@@ -100,12 +103,12 @@ bool tuned_eligible(const chop_cv_desc* d, const CvArgs& a) {
 }
 
 // Channel slice per lane and lanes per pixel.
-int plan_lanes(const chop_cv_desc* d, const CvArgs& a, int* cpl, int* lgl, bool strict) {
+int plan_lanes(const chop_cv_desc* d, const CvArgs& a, int* cpl, int* lgl, bool strict, bool backward) {
   int c = 1;
   if (d->dtype == CHOP_F32 && a.C % 4 == 0) c = 4;
   if (d->dtype == CHOP_F64 && a.C % 2 == 0) c = 2;
   if (d->dtype == CHOP_BF16 && a.C % 8 == 0) c = 8;
-  if (!strict && tuned_eligible(d, a)) c = 4;
+  if (!strict && tuned_eligible(d, a, backward)) c = 4;
   const int lanes = (a.C + c - 1) / c;
   if (lanes > 32) return CHOP_ERR_UNSUPPORTED;
   *cpl = c;
@@ -182,7 +185,7 @@ int chop_cost_volume_fwd(const chop_cv_desc* d, const void* ref, const void* src
     return chop::cv3_fwd_launch(d->dtype, d->reduce == CHOP_REDUCE_MIN, a, static_cast<cudaStream_t>(stream));
   }
   int cpl, lgl;
-  if (int e = plan_lanes(d, a, &cpl, &lgl, (d->flags & CHOP_FLAG_STRICT) != 0)) return e;
+  if (int e = plan_lanes(d, a, &cpl, &lgl, (d->flags & CHOP_FLAG_STRICT) != 0, false)) return e;
   const int mode = d->reduce == CHOP_REDUCE_MIN ? 2 : ((d->flags & CHOP_FLAG_STRICT) ? 1 : 0);
 
   CvPlan p;
@@ -205,6 +208,8 @@ int chop_cost_volume_fwd(const chop_cv_desc* d, const void* ref, const void* src
       } else if (mode == 0 && d->kind == CHOP_COST_AGGREGATE) {
         p.fwd.group_mode = chop::GROUP_XOR;
         p.fwd.run = LG;
+      } else if (d->kind == CHOP_COST_AGGREGATE) {
+        p.fwd.group_mode = chop::GROUP_ROWS;
       } else if (mode == 0 && sub % cpl == 0 && is_pow2(sub / cpl)) {
         p.fwd.group_mode = chop::GROUP_XOR;
         p.fwd.run = sub / cpl;
@@ -231,8 +236,8 @@ int chop_cost_volume_fwd(const chop_cv_desc* d, const void* ref, const void* src
 
   plan_chunks(&a, LG, 148 * 128, 16, g_fwd_chunk.load());
   p.fwd.smem_per_warp = ty.real_size == 8
-      ? chop::fwd_smem_per_warp<double>(a.N, 32 / LG, LG, cpl, p.fwd.group_mode == chop::GROUP_SMEM)
-      : chop::fwd_smem_per_warp<float>(a.N, 32 / LG, LG, cpl, p.fwd.group_mode == chop::GROUP_SMEM);
+      ? chop::fwd_smem_per_warp<double>(a.N, 32 / LG, LG, cpl, p.fwd.group_mode)
+      : chop::fwd_smem_per_warp<float>(a.N, 32 / LG, LG, cpl, p.fwd.group_mode);
   p.fwd.warps = pick_warps(p.fwd.smem_per_warp);
   if (p.fwd.warps == 0) return CHOP_ERR_UNSUPPORTED;
   const long long items = (long long)a.npb * a.nchunks;
@@ -277,7 +282,7 @@ int chop_cost_volume_bwd(const chop_cv_desc* d, const void* ref, const void* src
     return chop::cv3_bwd_launch(d->dtype, d->reduce == CHOP_REDUCE_MIN, a, st3);
   }
   int cpl, lgl;
-  if (int e = plan_lanes(d, a, &cpl, &lgl, false)) return e;
+  if (int e = plan_lanes(d, a, &cpl, &lgl, false, true)) return e;
   a.lg_log2 = lgl;
   const int LG = 1 << lgl;
   if (!aligned(ref, cpl * ty.feat_size) || !aligned(src, cpl * ty.feat_size) || !aligned(depth, ty.real_size) ||
@@ -285,6 +290,13 @@ int chop_cost_volume_bwd(const chop_cv_desc* d, const void* ref, const void* src
       !aligned(ref_grad, cpl * ty.real_size) || !aligned(src_grad, cpl * ty.real_size) ||
       !aligned(depth_grad, ty.real_size))
     return CHOP_ERR_ALIGN;
+  // the compile-time-C MIN kernel copies a lane's four arg indices as one 16-byte vector
+  if (d->kind == CHOP_COST_VOLUME && d->reduce == CHOP_REDUCE_MIN && cpl == 4 && !aligned(mask, 16)) return CHOP_ERR_ALIGN;
+  if (d->kind == CHOP_COST_VOLUME_V2 && tuned_eligible(d, a, true)) {
+    // a lane reads the 4/(C/G) groups of its four channels as one vector
+    const size_t ga = (size_t)(4 / (a.C / a.G)) * 4;
+    if (!aligned(cost_grad, ga) || !aligned(mask, ga)) return CHOP_ERR_ALIGN;
+  }
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (!(d->flags & CHOP_FLAG_ACCUMULATE)) {

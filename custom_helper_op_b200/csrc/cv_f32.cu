@@ -15,7 +15,7 @@ int cv_fwd_f32(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
     }
   }
   if (p.use_tuned && p.kind == 2 && p.mode == 0 && p.cpl == 4) {
-    const int r = tuned2_dispatch<float>(false, a, st);
+    const int r = tuned2_dispatch<float>(false, false, a, st);
     if (r != -4) return r;  // -4: no compile-time-C kernel for this (C, groups): generic kernel below
   }
   if (p.use_tuned && p.kind == 1 && p.mode == 0 && p.cpl == 4) {
@@ -39,8 +39,26 @@ int cv_bwd_f32(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
       default: break;
     }
   }
-  if (p.use_tuned && p.kind == 2 && !p.rmin && p.cpl == 4) {
-    const int r = tuned2_dispatch<float>(true, a, st);
+  if (p.use_tuned && p.kind == 3 && p.rmin && p.cpl == 4) {
+    switch (a.C) {
+      case 8: return bwd_tuned_go<float, 8, 4, true, true>(a, st);
+      case 16: return bwd_tuned_go<float, 16, 4, true, true>(a, st);
+      case 32: return bwd_tuned_go<float, 32, 4, true, true>(a, st);
+      case 64: return bwd_tuned_go<float, 64, 4, true, true>(a, st);
+      default: break;
+    }
+  }
+  if (p.use_tuned && p.kind == 1 && p.rmin && p.cpl == 4) {
+    switch (a.C) {
+      case 8: return bwd_tuned_go<float, 8, 4, false, true>(a, st);
+      case 16: return bwd_tuned_go<float, 16, 4, false, true>(a, st);
+      case 32: return bwd_tuned_go<float, 32, 4, false, true>(a, st);
+      case 64: return bwd_tuned_go<float, 64, 4, false, true>(a, st);
+      default: break;
+    }
+  }
+  if (p.use_tuned && p.kind == 2 && p.cpl == 4) {
+    const int r = tuned2_dispatch<float>(true, p.rmin != 0, a, st);
     if (r != -4) return r;
   }
   if (p.use_tuned && p.kind == 1 && !p.rmin && p.cpl == 4) {

@@ -20,7 +20,9 @@ namespace chop {
 enum GroupMode {
   GROUP_IN_LANE = 0,  // every group lies inside one lane's channel slice (CPL % (C/G) == 0)
   GROUP_XOR = 1,      // a group spans a power-of-two run of lanes: butterfly shuffle
-  GROUP_SMEM = 2      // anything else, and every unfused mode: sequential sum through shared memory
+  GROUP_SMEM = 2,     // anything else, and the unfused grouped modes: sequential sum through shared memory
+  GROUP_ROWS = 3      // unfused KIND 3: per-channel values of a block of depth planes are transposed
+                      // through shared memory, then every lane sums ONE plane's channels in order
 };
 
 struct FwdCfg {
@@ -31,11 +33,54 @@ struct FwdCfg {
   size_t smem_per_warp;
 };
 
+// Row stride (in values) of the GROUP_ROWS scratch: LG*CPL channel slots plus 16 bytes, so that the
+// 16-byte reads of lanes that own consecutive rows fall into different banks.
 template <typename R>
-__host__ __device__ inline size_t fwd_smem_per_warp(int N, int G, int LG, int CPL, bool scratch) {
+__host__ __device__ inline int rows_stride(int LG, int CPL) { return LG * CPL + 16 / (int)sizeof(R); }
+
+template <typename R>
+__host__ __device__ inline size_t fwd_smem_per_warp(int N, int G, int LG, int CPL, int group_mode) {
   size_t s = (size_t)N * G * sizeof(Coef<R>) + (size_t)N * 32 * sizeof(ProjF<R>);
-  if (scratch) s += (size_t)32 * CPL * sizeof(R);
+  if (group_mode == GROUP_SMEM) s += (size_t)32 * CPL * sizeof(R);
+  if (group_mode == GROUP_ROWS) s += (size_t)32 * rows_stride<R>(LG, CPL) * sizeof(R);
   return (s + 15) & ~(size_t)15;
+}
+
+// s + row[0] + row[1] + ... + row[n-1], added one by one in ascending order (unfused).  `vec` says
+// that row is 16-byte aligned and n a multiple of the 16-byte vector length.
+template <typename R>
+__device__ __forceinline__ R row_sum_ordered(const R* row, int n, bool vec, R s) {
+  if (vec) {
+    if constexpr (sizeof(R) == 4) {
+      for (int c = 0; c < n; c += 4) {
+        const float4 v = *reinterpret_cast<const float4*>(row + c);
+        s = xadd(xadd(xadd(xadd(s, v.x), v.y), v.z), v.w);
+      }
+    } else {
+      for (int c = 0; c < n; c += 2) {
+        const double2 v = *reinterpret_cast<const double2*>(row + c);
+        s = xadd(xadd(s, v.x), v.y);
+      }
+    }
+  } else {
+    for (int c = 0; c < n; ++c) s = xadd(s, row[c]);
+  }
+  return s;
+}
+
+// CPL consecutive values to shared memory, as 16-byte stores where the slice allows it.
+template <typename R, int CPL>
+__device__ __forceinline__ void store_slice(R* p, const R* v) {
+  if constexpr (sizeof(R) == 4 && CPL % 4 == 0) {
+#pragma unroll
+    for (int i = 0; i < CPL; i += 4) *reinterpret_cast<float4*>(p + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+  } else if constexpr (sizeof(R) == 8 && CPL % 2 == 0) {
+#pragma unroll
+    for (int i = 0; i < CPL; i += 2) *reinterpret_cast<double2*>(p + i) = make_double2(v[i], v[i + 1]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) p[i] = v[i];
+  }
 }
 
 
@@ -210,6 +255,63 @@ __global__ void __launch_bounds__(256) cv_fwd_kernel(const CvArgs a, const FwdCf
       }
       __syncwarp();
       continue;
+    }
+
+    if constexpr (KIND == 3 && MODE != 0) {
+      // ---- phase B, unfused aggregate: the reference adds the C squared differences of a (voxel,
+      // view) one by one (cost_aggregate_kernels_gpu.cu.cc:100-126, 190-223).  All lanes compute
+      // their channel slice for every plane of the block (coalesced gathers), the slices meet in
+      // shared memory, and lane li then owns plane dblk+li and runs that chain in order.
+      if (cfg.group_mode == GROUP_ROWS) {
+        const int jn = min(LG, dhi - dblk);
+        const int RS = rows_stride<R>(LG, CPL);
+        R* rows = scratch + (size_t)(g << lgl) * RS;
+        const bool vec = ((RS * (int)sizeof(R)) & 15) == 0 && (C % (16 / (int)sizeof(R))) == 0;
+        const ProjF<R>* rec = proj + (g << lgl);
+        R tot = RMIN ? Lim<R>::max() : (R)0;
+        int targ = -1, tused = 0;
+        for (int n = 0; n < a.N; ++n) {
+          for (int j = 0; j < jn; ++j) {
+            const ProjF<R> pr = rec[n * 32 + j];
+            R val[CPL];
+#pragma unroll
+            for (int k = 0; k < CPL; ++k) val[k] = (R)0;
+            if (pr.texel >= 0 && lane_on) {
+              R w00, w01, w11, w10;
+              bilinear_weights(pr.dh, pr.dw, w00, w01, w11, w10);
+              const T* p00 = src + (size_t)pr.texel * C + li * CPL;
+              R t00[CPL], t01[CPL], t10[CPL], t11[CPL];
+              Vec<T, R, CPL>::load(p00, t00);
+              Vec<T, R, CPL>::load(p00 + C, t01);
+              Vec<T, R, CPL>::load(p00 + (size_t)Ws * C, t10);
+              Vec<T, R, CPL>::load(p00 + (size_t)Ws * C + C, t11);
+#pragma unroll
+              for (int k = 0; k < CPL; ++k) {
+                const R s = xadd(xadd(xadd(xmul(w00, t00[k]), xmul(w01, t01[k])), xmul(w11, t11[k])), xmul(w10, t10[k]));
+                const R df = xsub(s, refv[k]);
+                val[k] = xmul(df, df);
+              }
+            }
+            store_slice<R, CPL>(rows + j * RS + li * CPL, val);
+          }
+          __syncwarp();
+          if (li < jn && rec[n * 32 + li].texel >= 0) {
+            const R s = row_sum_ordered<R>(rows + li * RS, C, vec, MODE == 1 ? tot : (R)0);
+            if (MODE == 1) { tot = s; ++tused; }
+            else if (tot > s) { tot = s; targ = n; }
+          }
+          __syncwarp();
+        }
+        if (pvalid && li < jn) {
+          const long long vox = pix * a.D + dblk + li;
+          R v;
+          if (MODE == 2) v = targ >= 0 ? xdiv(tot, (R)C) : (R)0;
+          else v = tused > 0 ? xdiv(tot, (R)(tused * C)) : (R)0;
+          __stcs(cost + vox, v);
+          if (RMIN) __stcs(a.mask + vox, targ);
+        }
+        continue;
+      }
     }
 
     // ---- phase B: channel work, one depth plane at a time -----------------------------------------

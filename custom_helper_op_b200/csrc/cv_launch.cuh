@@ -107,10 +107,10 @@ inline int fwd_tuned_go(const CvArgs& a, cudaStream_t st) {
   return (int)cudaGetLastError();
 }
 
-template <typename T, int C, int CPL, bool AGG = false>
+template <typename T, int C, int CPL, bool AGG = false, bool RMIN = false>
 inline int bwd_tuned_go(const CvArgs& a, cudaStream_t st) {
-  auto k = cv_bwd_tuned<T, C, CPL, AGG>;
-  const size_t spw = tuned_bwd_smem_per_warp<C>(a.N, 32 / (C / CPL));
+  auto k = cv_bwd_tuned<T, C, CPL, AGG, RMIN>;
+  const size_t spw = tuned_bwd_smem_per_warp<C>(a.N, 32 / (C / CPL), (RMIN && !AGG) ? 2 : 1);
   const int warps = 4;
   const size_t smem = spw * warps;
   if (smem > 200 * 1024) return -4;
@@ -139,9 +139,9 @@ inline int fwd2_tuned_go(const CvArgs& a, cudaStream_t st) {
   return (int)cudaGetLastError();
 }
 
-template <typename T, int C, int SUB>
+template <typename T, int C, int SUB, bool RMIN>
 inline int bwd2_tuned_go(const CvArgs& a, cudaStream_t st) {
-  auto k = cv2_bwd_tuned<T, C, SUB>;
+  auto k = cv2_bwd_tuned<T, C, SUB, RMIN>;
   const size_t spw = tuned2_bwd_smem_per_warp<T>(a.N, 32 / (C / 4));
   const int warps = 4;
   const size_t smem = spw * warps;
@@ -155,12 +155,16 @@ inline int bwd2_tuned_go(const CvArgs& a, cudaStream_t st) {
   return (int)cudaGetLastError();
 }
 
-// C in {8,16,32}, channels per group in {1,2,4}; returns -4 if there is no such kernel
+// C in {8,16,32}, channels per group in {1,2,4}; returns -4 if there is no such kernel (the forward
+// kernels exist for MEAN only)
 template <typename T>
-inline int tuned2_dispatch(bool backward, const CvArgs& a, cudaStream_t st) {
+inline int tuned2_dispatch(bool backward, bool rmin, const CvArgs& a, cudaStream_t st) {
   const int sub = a.C / a.G;
-#define CHOP_V2_CASE(CC, SS)                                                        \
-  if (a.C == CC && sub == SS) return backward ? bwd2_tuned_go<T, CC, SS>(a, st) : fwd2_tuned_go<T, CC, SS>(a, st);
+  if (rmin && !backward) return -4;
+#define CHOP_V2_CASE(CC, SS)                                                                            \
+  if (a.C == CC && sub == SS)                                                                           \
+    return backward ? (rmin ? bwd2_tuned_go<T, CC, SS, true>(a, st) : bwd2_tuned_go<T, CC, SS, false>(a, st)) \
+                    : fwd2_tuned_go<T, CC, SS>(a, st);
   CHOP_V2_CASE(8, 1) CHOP_V2_CASE(8, 2) CHOP_V2_CASE(8, 4)
   CHOP_V2_CASE(16, 1) CHOP_V2_CASE(16, 2) CHOP_V2_CASE(16, 4)
   CHOP_V2_CASE(32, 1) CHOP_V2_CASE(32, 2) CHOP_V2_CASE(32, 4)

@@ -207,10 +207,12 @@ struct alignas(8) RecG {
   float gh, gw;  // d(sample row)/d(depth), d(sample column)/d(depth)
 };
 
+// `staged` = per-channel tensors copied into shared memory ahead of use: cost_grad, and for MIN also
+// the arg-index tensor; each buffer holds G*LG*C values = 128*C bytes.
 template <int C>
-__host__ __device__ inline size_t tuned_bwd_smem_per_warp(int N, int G) {
+__host__ __device__ inline size_t tuned_bwd_smem_per_warp(int N, int G, int staged = 1) {
   return (size_t)N * G * sizeof(Coef<float>) + (size_t)N * 32 * (sizeof(ProjF<float>) + sizeof(RecG)) +
-         (size_t)CG_BUFS * 128 * C;  // cost_grad buffers of G*LG*C floats = 128*C bytes each
+         (size_t)staged * CG_BUFS * 128 * C;
 }
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
@@ -242,7 +244,10 @@ __device__ __forceinline__ void flush_corners(float* gp, size_t row, int C, floa
   red_add<float, CPL>(gp + row + C, m[3]);
 }
 
-template <typename T, int C, int CPL, bool AGG = false>
+// RMIN = true is the MIN reduction: `mask` holds the winning view per (voxel, channel) (per voxel for
+// AGG) and only that view receives the gradient (cost_volume_kernels_gpu.cu.cc:472-577,
+// cost_aggregate_kernels_gpu.cu.cc:462-568); a voxel whose first channel has no winner is skipped (:484).
+template <typename T, int C, int CPL, bool AGG = false, bool RMIN = false>
 __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const CvArgs a, const int warps, const size_t smem_per_warp) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int LG = C / CPL;
@@ -272,6 +277,8 @@ __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const C
   RecG* recG = reinterpret_cast<RecG*>(recA + N * 32);
   float* cgbuf = reinterpret_cast<float*>(recG + N * 32);             // [2][G][LG][C]
   float* cg_mine = cgbuf + (g * LG) * C + li * CPL;                    // + buf*32*C + j*C
+  constexpr bool STAGE_MASK = RMIN && !AGG;
+  constexpr int MK_OFF = CG_BUFS * 32 * C;                             // arg indices behind the cost_grad buffers
 
   stage_coefs<float>(a, coef, lane, G, pix0);
 
@@ -287,13 +294,19 @@ __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const C
   const size_t row = (size_t)a.Ws * C;
   float dsum = 0.0f;
   const float* cg_src = static_cast<const float*>(a.cost_grad) + (pix * D + dlo) * C + li * CPL;
+  const int* mk_src = a.mask + (pix * D + dlo) * C + li * CPL;  // + (plane - dlo) * C; read for MIN only
 
   // stage the first block's upstream gradient
   if constexpr (!AGG) {
 #pragma unroll
     for (int j = 0; j < LG; ++j) {
-      if (dlo + j < dhi) cp_async16(cg_mine + j * C, cg_src + j * C);
-      else *reinterpret_cast<float4*>(cg_mine + j * C) = make_float4(0.f, 0.f, 0.f, 0.f);  // never left uninitialised
+      if (dlo + j < dhi) {
+        cp_async16(cg_mine + j * C, cg_src + j * C);
+        if (STAGE_MASK) cp_async16(cg_mine + MK_OFF + j * C, mk_src + j * C);
+      } else {
+        *reinterpret_cast<float4*>(cg_mine + j * C) = make_float4(0.f, 0.f, 0.f, 0.f);  // never left uninitialised
+        if (STAGE_MASK) *reinterpret_cast<int4*>(cg_mine + MK_OFF + j * C) = make_int4(-1, -1, -1, -1);
+      }
     }
     cp_async_commit();
   }
@@ -308,8 +321,13 @@ __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const C
       float* dst = cg_mine + (buf ^ 1) * 32 * C;
 #pragma unroll
       for (int j = 0; j < LG; ++j) {
-        if (nxt + j < dhi) cp_async16(dst + j * C, cg_src + (LG + j) * C);
-        else *reinterpret_cast<float4*>(dst + j * C) = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (nxt + j < dhi) {
+          cp_async16(dst + j * C, cg_src + (LG + j) * C);
+          if (STAGE_MASK) cp_async16(dst + MK_OFF + j * C, mk_src + (nxt - dlo + j) * C);
+        } else {
+          *reinterpret_cast<float4*>(dst + j * C) = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (STAGE_MASK) *reinterpret_cast<int4*>(dst + MK_OFF + j * C) = make_int4(-1, -1, -1, -1);
+        }
       }
       cp_async_commit();
     } else {
@@ -322,13 +340,22 @@ __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const C
       const bool dv = pvalid && d < dhi;
       float depth = 0.0f, scale = 0.0f;
       bool live = false;
+      int m0 = 0;
       if (dv) {
         depth = xadd(base, offs[d]);
-        const int m0 = __ldg(a.mask + pix * D + d);
-        live = m0 > 0;                       // cost_volume_kernels_gpu.cu.cc:367
-        if (live) scale = 2.0f / (float)m0;  // :439
-        if (AGG && live)                     // one upstream value per voxel, divided by views*C
-          scale = 2.0f * __ldg(static_cast<const float*>(a.cost_grad) + pix * D + d) / (float)(m0 * C);
+        if constexpr (RMIN) {
+          m0 = __ldg(a.mask + (pix * D + d) * (AGG ? 1 : C));
+          live = m0 >= 0;                    // :484, aggregate :476
+          scale = 2.0f;                      // :560
+          if (AGG && live)                   // aggregate :500
+            scale = 2.0f * __ldg(static_cast<const float*>(a.cost_grad) + pix * D + d) / (float)C;
+        } else {
+          m0 = __ldg(a.mask + pix * D + d);
+          live = m0 > 0;                       // cost_volume_kernels_gpu.cu.cc:367
+          if (live) scale = 2.0f / (float)m0;  // :439
+          if (AGG && live)                     // one upstream value per voxel, divided by views*C
+            scale = 2.0f * __ldg(static_cast<const float*>(a.cost_grad) + pix * D + d) / (float)(m0 * C);
+        }
       }
       for (int n = 0; n < N; ++n) {
         ProjF<float> r;
@@ -337,7 +364,9 @@ __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const C
         r.dh = r.dw = 0.0f;
         r.aux = scale;
         q.gh = q.gw = 0.0f;
-        if (live) r.texel = project<float, true>(coef[n * G + g], depth, a.half_centor, a.Hs, a.Ws, r.dh, r.dw, q.gh, q.gw);
+        // aggregate MIN: only the winning view of the voxel is differentiated
+        if (live && (!(RMIN && AGG) || m0 == n))
+          r.texel = project<float, true>(coef[n * G + g], depth, a.half_centor, a.Hs, a.Ws, r.dh, r.dw, q.gh, q.gw);
         recA[n * 32 + lane] = r;
         recG[n * 32 + lane] = q;
       }
@@ -387,6 +416,13 @@ __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const C
           } else {
             const float4 cg4 = *reinterpret_cast<const float4*>(cgb + j * C);
             cgs[0] = cg4.x * rc.aux; cgs[1] = cg4.y * rc.aux; cgs[2] = cg4.z * rc.aux; cgs[3] = cg4.w * rc.aux;
+            if constexpr (RMIN) {  // :553 a channel's gradient goes to its winning view only
+              const int4 mk = *reinterpret_cast<const int4*>(cgb + MK_OFF + j * C);
+              if (mk.x != n) cgs[0] = 0.0f;
+              if (mk.y != n) cgs[1] = 0.0f;
+              if (mk.z != n) cgs[2] = 0.0f;
+              if (mk.w != n) cgs[3] = 0.0f;
+            }
           }
           // Per channel: gs = d(cost)/d(sample) (:439).  The four corner sums (:441-444) are kept as moments
           // sum gs, sum gs*dw, sum gs*dh, sum gs*dh*dw and turned into corner values when the footprint is
@@ -417,8 +453,13 @@ __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const C
       const int nxt = dblk + LG;
 #pragma unroll
       for (int j = 0; j < LG; ++j) {
-        if (nxt + j < dhi) cp_async16(cg_mine + j * C, cg_src + (LG + j) * C);
-        else *reinterpret_cast<float4*>(cg_mine + j * C) = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (nxt + j < dhi) {
+          cp_async16(cg_mine + j * C, cg_src + (LG + j) * C);
+          if (STAGE_MASK) cp_async16(cg_mine + MK_OFF + j * C, mk_src + (nxt - dlo + j) * C);
+        } else {
+          *reinterpret_cast<float4*>(cg_mine + j * C) = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (STAGE_MASK) *reinterpret_cast<int4*>(cg_mine + MK_OFF + j * C) = make_int4(-1, -1, -1, -1);
+        }
       }
       cp_async_commit();
     }
@@ -576,7 +617,9 @@ __global__ void __launch_bounds__(256, 3) cv2_fwd_tuned(const CvArgs a, const in
 // ref*(p01-p00), formed once per footprint.  The depth-hypothesis gradient is per voxel: every lane keeps
 // one partial per plane of the block, the partials are reduce-scattered over the pixel's lanes (lane li
 // ends up with plane li) and stored coalesced (zero where no view saw the voxel, v2:375-378).
-template <typename T, int C, int SUB>
+// RMIN = true: `mask` holds the winning view per (voxel, group); only that view is differentiated, with
+// no division by the view count (v2:483-601); a voxel whose first group has no winner is skipped.
+template <typename T, int C, int SUB, bool RMIN = false>
 __global__ void __launch_bounds__(128, 5) cv2_bwd_tuned(const CvArgs a, const int warps, const size_t smem_per_warp) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int CPL = 4;
@@ -620,8 +663,9 @@ __global__ void __launch_bounds__(128, 5) cv2_bwd_tuned(const CvArgs a, const in
   float* dgrad = static_cast<float*>(a.depth_grad) + pix * D;
   const size_t row = (size_t)a.Ws * C;
   const float* cg_lane = static_cast<const float*>(a.cost_grad) + (pix * D + dlo) * GR + li * NG;
+  const int* mk_lane = a.mask + (pix * D + dlo) * GR + li * NG;  // read for MIN only
 
-  for (int dblk = dlo; dblk < dhi; dblk += LG, cg_lane += LG * GR) {
+  for (int dblk = dlo; dblk < dhi; dblk += LG, cg_lane += LG * GR, mk_lane += LG * GR) {
     __syncwarp();
     // ---- phase A -----------------------------------------------------------------------------------------
     const int dA = dblk + li;
@@ -631,9 +675,14 @@ __global__ void __launch_bounds__(128, 5) cv2_bwd_tuned(const CvArgs a, const in
       bool live = false;
       if (dvA) {
         depth = __ldg(dgrid + dA);
-        const int m0 = __ldg(a.mask + pix * D + dA);
-        live = m0 > 0;                       // v2:375
-        if (live) scale = 1.0f / (float)m0;  // v2:461
+        if constexpr (RMIN) {
+          live = __ldg(a.mask + (pix * D + dA) * GR) >= 0;  // v2:495
+          scale = 1.0f;                                     // v2:583
+        } else {
+          const int m0 = __ldg(a.mask + pix * D + dA);
+          live = m0 > 0;                       // v2:375
+          if (live) scale = 1.0f / (float)m0;  // v2:461
+        }
       }
       for (int n = 0; n < N; ++n) {
         ProjF<float> r;
@@ -712,6 +761,13 @@ __global__ void __launch_bounds__(128, 5) cv2_bwd_tuned(const CvArgs a, const in
           const RecG rq = rGp[j];
           float cgv[NG];
           Vec<float, float, NG>::load(cg_lane + j * GR, cgv);
+          if constexpr (RMIN) {  // v2:575 a group's gradient goes to its winning view only
+            float mk[NG];
+            Vec<float, float, NG>::load(reinterpret_cast<const float*>(mk_lane) + j * GR, mk);
+#pragma unroll
+            for (int q = 0; q < NG; ++q)
+              if (__float_as_int(mk[q]) != n) cgv[q] = 0.0f;
+          }
           const float hw = rc.dh * rc.dw;
           float P = 0.0f, Q = 0.0f, R = 0.0f;
 #pragma unroll

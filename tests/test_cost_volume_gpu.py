@@ -110,18 +110,20 @@ def test_no_half_centor():
     check(got, want, np.float32, exact_cost=True)
 
 
+@pytest.mark.parametrize("reduce", ["MEAN", "MIN"])
 @pytest.mark.parametrize("kind,C,G", [(1, 32, 1), (1, 8, 1), (1, 64, 1), (2, 32, 8), (2, 16, 8), (2, 8, 8), (3, 32, 1), (3, 16, 1)])
-def test_bfloat16_features(kind, C, G):
+def test_bfloat16_features(kind, C, G, reduce):
     """bf16 features are an extension; the oracle is the float32 reference arithmetic on the
     bf16-rounded features."""
     c = helpers.make_case(kind, 500 + C, 1, 3, 10, 12, C, 6, "random", np.float32)
     for k in ("ref", "src"):
         c[k] = torch.from_numpy(c[k]).to(torch.bfloat16).to(torch.float32).numpy()
-    want = helpers.oracle_fwd_bwd(kind, c, "MEAN", G, True, np.float32)
-    got = run_gpu(kind, c, "MEAN", G, True, want["cost_grad"], strict=True, bf16=True)
+    want = helpers.oracle_fwd_bwd(kind, c, reduce, G, True, np.float32)
+    got = run_gpu(kind, c, reduce, G, True, want["cost_grad"], strict=True, bf16=True)
     check(got, want, np.float32, exact_cost=True)
-    got = run_gpu(kind, c, "MEAN", G, True, want["cost_grad"], strict=False, bf16=True)   # compile-time-C kernels for kind 1
-    check(got, want, np.float32, exact_cost=False)
+    # compile-time-C kernels (MEAN forward and backward, MIN backward)
+    got = run_gpu(kind, c, reduce, G, True, want["cost_grad"], strict=False, bf16=True)
+    check(got, want, np.float32, exact_cost=reduce == "MIN")
 
 
 def test_depth_range_calls_compose():
