@@ -22,14 +22,17 @@ using chop::ScArgs;
 
 inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// The tensor-core and register-tiled kernels move channel vectors as 16-byte words; a tensor that is not 16-byte
+// aligned takes the scalar kernels instead.
 int run_fwd(int dtype, const ScArgs& a, cudaStream_t st) {
-  if (chop::g_use_umma.load() && chop::sc_umma_supported(dtype, a)) return chop::sc_umma_fwd_launch(a, st);
+  if (chop::g_use_umma.load() && chop::sc_umma_supported(dtype, a) && al16(a.images) && al16(a.output) && al16(a.filters))
+    return chop::sc_umma_fwd_launch(a, st);
   if (chop::g_use_tile.load() && chop::sc_tile_supported(dtype, a) && al16(a.images) && al16(a.output) && al16(a.filters))
     return chop::sc_tile_fwd_launch(dtype, a, st);
   return chop::sc_fwd_simt_launch(dtype, a, st);
 }
 int run_wgrad(int dtype, const ScArgs& a, int nparts, cudaStream_t st) {
-  if (chop::g_use_umma.load() && chop::sc_umma_supported(dtype, a)) {
+  if (chop::g_use_umma.load() && chop::sc_umma_supported(dtype, a) && al16(a.images) && al16(a.out_grad) && al16(a.workspace)) {
     // a persistent CTA per partial slab; more CTAs than 128-voxel tiles would leave slabs unwritten
     const long long ntiles = (a.nvox_out + 127) / 128;
     if (nparts > ntiles) nparts = (int)ntiles;
@@ -43,7 +46,8 @@ int run_wgrad(int dtype, const ScArgs& a, int nparts, cudaStream_t st) {
 int run_dgrad(int dtype, const ScArgs& in, cudaStream_t st) {
   ScArgs a = in;
   a.pad_zero = 1;  // a padded tap contributes nothing to the image gradient (sparse_conv3d_fast_op.cc:306,321)
-  if (chop::g_use_umma.load() && chop::sc_umma_supported(dtype, a)) return chop::sc_umma_dgrad_launch(a, st);
+  if (chop::g_use_umma.load() && chop::sc_umma_supported(dtype, a) && al16(a.out_grad) && al16(a.images_grad) && al16(a.filters))
+    return chop::sc_umma_dgrad_launch(a, st);
   if (chop::g_use_tile.load() && chop::sc_tile_supported(dtype, a) && al16(a.out_grad) && al16(a.images_grad) && al16(a.filters))
     return chop::sc_tile_gather_launch(dtype, a, st);
   return chop::sc_dgrad_simt_launch(dtype, a, st);
@@ -174,7 +178,8 @@ int chop_sparse_conv3d_transpose_fwd(const chop_sc_desc* d, const void* images, 
   a.out_grad = images; a.images_grad = output;
   a.filters = filters; a.default_value = default_value; a.base_plane = base_plane;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (chop::g_use_umma.load() && chop::sc_umma_supported(d->dtype, a)) return chop::sc_umma_dgrad_launch(a, st);
+  if (chop::g_use_umma.load() && chop::sc_umma_supported(d->dtype, a) && al16(a.out_grad) && al16(a.images_grad) && al16(a.filters))
+    return chop::sc_umma_dgrad_launch(a, st);
   if (chop::g_use_tile.load() && chop::sc_tile_supported(d->dtype, a) && al16(a.out_grad) && al16(a.images_grad) && al16(a.filters))
     return chop::sc_tile_gather_launch(d->dtype, a, st);
   return chop::sc_tconv_simt_launch(d->dtype, a, st);
@@ -201,7 +206,7 @@ int chop_sparse_conv3d_transpose_bwd(const chop_sc_desc* d, const void* images, 
   // filter gradient: gathers the coarse input under every tap of every fine voxel
   a.images = images; a.out_grad = out_grad; a.filter_grad = filter_grad; a.workspace = workspace;
   const int nparts = chop::sc_wgrad_parts(a.nvox_in);
-  if (chop::g_use_umma.load() && chop::sc_umma_supported(d->dtype, a)) {
+  if (chop::g_use_umma.load() && chop::sc_umma_supported(d->dtype, a) && al16(a.images) && al16(a.out_grad) && al16(a.workspace)) {
     if (int e = chop::sc_umma_twgrad_launch(a, nparts, st)) return e;
   } else if (chop::g_use_tile.load() && chop::sc_tile_wgrad_supported(d->dtype, a, true) && al16(a.images) && al16(a.out_grad) &&
              al16(a.workspace)) {

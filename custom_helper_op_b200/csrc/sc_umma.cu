@@ -48,6 +48,11 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo, uint
   return d;
 }
 
+// The descriptor of the same layout `bytes` further on (the start-address field counts 16-byte units and a CTA's
+// shared memory cannot carry out of it).  Issuing an MMA then costs one addition per operand instead of
+// rebuilding the descriptor; a single thread issues them all, so this is the critical path of a tile.
+__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t desc, uint32_t bytes) { return desc + (uint64_t)(bytes >> 4); }
+
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
@@ -104,10 +109,19 @@ __device__ __forceinline__ VoxPos vox_pos(const ScArgs& a, long long v) {
   VoxPos p;
   constexpr bool S1 = SM == 1;
   const int d1 = (TG || S1) ? a.D : a.oD, d2 = (TG || S1) ? a.W : a.oW, d3 = (TG || S1) ? a.H : a.oH;
-  const int dz = (int)(v % d1); v /= d1;
-  const int cc = (int)(v % d2); v /= d2;
-  const int rr = (int)(v % d3);
-  p.b = (int)(v / d3);
+  int dz, cc, rr;
+  if (v <= 0x7fffffffLL) {   // 64-bit divisions cost several times the rest of this function
+    unsigned u = (unsigned)v;
+    dz = (int)(u % (unsigned)d1); u /= (unsigned)d1;
+    cc = (int)(u % (unsigned)d2); u /= (unsigned)d2;
+    rr = (int)(u % (unsigned)d3);
+    p.b = (int)(u / (unsigned)d3);
+  } else {
+    dz = (int)(v % d1); v /= d1;
+    cc = (int)(v % d2); v /= d2;
+    rr = (int)(v % d3);
+    p.b = (int)(v / d3);
+  }
   p.r = (TG || S1) ? rr : rr * a.sr;
   p.c = (TG || S1) ? cc : cc * a.sc;
   const int bp = __ldg(a.base_plane + (p.b * a.H + p.r) * a.W + p.c);
@@ -155,6 +169,30 @@ __device__ __forceinline__ long long tap_voxel(const ScArgs& a, const VoxPos& p,
   return oob(ind, a.D) ? -1 : base + ind;
 }
 
+// Filter [27][Cin_f][Cout_f] -> canonical K-major B tiles in shared memory, B[n][k] of tap t at sB + t*tap_bytes
+// (forward: n = output channel, k = input channel; DGRAD: the flipped tap with the channels swapped, whose rows are
+// contiguous in the filter tensor).  One 16-byte chunk (eight k of one n) per thread and step, its loads independent of
+// each other: every CTA repeats this, so it must not be a chain of dependent scalar loads.
+template <int CIN, int COUT, bool DGRAD>
+__device__ __forceinline__ void stage_filter_tiles(const unsigned short* flt, unsigned char* sB, int tid, uint32_t lbo,
+                                                   uint32_t sbo, int tap_bytes) {
+  constexpr int KC = CIN / 8;
+#pragma unroll 2
+  for (int e = tid; e < 27 * COUT * KC; e += 128) {
+    const int kg = e % KC, n = (e / KC) % COUT, t = e / (KC * COUT);
+    uint4 w;
+    if (DGRAD) {
+      w = __ldg(reinterpret_cast<const uint4*>(flt + ((size_t)(26 - t) * COUT + n) * CIN + kg * 8));  // f[flip t][ci = n][oc = k]
+    } else {
+      unsigned h[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) h[i] = __ldg(flt + ((size_t)t * CIN + kg * 8 + i) * COUT + n);        // f[t][ci = k][oc = n]
+      w = make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
+    }
+    *reinterpret_cast<uint4*>(sB + t * tap_bytes + (n / 8) * sbo + kg * lbo + (n % 8) * 16) = w;
+  }
+}
+
 // CIN: channels of the gathered tensor (K per tap), COUT: channels produced (N).
 template <int CIN, int COUT, bool DGRAD, int SM>
 __global__ void __launch_bounds__(128) sc_umma_kernel(const ScArgs a, const long long nvox, const int ntiles) {
@@ -174,14 +212,7 @@ __global__ void __launch_bounds__(128) sc_umma_kernel(const ScArgs a, const long
 
   // ---- filter -> canonical K-major B tiles: B[n][k] of tap t at sB + t*B_TAP_BYTES -----------------------
   {
-    const unsigned short* flt = static_cast<const unsigned short*>(a.filters);  // [27][Cin_f][Cout_f]
-    for (int e = tid; e < 27 * COUT * CIN; e += 128) {
-      const int k = e % CIN, n = (e / CIN) % COUT, t = e / (CIN * COUT);
-      unsigned short w;
-      if (!DGRAD) w = __ldg(flt + ((size_t)t * CIN + k) * COUT + n);         // B[n=oc][k=ci] = f[t][ci][oc]
-      else w = __ldg(flt + ((size_t)(26 - t) * COUT + n) * CIN + k);          // B[n=ci][k=oc] = f[flip t][ci][oc]
-      *reinterpret_cast<unsigned short*>(sB + t * B_TAP_BYTES + (n / 8) * SBO + (k / 8) * LBO + (n % 8) * 16 + (k % 8) * 2) = w;
-    }
+    stage_filter_tiles<CIN, COUT, DGRAD>(static_cast<const unsigned short*>(a.filters), sB, tid, LBO, SBO, B_TAP_BYTES);
   }
   if (warp == 0) {
     uint32_t slot = smem_u32(&tmem_base_s), ncols = 32;
@@ -311,7 +342,7 @@ __global__ void __launch_bounds__(128) sc_umma_kernel(const ScArgs a, const long
 // behind one barrier (one commit, one wait) and reads every neighbour plane once.
 // ---------------------------------------------------------------------------------------------------------
 template <int CIN, int COUT, bool DGRAD>
-__global__ void __launch_bounds__(128) sc_umma_rows_kernel(const ScArgs a, const int ntiles, const int PT) {
+__global__ void __launch_bounds__(128, CIN <= 16 ? 4 : 2) sc_umma_rows_kernel(const ScArgs a, const int ntiles, const int PT) {
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t mbar_s;
   __shared__ uint32_t tmem_base_s;
@@ -329,14 +360,7 @@ __global__ void __launch_bounds__(128) sc_umma_rows_kernel(const ScArgs a, const
   __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(DGRAD ? a.images_grad : a.output);
 
   {
-    const unsigned short* flt = static_cast<const unsigned short*>(a.filters);  // [27][Cin_f][Cout_f]
-    for (int e = tid; e < 27 * COUT * CIN; e += 128) {
-      const int k = e % CIN, n = (e / CIN) % COUT, t = e / (CIN * COUT);
-      unsigned short w;
-      if (!DGRAD) w = __ldg(flt + ((size_t)t * CIN + k) * COUT + n);         // B[n=oc][k=ci] = f[t][ci][oc]
-      else w = __ldg(flt + ((size_t)(26 - t) * COUT + n) * CIN + k);          // B[n=ci][k=oc] = f[flip t][ci][oc]
-      *reinterpret_cast<unsigned short*>(sB + t * B_TAP_BYTES + (n / 8) * B_SBO + (k / 8) * B_LBO + (n % 8) * 16 + (k % 8) * 2) = w;
-    }
+    stage_filter_tiles<CIN, COUT, DGRAD>(static_cast<const unsigned short*>(a.filters), sB, tid, B_LBO, B_SBO, B_TAP_BYTES);
     // rows 128..135 of every column buffer are only ever read into discarded output rows; keep them defined
     for (int e = tid; e < 9 * KC * (NRB - 128); e += 128) {
       const int rr = e % (NRB - 128), kc = (e / (NRB - 128)) % KC, col = e / ((NRB - 128) * KC);
@@ -373,20 +397,22 @@ __global__ void __launch_bounds__(128) sc_umma_rows_kernel(const ScArgs a, const
   const bool row_used = p_in_tile < PT;
   uint32_t phase = 0;
   bool alive = true;
-  for (int tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
-    const long long pix = (long long)tile * PT + p_in_tile;
-    const bool rvalid = row_used && pix < npix;
+  // Source voxel (or -1) of this thread's row in each of the nine filter columns of a tile.
+  long long pix = 0;
+  bool rvalid = false;
+  long long sv[9];
+  auto locate = [&](int tile) {
+    pix = (long long)tile * PT + p_in_tile;
+    rvalid = row_used && tile < ntiles && pix < npix;
     int b = 0, r = 0, c = 0, bp_out = 0;
     if (rvalid) {
-      c = (int)(pix % W);
-      const long long t = pix / W;
-      r = (int)(t % H);
-      b = (int)(t / H);
+      const unsigned p32 = (unsigned)pix;   // pixel counts are validated to fit 31 bits
+      c = (int)(p32 % (unsigned)W);
+      const unsigned t = p32 / (unsigned)W;
+      r = (int)(t % (unsigned)H);
+      b = (int)(t / (unsigned)H);
       bp_out = __ldg(a.base_plane + pix);
     }
-    // ---- stage the nine filter columns: one row per thread and column --------------------------------------
-    // three passes so that the nine base-plane lookups, then the nine neighbour rows, are all in flight together
-    long long sv[9];
 #pragma unroll
     for (int col = 0; col < 9; ++col) {
       const int orow = r - 1 + col / 3, ocol = c - 1 + col % 3;
@@ -395,16 +421,26 @@ __global__ void __launch_bounds__(128) sc_umma_rows_kernel(const ScArgs a, const
       const int plane = j - 1 + bp_out - __ldg(a.base_plane + np);
       sv[col] = (inb && !oob(plane, D)) ? (long long)np * D + plane : -1;
     }
+  };
+  locate(blockIdx.x);
+  const uint64_t da0 = umma_desc(smem_u32(sX), A_LBO, A_SBO);
+  const uint64_t db0 = umma_desc(smem_u32(sB), B_LBO, B_SBO);
+  for (int tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
+    // ---- stage the nine filter columns: one row per thread and column; the nine neighbour rows are all in
+    // flight together (their addresses were resolved during the previous tile) -------------------------------
+    const long long pix_out = pix;
+    const bool rvalid_out = rvalid;
     uint4 val[9][KC];
 #pragma unroll
     for (int col = 0; col < 9; ++col) {
       const uint4* p = reinterpret_cast<const uint4*>(src + (size_t)(sv[col] >= 0 ? sv[col] : 0) * CIN);
 #pragma unroll
       for (int kc = 0; kc < KC; ++kc) {
-        val[col][kc] = rvalid ? padv : make_uint4(0, 0, 0, 0);
+        val[col][kc] = rvalid_out ? padv : make_uint4(0, 0, 0, 0);
         if (sv[col] >= 0) val[col][kc] = __ldg(p + kc);
       }
     }
+    locate(tile + gridDim.x);   // the next tile's base-plane lookups run while this tile's rows are in flight
 #pragma unroll
     for (int col = 0; col < 9; ++col) {
       unsigned char* dx = sX + col * COL_BYTES + tid * 16;
@@ -422,8 +458,8 @@ __global__ void __launch_bounds__(128) sc_umma_rows_kernel(const ScArgs a, const
         for (int fz = 0; fz < 3; ++fz) {
 #pragma unroll
           for (int k16 = 0; k16 < CIN / 16; ++k16) {
-            const uint64_t da = umma_desc(smem_u32(sX + col * COL_BYTES + k16 * 2 * A_LBO + fz * 16), A_LBO, A_SBO);
-            const uint64_t db = umma_desc(smem_u32(sB + (col * 3 + fz) * B_TAP_BYTES + k16 * 2 * B_LBO), B_LBO, B_SBO);
+            const uint64_t da = umma_desc_advance(da0, col * COL_BYTES + k16 * 2 * A_LBO + fz * 16);
+            const uint64_t db = umma_desc_advance(db0, (col * 3 + fz) * B_TAP_BYTES + k16 * 2 * B_LBO);
             umma_bf16(tmem, da, db, IDESC, (col | fz | k16) != 0 ? 1u : 0u);
           }
         }
@@ -443,8 +479,8 @@ __global__ void __launch_bounds__(128) sc_umma_rows_kernel(const ScArgs a, const
     uint32_t acc[COUT];
     tmem_ld<COUT>(tmem + ((uint32_t)(warp * 32) << 16), acc);
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-    if (rvalid && j < D) {
-      uint4* o = reinterpret_cast<uint4*>(dst + ((size_t)pix * D + j) * COUT);
+    if (rvalid_out && j < D) {
+      uint4* o = reinterpret_cast<uint4*>(dst + ((size_t)pix_out * D + j) * COUT);
 #pragma unroll
       for (int q = 0; q < COUT / 8; ++q) {
         uint32_t w[4];
@@ -672,7 +708,7 @@ __global__ void __launch_bounds__(128) sc_umma_wgrad_kernel(const ScArgs a, cons
 // TG (transposed convolution) only changes the operand roles, exactly as in sc_umma_wgrad_kernel.
 // ---------------------------------------------------------------------------------------------------------
 template <int COUT, bool TG>
-__global__ void __launch_bounds__(128) sc_umma_wgrad_rows_kernel(const ScArgs a, const int ntiles, const int PT) {
+__global__ void __launch_bounds__(128, 4) sc_umma_wgrad_rows_kernel(const ScArgs a, const int ntiles, const int PT) {
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t mbar_s;
   __shared__ uint32_t tmem_base_s;
@@ -733,28 +769,31 @@ __global__ void __launch_bounds__(128) sc_umma_wgrad_rows_kernel(const ScArgs a,
   bool alive = true, first = true;
   float dacc = 0.f;
 
-  for (int tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
+  // This thread's row of a tile: its pixel, its out_grad row (zeros for rows that are not voxels) and its source
+  // voxel (or -1) in each of the nine filter columns (as in sc_umma_rows_kernel).
+  bool rvalid = false;
+  long long sv[9];
+  unsigned padmask = 0;                              // bit col: this row of column col is padding
+  uint4 gx[COUT / 8];
+  auto locate = [&](int tile) {
     const long long pix = (long long)tile * PT + p_in_tile;
-    const bool rvalid = row_used && pix < npix;
+    rvalid = row_used && tile < ntiles && pix < npix;
     const bool is_voxel = rvalid && j < D;          // rows j = D, D+1 of a pixel are halo rows, not output voxels
     int b = 0, r = 0, c = 0, bp_out = 0;
     if (rvalid) {
-      c = (int)(pix % W);
-      const long long t = pix / W;
-      r = (int)(t % H);
-      b = (int)(t / H);
+      const unsigned p32 = (unsigned)pix;   // pixel counts are validated to fit 31 bits
+      c = (int)(p32 % (unsigned)W);
+      const unsigned t = p32 / (unsigned)W;
+      r = (int)(t % (unsigned)H);
+      b = (int)(t / (unsigned)H);
       bp_out = __ldg(a.base_plane + pix);
     }
-    // out_grad row of this voxel -> G tile (zeros for rows that are not voxels)
 #pragma unroll
     for (int nc = 0; nc < COUT / 8; ++nc) {
-      uint4 x = zero4;
-      if (is_voxel) x = __ldg(reinterpret_cast<const uint4*>(og + ((size_t)pix * D + j) * COUT) + nc);
-      *reinterpret_cast<uint4*>(g_row + nc * G_SBO) = x;
+      gx[nc] = zero4;
+      if (is_voxel) gx[nc] = __ldg(reinterpret_cast<const uint4*>(og + ((size_t)pix * D + j) * COUT) + nc);
     }
-    // the nine filter columns, one row per thread and column (as in sc_umma_rows_kernel)
-    long long sv[9];
-    unsigned padmask = 0;                            // bit col: this row of column col is padding
+    padmask = 0;
 #pragma unroll
     for (int col = 0; col < 9; ++col) {
       const int orow = r - 1 + col / 3, ocol = c - 1 + col % 3;
@@ -765,16 +804,27 @@ __global__ void __launch_bounds__(128) sc_umma_wgrad_rows_kernel(const ScArgs a,
       sv[col] = ok ? (long long)np * D + plane : -1;
       if (!ok) padmask |= 1u << col;
     }
+  };
+  locate(blockIdx.x);
+  const uint64_t da0 = umma_desc(smem_u32(sX), X_LBO, X_SBO);
+  const uint64_t db0 = umma_desc(smem_u32(sG), G_LBO, G_SBO);
+
+  for (int tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
+#pragma unroll
+    for (int nc = 0; nc < COUT / 8; ++nc) *reinterpret_cast<uint4*>(g_row + nc * G_SBO) = gx[nc];
+    const bool rvalid_cur = rvalid;
+    const unsigned padmask_cur = padmask;
     uint4 val[9][KC];
 #pragma unroll
     for (int col = 0; col < 9; ++col) {
       const uint4* p = reinterpret_cast<const uint4*>(img + (size_t)(sv[col] >= 0 ? sv[col] : 0) * CIN);
 #pragma unroll
       for (int kc = 0; kc < KC; ++kc) {
-        val[col][kc] = rvalid ? padv : zero4;
+        val[col][kc] = rvalid_cur ? padv : zero4;
         if (sv[col] >= 0) val[col][kc] = __ldg(p + kc);
       }
     }
+    locate(tile + gridDim.x);   // the next tile's lookups and out_grad row run while this tile's rows are in flight
 #pragma unroll
     for (int col = 0; col < 9; ++col)
 #pragma unroll
@@ -791,8 +841,8 @@ __global__ void __launch_bounds__(128) sc_umma_wgrad_rows_kernel(const ScArgs a,
         for (int blk = 0; blk < 2; ++blk) {
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {   // 16 tile rows (two 8-row groups) per MMA
-            const uint64_t da = umma_desc(smem_u32(sX + blk * 2 * X_SBO + fz * 16 + ks * 2 * X_LBO), X_LBO, X_SBO);
-            const uint64_t db = umma_desc(smem_u32(sG + ks * 2 * G_LBO), G_LBO, G_SBO);
+            const uint64_t da = umma_desc_advance(da0, blk * 2 * X_SBO + fz * 16 + ks * 2 * X_LBO);
+            const uint64_t db = umma_desc_advance(db0, ks * 2 * G_LBO);
             umma_bf16(tmem + (fz * 2 + blk) * COUT, da, db, IDESC, (first && ks == 0) ? 0u : 1u);
           }
         }
@@ -805,7 +855,7 @@ __global__ void __launch_bounds__(128) sc_umma_wgrad_rows_kernel(const ScArgs a,
       // G tile (read here, behind the barrier above) holds that voxel's out_grad row at tile row tid - fz.
       for (int fz = 0; fz < 3; ++fz) {
         const int dv = j - fz;
-        if (!rvalid || dv < 0 || dv >= D || padmask == 0) continue;
+        if (!rvalid_cur || dv < 0 || dv >= D || padmask_cur == 0) continue;
         const unsigned char* grow = sG + ((tid - fz) / 8) * G_LBO + ((tid - fz) % 8) * 16;
         float gf[COUT];
 #pragma unroll
@@ -819,7 +869,7 @@ __global__ void __launch_bounds__(128) sc_umma_wgrad_rows_kernel(const ScArgs a,
           }
         }
         for (int col = 0; col < 9; ++col) {
-          if (!((padmask >> col) & 1u)) continue;
+          if (!((padmask_cur >> col) & 1u)) continue;
           const float* ws = wsum + (col * 3 + fz) * COUT;
 #pragma unroll
           for (int n = 0; n < COUT; ++n) dacc = fmaf(ws[n], gf[n], dacc);
