@@ -347,7 +347,9 @@ __global__ void __launch_bounds__(128, CIN <= 16 ? 4 : 2) sc_umma_rows_kernel(co
   __shared__ __align__(8) uint64_t mbar_s;
   __shared__ uint32_t tmem_base_s;
   constexpr int KC = CIN / 8;
-  constexpr int NRB = 136;                              // rows per column buffer: 128 + the two shifted reads, padded to 8
+  // rows per column buffer: 128 + the two shifted reads; 132 rows make the K-chunk stride 64 bytes off a multiple
+  // of 128, so the KC lanes that store the chunks of one row hit different banks
+  constexpr int NRB = 132;
   constexpr uint32_t B_LBO = 128, B_SBO = KC * 128;     // filter tiles: K-chunks adjacent, then 8-row groups
   constexpr uint32_t A_LBO = NRB * 16, A_SBO = 128;     // column buffers: rows linear, K-chunks NRB rows apart
   constexpr int B_TAP_BYTES = COUT * CIN * 2;
@@ -397,10 +399,11 @@ __global__ void __launch_bounds__(128, CIN <= 16 ? 4 : 2) sc_umma_rows_kernel(co
   const bool row_used = p_in_tile < PT;
   uint32_t phase = 0;
   bool alive = true;
-  // Source voxel (or -1) of this thread's row in each of the nine filter columns of a tile.
+  // Source voxel of this thread's row in each of the nine filter columns of a tile; -1 = padding (default_value),
+  // -2 = the row is not part of the tile (zeros).  Voxel indices fit 31 bits (checked on the host).
   long long pix = 0;
   bool rvalid = false;
-  long long sv[9];
+  int sv[9];
   auto locate = [&](int tile) {
     pix = (long long)tile * PT + p_in_tile;
     rvalid = row_used && tile < ntiles && pix < npix;
@@ -419,7 +422,7 @@ __global__ void __launch_bounds__(128, CIN <= 16 ? 4 : 2) sc_umma_rows_kernel(co
       const bool inb = rvalid && !oob(orow, H) && !oob(ocol, W);
       const int np = inb ? (b * H + orow) * W + ocol : 0;
       const int plane = j - 1 + bp_out - __ldg(a.base_plane + np);
-      sv[col] = (inb && !oob(plane, D)) ? (long long)np * D + plane : -1;
+      sv[col] = (inb && !oob(plane, D)) ? np * D + plane : (rvalid ? -1 : -2);
     }
   };
   locate(blockIdx.x);
@@ -430,22 +433,27 @@ __global__ void __launch_bounds__(128, CIN <= 16 ? 4 : 2) sc_umma_rows_kernel(co
     // flight together (their addresses were resolved during the previous tile) -------------------------------
     const long long pix_out = pix;
     const bool rvalid_out = rvalid;
+    // The KC 16-byte chunks of a row are fetched by KC neighbouring lanes (the row's owner hands its source voxel
+    // over by shuffle), so a warp-wide load covers whole rows - contiguous 32*16 bytes where the rows are
+    // consecutive planes of one pixel - instead of every other 16 bytes of twice the span: half the L1 wavefronts.
+    // Pass i of lane l: row 32*warp + l/KC + i*(32/KC), chunk l%KC.
     uint4 val[9][KC];
+    const int lane = tid & 31, chunk = lane % KC, lrow = lane / KC;
 #pragma unroll
     for (int col = 0; col < 9; ++col) {
-      const uint4* p = reinterpret_cast<const uint4*>(src + (size_t)(sv[col] >= 0 ? sv[col] : 0) * CIN);
 #pragma unroll
-      for (int kc = 0; kc < KC; ++kc) {
-        val[col][kc] = rvalid_out ? padv : make_uint4(0, 0, 0, 0);
-        if (sv[col] >= 0) val[col][kc] = __ldg(p + kc);
+      for (int i = 0; i < KC; ++i) {
+        const int sr = __shfl_sync(0xffffffffu, sv[col], lrow + i * (32 / KC));
+        val[col][i] = sr == -2 ? make_uint4(0, 0, 0, 0) : padv;
+        if (sr >= 0) val[col][i] = __ldg(reinterpret_cast<const uint4*>(src + (size_t)sr * CIN) + chunk);
       }
     }
     locate(tile + gridDim.x);   // the next tile's base-plane lookups run while this tile's rows are in flight
 #pragma unroll
     for (int col = 0; col < 9; ++col) {
-      unsigned char* dx = sX + col * COL_BYTES + tid * 16;
+      unsigned char* dx = sX + col * COL_BYTES + chunk * A_LBO + (warp * 32 + lrow) * 16;
 #pragma unroll
-      for (int kc = 0; kc < KC; ++kc) *reinterpret_cast<uint4*>(dx + kc * A_LBO) = val[col][kc];
+      for (int i = 0; i < KC; ++i) *reinterpret_cast<uint4*>(dx + i * (32 / KC) * 16) = val[col][i];
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -714,7 +722,7 @@ __global__ void __launch_bounds__(128, 4) sc_umma_wgrad_rows_kernel(const ScArgs
   __shared__ uint32_t tmem_base_s;
   __shared__ float red_s[128];
   constexpr int CIN = 16, KC = 2;
-  constexpr int NRB = 136;
+  constexpr int NRB = 132;                         // as in sc_umma_rows_kernel
   constexpr uint32_t X_SBO = NRB * 16;             // chunk stride (M direction)
   constexpr uint32_t X_LBO = 128;                  // eight voxels further (reduction direction): rows are linear
   constexpr uint32_t G_SBO = 128, G_LBO = (COUT / 8) * 128;
@@ -772,7 +780,7 @@ __global__ void __launch_bounds__(128, 4) sc_umma_wgrad_rows_kernel(const ScArgs
   // This thread's row of a tile: its pixel, its out_grad row (zeros for rows that are not voxels) and its source
   // voxel (or -1) in each of the nine filter columns (as in sc_umma_rows_kernel).
   bool rvalid = false;
-  long long sv[9];
+  int sv[9];                                         // -1 = padding, -2 = row not in the tile
   unsigned padmask = 0;                              // bit col: this row of column col is padding
   uint4 gx[COUT / 8];
   auto locate = [&](int tile) {
@@ -801,7 +809,7 @@ __global__ void __launch_bounds__(128, 4) sc_umma_wgrad_rows_kernel(const ScArgs
       const int np = inb ? (b * H + orow) * W + ocol : 0;
       const int plane = j - 1 + bp_out - __ldg(a.base_plane + np);
       const bool ok = inb && !oob(plane, D);
-      sv[col] = ok ? (long long)np * D + plane : -1;
+      sv[col] = ok ? np * D + plane : (rvalid ? -1 : -2);
       if (!ok) padmask |= 1u << col;
     }
   };
@@ -814,21 +822,25 @@ __global__ void __launch_bounds__(128, 4) sc_umma_wgrad_rows_kernel(const ScArgs
     for (int nc = 0; nc < COUT / 8; ++nc) *reinterpret_cast<uint4*>(g_row + nc * G_SBO) = gx[nc];
     const bool rvalid_cur = rvalid;
     const unsigned padmask_cur = padmask;
+    // the two 16-byte chunks of a row are fetched by neighbouring lanes (see sc_umma_rows_kernel)
     uint4 val[9][KC];
+    const int lane = tid & 31, chunk = lane % KC, lrow = lane / KC;
 #pragma unroll
     for (int col = 0; col < 9; ++col) {
-      const uint4* p = reinterpret_cast<const uint4*>(img + (size_t)(sv[col] >= 0 ? sv[col] : 0) * CIN);
 #pragma unroll
-      for (int kc = 0; kc < KC; ++kc) {
-        val[col][kc] = rvalid_cur ? padv : zero4;
-        if (sv[col] >= 0) val[col][kc] = __ldg(p + kc);
+      for (int i = 0; i < KC; ++i) {
+        const int sr = __shfl_sync(0xffffffffu, sv[col], lrow + i * (32 / KC));
+        val[col][i] = sr == -2 ? zero4 : padv;
+        if (sr >= 0) val[col][i] = __ldg(reinterpret_cast<const uint4*>(img + (size_t)sr * CIN) + chunk);
       }
     }
     locate(tile + gridDim.x);   // the next tile's lookups and out_grad row run while this tile's rows are in flight
 #pragma unroll
-    for (int col = 0; col < 9; ++col)
+    for (int col = 0; col < 9; ++col) {
+      unsigned char* dx = sX + (col * KC + chunk) * X_SBO + (warp * 32 + lrow) * 16;
 #pragma unroll
-      for (int kc = 0; kc < KC; ++kc) *reinterpret_cast<uint4*>(sX + (col * KC + kc) * X_SBO + tid * 16) = val[col][kc];
+      for (int i = 0; i < KC; ++i) *reinterpret_cast<uint4*>(dx + i * (32 / KC) * 16) = val[col][i];
+    }
 
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -986,7 +998,7 @@ __global__ void __launch_bounds__(256) sc_umma_wgrad_reduce_t(const float* part,
 template <int COUT, bool TG>
 int launch_wgrad_rows(const ScArgs& a, int nparts, cudaStream_t st) {
   auto k = sc_umma_wgrad_rows_kernel<COUT, TG>;
-  const size_t smem = (size_t)18 * 136 * 16 + (size_t)16 * (COUT / 8) * 128 + (size_t)27 * COUT * 4 + 1024;
+  const size_t smem = (size_t)18 * 132 * 16 + (size_t)16 * (COUT / 8) * 128 + (size_t)27 * COUT * 4 + 1024;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -1042,7 +1054,7 @@ int launch_wgrad(const ScArgs& a, int nparts, cudaStream_t st) {
 template <int CIN, int COUT, bool DGRAD>
 int launch_rows(const ScArgs& a, cudaStream_t st) {
   auto k = sc_umma_rows_kernel<CIN, COUT, DGRAD>;
-  const size_t smem = (size_t)27 * COUT * CIN * 2 + (size_t)9 * (CIN / 8) * 136 * 16 + 1024;
+  const size_t smem = (size_t)27 * COUT * CIN * 2 + (size_t)9 * (CIN / 8) * 132 * 16 + 1024;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
