@@ -725,7 +725,11 @@ __global__ void __launch_bounds__(128, 4) sc_umma_wgrad_rows_kernel(const ScArgs
   constexpr int NRB = 132;                         // as in sc_umma_rows_kernel
   constexpr uint32_t X_SBO = NRB * 16;             // chunk stride (M direction)
   constexpr uint32_t X_LBO = 128;                  // eight voxels further (reduction direction): rows are linear
-  constexpr uint32_t G_SBO = 128, G_LBO = (COUT / 8) * 128;
+  // out_grad tile with the three depth taps side by side in N: chunk fz*(COUT/8) + nc of voxel group m'/8 holds
+  // channels nc*8.. of out_grad row m' - fz, so ONE MMA with N = 3*COUT per 16 tile rows serves the three taps
+  // (an N = 16 MMA costs the issuing thread as much as an N = 48 one, and that thread is the tile's critical path)
+  constexpr int NCH = 3 * (COUT / 8);              // 16-byte chunks per row of the widened tile
+  constexpr uint32_t G_SBO = 128, G_LBO = NCH * 128;
   constexpr int TMEM_COLS = 6 * COUT <= 128 ? 128 : 256;
   unsigned char* sX = smem;                        // 18 chunks x NRB rows x 16 B
   unsigned char* sG = smem + 18 * X_SBO;           // 16 voxel groups x G_LBO
@@ -744,6 +748,12 @@ __global__ void __launch_bounds__(128, 4) sc_umma_wgrad_rows_kernel(const ScArgs
       wsum[e] = sum;
     }
   }
+  // rows 0 (tap 1) and 0, 1 (tap 2) of the widened out_grad tile have no source row: zero, once
+  if (tid < 3 * (COUT / 8)) {
+    const int which = tid / (COUT / 8), nc = tid % (COUT / 8);          // (tap 1,row 0), (tap 2,row 0), (tap 2,row 1)
+    const int fz = which == 0 ? 1 : 2, row = which == 2 ? 1 : 0;
+    *reinterpret_cast<uint4*>(sG + (fz * (COUT / 8) + nc) * G_SBO + row * 16) = make_uint4(0, 0, 0, 0);
+  }
   for (int e = tid; e < 18 * (NRB - 128); e += 128)   // rows 128..135: only multiplied by zero rows of out_grad, but
     *reinterpret_cast<uint4*>(sX + (e / (NRB - 128)) * X_SBO + (128 + e % (NRB - 128)) * 16) = make_uint4(0, 0, 0, 0);  // must be finite
   if (warp == 0) {
@@ -761,7 +771,7 @@ __global__ void __launch_bounds__(128, 4) sc_umma_wgrad_rows_kernel(const ScArgs
   const uint32_t tmem = tmem_base_s;
   const uint32_t mbar = smem_u32(&mbar_s);
   // D f32, A/B bf16, both operands MN-major (bits 15, 16), N = COUT, M = 128
-  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(COUT >> 3) << 17) |
+  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((uint32_t)((3 * COUT) >> 3) << 17) |
                              ((128u >> 4) << 24);
   const unsigned d16 = __ldg(static_cast<const unsigned short*>(a.default_value));
   const unsigned d32 = d16 | (d16 << 16);
@@ -772,7 +782,6 @@ __global__ void __launch_bounds__(128, 4) sc_umma_wgrad_rows_kernel(const ScArgs
   const long long npix = (long long)a.B * H * W;
   const int p_in_tile = tid / RP, j = tid - p_in_tile * RP;
   const bool row_used = p_in_tile < PT;
-  unsigned char* g_row = sG + (tid / 8) * G_LBO + (tid % 8) * 16;
   uint32_t phase = 0;
   bool alive = true, first = true;
   float dacc = 0.f;
@@ -818,8 +827,16 @@ __global__ void __launch_bounds__(128, 4) sc_umma_wgrad_rows_kernel(const ScArgs
   const uint64_t db0 = umma_desc(smem_u32(sG), G_LBO, G_SBO);
 
   for (int tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
+    // this thread's out_grad row m goes to row m + fz of tap block fz (rows 126, 127 are never voxels)
 #pragma unroll
-    for (int nc = 0; nc < COUT / 8; ++nc) *reinterpret_cast<uint4*>(g_row + nc * G_SBO) = gx[nc];
+    for (int fz = 0; fz < 3; ++fz) {
+      const int m = tid + fz;
+      if (m < 128) {
+        unsigned char* g_row = sG + (m / 8) * G_LBO + (m % 8) * 16 + fz * (COUT / 8) * G_SBO;
+#pragma unroll
+        for (int nc = 0; nc < COUT / 8; ++nc) *reinterpret_cast<uint4*>(g_row + nc * G_SBO) = gx[nc];
+      }
+    }
     const bool rvalid_cur = rvalid;
     const unsigned padmask_cur = padmask;
     // the two 16-byte chunks of a row are fetched by neighbouring lanes (see sc_umma_rows_kernel)
@@ -848,15 +865,12 @@ __global__ void __launch_bounds__(128, 4) sc_umma_wgrad_rows_kernel(const ScArgs
     if (tid == 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-      for (int fz = 0; fz < 3; ++fz) {
+      for (int blk = 0; blk < 2; ++blk) {
 #pragma unroll
-        for (int blk = 0; blk < 2; ++blk) {
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {   // 16 tile rows (two 8-row groups) per MMA
-            const uint64_t da = umma_desc_advance(da0, blk * 2 * X_SBO + fz * 16 + ks * 2 * X_LBO);
-            const uint64_t db = umma_desc_advance(db0, ks * 2 * G_LBO);
-            umma_bf16(tmem + (fz * 2 + blk) * COUT, da, db, IDESC, (first && ks == 0) ? 0u : 1u);
-          }
+        for (int ks = 0; ks < 8; ++ks) {   // 16 tile rows (two 8-row groups) per MMA
+          const uint64_t da = umma_desc_advance(da0, blk * 2 * X_SBO + ks * 2 * X_LBO);
+          const uint64_t db = umma_desc_advance(db0, ks * 2 * G_LBO);
+          umma_bf16(tmem + blk * 3 * COUT, da, db, IDESC, (first && ks == 0) ? 0u : 1u);
         }
       }
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
@@ -909,7 +923,7 @@ __global__ void __launch_bounds__(128, 4) sc_umma_wgrad_rows_kernel(const ScArgs
       for (int blk = 0; blk < 2; ++blk) {
         uint32_t acc[COUT];
         if (!first) {
-          tmem_ld<COUT>(tmem + ((uint32_t)(warp * 32) << 16) + (fz * 2 + blk) * COUT, acc);
+          tmem_ld<COUT>(tmem + ((uint32_t)(warp * 32) << 16) + (blk * 3 + fz) * COUT, acc);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         }
         // MMA row tid of block blk is chunk q = 2*blk + tid/8, element tid%8: column q/2, channel (q%2)*8 + tid%8.
@@ -998,7 +1012,7 @@ __global__ void __launch_bounds__(256) sc_umma_wgrad_reduce_t(const float* part,
 template <int COUT, bool TG>
 int launch_wgrad_rows(const ScArgs& a, int nparts, cudaStream_t st) {
   auto k = sc_umma_wgrad_rows_kernel<COUT, TG>;
-  const size_t smem = (size_t)18 * 132 * 16 + (size_t)16 * (COUT / 8) * 128 + (size_t)27 * COUT * 4 + 1024;
+  const size_t smem = (size_t)18 * 132 * 16 + (size_t)16 * 3 * (COUT / 8) * 128 + (size_t)27 * COUT * 4 + 1024;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
