@@ -328,6 +328,46 @@ __global__ void __launch_bounds__(128) sc_umma_kernel(const ScArgs a, const long
 }
 
 
+// ---- per-tile table of filter columns for the shifted-row kernels -------------------------------------------
+// Entry (pixel q of the tile, filter column col) = {first voxel of the neighbour pixel (-1: outside the image,
+// -2: the tile has no such pixel), base_plane[pixel] - base_plane[neighbour]}.  The D + 2 rows of a pixel share
+// these nine entries, so the CTA computes each once (one entry per thread) instead of once per row.
+constexpr int ROWS_TAB = 42 * 9;   // a tile has at most 128 / 3 pixels
+__device__ __forceinline__ void rows_tab_write(const ScArgs& a, int2* tab, int tile, int ntiles, int PT, long long npix, int tid) {
+  for (int e = tid; e < PT * 9; e += 128) {
+    const int q = e / 9, col = e - q * 9;
+    const long long pix = (long long)tile * PT + q;
+    int2 ent = make_int2(-2, 0);
+    if (tile < ntiles && pix < npix) {
+      const unsigned p32 = (unsigned)pix;   // pixel counts are validated to fit 31 bits
+      const int c = (int)(p32 % (unsigned)a.W);
+      const unsigned t = p32 / (unsigned)a.W;
+      const int r = (int)(t % (unsigned)a.H), b = (int)(t / (unsigned)a.H);
+      const int orow = r - 1 + col / 3, ocol = c - 1 + col % 3;
+      ent.x = -1;
+      if (!oob(orow, a.H) && !oob(ocol, a.W)) {
+        const int np = (b * a.H + orow) * a.W + ocol;
+        ent.x = np * a.D;                   // voxel indices fit 31 bits (checked on the host)
+        ent.y = __ldg(a.base_plane + pix) - __ldg(a.base_plane + np);
+      }
+    }
+    tab[e] = ent;
+  }
+}
+// Source voxel of row j of pixel q in each column: >= 0, -1 = padding (default_value), -2 = not part of the tile.
+__device__ __forceinline__ void rows_tab_read(const int2* tab, int q, int j, int D, bool row_used, int* sv) {
+#pragma unroll
+  for (int col = 0; col < 9; ++col) {
+    int v = -2;
+    if (row_used) {
+      const int2 e = tab[q * 9 + col];
+      const int plane = j - 1 + e.y;
+      v = e.x >= 0 ? (oob(plane, D) ? -1 : e.x + plane) : e.x;
+    }
+    sv[col] = v;
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // Stride-1 variant with ONE staged copy per neighbour pixel instead of one per tap.
 //
@@ -346,6 +386,7 @@ __global__ void __launch_bounds__(128, CIN <= 16 ? 4 : 2) sc_umma_rows_kernel(co
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t mbar_s;
   __shared__ uint32_t tmem_base_s;
+  __shared__ int2 tab_s[ROWS_TAB];
   constexpr int KC = CIN / 8;
   // rows per column buffer: 128 + the two shifted reads; 132 rows make the K-chunk stride 64 bytes off a multiple
   // of 128, so the KC lanes that store the chunks of one row hit different banks
@@ -378,6 +419,7 @@ __global__ void __launch_bounds__(128, CIN <= 16 ? 4 : 2) sc_umma_rows_kernel(co
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&mbar_s)), "r"(1) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  rows_tab_write(a, tab_s, blockIdx.x, ntiles, PT, (long long)a.B * a.H * a.W, tid);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -404,41 +446,18 @@ __global__ void __launch_bounds__(128, CIN <= 16 ? 4 : 2) sc_umma_rows_kernel(co
   long long pix = 0;
   bool rvalid = false;
   int sv[9];
-  auto locate = [&](int tile) {
+  auto locate = [&](int tile) {   // from the table that rows_tab_write(tile) left in shared memory
     pix = (long long)tile * PT + p_in_tile;
     rvalid = row_used && tile < ntiles && pix < npix;
-    int b = 0, r = 0, c = 0, bp_out = 0;
-    if (rvalid) {
-      const unsigned p32 = (unsigned)pix;   // pixel counts are validated to fit 31 bits
-      c = (int)(p32 % (unsigned)W);
-      const unsigned t = p32 / (unsigned)W;
-      r = (int)(t % (unsigned)H);
-      b = (int)(t / (unsigned)H);
-      bp_out = __ldg(a.base_plane + pix);
-    }
-#pragma unroll
-    for (int col = 0; col < 9; ++col) {
-      const int orow = r - 1 + col / 3, ocol = c - 1 + col % 3;
-      const bool inb = rvalid && !oob(orow, H) && !oob(ocol, W);
-      const int np = inb ? (b * H + orow) * W + ocol : 0;
-      const int plane = j - 1 + bp_out - __ldg(a.base_plane + np);
-      sv[col] = (inb && !oob(plane, D)) ? np * D + plane : (rvalid ? -1 : -2);
-    }
+    rows_tab_read(tab_s, p_in_tile, j, D, row_used, sv);
   };
-  locate(blockIdx.x);
-  const uint64_t da0 = umma_desc(smem_u32(sX), A_LBO, A_SBO);
-  const uint64_t db0 = umma_desc(smem_u32(sB), B_LBO, B_SBO);
-  for (int tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
-    // ---- stage the nine filter columns: one row per thread and column; the nine neighbour rows are all in
-    // flight together (their addresses were resolved during the previous tile) -------------------------------
-    const long long pix_out = pix;
-    const bool rvalid_out = rvalid;
-    // The KC 16-byte chunks of a row are fetched by KC neighbouring lanes (the row's owner hands its source voxel
-    // over by shuffle), so a warp-wide load covers whole rows - contiguous 32*16 bytes where the rows are
-    // consecutive planes of one pixel - instead of every other 16 bytes of twice the span: half the L1 wavefronts.
-    // Pass i of lane l: row 32*warp + l/KC + i*(32/KC), chunk l%KC.
-    uint4 val[9][KC];
-    const int lane = tid & 31, chunk = lane % KC, lrow = lane / KC;
+  // The KC 16-byte chunks of a row are fetched by KC neighbouring lanes (the row's owner hands its source voxel
+  // over by shuffle), so a warp-wide load covers whole rows - contiguous 32*16 bytes where the rows are
+  // consecutive planes of one pixel - instead of every other 16 bytes of twice the span: half the L1 wavefronts.
+  // Pass i of lane l: row 32*warp + l/KC + i*(32/KC), chunk l%KC.
+  uint4 val[9][KC];
+  const int lane = tid & 31, chunk = lane % KC, lrow = lane / KC;
+  auto request = [&]() {
 #pragma unroll
     for (int col = 0; col < 9; ++col) {
 #pragma unroll
@@ -448,7 +467,19 @@ __global__ void __launch_bounds__(128, CIN <= 16 ? 4 : 2) sc_umma_rows_kernel(co
         if (sr >= 0) val[col][i] = __ldg(reinterpret_cast<const uint4*>(src + (size_t)sr * CIN) + chunk);
       }
     }
-    locate(tile + gridDim.x);   // the next tile's base-plane lookups run while this tile's rows are in flight
+  };
+  locate(blockIdx.x);
+  request();
+  const uint64_t da0 = umma_desc(smem_u32(sX), A_LBO, A_SBO);
+  const uint64_t db0 = umma_desc(smem_u32(sB), B_LBO, B_SBO);
+  for (int tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
+    // ---- stage the nine filter columns: this tile's rows were requested a tile ago and waited in registers
+    // while the previous tile's MMAs and epilogue ran (the gather latency is the longest step of a tile) --------
+    const long long pix_out = pix;
+    const bool rvalid_out = rvalid;
+    // the next tile's column table (everybody has read the current one: it was consumed before the barrier that
+    // closed the previous tile)
+    rows_tab_write(a, tab_s, tile + gridDim.x, ntiles, PT, npix, tid);
 #pragma unroll
     for (int col = 0; col < 9; ++col) {
       unsigned char* dx = sX + col * COL_BYTES + chunk * A_LBO + (warp * 32 + lrow) * 16;
@@ -474,6 +505,8 @@ __global__ void __launch_bounds__(128, CIN <= 16 ? 4 : 2) sc_umma_rows_kernel(co
       }
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
     }
+    locate(tile + gridDim.x);   // table written before the barrier above; read here, before the barrier below
+    request();                  // in flight during this tile's MMAs and epilogue
     const bool done = mbar_wait(mbar, phase);
     phase ^= 1;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
