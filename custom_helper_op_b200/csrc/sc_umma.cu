@@ -470,6 +470,7 @@ __global__ void __launch_bounds__(128, CIN <= 16 ? 4 : 2) sc_umma_rows_kernel(co
   };
   locate(blockIdx.x);
   request();
+  __syncthreads();   // everybody has read the first tile's table before the loop writes the next one
   const uint64_t da0 = umma_desc(smem_u32(sX), A_LBO, A_SBO);
   const uint64_t db0 = umma_desc(smem_u32(sB), B_LBO, B_SBO);
   for (int tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
