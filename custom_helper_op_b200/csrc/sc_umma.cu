@@ -288,14 +288,16 @@ __global__ void __launch_bounds__(128) sc_umma_kernel(const ScArgs a, const long
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
       }
       // ---- everyone waits until the tensor core has consumed the staging buffer ------------------------------
-      const bool done = mbar_wait(mbar, phase);
+      // one warp polls the mbarrier (every poll is a shared-memory access); the others wait at the hardware barrier
+      bool done = true;
+      if (warp == 0) done = mbar_wait(mbar, phase);
       phase ^= 1;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (!__syncthreads_and(done)) {
         if (tid == 0) atomicAdd(&g_umma_timeouts, 1);
         alive = false;
         break;
       }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
     if (!alive) break;
 
@@ -508,14 +510,16 @@ __global__ void __launch_bounds__(128, CIN <= 16 ? 4 : 2) sc_umma_rows_kernel(co
     }
     locate(tile + gridDim.x);   // table written before the barrier above; read here, before the barrier below
     request();                  // in flight during this tile's MMAs and epilogue
-    const bool done = mbar_wait(mbar, phase);
+    // one warp polls the mbarrier (every poll is a shared-memory access); the others wait at the hardware barrier
+    bool done = true;
+    if (warp == 0) done = mbar_wait(mbar, phase);
     phase ^= 1;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (!__syncthreads_and(done)) {
       if (tid == 0) atomicAdd(&g_umma_timeouts, 1);
       alive = false;
       break;
     }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
     // ---- epilogue: MMA row m = this thread's row; it is output voxel (pixel, j) when j < D -----------------------
     uint32_t acc[COUT];
@@ -690,14 +694,16 @@ __global__ void __launch_bounds__(128) sc_umma_wgrad_kernel(const ScArgs a, cons
         }
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
       }
-      const bool done = mbar_wait(mbar, phase);
+      // one warp polls the mbarrier (every poll is a shared-memory access); the others wait at the hardware barrier
+      bool done = true;
+      if (warp == 0) done = mbar_wait(mbar, phase);
       phase ^= 1;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (!__syncthreads_and(done)) {
         if (tid == 0) atomicAdd(&g_umma_timeouts, 1);
         alive = false;
         break;
       }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
     first = false;
   }
@@ -936,14 +942,16 @@ __global__ void __launch_bounds__(128, 4) sc_umma_wgrad_rows_kernel(const ScArgs
         }
       }
     }
-    const bool done = mbar_wait(mbar, phase);
+    // one warp polls the mbarrier (every poll is a shared-memory access); the others wait at the hardware barrier
+    bool done = true;
+    if (warp == 0) done = mbar_wait(mbar, phase);
     phase ^= 1;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (!__syncthreads_and(done)) {
       if (tid == 0) atomicAdd(&g_umma_timeouts, 1);
       alive = false;
       break;
     }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     first = false;
   }
 
