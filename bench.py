@@ -436,7 +436,8 @@ def secondary_main(args):
     hot path.  c4_updown: the strided manifold convolution (2,2,2) that halves the c4 band, the transposed
     convolution that brings it back and SparsePad, bf16, forward + gradient each.  c1_v3: CostVolumeV3 (8 groups,
     MEAN) forward + gradient on the c1 shapes, fp32.  c1_fa: FeatureAggregate forward + gradient on the c1 shapes
-    (the forward allocates its 1 GB output every step, as the op does).  Single GPU, L2 flushed between steps."""
+    (the forward allocates its 1 GB output every step, as the op does).  c1_min: CostVolume and CostAggregate with the MIN
+    reduction, forward + gradient each, c1 shapes, fp32.  Single GPU, L2 flushed between steps."""
     import torch
 
     from custom_helper_op_b200 import synth
@@ -492,6 +493,31 @@ def secondary_main(args):
         units, unit = fine.numel() // C, "fine voxels/s"
         desc = "c4_updown: SparseConv3DFast strides (2,2,2) + SparseConv3DTransposeFast + SparsePad, fine band %dx%dx%d, " \
                "3x3x3, %d->%d, bf16/fp32-acc" % (H, W_, D, C, C)
+        launches = 10
+    elif args.workload == "c1_min":
+        # the MIN reduction (the reference layers' default): CostVolume and CostAggregate, forward + gradient
+        wl = synth.make("c1_mvsnet", with_grad=False)
+        t = {k: torch.from_numpy(v).to(dev) for k, v in wl.items()}
+        B, H, W_, C = t["ref"].shape
+        D, N = t["offsets"].shape[1], t["src"].shape[1]
+        a = (t["ref"], t["src"], t["base_plane"], t["offsets"], t["Rs"], t["Ts"])
+        cost1, mask1 = ops.cost_forward(1, *a, "MIN")
+        cg1 = torch.randn_like(cost1)
+        cost3, mask3 = ops.cost_forward(3, *a, "MIN")
+        cg3 = torch.randn_like(cost3)
+        names = ["cost_volume_min_fwd", "cost_volume_min_bwd", "cost_aggregate_min_fwd", "cost_aggregate_min_bwd"]
+        ms = timed([lambda: ops.cost_forward(1, *a, "MIN", out=(cost1, mask1)),
+                    lambda: ops.cost_backward(1, *a, cg1, mask1, "MIN"),
+                    lambda: ops.cost_forward(3, *a, "MIN", out=(cost3, mask3)),
+                    lambda: ops.cost_backward(3, *a, cg3, mask3, "MIN")])
+        feats = (1 + N) * B * H * W_ * C * 4
+        vox = B * H * W_ * D
+        small = 4 * B * H * W_
+        # cost and arg indices are both [.., C] for CostVolume MIN, one value per voxel for CostAggregate
+        alg = [feats + 8 * vox * C + small, 2 * feats + 8 * vox * C + 2 * small,
+               feats + 8 * vox + small, 2 * feats + 8 * vox + 2 * small]
+        units, unit = 2 * vox * N, UNIT
+        desc = "c1_min: CostVolume and CostAggregate, MIN, fwd+bwd fp32, B=%d, V=%d, C=%d, %dx%d, D=%d" % (B, N + 1, C, H, W_, D)
         launches = 10
     elif args.workload == "c1_fa":
         wl = synth.make("c1_mvsnet", with_grad=False)
@@ -574,7 +600,7 @@ def main():
     ap.add_argument("--profile", action="store_true",
                     help="device-timed loop only (no clock probe loop, e2e leg or CPU baseline): the command to run under ncu")
     args = ap.parse_args()
-    if args.workload in ("c4_updown", "c1_v3", "c1_fa"):
+    if args.workload in ("c4_updown", "c1_v3", "c1_fa", "c1_min"):
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "secondary workload: timed on the GPU only"}))
         else:
