@@ -89,10 +89,10 @@ int validate(const chop_cv_desc* d, CvArgs* a, Typed* ty) {
 
 // CostVolume MEAN (fused arithmetic) with a common channel count runs the compile-time-C kernels of
 // cv_tuned.cuh, which use four channels per lane for float32 and bfloat16 features alike.
-// The backward kernels also exist for MIN.
 bool tuned_eligible(const chop_cv_desc* d, const CvArgs& a, bool backward) {
   if (!g_tuned.load() || !(d->dtype == CHOP_F32 || d->dtype == CHOP_BF16)) return false;
-  const bool min_ok = backward;
+  // MIN: every gradient kernel, and the CostVolume forward for up to 32 channels and 254 views
+  const bool min_ok = backward || (d->kind == CHOP_COST_VOLUME && a.C <= 32 && a.N <= 254);
   if (d->reduce != CHOP_REDUCE_MEAN && !min_ok) return false;
   if (d->kind == CHOP_COST_VOLUME || d->kind == CHOP_COST_AGGREGATE) return a.C == 8 || a.C == 16 || a.C == 32 || a.C == 64;
   if (d->kind == CHOP_COST_VOLUME_V2) {
