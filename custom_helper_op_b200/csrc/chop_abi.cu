@@ -91,8 +91,9 @@ int validate(const chop_cv_desc* d, CvArgs* a, Typed* ty) {
 // cv_tuned.cuh, which use four channels per lane for float32 and bfloat16 features alike.
 bool tuned_eligible(const chop_cv_desc* d, const CvArgs& a, bool backward) {
   if (!g_tuned.load() || !(d->dtype == CHOP_F32 || d->dtype == CHOP_BF16)) return false;
-  // MIN: every gradient kernel, and the CostVolume forward for up to 32 channels and 254 views
-  const bool min_ok = backward || (d->kind == CHOP_COST_VOLUME && a.C <= 32 && a.N <= 254);
+  // MIN: every gradient kernel, and the CostVolume / CostAggregate forward for up to 32 channels (254 views)
+  const bool min_ok = backward || (d->kind == CHOP_COST_VOLUME && a.C <= 32 && a.N <= 254) ||
+                      (d->kind == CHOP_COST_AGGREGATE && a.C <= 32);
   if (d->reduce != CHOP_REDUCE_MEAN && !min_ok) return false;
   if (d->kind == CHOP_COST_VOLUME || d->kind == CHOP_COST_AGGREGATE) return a.C == 8 || a.C == 16 || a.C == 32 || a.C == 64;
   if (d->kind == CHOP_COST_VOLUME_V2) {

@@ -18,6 +18,14 @@ int cv_fwd_f32(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
     const int r = tuned2_dispatch<float>(false, false, a, st);
     if (r != -4) return r;  // -4: no compile-time-C kernel for this (C, groups): generic kernel below
   }
+  if (p.use_tuned && p.kind == 3 && p.mode == 2 && p.cpl == 4) {
+    switch (a.C) {
+      case 8: return agg_min_fwd_tuned_go<float, 8, 4>(a, st);
+      case 16: return agg_min_fwd_tuned_go<float, 16, 4>(a, st);
+      case 32: return agg_min_fwd_tuned_go<float, 32, 4>(a, st);
+      default: break;
+    }
+  }
   if (p.use_tuned && p.kind == 1 && p.mode == 2 && p.cpl == 4 && a.N <= 254) {
     switch (a.C) {
       case 8: return fwd_min_tuned_go<float, 8, 4>(a, st);

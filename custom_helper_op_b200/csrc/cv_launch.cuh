@@ -123,6 +123,22 @@ inline int fwd_min_tuned_go(const CvArgs& a, cudaStream_t st) {
   return (int)cudaGetLastError();
 }
 
+template <typename T, int C, int CPL>
+inline int agg_min_fwd_tuned_go(const CvArgs& a, cudaStream_t st) {
+  auto k = cv_agg_min_fwd_tuned<T, C, CPL>;
+  const size_t spw = tuned_fwd_smem_per_warp<T>(a.N, 32 / (C / CPL)) + (size_t)32 * (C + 4) * sizeof(float);
+  const int warps = tuned_warps(spw);
+  const size_t smem = spw * warps;
+  if (smem > 200 * 1024) return -4;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const long long items = (long long)a.npb * a.nchunks;
+  k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw);
+  return (int)cudaGetLastError();
+}
+
 template <typename T, int C, int CPL, bool AGG = false, bool RMIN = false>
 inline int bwd_tuned_go(const CvArgs& a, cudaStream_t st) {
   auto k = cv_bwd_tuned<T, C, CPL, AGG, RMIN>;

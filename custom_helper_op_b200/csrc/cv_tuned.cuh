@@ -306,6 +306,121 @@ __global__ void __launch_bounds__(256, 2) cv_fwd_min_tuned(const CvArgs a, const
   }
 }
 
+// CostAggregate MIN forward (cost_aggregate_kernels_gpu.cu.cc:129-227): the view with the smallest channel SUM of
+// squared differences wins the voxel.  The reference adds the C values one by one, so the sum is formed in that
+// order by one lane per plane after a transpose through shared memory (rows of C + 4 floats: conflict-free 16-byte
+// reads); the corners stay cached in registers along the planes as in the kernels above.
+template <typename T, int C, int CPL>
+__global__ void __launch_bounds__(256, 2) cv_agg_min_fwd_tuned(const CvArgs a, const int warps, const size_t smem_per_warp) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int LG = C / CPL;
+  constexpr int G = 32 / LG;
+  static_assert(CPL == 4 && LG * CPL == C && (LG & (LG - 1)) == 0 && LG <= 8, "four channels per lane, at most 8 lanes per pixel");
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  const int li = lane & (LG - 1);
+  const int g = lane / LG;
+
+  const long long item = (long long)blockIdx.x * warps + wib;
+  if (item >= (long long)a.npb * a.nchunks) return;
+  const int chunk_id = (int)(item / a.npb);
+  const int pb = (int)(item - (long long)chunk_id * a.npb);
+  const long long pix0 = (long long)pb * G;
+  const bool pvalid = pix0 + g < a.npix;
+  const long long pix = pvalid ? pix0 + g : a.npix - 1;
+  const int dlo = a.d_begin + chunk_id * a.chunk;
+  const int dhi = min(a.d_end, dlo + a.chunk);
+  const int N = a.N;
+  const int D = a.D;
+
+  unsigned char* mine = smem_raw + (size_t)wib * smem_per_warp;
+  Coef<float>* coef = reinterpret_cast<Coef<float>*>(mine);
+  ProjF<float>* proj = reinterpret_cast<ProjF<float>*>(coef + N * G);
+  constexpr int RS = C + 4;                                            // row stride of the transpose scratch (floats)
+  float* rows = reinterpret_cast<float*>(proj + N * 32) + (g * LG) * RS;   // this pixel's LG rows
+
+  stage_coefs<float>(a, coef, lane, G, pix0);
+  __syncwarp();
+
+  const T* src_lane = static_cast<const T*>(a.src) + li * CPL;
+  float refv[CPL];
+  Vec<T, float, CPL>::load(static_cast<const T*>(a.ref) + pix * C + li * CPL, refv);
+  const int b = (int)(pix / ((long long)a.H * a.W));
+  const float base = static_cast<const float*>(a.depth)[pix];
+  const float* offs = static_cast<const float*>(a.offsets) + (long long)b * D;
+  const size_t row = (size_t)a.Ws * C;
+  const ProjF<float>* myrec = proj + g * LG;
+  float* out = static_cast<float*>(a.cost) + pix * D + dlo + li;
+  int* outm = a.mask + pix * D + dlo + li;
+
+  for (int dblk = dlo; dblk < dhi; dblk += LG, out += LG, outm += LG) {
+    // ---- phase A: lane (g, li) projects plane dblk+li of pixel g into every view ---------------------
+    {
+      const int d = dblk + li;
+      const bool dv = pvalid && d < dhi;
+      const float depth = dv ? xadd(base, offs[d]) : 0.0f;
+      for (int n = 0; n < N; ++n) {
+        ProjF<float> r;
+        r.texel = -1;
+        r.dh = r.dw = r.aux = 0.0f;
+        if (dv) {
+          float gh, gw;
+          r.texel = project<float, false>(coef[n * G + g], depth, a.half_centor, a.Hs, a.Ws, r.dh, r.dw, gh, gw);
+        }
+        proj[n * 32 + lane] = r;
+      }
+    }
+    __syncwarp();
+
+    // ---- phase B: per view, every lane computes its four squared differences for the LG planes (footprint cached
+    // along the planes), the slices meet in shared memory and lane li adds plane li's C values in channel order -----
+    float tot = 3.402823466e+38f;
+    int targ = -1;
+    for (int n = 0; n < N; ++n) {
+      const ProjF<float>* r = myrec + n * 32;
+      int cur = -1;
+      float t00[CPL], t01[CPL], t10[CPL], t11[CPL];
+#pragma unroll
+      for (int k = 0; k < CPL; ++k) t00[k] = t01[k] = t10[k] = t11[k] = 0.0f;
+#pragma unroll
+      for (int j = 0; j < LG; ++j) {
+        const ProjF<float> rc = r[j];
+        if (rc.texel < 0) continue;            // the view does not see this plane: its row is not read either
+        if (rc.texel != cur) {
+          cur = rc.texel;
+          const T* p00 = src_lane + (size_t)rc.texel * C;
+          const T* p10 = p00 + row;
+          Vec<T, float, CPL>::load(p00, t00);
+          Vec<T, float, CPL>::load(p00 + C, t01);
+          Vec<T, float, CPL>::load(p10, t10);
+          Vec<T, float, CPL>::load(p10 + C, t11);
+        }
+        float w00, w01, w11, w10;
+        bilinear_weights(rc.dh, rc.dw, w00, w01, w11, w10);
+        float sq[CPL];
+#pragma unroll
+        for (int k = 0; k < CPL; ++k) {
+          const float s = xadd(xadd(xadd(xmul(w00, t00[k]), xmul(w01, t01[k])), xmul(w11, t11[k])), xmul(w10, t10[k]));
+          const float df = xsub(s, refv[k]);
+          sq[k] = xmul(df, df);
+        }
+        store_slice<float, CPL>(rows + j * RS + li * CPL, sq);
+      }
+      __syncwarp();
+      if (r[li].texel >= 0) {                  // cost_aggregate_kernels_gpu.cu.cc:190-223
+        const float s = row_sum_ordered<float>(rows + li * RS, C, true, 0.0f);
+        if (tot > s) { tot = s; targ = n; }
+      }
+      __syncwarp();
+    }
+    if (pvalid && dblk + li < dhi) {
+      __stcs(out, targ >= 0 ? xdiv(tot, (float)C) : 0.0f);
+      __stcs(outm, targ);
+    }
+    __syncwarp();
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------
 // backward
 //
