@@ -93,7 +93,7 @@ bool tuned_eligible(const chop_cv_desc* d, const CvArgs& a, bool backward) {
   if (!g_tuned.load() || !(d->dtype == CHOP_F32 || d->dtype == CHOP_BF16)) return false;
   // MIN: every gradient kernel, and the CostVolume / CostAggregate forward for up to 32 channels (254 views)
   const bool min_ok = backward || (d->kind == CHOP_COST_VOLUME && a.C <= 32 && a.N <= 254) ||
-                      (d->kind == CHOP_COST_AGGREGATE && a.C <= 32);
+                      (d->kind == CHOP_COST_AGGREGATE && a.C <= 32) || (d->kind == CHOP_COST_VOLUME_V2 && a.N <= 254);
   if (d->reduce != CHOP_REDUCE_MEAN && !min_ok) return false;
   if (d->kind == CHOP_COST_VOLUME || d->kind == CHOP_COST_AGGREGATE) return a.C == 8 || a.C == 16 || a.C == 32 || a.C == 64;
   if (d->kind == CHOP_COST_VOLUME_V2) {
@@ -234,6 +234,11 @@ int chop_cost_volume_fwd(const chop_cv_desc* d, const void* ref, const void* src
       !aligned(cost, (d->kind == CHOP_COST_VOLUME ? cpl : 1) * ty.real_size) || !aligned(mask, 4))
     return CHOP_ERR_ALIGN;
   if (d->kind == CHOP_COST_VOLUME && d->reduce == CHOP_REDUCE_MIN && !aligned(mask, cpl * 4)) return CHOP_ERR_ALIGN;
+  if (d->kind == CHOP_COST_VOLUME_V2 && cpl == 4 && tuned_eligible(d, a, false)) {
+    // the compile-time-C kernels store the 4/(C/G) groups of a lane's four channels as one vector
+    const size_t ga = (size_t)(4 / (a.C / a.G)) * 4;
+    if (!aligned(cost, ga) || (d->reduce == CHOP_REDUCE_MIN && !aligned(mask, ga))) return CHOP_ERR_ALIGN;
+  }
 
   plan_chunks(&a, LG, 148 * 128, 16, g_fwd_chunk.load());
   p.fwd.smem_per_warp = ty.real_size == 8

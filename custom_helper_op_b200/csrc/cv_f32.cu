@@ -14,8 +14,8 @@ int cv_fwd_f32(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
       default: break;
     }
   }
-  if (p.use_tuned && p.kind == 2 && p.mode == 0 && p.cpl == 4) {
-    const int r = tuned2_dispatch<float>(false, false, a, st);
+  if (p.use_tuned && p.kind == 2 && p.mode != 1 && p.cpl == 4) {
+    const int r = tuned2_dispatch<float>(false, p.mode == 2, a, st);
     if (r != -4) return r;  // -4: no compile-time-C kernel for this (C, groups): generic kernel below
   }
   if (p.use_tuned && p.kind == 3 && p.mode == 2 && p.cpl == 4) {

@@ -171,6 +171,22 @@ inline int fwd2_tuned_go(const CvArgs& a, cudaStream_t st) {
   return (int)cudaGetLastError();
 }
 
+template <typename T, int C, int SUB>
+inline int fwd2_min_tuned_go(const CvArgs& a, cudaStream_t st) {
+  auto k = cv2_fwd_min_tuned<T, C, SUB>;
+  const size_t spw = tuned_fwd_smem_per_warp<T>(a.N, 32 / (C / 4));
+  const int warps = tuned_warps(spw);
+  const size_t smem = spw * warps;
+  if (smem > 200 * 1024) return -4;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const long long items = (long long)a.npb * a.nchunks;
+  k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw);
+  return (int)cudaGetLastError();
+}
+
 template <typename T, int C, int SUB, bool RMIN>
 inline int bwd2_tuned_go(const CvArgs& a, cudaStream_t st) {
   auto k = cv2_bwd_tuned<T, C, SUB, RMIN>;
@@ -187,16 +203,15 @@ inline int bwd2_tuned_go(const CvArgs& a, cudaStream_t st) {
   return (int)cudaGetLastError();
 }
 
-// C in {8,16,32}, channels per group in {1,2,4}; returns -4 if there is no such kernel (the forward
-// kernels exist for MEAN only)
+// C in {8,16,32}, channels per group in {1,2,4}; returns -4 if there is no such kernel
 template <typename T>
 inline int tuned2_dispatch(bool backward, bool rmin, const CvArgs& a, cudaStream_t st) {
   const int sub = a.C / a.G;
-  if (rmin && !backward) return -4;
+  if (rmin && !backward && a.N > 254) return -4;   // the MIN forward packs the winning view into a byte
 #define CHOP_V2_CASE(CC, SS)                                                                            \
   if (a.C == CC && sub == SS)                                                                           \
     return backward ? (rmin ? bwd2_tuned_go<T, CC, SS, true>(a, st) : bwd2_tuned_go<T, CC, SS, false>(a, st)) \
-                    : fwd2_tuned_go<T, CC, SS>(a, st);
+                    : (rmin ? fwd2_min_tuned_go<T, CC, SS>(a, st) : fwd2_tuned_go<T, CC, SS>(a, st));
   CHOP_V2_CASE(8, 1) CHOP_V2_CASE(8, 2) CHOP_V2_CASE(8, 4)
   CHOP_V2_CASE(16, 1) CHOP_V2_CASE(16, 2) CHOP_V2_CASE(16, 4)
   CHOP_V2_CASE(32, 1) CHOP_V2_CASE(32, 2) CHOP_V2_CASE(32, 4)

@@ -848,6 +848,130 @@ __global__ void __launch_bounds__(256, 3) cv2_fwd_tuned(const CvArgs a, const in
   }
 }
 
+// CostVolumeV2 "MIN" forward (cost_volume_kernels_gpu_v2.cu.cc:137-235; it keeps the LARGEST group correlation and the
+// view that gave it): the nest and the register-cached RAW corners of the kernels above, every operation unfused and in
+// the reference's order (cost and arg index bit-exact), arg indices a byte per group.
+template <typename T, int C, int SUB>
+__global__ void __launch_bounds__(256, 2) cv2_fwd_min_tuned(const CvArgs a, const int warps, const size_t smem_per_warp) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int CPL = 4;
+  constexpr int LG = C / CPL;
+  constexpr int G = 32 / LG;
+  constexpr int NG = CPL / SUB;   // groups per lane
+  constexpr int GR = C / SUB;     // groups per voxel
+  static_assert(LG * CPL == C && (LG & (LG - 1)) == 0 && LG <= 32 && NG * SUB == CPL, "unsupported C / SUB");
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  const int li = lane & (LG - 1);
+  const int g = lane / LG;
+
+  const long long item = (long long)blockIdx.x * warps + wib;
+  if (item >= (long long)a.npb * a.nchunks) return;
+  const int chunk_id = (int)(item / a.npb);
+  const int pb = (int)(item - (long long)chunk_id * a.npb);
+  const long long pix0 = (long long)pb * G;
+  const bool pvalid = pix0 + g < a.npix;
+  const long long pix = pvalid ? pix0 + g : a.npix - 1;
+  const int dlo = a.d_begin + chunk_id * a.chunk;
+  const int dhi = min(a.d_end, dlo + a.chunk);
+  const int N = a.N;
+  const int D = a.D;
+
+  unsigned char* mine = smem_raw + (size_t)wib * smem_per_warp;
+  Coef<float>* coef = reinterpret_cast<Coef<float>*>(mine);
+  ProjF<float>* proj = reinterpret_cast<ProjF<float>*>(coef + N * G);
+
+  stage_coefs<float>(a, coef, lane, G, pix0);
+  __syncwarp();
+
+  const T* src_lane = static_cast<const T*>(a.src) + li * CPL;
+  float refv[CPL];
+  Vec<T, float, CPL>::load(static_cast<const T*>(a.ref) + pix * C + li * CPL, refv);
+  const float* dgrid = static_cast<const float*>(a.depth) + pix * D;
+  const size_t row = (size_t)a.Ws * C;
+  const ProjF<float>* myrec = proj + g * LG;
+  float* out = static_cast<float*>(a.cost) + (pix * D + dlo) * GR + li * NG;
+  int* outm = a.mask + (pix * D + dlo) * GR + li * NG;
+
+  for (int dblk = dlo; dblk < dhi; dblk += LG, out += LG * GR, outm += LG * GR) {
+    {
+      const int d = dblk + li;
+      const bool dv = pvalid && d < dhi;
+      const float depth = dv ? __ldg(dgrid + d) : 0.0f;
+      for (int n = 0; n < N; ++n) {
+        ProjF<float> r;
+        r.texel = -1;
+        r.dh = r.dw = r.aux = 0.0f;
+        if (dv) {
+          float gh, gw;
+          r.texel = project<float, false>(coef[n * G + g], depth, a.half_centor, a.Hs, a.Ws, r.dh, r.dw, gh, gw);
+        }
+        proj[n * 32 + lane] = r;
+      }
+    }
+    __syncwarp();
+
+    float acc[LG][NG];
+    unsigned argp[LG];   // winning view per group, a byte each (0xFF = -1)
+#pragma unroll
+    for (int j = 0; j < LG; ++j) {
+      argp[j] = 0xFFFFFFFFu;
+#pragma unroll
+      for (int q = 0; q < NG; ++q) acc[j][q] = 1.175494351e-38f;   // v2:179-180: numeric_limits<T>::min()
+    }
+
+    for (int n = 0; n < N; ++n) {
+      const ProjF<float>* r = myrec + n * 32;
+      int cur = -1;
+      float t00[CPL], t01[CPL], t10[CPL], t11[CPL];
+#pragma unroll
+      for (int k = 0; k < CPL; ++k) t00[k] = t01[k] = t10[k] = t11[k] = 0.0f;
+#pragma unroll
+      for (int j = 0; j < LG; ++j) {
+        const ProjF<float> rc = r[j];
+        if (rc.texel < 0) continue;            // the view does not see this plane
+        if (rc.texel != cur) {
+          cur = rc.texel;
+          const T* p00 = src_lane + (size_t)rc.texel * C;
+          const T* p10 = p00 + row;
+          Vec<T, float, CPL>::load(p00, t00);
+          Vec<T, float, CPL>::load(p00 + C, t01);
+          Vec<T, float, CPL>::load(p10, t10);
+          Vec<T, float, CPL>::load(p10 + C, t11);
+        }
+        float w00, w01, w11, w10;
+        bilinear_weights(rc.dh, rc.dw, w00, w01, w11, w10);
+        float val[CPL], gs[NG];
+#pragma unroll
+        for (int k = 0; k < CPL; ++k) {
+          const float sm = xadd(xadd(xadd(xmul(w00, t00[k]), xmul(w01, t01[k])), xmul(w11, t11[k])), xmul(w10, t10[k]));
+          val[k] = xmul(sm, refv[k]);          // v2:213-216
+        }
+        in_lane_groups_t<float, CPL, SUB, true>(val, gs);
+#pragma unroll
+        for (int q = 0; q < NG; ++q) {
+          if (acc[j][q] < gs[q]) {             // v2:221-224: the LARGEST group correlation wins, first view on ties
+            acc[j][q] = gs[q];
+            argp[j] = (argp[j] & ~(0xFFu << (8 * q))) | ((unsigned)n << (8 * q));
+          }
+        }
+      }
+    }
+
+#pragma unroll
+    for (int j = 0; j < LG; ++j) {
+      if (pvalid && dblk + j < dhi) {
+        store_stream<float, NG>(out + j * GR, acc[j]);
+        int arg[NG];
+#pragma unroll
+        for (int q = 0; q < NG; ++q) arg[q] = (int)(signed char)((argp[j] >> (8 * q)) & 0xFFu);
+        store_stream<int, NG>(outm + j * GR, arg);
+      }
+    }
+    __syncwarp();
+  }
+}
+
 // Gradient.  With bg = cost_grad[group]/views (v2:461) everything a plane contributes is linear in bg times
 // a function of (dh, dw), so per (plane, view, group) only the bilinear moments
 //   m0 += bg, m1 += bg*dw, m2 += bg*dh, m3 += bg*dh*dw
