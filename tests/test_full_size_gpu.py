@@ -74,6 +74,56 @@ def test_cost_volume_full_size(name):
     _band_check(w, cost, mask, rg, bg, g1, rows=3)
 
 
+@pytest.mark.parametrize("kind", [1, 3])
+def test_min_reduction_full_size(kind):
+    """MIN (the reference layers' default) at the c1 size, CostVolume (1) and CostAggregate (3): the compile-time-C
+    kernels against the generic kernels (two implementations of the same unfused arithmetic: cost and arg indices
+    bit-identical, gradients to rounding), the oracle on a band of rows, and depth-range calls composing."""
+    w = synth.make("c1_mvsnet", with_grad=False)
+    t = {k: torch.from_numpy(v).to(DEV) for k, v in w.items()}
+    args = (t["ref"], t["src"], t["base_plane"], t["offsets"], t["Rs"], t["Ts"])
+    cost, mask = ops.cost_forward(kind, *args, "MIN")
+    g = torch.Generator(device=DEV)
+    g.manual_seed(7)
+    cg = torch.randn(cost.shape, device=DEV, generator=g)
+    grads = ops.cost_backward(kind, *args, cg, mask, "MIN")
+    try:
+        _lib.set_tuning("tuned", 0)
+        cost_g, mask_g = ops.cost_forward(kind, *args, "MIN")
+        grads_g = ops.cost_backward(kind, *args, cg, mask, "MIN")
+    finally:
+        _lib.set_tuning("tuned", 1)
+    assert torch.equal(mask, mask_g) and torch.equal(cost, cost_g)
+    assert float((mask >= 0).float().mean()) > 0.9
+    for a, b in zip(grads, grads_g):
+        assert float((a - b).abs().max()) <= 1e-4 * float(b.abs().max())
+    # oracle on the first rows of the image (cost, arg indices, d(ref), d(base_plane) are per pixel)
+    rows = 2
+    ref = np.ascontiguousarray(w["ref"][:1, :rows])
+    base = np.ascontiguousarray(w["base_plane"][:1, :rows])
+    c_o, m_o = oracle.cost_fwd(kind, ref, w["src"][:1], base, w["offsets"][:1], w["Rs"][:1], w["Ts"][:1], reduce_method="MIN")
+    assert helpers.bits_equal(mask[:1, :rows].cpu().numpy(), m_o)
+    assert helpers.bits_equal(cost[:1, :rows].cpu().numpy(), c_o)
+    rg_o, _, bg_o = oracle.cost_bwd(kind, ref, w["src"][:1], base, w["offsets"][:1], w["Rs"][:1], w["Ts"][:1],
+                                    cg[:1, :rows].cpu().numpy(), m_o, reduce_method="MIN")
+    assert helpers.rel_err(grads[0][:1, :rows].cpu().numpy(), rg_o) <= 1e-4
+    assert helpers.rel_err(grads[2][:1, :rows].cpu().numpy(), bg_o) <= 1e-4
+    # depth-range calls compose
+    D = t["offsets"].shape[1]
+    cost_r = torch.zeros_like(cost)
+    mask_r = torch.zeros_like(mask)
+    acc = None
+    for d0, d1 in ((0, 7), (7, D // 2 + 3), (D // 2 + 3, D)):
+        ops.cost_forward(kind, *args, "MIN", d_range=(d0, d1), out=(cost_r, mask_r))
+        if acc is None:
+            acc = ops.cost_backward(kind, *args, cg, mask, "MIN", d_range=(d0, d1))
+        else:
+            ops.cost_backward(kind, *args, cg, mask, "MIN", d_range=(d0, d1), accumulate_into=acc)
+    assert torch.equal(cost_r, cost) and torch.equal(mask_r, mask)
+    for a, b in zip(acc, grads):
+        assert float((a - b).abs().max()) <= 1e-4 * float(b.abs().max())
+
+
 def test_large_item_bf16_features():
     """One batch item of the large multi-view configuration (V=7, 296x400, D=256, inverse-depth planes),
     bf16 features: band check against the float32 oracle on the bf16-rounded features."""
