@@ -437,7 +437,7 @@ def secondary_main(args):
     convolution that brings it back and SparsePad, bf16, forward + gradient each.  c1_v3: CostVolumeV3 (8 groups,
     MEAN) forward + gradient on the c1 shapes, fp32.  c1_fa: FeatureAggregate forward + gradient on the c1 shapes
     (the forward allocates its 1 GB output every step, as the op does).  c1_min: CostVolume and CostAggregate with the MIN
-    reduction, forward + gradient each, c1 shapes, fp32.  c2_min: CostVolumeV2 MIN on the first cascade stage.  Single GPU, L2 flushed between steps."""
+    reduction, forward + gradient each, c1 shapes, fp32.  c2_min: CostVolumeV2 MIN on the first cascade stage; c2_cascade: CostVolumeV2 MEAN on all three.  Single GPU, L2 flushed between steps."""
     import torch
 
     from custom_helper_op_b200 import synth
@@ -519,6 +519,32 @@ def secondary_main(args):
         units, unit = 2 * vox * N, UNIT
         desc = "c1_min: CostVolume and CostAggregate, MIN, fwd+bwd fp32, B=%d, V=%d, C=%d, %dx%d, D=%d" % (B, N + 1, C, H, W_, D)
         launches = 10
+    elif args.workload == "c2_cascade":
+        # CostVolumeV2 MEAN on the three cascade stages (bf16 features, 8 groups), forward + gradient each
+        names, ms, alg, units = [], [], [], 0
+        parts = []
+        for st_name in ("c2_stage1", "c2_stage2", "c2_stage3"):
+            wl = synth.make(st_name, with_grad=False)
+            t = {k: (torch.from_numpy(v).to(dev) if isinstance(v, np.ndarray) else v) for k, v in wl.items()}
+            B, H, W_, C = t["ref"].shape
+            D, N, G = t["depth_grid"].shape[3], t["src"].shape[1], 8
+            a = (t["ref"].bfloat16(), t["src"].bfloat16(), t["depth_grid"], None, t["Rs"], t["Ts"])
+            cost, mask = ops.cost_forward(2, *a, "MEAN", G)
+            cg = torch.randn_like(cost)
+            m2 = timed([lambda: ops.cost_forward(2, *a, "MEAN", G, out=(cost, mask)),
+                        lambda: ops.cost_backward(2, *a, cg, mask, "MEAN", G)])
+            feats = (1 + N) * B * H * W_ * C * 2
+            vox = B * H * W_ * D
+            names += [st_name + "_fwd", st_name + "_bwd"]
+            ms += m2
+            alg += [feats + 4 * vox + 4 * vox * G + 4 * vox, feats + 4 * vox + 4 * vox * G + 4 * vox + 4 * (1 + N) * B * H * W_ * C + 4 * vox]
+            units += vox * N
+            parts.append("%s %.1f G units/s" % (st_name, vox * N / (sum(m2) * 1e-3) / 1e9))
+            del t, a, cost, mask, cg
+            torch.cuda.empty_cache()
+        unit = UNIT
+        desc = "c2_cascade: CostVolumeV2 MEAN fwd+bwd on the three cascade stages, bf16 features, V=5, groups=8 (" + "; ".join(parts) + ")"
+        launches = 12
     elif args.workload == "c2_min":
         # CostVolumeV2 with the MIN reduction on the first cascade stage (bf16 features, 8 groups)
         wl = synth.make("c2_stage1", with_grad=False)
@@ -618,7 +644,7 @@ def main():
     ap.add_argument("--profile", action="store_true",
                     help="device-timed loop only (no clock probe loop, e2e leg or CPU baseline): the command to run under ncu")
     args = ap.parse_args()
-    if args.workload in ("c4_updown", "c1_v3", "c1_fa", "c1_min", "c2_min"):
+    if args.workload in ("c4_updown", "c1_v3", "c1_fa", "c1_min", "c2_min", "c2_cascade"):
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "secondary workload: timed on the GPU only"}))
         else:
