@@ -437,7 +437,7 @@ def secondary_main(args):
     convolution that brings it back and SparsePad, bf16, forward + gradient each.  c1_v3: CostVolumeV3 (8 groups,
     MEAN) forward + gradient on the c1 shapes, fp32.  c1_fa: FeatureAggregate forward + gradient on the c1 shapes
     (the forward allocates its 1 GB output every step, as the op does).  c1_min: CostVolume and CostAggregate with the MIN
-    reduction, forward + gradient each, c1 shapes, fp32.  c2_min: CostVolumeV2 MIN on the first cascade stage; c2_cascade: CostVolumeV2 MEAN on all three.  Single GPU, L2 flushed between steps."""
+    reduction, forward + gradient each, c1 shapes, fp32.  c2_min: CostVolumeV2 MIN on the first cascade stage; c2_cascade: CostVolumeV2 MEAN on all three.  c3_item: one batch item of the large configuration.  Single GPU, L2 flushed between steps."""
     import torch
 
     from custom_helper_op_b200 import synth
@@ -545,6 +545,24 @@ def secondary_main(args):
         unit = UNIT
         desc = "c2_cascade: CostVolumeV2 MEAN fwd+bwd on the three cascade stages, bf16 features, V=5, groups=8 (" + "; ".join(parts) + ")"
         launches = 12
+    elif args.workload == "c3_item":
+        # one batch item of the large configuration (what one GPU holds at 8-way batch sharding), bf16 features
+        wl = synth.make("c3_large", with_grad=False, B=1)
+        t = {k: torch.from_numpy(v).to(dev) for k, v in wl.items()}
+        B, H, W_, C = t["ref"].shape
+        D, N = t["offsets"].shape[1], t["src"].shape[1]
+        a = (t["ref"].bfloat16(), t["src"].bfloat16(), t["base_plane"], t["offsets"], t["Rs"], t["Ts"])
+        cost, mask = ops.cost_forward(1, *a)
+        cg = torch.randn_like(cost)
+        names = ["c3_fwd", "c3_bwd"]
+        ms = timed([lambda: ops.cost_forward(1, *a, out=(cost, mask)), lambda: ops.cost_backward(1, *a, cg, mask)])
+        feats = (1 + N) * B * H * W_ * C * 2
+        vox = B * H * W_ * D
+        small = 4 * B * H * W_ + 4 * B * D
+        alg = [feats + small + 4 * vox * C + 4 * vox, 4 * vox * C + 4 * vox + feats + small + 4 * (1 + N) * B * H * W_ * C + 4 * B * H * W_]
+        units, unit = vox * N, UNIT
+        desc = "c3_item: CostVolume MEAN fwd+bwd, bf16 features, B=%d, V=%d, C=%d, %dx%d, D=%d" % (B, N + 1, C, H, W_, D)
+        launches = 5
     elif args.workload == "c2_min":
         # CostVolumeV2 with the MIN reduction on the first cascade stage (bf16 features, 8 groups)
         wl = synth.make("c2_stage1", with_grad=False)
@@ -644,7 +662,7 @@ def main():
     ap.add_argument("--profile", action="store_true",
                     help="device-timed loop only (no clock probe loop, e2e leg or CPU baseline): the command to run under ncu")
     args = ap.parse_args()
-    if args.workload in ("c4_updown", "c1_v3", "c1_fa", "c1_min", "c2_min", "c2_cascade"):
+    if args.workload in ("c4_updown", "c1_v3", "c1_fa", "c1_min", "c2_min", "c2_cascade", "c3_item"):
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "secondary workload: timed on the GPU only"}))
         else:
