@@ -982,10 +982,14 @@ __global__ void __launch_bounds__(256, 2) cv2_fwd_min_tuned(const CvArgs a, cons
 // ref*(p01-p00), formed once per footprint.  The depth-hypothesis gradient is per voxel: every lane keeps
 // one partial per plane of the block, the partials are reduce-scattered over the pixel's lanes (lane li
 // ends up with plane li) and stored coalesced (zero where no view saw the voxel, v2:375-378).
+// five 128-thread CTAs per SM measured fastest (four: 4-5 % slower at the c2 stages)
+#ifndef CHOP_V2_BWD_MIN_BLOCKS
+#define CHOP_V2_BWD_MIN_BLOCKS 5
+#endif
 // RMIN = true: `mask` holds the winning view per (voxel, group); only that view is differentiated, with
 // no division by the view count (v2:483-601); a voxel whose first group has no winner is skipped.
 template <typename T, int C, int SUB, bool RMIN = false>
-__global__ void __launch_bounds__(128, 5) cv2_bwd_tuned(const CvArgs a, const int warps, const size_t smem_per_warp) {
+__global__ void __launch_bounds__(128, CHOP_V2_BWD_MIN_BLOCKS) cv2_bwd_tuned(const CvArgs a, const int warps, const size_t smem_per_warp) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int CPL = 4;
   constexpr int LG = C / CPL;
@@ -1067,6 +1071,27 @@ __global__ void __launch_bounds__(128, 5) cv2_bwd_tuned(const CvArgs a, const in
     float dv[LG];
 #pragma unroll
     for (int j = 0; j < LG; ++j) dv[j] = 0.0f;
+    // the block's upstream gradient (and winners): one request per plane, all in flight together and shared by the
+    // views, instead of a dependent load per (plane, view)
+    float cgall[LG][NG];
+    int mkall[RMIN ? LG : 1][NG];
+#pragma unroll
+    for (int j = 0; j < LG; ++j) {
+#pragma unroll
+      for (int q = 0; q < NG; ++q) {
+        cgall[j][q] = 0.0f;
+        if (RMIN) mkall[j][q] = -1;
+      }
+      if (dblk + j < dhi) {
+        Vec<float, float, NG>::load(cg_lane + j * GR, cgall[j]);
+        if constexpr (RMIN) {
+          float mk[NG];
+          Vec<float, float, NG>::load(reinterpret_cast<const float*>(mk_lane) + j * GR, mk);
+#pragma unroll
+          for (int q = 0; q < NG; ++q) mkall[j][q] = __float_as_int(mk[q]);
+        }
+      }
+    }
     for (int n = 0; n < N; ++n) {
       const ProjF<float>* rA = recA + n * 32 + g * LG;
       const RecG* rGp = recG + n * 32 + g * LG;
@@ -1102,9 +1127,9 @@ __global__ void __launch_bounds__(128, 5) cv2_bwd_tuned(const CvArgs a, const in
           if (rc.texel != cur) {
             if (cur >= 0) flush();
             cur = rc.texel;
+            float t00[CPL], t01[CPL], t10[CPL], t11[CPL];
             const T* p00 = src_lane + (size_t)rc.texel * C;
             const T* p10 = p00 + row;
-            float t00[CPL], t01[CPL], t10[CPL], t11[CPL];
             Vec<T, float, CPL>::load(p00, t00);
             Vec<T, float, CPL>::load(p00 + C, t01);
             Vec<T, float, CPL>::load(p10, t10);
@@ -1125,13 +1150,12 @@ __global__ void __launch_bounds__(128, 5) cv2_bwd_tuned(const CvArgs a, const in
           }
           const RecG rq = rGp[j];
           float cgv[NG];
-          Vec<float, float, NG>::load(cg_lane + j * GR, cgv);
+#pragma unroll
+          for (int q = 0; q < NG; ++q) cgv[q] = cgall[j][q];
           if constexpr (RMIN) {  // v2:575 a group's gradient goes to its winning view only
-            float mk[NG];
-            Vec<float, float, NG>::load(reinterpret_cast<const float*>(mk_lane) + j * GR, mk);
 #pragma unroll
             for (int q = 0; q < NG; ++q)
-              if (__float_as_int(mk[q]) != n) cgv[q] = 0.0f;
+              if (mkall[j][q] != n) cgv[q] = 0.0f;
           }
           const float hw = rc.dh * rc.dw;
           float P = 0.0f, Q = 0.0f, R = 0.0f;
