@@ -1,0 +1,1 @@
+"""Mirror of the reference package layout (custom_helper_op/python/layers)."""

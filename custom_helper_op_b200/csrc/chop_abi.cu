@@ -23,7 +23,7 @@ namespace {
 using chop::CvArgs;
 using chop::CvPlan;
 
-std::atomic<int> g_fwd_chunk{0}, g_bwd_chunk{0}, g_bwd_views{0}, g_tuned{1};
+std::atomic<int> g_fwd_chunk{0}, g_bwd_chunk{0}, g_bwd_views{0}, g_tuned{1}, g_packed{1};
 
 inline int pow2ceil_log2(int x) {
   int l = 0;
@@ -194,6 +194,7 @@ int chop_cost_volume_fwd(const chop_cv_desc* d, const void* ref, const void* src
   p.kind = d->kind;
   p.mode = mode;
   p.use_tuned = g_tuned.load();
+  p.use_packed = g_packed.load();
   // how lanes combine channels into groups (kinds 2 and 3)
   p.fwd.group_mode = chop::GROUP_IN_LANE;
   p.fwd.sub = 1;
@@ -322,6 +323,7 @@ int chop_cost_volume_bwd(const chop_cv_desc* d, const void* ref, const void* src
   p.kind = d->kind;
   p.cpl = cpl;
   p.use_tuned = g_tuned.load();
+  p.use_packed = g_packed.load();
   p.rmin = d->reduce == CHOP_REDUCE_MIN;
   int nv = g_bwd_views.load();
   if (nv <= 0) {
@@ -466,6 +468,7 @@ int chop_set_tuning(const char* name, int value) {
   if (!std::strcmp(name, "bwd_chunk")) { g_bwd_chunk = value; return CHOP_OK; }
   if (!std::strcmp(name, "bwd_views")) { g_bwd_views = value; return CHOP_OK; }
   if (!std::strcmp(name, "tuned")) { g_tuned = value; return CHOP_OK; }
+  if (!std::strcmp(name, "packed")) { g_packed = value; return CHOP_OK; }
   if (!std::strcmp(name, "umma")) { chop::g_use_umma = value; return CHOP_OK; }
   if (!std::strcmp(name, "umma_rows")) { chop::sc_umma_set_rows(value); return CHOP_OK; }
   if (!std::strcmp(name, "tile")) { chop::g_use_tile = value; return CHOP_OK; }

@@ -34,6 +34,16 @@ int cv_fwd_bf16(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
       default: break;
     }
   }
+  if (p.use_tuned && p.use_packed && p.kind == 1 && p.mode == 0 && p.cpl == 4) {
+    int r = -4;
+    switch (a.C) {
+      case 8: r = fwd_packed_go<__nv_bfloat16, 8>(a, st); break;
+      case 16: r = fwd_packed_go<__nv_bfloat16, 16>(a, st); break;
+      case 32: r = fwd_packed_go<__nv_bfloat16, 32>(a, st); break;
+      default: break;
+    }
+    if (r != -4) return r;
+  }
   if (p.use_tuned && p.kind == 1 && p.mode == 0 && p.cpl == 4) {
     switch (a.C) {
       case 8: return fwd_tuned_go<__nv_bfloat16, 8, 4>(a, st);
@@ -75,6 +85,16 @@ int cv_bwd_bf16(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
   }
   if (p.use_tuned && p.kind == 2 && p.cpl == 4) {
     const int r = tuned2_dispatch<__nv_bfloat16>(true, p.rmin != 0, a, st);
+    if (r != -4) return r;
+  }
+  if (p.use_tuned && p.use_packed && p.kind == 1 && !p.rmin && p.cpl == 4) {
+    int r = -4;
+    switch (a.C) {
+      case 8: r = bwd_packed_go<__nv_bfloat16, 8>(a, st); break;
+      case 16: r = bwd_packed_go<__nv_bfloat16, 16>(a, st); break;
+      case 32: r = bwd_packed_go<__nv_bfloat16, 32>(a, st); break;
+      default: break;
+    }
     if (r != -4) return r;
   }
   if (p.use_tuned && p.kind == 1 && !p.rmin && p.cpl == 4) {

@@ -1,8 +1,11 @@
 // Typed kernel selection for the cost-volume kernels.  Each cv_<dtype>.cu instantiates this header
 // for one feature type so the three translation units compile in parallel.
 #pragma once
+#include <atomic>
+
 #include "cv_bwd.cuh"
 #include "cv_fwd.cuh"
+#include "cv_packed.cuh"
 #include "cv_tuned.cuh"
 
 namespace chop {
@@ -15,6 +18,7 @@ struct CvPlan {
   int nv;     // backward: source views tracked per pass
   int blocks;
   int use_tuned;  // allow the compile-time-C kernels of cv_tuned.cuh where one exists
+  int use_packed; // allow the packed-pair kernels of cv_packed.cuh where one exists
   FwdCfg fwd;
   BwdCfg bwd;
 };
@@ -200,6 +204,57 @@ inline int bwd2_tuned_go(const CvArgs& a, cudaStream_t st) {
   }
   const long long items = (long long)a.npb * a.nchunks;
   k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw);
+  return (int)cudaGetLastError();
+}
+
+// ---- packed-pair kernels (cv_packed.cuh) ----------------------------------------------------------------
+// Opt-in to more than 48 KB of dynamic shared memory is a per-(device, kernel) attribute: it is set the
+// first time a launch of that kernel on that device needs it, not on every call.
+struct SmemGrant {
+  std::atomic<int> bytes[64];
+};
+template <typename K>
+inline int grant_smem(K kernel, size_t smem, SmemGrant& gr) {
+  if (smem <= 48 * 1024) return 0;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev >= 0 && dev < 64 && gr.bytes[dev].load(std::memory_order_acquire) >= (int)smem) return 0;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  if (dev >= 0 && dev < 64) {
+    int seen = gr.bytes[dev].load();
+    while (seen < (int)smem && !gr.bytes[dev].compare_exchange_weak(seen, (int)smem)) {}
+  }
+  return 0;
+}
+
+template <typename T, int C>
+inline int fwd_packed_go(const CvArgs& a, cudaStream_t st) {
+  static SmemGrant gr;
+  auto k = cv_fwd_packed<T, C>;
+  const size_t spw = packed_fwd_smem_per_warp(a.N, 32 / (C / 4));
+  const int warps = tuned_warps(spw);
+  const size_t smem = spw * warps;
+  if (smem > 200 * 1024) return -4;
+  if (int e = grant_smem(k, smem, gr)) return e;
+  const long long items = (long long)a.npb * a.nchunks;
+  k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw);
+  return (int)cudaGetLastError();
+}
+
+template <typename T, int C>
+inline int bwd_packed_go(const CvArgs& a, cudaStream_t st) {
+  static SmemGrant gr;
+  auto k = cv_bwd_packed<T, C>;
+  const int vpp = a.N < 2 ? a.N : 2;   // views per pass: shared memory per warp independent of N
+  const size_t spw = packed_bwd_smem_per_warp<C>(a.N, 32 / (C / 4), vpp);
+  const int warps = 4;
+  const size_t smem = spw * warps;
+  if (smem > 200 * 1024) return -4;
+  if (int e = grant_smem(k, smem, gr)) return e;
+  const long long items = (long long)a.npb * a.nchunks;
+  k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw, vpp);
   return (int)cudaGetLastError();
 }
 

@@ -73,14 +73,16 @@ def pack_layout(shapes):
 
 
 class GradReducer:
-    """Packed gradient buffer of one batch item + the all-reduce over the ranks sharing that item."""
+    """Packed gradient buffer of one batch item + the all-reduce over the ranks sharing that item.
+    The buffer starts uninitialised (`zero=False`): the gradient op zero-fills the three views it is given."""
 
-    def __init__(self, shapes, dtype, device, group=None):
+    def __init__(self, shapes, dtype, device, group=None, zero=False):
         self.shapes = [tuple(int(x) for x in s) for s in shapes]
         offs, total = pack_layout(self.shapes)
-        self.flat = torch.zeros(total, dtype=dtype, device=device)
+        self.flat = (torch.zeros if zero else torch.empty)(total, dtype=dtype, device=device)
         self.views = [self.flat[o:o + n].view(s) for (o, n), s in zip(offs, self.shapes)]
         self.group = group
+        self.work = None
 
     def zero_(self):
         self.flat.zero_()
@@ -89,6 +91,50 @@ class GradReducer:
         if self.group is not None:
             dist.all_reduce(self.flat, group=self.group)
         return self.views
+
+    def all_reduce_async(self):
+        """Issue the all-reduce without making the caller's stream wait for it: the collective runs on the
+        backend's own stream (after the work already enqueued on the current stream) and what the caller
+        launches next - the following step's forward - overlaps it.  `wait()` joins it."""
+        if self.group is not None:
+            self.work = dist.all_reduce(self.flat, group=self.group, async_op=True)
+
+    def wait(self):
+        if self.work is not None:
+            self.work.wait()
+            self.work = None
+        return self.views
+
+
+class PipelinedReducer:
+    """Two packed buffers used in turn by consecutive steps of a depth-sharded item.  Step k's backward
+    writes its partial gradients into buffer k % 2 and `reduce_async()` starts their all-reduce; the compute
+    stream goes straight on with step k+1's forward and backward (other buffer).  A buffer is joined just
+    before it is written again (`next_views`) or read (`result`, `finish`), so at most one collective is in
+    flight behind the compute stream and its latency hides behind the next step's kernels."""
+
+    def __init__(self, shapes, dtype, device, group):
+        self.slots = [GradReducer(shapes, dtype, device, group), GradReducer(shapes, dtype, device, group)]
+        self.k = 0
+
+    def next_views(self):
+        slot = self.slots[self.k % 2]
+        slot.wait()
+        return slot.views
+
+    def reduce_async(self):
+        slot = self.slots[self.k % 2]
+        slot.all_reduce_async()
+        self.k += 1
+        return slot
+
+    def result(self, slot):
+        """The summed gradients of the step whose reduce_async() returned `slot`."""
+        return slot.wait()
+
+    def finish(self):
+        for s in self.slots:
+            s.wait()
 
 
 def make_groups(plan: List[List[Shard]]):
@@ -110,18 +156,42 @@ def sharded_forward_backward(rank, plan, groups, inputs, cost_grad_fn, compute_f
     base_plane, offsets, Rs, Ts); `cost_grad_fn(b, cost)` supplies the upstream gradient for the planes
     this rank computed (a [1,H,W,D,C] tensor, only [d_begin,d_end) is read).
     compute_fwd(inp, d0, d1) -> (cost, mask) full-extent tensors with planes [d0,d1) filled;
-    compute_bwd(inp, cost_grad, mask, d0, d1, (ref_grad, src_grad, base_grad)) adds into the three views.
+    compute_bwd(inp, cost_grad, mask, d0, d1, (ref_grad, src_grad, base_grad)) WRITES the partial gradients
+    of planes [d0,d1) into the three views (they arrive uninitialised: the CUDA op zero-fills its outputs).
+    The all-reduces are issued asynchronously and joined after the last shard has been launched.
     Returns {item: (cost, mask, ref_grad, src_grad, base_plane_grad)}; the gradients are complete (summed
     over the item's ranks) on every rank of the item's group."""
-    results = {}
+    pending = []
     for sh in plan[rank]:
         inp = inputs[sh.item]
+        empty = sh.d_end <= sh.d_begin          # more ranks than planes: this rank contributes zeros
         red = GradReducer([inp["ref"].shape, inp["src"].shape, inp["base_plane"].shape], inp["base_plane"].dtype, device,
-                          groups.get(sh.group_ranks))
+                          groups.get(sh.group_ranks), zero=empty)
         cost = mask = None
-        if sh.d_end > sh.d_begin:
+        if not empty:
             cost, mask = compute_fwd(inp, sh.d_begin, sh.d_end)
             compute_bwd(inp, cost_grad_fn(sh.item, cost), mask, sh.d_begin, sh.d_end, tuple(red.views))
-        rg, sg, bg = red.all_reduce()
-        results[sh.item] = (cost, mask, rg, sg, bg)
+        red.all_reduce_async()
+        pending.append((sh.item, cost, mask, red))
+    results = {}
+    for item, cost, mask, red in pending:
+        rg, sg, bg = red.wait()
+        results[item] = (cost, mask, rg, sg, bg)
     return results
+
+
+def cuda_compute_fns(half_centor=True, buffers=None):
+    """compute_fwd / compute_bwd over the CUDA ops for sharded_forward_backward.  With `buffers` = (cost, mask)
+    preallocated full-extent tensors they are reused for every shard (one item at a time fits a GPU even when
+    a batch of them does not)."""
+    from custom_helper_op_b200.python.ops import custom_helper_ops as ops
+
+    def fwd(inp, d0, d1):
+        return ops.cost_forward(1, inp["ref"], inp["src"], inp["base_plane"], inp["offsets"], inp["Rs"], inp["Ts"],
+                                half_centor=half_centor, d_range=(d0, d1), out=buffers)
+
+    def bwd(inp, cost_grad, mask, d0, d1, views):
+        ops.cost_backward(1, inp["ref"], inp["src"], inp["base_plane"], inp["offsets"], inp["Rs"], inp["Ts"], cost_grad, mask,
+                          half_centor=half_centor, d_range=(d0, d1), zero_into=views)
+
+    return fwd, bwd

@@ -73,3 +73,24 @@ def rel_err(a, b):
     b = np.asarray(b, np.float64)
     den = np.abs(b).max()
     return float(np.abs(a - b).max() / den) if den > 0 else float(np.abs(a - b).max())
+
+
+def elementwise_excess(got, want, rtol, atol_rel=1e-6):
+    """Element-wise closeness in the sense of the reference tests' assertAllClose(rtol=..) on a float32
+    tensor (cost_volume_op_test.py:197-209): returns max over elements of |got-want| / (rtol*|want| + atol),
+    where atol = atol_rel * max|want| plays the part of assertAllClose's default absolute tolerance (1e-6)
+    on tensors of order one.  A value <= 1 passes."""
+    g = np.asarray(got, np.float64).reshape(-1)
+    w = np.asarray(want, np.float64).reshape(g.shape)
+    atol = atol_rel * float(np.abs(w).max()) if w.size else 0.0
+    bound = rtol * np.abs(w) + atol
+    bound[bound == 0] = np.finfo(np.float64).tiny
+    return float((np.abs(g - w) / bound).max()) if g.size else 0.0
+
+
+def worst_relative(got, want, floor_rel=1e-3):
+    """Largest |got-want|/|want| over the elements with |want| >= floor_rel * max|want| (reported, not asserted)."""
+    g = np.asarray(got, np.float64).reshape(-1)
+    w = np.asarray(want, np.float64).reshape(g.shape)
+    keep = np.abs(w) >= floor_rel * np.abs(w).max()
+    return float((np.abs(g - w)[keep] / np.abs(w)[keep]).max()) if keep.any() else 0.0

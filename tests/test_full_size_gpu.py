@@ -16,17 +16,41 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _band_check(w, cost, mask, rg, bg, cg, rows):
-    """Oracle on image rows [0, rows) of batch item 0 against the full GPU result."""
-    ref = np.ascontiguousarray(w["ref"][:1, :rows])
-    base = np.ascontiguousarray(w["base_plane"][:1, :rows])
-    c_o, m_o = oracle.cost_fwd(1, ref, w["src"][:1], base, w["offsets"][:1], w["Rs"][:1], w["Ts"][:1])
-    assert helpers.bits_equal(mask[:1, :rows].cpu().numpy(), m_o)
-    assert helpers.rel_err(cost[:1, :rows].cpu().numpy(), c_o) <= 1e-5
-    rg_o, _, bg_o = oracle.cost_bwd(1, ref, w["src"][:1], base, w["offsets"][:1], w["Rs"][:1], w["Ts"][:1],
-                                    cg[:1, :rows].cpu().numpy(), m_o)
-    assert helpers.rel_err(rg[:1, :rows].cpu().numpy(), rg_o) <= 1e-4
-    assert helpers.rel_err(bg[:1, :rows].cpu().numpy(), bg_o) <= 1e-4
+def _band_check(w, cost, mask, rg, bg, cg, rows, item=0, args=None):
+    """Oracle on image rows [0, rows) of one batch item against the full GPU result: cost, mask, d(ref) and
+    d(base_plane) are per pixel.  Element-wise as well as scale-relative: |got - want| <= rtol*|want| + atol with
+    atol = 1e-6 * max|want| (1e-5 * max for gradients, which are sums in atomic order), rtol 1e-5 forward and
+    1e-4 gradients.  With `args` (the op's device inputs) the source-feature gradient is checked too: the oracle's
+    gradient over the band is the partial d(src) of those pixels, and the GPU gradient with the upstream gradient
+    zeroed everywhere else must reproduce the whole of it."""
+    b = slice(item, item + 1)
+    ref = np.ascontiguousarray(w["ref"][b, :rows])
+    base = np.ascontiguousarray(w["base_plane"][b, :rows])
+    c_o, m_o = oracle.cost_fwd(1, ref, w["src"][b], base, w["offsets"][b], w["Rs"][b], w["Ts"][b])
+    assert helpers.bits_equal(mask[b, :rows].cpu().numpy(), m_o)
+    c_g = cost[b, :rows].cpu().numpy()
+    assert helpers.rel_err(c_g, c_o) <= 1e-5
+    assert helpers.elementwise_excess(c_g, c_o, 1e-5) <= 1.0
+    cg_band = cg[b, :rows].cpu().numpy()
+    rg_o, sg_o, bg_o = oracle.cost_bwd(1, ref, w["src"][b], base, w["offsets"][b], w["Rs"][b], w["Ts"][b], cg_band, m_o)
+    for got, want in ((rg[b, :rows], rg_o), (bg[b, :rows], bg_o)):
+        got = got.cpu().numpy()
+        assert helpers.rel_err(got, want) <= 1e-4
+        assert helpers.elementwise_excess(got, want, 1e-4, 1e-5) <= 1.0
+    if args is not None:
+        cg_only = torch.zeros_like(cg)
+        cg_only[b, :rows] = cg[b, :rows]
+        rg2, sg2, bg2 = ops.cost_backward(1, *args, cg_only, mask)
+        del cg_only
+        sg_g = sg2[b].cpu().numpy()
+        assert helpers.rel_err(sg_g, sg_o) <= 1e-4
+        assert helpers.elementwise_excess(sg_g, sg_o, 1e-4, 1e-5) <= 1.0
+        # nothing leaks to the other items' source gradients or to reference pixels outside the band
+        for o in range(sg2.shape[0]):
+            if o != item:
+                assert float(sg2[o].abs().max()) == 0.0
+        assert float(rg2[b, rows:].abs().max()) == 0.0
+        assert helpers.rel_err(rg2[b, :rows].cpu().numpy(), rg_o) <= 1e-4
 
 
 @pytest.mark.parametrize("name", ["c0_cpu", "c1_mvsnet"])
@@ -71,7 +95,7 @@ def test_cost_volume_full_size(name):
     assert torch.equal(cost_r, cost) and torch.equal(mask_r, mask)
     for a, b in zip(acc, r1):
         assert float((a - b).abs().max()) <= 1e-4 * float(b.abs().max())
-    _band_check(w, cost, mask, rg, bg, g1, rows=3)
+    _band_check(w, cost, mask, rg, bg, g1, rows=3, args=args)
 
 
 @pytest.mark.parametrize("kind", [1, 3])
@@ -140,14 +164,53 @@ def test_large_item_bf16_features():
     lhs = sg.double().sum(dim=(0, 1, 2, 3))
     rhs = -rg.double().sum(dim=(0, 1, 2))
     assert float((lhs - rhs).abs().max()) <= 1e-4 * float(rhs.abs().max())
-    _band_check(w, cost, mask, rg, bg, cg, rows=2)
+    _band_check(w, cost, mask, rg, bg, cg, rows=2, args=args)
 
 
-@pytest.mark.parametrize("name", ["c2_stage1", "c2_stage3"])
+def test_more_than_2_31_cost_elements():
+    """Three items of the large configuration in ONE call (bf16 features): cost and cost_grad hold 2.91 G elements
+    each, so the voxel offsets of the last item exceed 32 bits - where the reference switches to 64-bit indices
+    (cost_volume_kernels_gpu.cu.cc:313,619).  Band check on the LAST item, forward and all three gradients."""
+    B = 3
+    w = synth.make("c3_large", with_grad=False, B=B)
+    for k in ("ref", "src"):
+        w[k] = torch.from_numpy(w[k]).to(torch.bfloat16).float().numpy()
+    t = {k: torch.from_numpy(v).to(DEV) for k, v in w.items()}
+    args = (t["ref"].to(torch.bfloat16), t["src"].to(torch.bfloat16), t["base_plane"], t["offsets"], t["Rs"], t["Ts"])
+    cost, mask = ops.cost_forward(1, *args)
+    assert cost.numel() > 2 ** 31
+    rows = 2
+    g = torch.Generator(device=DEV)
+    g.manual_seed(8)
+    cg = torch.zeros_like(cost)
+    cg[B - 1, :rows] = torch.randn(cg[B - 1, :rows].shape, device=DEV, generator=g)
+    rg, sg, bg = ops.cost_backward(1, *args, cg, mask)
+    b = slice(B - 1, B)
+    ref = np.ascontiguousarray(w["ref"][b, :rows])
+    base = np.ascontiguousarray(w["base_plane"][b, :rows])
+    c_o, m_o = oracle.cost_fwd(1, ref, w["src"][b], base, w["offsets"][b], w["Rs"][b], w["Ts"][b])
+    assert helpers.bits_equal(mask[b, :rows].cpu().numpy(), m_o)
+    c_g = cost[b, :rows].cpu().numpy()
+    assert helpers.rel_err(c_g, c_o) <= 1e-5 and helpers.elementwise_excess(c_g, c_o, 1e-5) <= 1.0
+    rg_o, sg_o, bg_o = oracle.cost_bwd(1, ref, w["src"][b], base, w["offsets"][b], w["Rs"][b], w["Ts"][b],
+                                       cg[b, :rows].cpu().numpy(), m_o)
+    for got, want in ((rg[b, :rows], rg_o), (sg[b], sg_o), (bg[b, :rows], bg_o)):
+        got = got.cpu().numpy()
+        assert helpers.rel_err(got, want) <= 1e-4
+        assert helpers.elementwise_excess(got, want, 1e-4, 1e-5) <= 1.0
+    assert float(sg[:B - 1].abs().max()) == 0.0 and float(rg[:B - 1].abs().max()) == 0.0
+    # the first item of the same call against its own band (offsets below 2^31): same code path, small indices
+    c_o0, m_o0 = oracle.cost_fwd(1, np.ascontiguousarray(w["ref"][:1, :rows]), w["src"][:1],
+                                 np.ascontiguousarray(w["base_plane"][:1, :rows]), w["offsets"][:1], w["Rs"][:1], w["Ts"][:1])
+    assert helpers.bits_equal(mask[:1, :rows].cpu().numpy(), m_o0)
+    assert helpers.rel_err(cost[:1, :rows].cpu().numpy(), c_o0) <= 1e-5
+
+
+@pytest.mark.parametrize("name", ["c2_stage1", "c2_stage2", "c2_stage3"])
 def test_cascade_stage_v2(name):
-    """CostVolumeV2 stages (V=5, 8 groups, bf16 features): band check of cost, mask, d(ref) and the per-voxel
-    depth-hypothesis gradient against the oracle."""
-    w = synth.make(name, with_grad=False, scale=0.5)
+    """CostVolumeV2 stages at full size (V=5, 8 groups, bf16 features): band check of cost, mask, d(ref) and the
+    per-voxel depth-hypothesis gradient against the oracle; d(src) through the band-only upstream gradient."""
+    w = synth.make(name, with_grad=False)
     G = w.pop("groups")
     for k in ("ref", "src"):
         w[k] = torch.from_numpy(w[k]).to(torch.bfloat16).float().numpy()
@@ -164,10 +227,16 @@ def test_cascade_stage_v2(name):
     c_o, m_o = oracle.cost_fwd(2, ref, w["src"][:1], grid, None, w["Rs"][:1], w["Ts"][:1], groups=G)
     assert helpers.bits_equal(mask[:1, :rows].cpu().numpy(), m_o)
     assert helpers.rel_err(cost[:1, :rows].cpu().numpy(), c_o) <= 1e-5
-    rg_o, _, dg_o = oracle.cost_bwd(2, ref, w["src"][:1], grid, None, w["Rs"][:1], w["Ts"][:1], cg[:1, :rows].cpu().numpy(), m_o,
-                                    groups=G)
+    rg_o, sg_o, dg_o = oracle.cost_bwd(2, ref, w["src"][:1], grid, None, w["Rs"][:1], w["Ts"][:1], cg[:1, :rows].cpu().numpy(), m_o,
+                                       groups=G)
     assert helpers.rel_err(rg[:1, :rows].cpu().numpy(), rg_o) <= 1e-4
     assert helpers.rel_err(dg[:1, :rows].cpu().numpy(), dg_o) <= 1e-4
+    assert helpers.elementwise_excess(cost[:1, :rows].cpu().numpy(), c_o, 1e-5) <= 1.0
+    cg_only = torch.zeros_like(cg)
+    cg_only[:1, :rows] = cg[:1, :rows]
+    _, sg2, _ = ops.cost_backward(2, *args, cg_only, mask, groups=G)
+    assert helpers.rel_err(sg2[:1].cpu().numpy(), sg_o) <= 1e-4
+    assert helpers.elementwise_excess(sg2[:1].cpu().numpy(), sg_o, 1e-4, 1e-5) <= 1.0
 
 
 def test_manifold_conv_full_size():

@@ -80,7 +80,7 @@ def _worker(rank, world, port, batch, tmp):
                                 inp["offsets"].numpy()[:, d0:d1], inp["Rs"].numpy(), inp["Ts"].numpy(),
                                 cost_grad.numpy()[:, :, :, d0:d1], mask.numpy()[:, :, :, d0:d1])
             for v, x in zip(views, g):
-                v += torch.from_numpy(x)
+                v.copy_(torch.from_numpy(x))       # the op writes its outputs (the CUDA op zero-fills them first)
 
         res = shard.sharded_forward_backward(rank, plan, groups, items, lambda b, cost: torch.from_numpy(full[b]["cost_grad"]),
                                              fwd, bwd, "cpu")
@@ -95,6 +95,49 @@ def _worker(rank, world, port, batch, tmp):
         open(os.path.join(tmp, "rank%d.ok" % rank), "w").write("1" if ok else "0")
     finally:
         dist.destroy_process_group()
+
+
+def _pipeline_worker(rank, world, port, tmp):
+    """Three consecutive steps of one depth-split item through PipelinedReducer: every step's reduced gradients
+    equal the unsharded ones although step k's all-reduce is only joined after step k+1 has been issued."""
+    import oracle
+    from tests import helpers
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        D = 10
+        c = helpers.make_case(1, 61, 1, 2, 8, 10, 4, D, "random", np.float32)
+        steps = [helpers.oracle_fwd_bwd(1, c, "MEAN", 1, True, np.float32, seed=80 + k) for k in range(3)]
+        mine = shard.partition(1, D, world)[rank][0]
+        d0, d1 = mine.d_begin, mine.d_end
+        pipe = shard.PipelinedReducer([c["ref"].shape, c["src"].shape, c["depth"].shape], torch.float32, "cpu", dist.group.WORLD)
+        slots = []
+        for k in range(3):
+            views = pipe.next_views()
+            g = oracle.cost_bwd(1, c["ref"], c["src"], c["depth"], c["offsets"][:, d0:d1], c["Rs"], c["Ts"],
+                                steps[k]["cost_grad"][:, :, :, d0:d1], steps[k]["mask"][:, :, :, d0:d1])
+            for v, x in zip(views, g):
+                v.copy_(torch.from_numpy(x))
+            slots.append(pipe.reduce_async())
+            if k >= 1:   # read step k-1 only now: its collective overlapped this step's work
+                got = [t.clone() for t in pipe.result(slots[k - 1])]
+                slots[k - 1] = got
+        slots[2] = [t.clone() for t in pipe.result(slots[2])]
+        pipe.finish()
+        ok = True
+        for k in range(3):
+            for got, key in zip(slots[k], ("ref_grad", "src_grad", "depth_grad")):
+                ok &= helpers.rel_err(got.numpy(), steps[k][key]) < 1e-5
+        open(os.path.join(tmp, "rank%d.ok" % rank), "w").write("1" if ok else "0")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_pipelined_reducer_over_gloo(tmp_path):
+    port = _free_port()
+    mp.spawn(_pipeline_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert [open(tmp_path / ("rank%d.ok" % r)).read() for r in range(2)] == ["1", "1"]
 
 
 @pytest.mark.parametrize("batch", [1, 2])
