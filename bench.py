@@ -31,9 +31,33 @@ if ROOT not in sys.path:
 
 import numpy as np  # noqa: E402
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, ncu capture of `bench.py --profile` on this workload
-NCU_DRAM_BYTES = {("c1_mvsnet", "fwd"): 471.7e6, ("c1_mvsnet", "bwd"): 575.9e6}
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "dram_traffic.json")
+KERNEL_SOURCES = ("cv_packed.cuh", "cv_tuned.cuh", "cv_project.cuh", "chop_common.cuh", "cv_launch.cuh")
 
+
+def kernel_source_digest():
+    """sha1 over the kernel sources the c1 step compiles from: ties a recorded ncu figure to the code it was taken on."""
+    import hashlib
+    h = hashlib.sha1()
+    for name in KERNEL_SOURCES:
+        with open(os.path.join(ROOT, "custom_helper_op_b200", "csrc", name), "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()
+
+
+def recorded_traffic(workload, which):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of the workload's forward / backward kernel, as written
+    into profiles/dram_traffic.json when the ncu capture was summarised.  None if there is no record, or if the kernel
+    sources have changed since (a stale figure is worse than none)."""
+    try:
+        rec = json.load(open(TRAFFIC_FILE))[workload]
+        if rec.get("source_sha1") != kernel_source_digest():
+            return None
+        return float(rec[which]["dram_bytes"])
+    except Exception:
+        return None
+
+LAUNCHES_PER_STEP = 3
 METRIC = "cost_volume_fwd_bwd_voxel_views_per_s"
 UNIT = "voxel*views/s"
 
@@ -327,16 +351,57 @@ def gpu_main(args):
             dt = float(tt.item())
         e2e = {"value": units_rank * world / dt, "unit": UNIT, "h2d_bytes_per_step": int(h2d),
                "d2h_bytes_per_step": int(d2h), "ms_per_step": dt * 1e3, "steps": ke}
+        # copy-only probe: the step's host->device and device->host bytes from the same pinned buffers, both directions
+        # at once, no kernel, all ranks together - the floor the host side sets for ms_per_step at this N
+        s_a, s_b = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+        def copy_only():
+            with torch.cuda.stream(s_a):
+                for k in t:
+                    t[k].copy_(host[k], non_blocking=True)
+                cost_grad.copy_(h_cg, non_blocking=True)
+            with torch.cuda.stream(s_b):
+                h_out["cost"].copy_(cost, non_blocking=True)
+                h_out["mask"].copy_(mask, non_blocking=True)
+                for name, g_ in zip(("ref_grad", "src_grad", "base_plane_grad"), grads):
+                    h_out[name].copy_(g_, non_blocking=True)
+            s_a.synchronize()
+            s_b.synchronize()
+
+        copy_only()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(ke):
+            copy_only()
+        barrier()
+        dtc = (time.perf_counter() - t0) / ke
+        if world > 1:
+            tt = torch.tensor([dtc], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            dtc = float(tt.item())
+        e2e["copy_only_ms"] = dtc * 1e3
+        e2e["copy_only_gbs_per_rank"] = (h2d + d2h) / dtc / 1e9
+        e2e["copy_only_gbs_aggregate"] = (h2d + d2h) * world / dtc / 1e9
+        del pipe, h_cg, h_out
+
+    # ---- the legs that exercise the sharding module: one item split by depth, and the large batch dealt out ----
+    depth_leg = c3_leg = None
+    if args.shard == "batch" and not args.profile and not args.no_extra_legs:
+        del cost, mask, cost_grad
+        torch.cuda.empty_cache()
+        if world > 1:
+            depth_leg = depth_shard_leg(args, rank, world, dev, ms_per_step)
+        c3_leg = c3_batch_leg(args, rank, world, dev)
 
     if rank == 0:
         fwd_b, bwd_b = algorithmic_bytes(dict(dims, D=(d_hi - d_lo)))
         peak, peak_kind = measured_peak()
-        dom = ("cv_bwd_tuned (+ 3 zero-fill memsets)", bwd_b, bwd_ms, "bwd") if bwd_ms >= fwd_ms else \
-              ("cv_fwd_tuned", fwd_b, fwd_ms, "fwd")
+        dom = ("CostVolumeGrad kernel (+ the zero fill of the gradient outputs)", bwd_b, bwd_ms, "bwd") if bwd_ms >= fwd_ms else \
+              ("CostVolume kernel", fwd_b, fwd_ms, "fwd")
         ach = dom[1] / (dom[2] * 1e-3) / 1e9
-        # DRAM bytes per launch of the dominant kernel from the committed ncu capture of this workload
-        # (profiles/cost_volume_c1_mvsnet_ncu.md: dram__bytes_read.sum + dram__bytes_write.sum); null elsewhere
-        traffic = NCU_DRAM_BYTES.get((args.workload, dom[3])) if (args.shard == "batch" and d_lo == 0 and d_hi == D) else None
+        # DRAM bytes per launch of the dominant kernel from the recorded ncu capture of this workload; null when the
+        # kernel sources are newer than the record
+        traffic = recorded_traffic(args.workload, dom[3]) if (args.shard == "batch" and d_lo == 0 and d_hi == D) else None
         roof = {"bound": "hbm", "kernel": dom[0], "achieved": ach, "peak": peak, "peak_source": peak_kind,
                 "unit": "GB/s", "frac": ach / peak, "traffic": traffic,
                 "fwd": {"ms": fwd_ms, "algorithmic_bytes": fwd_b, "gbs": fwd_b / (fwd_ms * 1e-3) / 1e9},
@@ -347,6 +412,10 @@ def gpu_main(args):
         if world == 1 and not args.no_cpu_baseline and not args.profile:
             v, info = cpu_reference_run(args.workload, budget_s=6.0, steps=3)
             cpu = {"value": v, "unit": UNIT, "cores": info["cores"], "kind": info["kind"], "sample": info["sample"]}
+            # the reference's CPU-sized configuration (BASELINE configs[0]) in full, beside the sample of this workload
+            v0, info0 = cpu_reference_run("c0_cpu", budget_s=1e9, steps=5, warmup=1)
+            cpu["c0_cpu"] = {"value": v0, "unit": UNIT, "cores": info0["cores"], "kind": info0["kind"],
+                             "sample": info0["sample"], "ms_per_step": info0["ms_per_step"]}
         out = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K,
                "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
                "scaling": "weak" if args.shard == "batch" else "strong", "vs_baseline": None, "dtype": "f32",
@@ -355,11 +424,180 @@ def gpu_main(args):
                                       (args.workload, B, N + 1, C, H, W, D),
                           "shard": args.shard, "l2": "inputs_exceed_l2 (cost and cost_grad are %d MB each, L2 is 126 MB)" %
                                                      (B * H * W * D * C * 4 // 2**20)},
-               "clocks": sampler.summary(t_wall0, t_wall1), "e2e": e2e, "gpu_launches": 2 * K,
+               "clocks": sampler.summary(t_wall0, t_wall1), "e2e": e2e,
+               # per step: the forward kernel, one zero-fill kernel over the three gradient outputs, the gradient kernel
+               "gpu_launches": LAUNCHES_PER_STEP * K,
                "roofline": roof, "cpu_baseline": cpu}
+        if depth_leg is not None:
+            out["depth_shard"] = depth_leg
+        if c3_leg is not None:
+            out["c3"] = c3_leg
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def depth_shard_leg(args, rank, world, dev, n1_ms):
+    """ONE item of the workload split over all ranks by depth range (shard.partition(1, D, world)): every rank runs
+    forward + backward on its planes and the partial [ref_grad | src_grad | base_plane_grad] are summed by one NCCL
+    all-reduce on a packed buffer, inside the timed region.  Consecutive steps alternate between two packed buffers,
+    so a step's all-reduce overlaps the next step's forward (shard.PipelinedReducer).  `check` compares the reduced
+    gradients with this rank's own full-range backward on the same inputs, outside the timed region."""
+    import torch
+    import torch.distributed as dist
+
+    from custom_helper_op_b200 import shard, synth
+    from custom_helper_op_b200.python.ops import custom_helper_ops as ops
+
+    dims = workload_dims(args.workload)
+    B, N, C, H, W, D = 1, dims["N"], dims["C"], dims["H"], dims["W"], dims["D"]
+    wl = synth.make(args.workload, with_grad=False)          # the same item on every rank
+    t = {k: torch.from_numpy(np.ascontiguousarray(v[:1])).to(dev) for k, v in wl.items()}
+    a = (t["ref"], t["src"], t["base_plane"], t["offsets"], t["Rs"], t["Ts"])
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4321)                                     # the same upstream gradient on every rank
+    cost_grad = torch.randn((B, H, W, D, C), device=dev, generator=gen)
+    cost = torch.empty((B, H, W, D, C), device=dev)
+    mask = torch.empty((B, H, W, D, 1), dtype=torch.int32, device=dev)
+    mine = shard.partition(1, D, world)[rank][0]
+    d0, d1 = mine.d_begin, mine.d_end
+    shapes = [(B, H, W, C), (B, N, H, W, C), (B, H, W, 1)]
+    pipe = shard.PipelinedReducer(shapes, torch.float32, dev, dist.group.WORLD)
+
+    def step():
+        if d1 > d0:
+            ops.cost_forward(1, *a, d_range=(d0, d1), out=(cost, mask))
+        views = pipe.next_views()                             # joins the all-reduce issued two steps ago
+        if d1 > d0:
+            ops.cost_backward(1, *a, cost_grad, mask, d_range=(d0, d1), zero_into=tuple(views))
+        else:
+            pipe.slots[pipe.k % 2].zero_()
+        return pipe.reduce_async()
+
+    def sync():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(5):
+        step()
+    pipe.finish()
+    sync()
+    K = max(20, min(args.steps, 200))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        last = step()
+    pipe.finish()
+    e1.record()
+    sync()
+    ms = e0.elapsed_time(e1) / K
+    # the collective alone (no overlap), and a serial step for comparison
+    red = shard.GradReducer(shapes, torch.float32, dev, dist.group.WORLD, zero=True)
+    for _ in range(3):
+        red.all_reduce()
+    sync()
+    e0.record()
+    for _ in range(20):
+        red.all_reduce()
+    e1.record()
+    sync()
+    ar_ms = e0.elapsed_time(e1) / 20
+    e0.record()
+    for _ in range(20):
+        if d1 > d0:
+            ops.cost_forward(1, *a, d_range=(d0, d1), out=(cost, mask))
+            ops.cost_backward(1, *a, cost_grad, mask, d_range=(d0, d1), zero_into=tuple(red.views))
+        red.all_reduce()
+    e1.record()
+    sync()
+    serial_ms = e0.elapsed_time(e1) / 20
+    stats = torch.tensor([ms, ar_ms, serial_ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    ms, ar_ms, serial_ms = (float(x) for x in stats.tolist())
+    # result check, outside the timed region: the reduced gradients of the last step against this rank's own
+    # full-range gradient (the full mask comes from a full-range forward)
+    got = [g.clone() for g in pipe.result(last)]
+    ops.cost_forward(1, *a, out=(cost, mask))
+    want = ops.cost_backward(1, *a, cost_grad, mask)
+    scale_err, elem_err = 0.0, 0.0
+    for g, w_ in zip(got, want):
+        diff = (g - w_).abs()
+        top = float(w_.abs().max())
+        scale_err = max(scale_err, float(diff.max()) / max(top, 1e-30))
+        elem_err = max(elem_err, float((diff / (1e-4 * w_.abs() + 1e-5 * top)).max()))
+    chk = torch.tensor([scale_err, elem_err], device=dev, dtype=torch.float64)
+    dist.all_reduce(chk, op=dist.ReduceOp.MAX)
+    units = H * W * D * N
+    return {"what": "one %s item split by depth over %d ranks, packed all-reduce of %.1f MB per step in the timed region, "
+                    "overlapped with the next step's forward" % (args.workload, world, sum(int(np.prod(s_)) for s_ in shapes) * 4 / 1e6),
+            "ms_per_step": ms, "value": units / (ms * 1e-3), "unit": UNIT, "steps": K, "planes_per_rank": d1 - d0,
+            "speedup_vs_n1": n1_ms / ms, "allreduce_ms": ar_ms, "serial_ms_per_step": serial_ms,
+            "check": {"max_scale_relative_error": float(chk[0]), "elementwise_excess_rtol1e-4_atol1e-5max": float(chk[1]),
+                      "pass": bool(float(chk[0]) <= 1e-4 and float(chk[1]) <= 1.0)}}
+
+
+def c3_batch_leg(args, rank, world, dev):
+    """BASELINE configs[3]: B=8, V=7, C=32, 296x400, D=256 (inverse-depth planes), bf16 features, dealt out by
+    shard.partition(8, 256, world) and run through shard.sharded_forward_backward: with world <= 8 every rank owns
+    whole items (8/world each) and nothing is exchanged; with more ranks than items the depth ranges of an item are
+    all-reduced.  Features are drawn on the device (N(0,1) rounded to bf16), cameras and depths as in synth."""
+    import torch
+    import torch.distributed as dist
+
+    from custom_helper_op_b200 import shard, synth
+
+    cfg = synth.CONFIGS["c3_large"]
+    Bt, N, C, H, W, D = cfg["B"], cfg["V"] - 1, cfg["C"], cfg["H"], cfg["W"], cfg["D"]
+    plan = shard.partition(Bt, D, world)
+    groups = shard.make_groups(plan) if world > 1 else {}
+    inputs = {}
+    lo, hi = cfg["depth_range"]
+    offs = torch.tensor(1.0 / np.linspace(1.0 / lo, 1.0 / hi, D), dtype=torch.float32, device=dev)[None]
+    for sh in plan[rank]:
+        b = sh.item
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(20245 * 100 + b)
+        Rs, Ts = synth.random_cameras(np.random.default_rng(20245 * 100 + b), 1, N, H, W)
+        inputs[b] = dict(ref=torch.randn((1, H, W, C), device=dev, generator=gen).bfloat16(),
+                         src=torch.randn((1, N, H, W, C), device=dev, generator=gen).bfloat16(),
+                         base_plane=torch.zeros((1, H, W, 1), device=dev), offsets=offs,
+                         Rs=torch.from_numpy(Rs.astype(np.float32)).to(dev), Ts=torch.from_numpy(Ts.astype(np.float32)).to(dev))
+    cost = torch.empty((1, H, W, D, C), device=dev)
+    mask = torch.empty((1, H, W, D, 1), dtype=torch.int32, device=dev)
+    cost_grad = torch.randn((1, H, W, D, C), device=dev)
+    fwd, bwd = shard.cuda_compute_fns(buffers=(cost, mask))
+
+    def step():
+        return shard.sharded_forward_backward(rank, plan, groups, inputs, lambda b, c_: cost_grad, fwd, bwd, dev)
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    step()
+    sync()
+    K = 3
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        res = step()
+    e1.record()
+    sync()
+    ms = e0.elapsed_time(e1) / K
+    seen = float(sum((r[1] > 0).float().mean().item() for r in res.values() if r[1] is not None) / max(1, len(res)))
+    if world > 1:
+        tt = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt.item())
+    units = Bt * H * W * D * N
+    fwd_b, bwd_b = algorithmic_bytes(dict(kind=1, B=Bt, N=N, C=C, H=H, W=W, D=D, G=1), feat_bytes=2)
+    peak, _ = measured_peak()
+    return {"what": "c3_large: CostVolume fwd+bwd, bf16 features / fp32 accumulate, B=%d, V=%d, C=%d, %dx%d, D=%d; "
+                    "%d item(s) per rank" % (Bt, N + 1, C, H, W, D, len(plan[rank])),
+            "ms_per_step": ms, "value": units / (ms * 1e-3), "unit": UNIT, "steps": K, "items_per_rank": len(plan[rank]),
+            "algorithmic_bytes": fwd_b + bwd_b, "hbm_frac_per_gpu": (fwd_b + bwd_b) / world / (ms * 1e-3) / 1e9 / peak,
+            "voxels_seen_fraction": seen}
 
 
 def sparse_conv_main(args):
@@ -659,6 +897,8 @@ def main():
     ap.add_argument("--shard", default="batch", choices=["batch", "depth"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-chunks", type=int, default=2, help="depth chunks of the host-buffer pipeline")
+    ap.add_argument("--no-extra-legs", action="store_true",
+                    help="skip the depth-shard leg (N > 1) and the c3 batch leg that follow the headline measurement")
     ap.add_argument("--profile", action="store_true",
                     help="device-timed loop only (no clock probe loop, e2e leg or CPU baseline): the command to run under ncu")
     args = ap.parse_args()

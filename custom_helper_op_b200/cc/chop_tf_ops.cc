@@ -9,7 +9,7 @@
 // (custom_helper_op/cc/ops/custom_helper_ops.cc:190-307 CostVolume*, :311-371 CostVolumeV3*, :374-411
 // CostAggregate*, :498-535 SparsePad*, :590-641 SparseConv3DFast*, :644-715 SparseConv3DTransposeFast*), so its
 // Python wrapper and its tf.RegisterGradient functions work unchanged.  The
-// dtype list additionally admits bfloat16.  As in the reference only DEVICE_GPU kernels are registered.
+// As in the reference only DEVICE_GPU kernels are registered (DecodePfm is a host op there and here).
 #include <string>
 #include <vector>
 
@@ -67,7 +67,10 @@ Status GradLikeInputs(InferenceContext* c) {
 
 }  // namespace
 
-#define CHOP_FLOAT_TYPES "{float, double, bfloat16}"
+// The reference's dtype list.  bfloat16 features are reachable through the C ABI and the torch wrapper only: that
+// mode keeps depths, cameras, cost and all gradients in float32 (include/chop.h), which a schema with one type
+// attribute cannot express, and this binding registers no kernel for it.
+#define CHOP_FLOAT_TYPES "{float, double}"
 
 REGISTER_OP("CostVolume")
     .Input("ref_image: dtype").Input("src_images: dtype").Input("base_plane: dtype").Input("offsets: dtype")
@@ -225,16 +228,62 @@ REGISTER_OP("SparseConv3DFastGrad")
     .SetShapeFn(GradLikeInputs);
 
 #if GOOGLE_CUDA
+REGISTER_OP("FeatureAggregate")
+    .Input("src_images: dtype").Input("base_plane: dtype").Input("offsets: dtype").Input("rs: dtype").Input("ts: dtype")
+    .Output("mapped_feature: dtype").Output("mapped_mask: int32")
+    .Attr("dtype: " CHOP_FLOAT_TYPES).Attr("half_centor: bool")
+    .SetShapeFn([](InferenceContext* c) {
+      // [B,H,W,D,N,C] and [B,H,W,D,N,1]: custom_helper_ops.cc:414-441 of the reference
+      ShapeHandle src, base, offs;
+      TF_RETURN_IF_ERROR(c->WithRank(c->input(0), 5, &src));
+      TF_RETURN_IF_ERROR(c->WithRank(c->input(1), 4, &base));
+      TF_RETURN_IF_ERROR(c->WithRank(c->input(2), 2, &offs));
+      c->set_output(0, c->MakeShape({c->Dim(src, 0), c->Dim(base, 1), c->Dim(base, 2), c->Dim(offs, 1), c->Dim(src, 1),
+                                     c->Dim(src, 4)}));
+      c->set_output(1, c->MakeShape({c->Dim(src, 0), c->Dim(base, 1), c->Dim(base, 2), c->Dim(offs, 1), c->Dim(src, 1),
+                                     c->MakeDim(1)}));
+      return Status::OK();
+    });
+
+REGISTER_OP("FeatureAggregateGrad")
+    .Input("src_images: dtype").Input("base_plane: dtype").Input("offsets: dtype").Input("rs: dtype").Input("ts: dtype")
+    .Input("mapped_feature_grad: dtype").Input("mapped_mask: int32")
+    .Output("src_images_grad: dtype").Output("base_plane_grad: dtype")
+    .Attr("dtype: " CHOP_FLOAT_TYPES).Attr("half_centor: bool")
+    .SetShapeFn([](InferenceContext* c) {
+      c->set_output(0, c->input(0));
+      c->set_output(1, c->input(1));
+      return Status::OK();
+    });
+
+REGISTER_OP("IndexInitializer")
+    .Input("output_shape: int32")
+    .Output("output: dtype")
+    .Attr("half_centor: bool").Attr("dtype: " CHOP_FLOAT_TYPES)
+    .SetShapeFn([](InferenceContext* c) {
+      ShapeHandle out;
+      TF_RETURN_IF_ERROR(c->MakeShapeFromShapeTensor(0, &out));   // (height, width, 3)
+      TF_RETURN_IF_ERROR(c->WithRank(out, 3, &out));
+      c->set_output(0, out);
+      return Status::OK();
+    });
+
+REGISTER_OP("DecodePfm")
+    .Input("input: string")
+    .Output("image: float")
+    .SetShapeFn([](InferenceContext* c) {
+      ShapeHandle unused;
+      TF_RETURN_IF_ERROR(c->WithRank(c->input(0), 0, &unused));
+      c->set_output(0, c->MakeShape({c->UnknownDim(), c->UnknownDim(), c->MakeDim(1)}));
+      return Status::OK();
+    });
+
 // ---- kernels ---------------------------------------------------------------------------------------------
 namespace {
 
 template <typename T> struct DtypeOf;
 template <> struct DtypeOf<float> { static constexpr int value = CHOP_F32; };
 template <> struct DtypeOf<double> { static constexpr int value = CHOP_F64; };
-template <> struct DtypeOf<bfloat16> { static constexpr int value = CHOP_BF16; };
-// bfloat16 ops keep depths / cameras / cost in float32 (see chop.h); they are registered with those inputs
-// cast by the Python wrapper, which is why the kernels below read every tensor through tensor_data().
-
 inline const void* In(OpKernelContext* ctx, int i) { return ctx->input(i).tensor_data().data(); }
 inline void* Out(Tensor* t) { return const_cast<char*>(t->tensor_data().data()); }
 inline void* StreamOf(OpKernelContext* ctx) { return ctx->eigen_device<Eigen::GpuDevice>().stream(); }
@@ -506,6 +555,106 @@ class ManifoldPadOp : public OpKernel {
   std::vector<int32> strides_;
 };
 
+// FeatureAggregate / FeatureAggregateGrad (reference kernels: feature_aggregate_kernels.cc:60-130,170-250)
+template <typename T, bool GRADIENT>
+class FeatureAggregateOp : public OpKernel {
+ public:
+  explicit FeatureAggregateOp(OpKernelConstruction* ctx) : OpKernel(ctx) {
+    OP_REQUIRES_OK(ctx, ctx->GetAttr("half_centor", &half_centor_));
+  }
+  void Compute(OpKernelContext* ctx) override {
+    const Tensor& src = ctx->input(0);
+    const Tensor& base = ctx->input(1);
+    const Tensor& offsets = ctx->input(2);
+    const Tensor& Rs = ctx->input(3);
+    const Tensor& Ts = ctx->input(4);
+    OP_REQUIRES(ctx, src.dims() == 5, errors::InvalidArgument("src image must have rank 5"));
+    const int64 B = src.dim_size(0), N = src.dim_size(1), C = src.dim_size(4);
+    OP_REQUIRES(ctx, base.dims() == 4 && base.dim_size(0) == B && base.dim_size(3) == 1,
+                errors::InvalidArgument("base_plane must have rank 4, and must compate to src_images"));
+    OP_REQUIRES(ctx, offsets.dims() == 2 && offsets.dim_size(0) == B,
+                errors::InvalidArgument("offsets must have rank 2, and must compate to src_images"));
+    OP_REQUIRES(ctx, Rs.dims() == 4 && Rs.dim_size(0) == B && Rs.dim_size(1) == N && Rs.dim_size(2) == 3 && Rs.dim_size(3) == 3,
+                errors::InvalidArgument("Rs must have rank 4, and must compate to src_images"));
+    OP_REQUIRES(ctx, Ts.dims() == 3 && Ts.dim_size(0) == B && Ts.dim_size(1) == N && Ts.dim_size(2) == 3,
+                errors::InvalidArgument("Ts must have rank 3, and must compate to src_images"));
+    const int64 H = base.dim_size(1), W = base.dim_size(2), D = offsets.dim_size(1);
+    chop_cv_desc d = {};
+    d.dtype = DtypeOf<T>::value;
+    d.half_centor = half_centor_;
+    d.groups = 1;
+    d.B = B; d.H = H; d.W = W; d.C = C; d.D = D; d.N = N; d.Hs = src.dim_size(2); d.Ws = src.dim_size(3);
+    int status;
+    if (!GRADIENT) {
+      Tensor *mapped = nullptr, *mask = nullptr;
+      OP_REQUIRES_OK(ctx, ctx->allocate_output(0, TensorShape({B, H, W, D, N, C}), &mapped));
+      OP_REQUIRES_OK(ctx, ctx->allocate_output(1, TensorShape({B, H, W, D, N, 1}), &mask));
+      status = chop_feature_aggregate_fwd(&d, In(ctx, 0), In(ctx, 1), In(ctx, 2), In(ctx, 3), In(ctx, 4), Out(mapped),
+                                          static_cast<int32_t*>(Out(mask)), StreamOf(ctx));
+    } else {
+      const Tensor& mg = ctx->input(5);
+      const Tensor& mm = ctx->input(6);
+      OP_REQUIRES(ctx, mg.NumElements() == B * H * W * D * N * C,
+                  errors::InvalidArgument("mapped_feature_grad must have rank 6, and must compate to src_images"));
+      OP_REQUIRES(ctx, mm.NumElements() == B * H * W * D * N,
+                  errors::InvalidArgument("mapped_mask must be the mask returned by the forward op"));
+      Tensor *sg = nullptr, *bg = nullptr;
+      OP_REQUIRES_OK(ctx, ctx->allocate_output(0, src.shape(), &sg));
+      OP_REQUIRES_OK(ctx, ctx->allocate_output(1, base.shape(), &bg));
+      status = chop_feature_aggregate_bwd(&d, In(ctx, 0), In(ctx, 1), In(ctx, 2), In(ctx, 3), In(ctx, 4), In(ctx, 5),
+                                          static_cast<const int32_t*>(In(ctx, 6)), Out(sg), Out(bg), StreamOf(ctx));
+    }
+    OP_REQUIRES(ctx, status == 0, errors::Internal("libchop_b200: ", chop_status_string(status)));
+  }
+
+ private:
+  bool half_centor_ = true;
+};
+
+// IndexInitializer (index_initializer_kernels.cc:52-100): output_shape = (height, width, 3) in host memory
+template <typename T>
+class IndexInitializerOp : public OpKernel {
+ public:
+  explicit IndexInitializerOp(OpKernelConstruction* ctx) : OpKernel(ctx) {
+    OP_REQUIRES_OK(ctx, ctx->GetAttr("half_centor", &half_centor_));
+  }
+  void Compute(OpKernelContext* ctx) override {
+    const Tensor& shape = ctx->input(0);
+    OP_REQUIRES(ctx, shape.dims() == 1 && shape.NumElements() == 3,
+                errors::InvalidArgument("output_shape must be a 1-D vector of 3 elements (height, width, 3)"));
+    const auto v = shape.vec<int32>();
+    OP_REQUIRES(ctx, v(0) > 0 && v(1) > 0 && v(2) == 3, errors::InvalidArgument("output_shape must be (height > 0, width > 0, 3)"));
+    Tensor* out = nullptr;
+    OP_REQUIRES_OK(ctx, ctx->allocate_output(0, TensorShape({v(0), v(1), 3}), &out));
+    const int status = chop_index_initializer(DtypeOf<T>::value, half_centor_, v(0), v(1), Out(out), StreamOf(ctx));
+    OP_REQUIRES(ctx, status == 0, errors::Internal("libchop_b200: ", chop_status_string(status)));
+  }
+
+ private:
+  bool half_centor_ = true;
+};
+
+// DecodePfm (pfm_decoder_kernels.cc:30-118): a host op; the parser reports the reference's error texts
+class DecodePfmOp : public OpKernel {
+ public:
+  explicit DecodePfmOp(OpKernelConstruction* ctx) : OpKernel(ctx) {}
+  void Compute(OpKernelContext* ctx) override {
+    const Tensor& contents = ctx->input(0);
+    OP_REQUIRES(ctx, TensorShapeUtils::IsScalar(contents.shape()), errors::InvalidArgument("contents must be scalar"));
+    const tstring& data = contents.scalar<tstring>()();
+    int64_t h = 0, w = 0, ch = 0;
+    char msg[256] = {0};
+    int status = chop_decode_pfm(data.data(), data.size(), &h, &w, &ch, nullptr, 0, msg, sizeof(msg));
+    OP_REQUIRES(ctx, status == 0, errors::InvalidArgument(msg[0] ? msg : chop_status_string(status)));
+    Tensor* image = nullptr;
+    OP_REQUIRES_OK(ctx, ctx->allocate_output(0, TensorShape({h, w, ch}), &image));
+    status = chop_decode_pfm(data.data(), data.size(), &h, &w, &ch, image->flat<float>().data(), (size_t)(h * w * ch), msg,
+                             sizeof(msg));
+    OP_REQUIRES(ctx, status == 0, errors::InvalidArgument(msg[0] ? msg : chop_status_string(status)));
+  }
+};
+REGISTER_KERNEL_BUILDER(Name("DecodePfm").Device(DEVICE_CPU), DecodePfmOp);
+
 #define CHOP_REGISTER(T)                                                                                                   \
   REGISTER_KERNEL_BUILDER(Name("CostVolume").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), CostOp<T, CHOP_COST_VOLUME, false>);      \
   REGISTER_KERNEL_BUILDER(Name("CostVolumeGrad").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), CostOp<T, CHOP_COST_VOLUME, true>);   \
@@ -522,7 +671,11 @@ class ManifoldPadOp : public OpKernel {
   REGISTER_KERNEL_BUILDER(Name("SparseConv3DTransposeFastGrad").Device(DEVICE_GPU).TypeConstraint<T>("dtype").HostMemory("output_size"), \
                           ManifoldConvTransposeOp<T, true>);                                                                          \
   REGISTER_KERNEL_BUILDER(Name("SparsePad").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), ManifoldPadOp<T, false>);                  \
-  REGISTER_KERNEL_BUILDER(Name("SparsePadGrad").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), ManifoldPadOp<T, true>);
+  REGISTER_KERNEL_BUILDER(Name("SparsePadGrad").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), ManifoldPadOp<T, true>);                \
+  REGISTER_KERNEL_BUILDER(Name("FeatureAggregate").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), FeatureAggregateOp<T, false>);     \
+  REGISTER_KERNEL_BUILDER(Name("FeatureAggregateGrad").Device(DEVICE_GPU).TypeConstraint<T>("dtype"), FeatureAggregateOp<T, true>);  \
+  REGISTER_KERNEL_BUILDER(Name("IndexInitializer").Device(DEVICE_GPU).TypeConstraint<T>("dtype").HostMemory("output_shape"),         \
+                          IndexInitializerOp<T>);
 
 CHOP_REGISTER(float)
 CHOP_REGISTER(double)

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 
 #include "../../include/chop.h"
@@ -53,6 +54,7 @@ int validate(const chop_cv_desc* d, CvArgs* a, Typed* ty) {
   if (d->kind < CHOP_COST_VOLUME || d->kind > CHOP_COST_VOLUME_V3) return CHOP_ERR_ATTR;
   if (d->reduce != CHOP_REDUCE_MEAN && d->reduce != CHOP_REDUCE_MIN) return CHOP_ERR_ATTR;
   if (int e = typed_of(d->dtype, ty)) return e;
+  if (d->flags & ~(CHOP_FLAG_STRICT | CHOP_FLAG_ACCUMULATE)) return CHOP_ERR_ATTR;  // a bit this build does not know
   const int64_t dims[] = {d->B, d->H, d->W, d->C, d->D, d->N, d->Hs, d->Ws};
   for (int64_t v : dims)
     if (v < 1 || v > INT32_MAX) return CHOP_ERR_SHAPE;
@@ -157,6 +159,43 @@ int dispatch_bwd(int dtype, const CvArgs& a, const CvPlan& p, cudaStream_t st) {
     case CHOP_F64: return chop::cv_bwd_f64(a, p, st);
     default: return chop::cv_bwd_bf16(a, p, st);
   }
+}
+
+// Zero fill of up to three gradient outputs in ONE launch (the reference launcher issues three,
+// cost_volume_kernels_gpu.cu.cc:637-642).  Sizes in bytes, multiples of 4; 16-byte stores where a buffer's
+// base allows it.
+struct ZeroJob {
+  void* p[3];
+  unsigned long long bytes[3];
+};
+__global__ void __launch_bounds__(256) zero_fill_kernel(const ZeroJob z) {
+  const unsigned long long tid = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const unsigned long long nth = (unsigned long long)gridDim.x * blockDim.x;
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    if (!z.p[i]) continue;
+    unsigned char* base = static_cast<unsigned char*>(z.p[i]);
+    const unsigned long long n = z.bytes[i];
+    if ((reinterpret_cast<uintptr_t>(base) & 15) == 0) {
+      const unsigned long long n16 = n / 16;
+      for (unsigned long long k = tid; k < n16; k += nth) reinterpret_cast<uint4*>(base)[k] = make_uint4(0u, 0u, 0u, 0u);
+      for (unsigned long long k = n16 * 4 + tid; k < n / 4; k += nth) reinterpret_cast<unsigned*>(base)[k] = 0u;
+    } else {
+      for (unsigned long long k = tid; k < n / 4; k += nth) reinterpret_cast<unsigned*>(base)[k] = 0u;
+    }
+  }
+}
+int zero_fill(void* p0, size_t b0, void* p1, size_t b1, void* p2, size_t b2, cudaStream_t st) {
+  ZeroJob z;
+  z.p[0] = p0; z.bytes[0] = b0;
+  z.p[1] = p1; z.bytes[1] = b1;
+  z.p[2] = p2; z.bytes[2] = b2;
+  const size_t most = (b0 > b1 ? (b0 > b2 ? b0 : b2) : (b1 > b2 ? b1 : b2));
+  size_t blocks = (most / 16 + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  zero_fill_kernel<<<(unsigned)blocks, 256, 0, st>>>(z);
+  return (int)cudaGetLastError();
 }
 
 }  // namespace
@@ -275,10 +314,9 @@ int chop_cost_volume_bwd(const chop_cv_desc* d, const void* ref, const void* src
       return CHOP_ERR_ALIGN;
     cudaStream_t st3 = static_cast<cudaStream_t>(stream);
     if (!(d->flags & CHOP_FLAG_ACCUMULATE)) {   // zero fill: cost_volume_kernels_gpu_v3.cu.cc:667-672
-      cudaError_t e = cudaMemsetAsync(ref_grad, 0, (size_t)a.npix * a.C * ty.real_size, st3);
-      if (e == cudaSuccess) e = cudaMemsetAsync(src_grad, 0, (size_t)a.B * a.N * a.Hs * a.Ws * a.C * ty.real_size, st3);
-      if (e == cudaSuccess) e = cudaMemsetAsync(depth_grad, 0, (size_t)a.npix * ty.real_size, st3);
-      if (e != cudaSuccess) return (int)e;
+      if (int e = zero_fill(ref_grad, (size_t)a.npix * a.C * ty.real_size, src_grad,
+                            (size_t)a.B * a.N * a.Hs * a.Ws * a.C * ty.real_size, depth_grad, (size_t)a.npix * ty.real_size, st3))
+        return e;
     }
     if (a.d_begin == a.d_end) return CHOP_OK;
     a.lg_log2 = pow2ceil_log2(a.G);
@@ -309,12 +347,10 @@ int chop_cost_volume_bwd(const chop_cv_desc* d, const void* ref, const void* src
   if (!(d->flags & CHOP_FLAG_ACCUMULATE)) {
     // the reference launcher zero-fills the three outputs (cost_volume_kernels_gpu.cu.cc:637-642);
     // the v2 depth gradient is a per-voxel store and needs no fill
-    cudaError_t e = cudaMemsetAsync(ref_grad, 0, (size_t)a.npix * a.C * ty.real_size, st);
-    if (e == cudaSuccess)
-      e = cudaMemsetAsync(src_grad, 0, (size_t)a.B * a.N * a.Hs * a.Ws * a.C * ty.real_size, st);
-    if (e == cudaSuccess && d->kind != CHOP_COST_VOLUME_V2)
-      e = cudaMemsetAsync(depth_grad, 0, (size_t)a.npix * ty.real_size, st);
-    if (e != cudaSuccess) return (int)e;
+    if (int e = zero_fill(ref_grad, (size_t)a.npix * a.C * ty.real_size, src_grad,
+                          (size_t)a.B * a.N * a.Hs * a.Ws * a.C * ty.real_size,
+                          d->kind != CHOP_COST_VOLUME_V2 ? depth_grad : nullptr, (size_t)a.npix * ty.real_size, st))
+      return e;
   }
   if (a.d_begin == a.d_end) return CHOP_OK;
 
@@ -358,6 +394,9 @@ namespace {
 int fa_prepare(const chop_cv_desc* d, CvArgs* a, Typed* ty, int* cpl) {
   if (!d) return CHOP_ERR_NULL;
   if (int e = typed_of(d->dtype, ty)) return e;
+  // FeatureAggregate has no kind / reduce_method / groups: the fields must be left at zero (groups: 0 or 1)
+  if (d->kind != 0 || d->reduce != 0 || d->groups < 0 || d->groups > 1) return CHOP_ERR_ATTR;
+  if (d->flags & ~CHOP_FLAG_ACCUMULATE) return CHOP_ERR_ATTR;
   const int64_t dims[] = {d->B, d->H, d->W, d->C, d->D, d->N, d->Hs, d->Ws};
   for (int64_t v : dims)
     if (v < 1 || v > INT32_MAX) return CHOP_ERR_SHAPE;
@@ -415,9 +454,9 @@ int chop_feature_aggregate_bwd(const chop_cv_desc* d, const void* src, const voi
     return CHOP_ERR_ALIGN;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (!(d->flags & CHOP_FLAG_ACCUMULATE)) {
-    cudaError_t e = cudaMemsetAsync(src_grad, 0, (size_t)a.B * a.N * a.Hs * a.Ws * a.C * ty.real_size, st);
-    if (e == cudaSuccess) e = cudaMemsetAsync(base_plane_grad, 0, (size_t)a.npix * ty.real_size, st);
-    if (e != cudaSuccess) return (int)e;
+    if (int e = zero_fill(src_grad, (size_t)a.B * a.N * a.Hs * a.Ws * a.C * ty.real_size, base_plane_grad,
+                          (size_t)a.npix * ty.real_size, nullptr, 0, st))
+      return e;
   }
   if (a.d_begin == a.d_end) return CHOP_OK;
   plan_chunks(&a, 1 << a.lg_log2, 148 * 128, 16, g_bwd_chunk.load());
@@ -464,6 +503,9 @@ int chop_version(void) { return 100; }
 
 int chop_set_tuning(const char* name, int value) {
   if (!name) return CHOP_ERR_NULL;
+  // the knobs are process-wide: a test / benchmark facility, refused unless the process opted in
+  static const bool enabled = [] { const char* e = std::getenv("CHOP_ENABLE_TUNING"); return e && e[0] == '1'; }();
+  if (!enabled) return CHOP_ERR_UNSUPPORTED;
   if (!std::strcmp(name, "fwd_chunk")) { g_fwd_chunk = value; return CHOP_OK; }
   if (!std::strcmp(name, "bwd_chunk")) { g_bwd_chunk = value; return CHOP_OK; }
   if (!std::strcmp(name, "bwd_views")) { g_bwd_views = value; return CHOP_OK; }

@@ -1,12 +1,11 @@
 // Typed kernel selection for the cost-volume kernels.  Each cv_<dtype>.cu instantiates this header
 // for one feature type so the three translation units compile in parallel.
 #pragma once
-#include <atomic>
-
 #include "cv_bwd.cuh"
 #include "cv_fwd.cuh"
 #include "cv_packed.cuh"
 #include "cv_tuned.cuh"
+#include "smem_grant.h"
 
 namespace chop {
 
@@ -27,10 +26,7 @@ template <typename T, typename R, int CPL, int KIND, int MODE>
 inline int fwd_go(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
   auto k = cv_fwd_kernel<T, R, CPL, KIND, MODE>;
   const size_t smem = p.fwd.smem_per_warp * p.fwd.warps;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int e = grant_smem(k, smem)) return e;
   k<<<p.blocks, p.fwd.warps * 32, smem, st>>>(a, p.fwd);
   return (int)cudaGetLastError();
 }
@@ -57,10 +53,7 @@ template <typename T, typename R, int CPL, int KIND, bool RMIN, int NV>
 inline int bwd_go(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
   auto k = cv_bwd_kernel<T, R, CPL, KIND, RMIN, NV>;
   const size_t smem = p.bwd.smem_per_warp * p.bwd.warps;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int e = grant_smem(k, smem)) return e;
   k<<<p.blocks, p.bwd.warps * 32, smem, st>>>(a, p.bwd);
   return (int)cudaGetLastError();
 }
@@ -102,10 +95,7 @@ inline int fwd_tuned_go(const CvArgs& a, cudaStream_t st) {
   const int warps = tuned_warps(spw);
   const size_t smem = spw * warps;
   if (smem > 200 * 1024) return -4;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int e = grant_smem(k, smem)) return e;
   const long long items = (long long)a.npb * a.nchunks;
   k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw);
   return (int)cudaGetLastError();
@@ -118,10 +108,7 @@ inline int fwd_min_tuned_go(const CvArgs& a, cudaStream_t st) {
   const int warps = tuned_warps(spw);
   const size_t smem = spw * warps;
   if (smem > 200 * 1024) return -4;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int e = grant_smem(k, smem)) return e;
   const long long items = (long long)a.npb * a.nchunks;
   k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw);
   return (int)cudaGetLastError();
@@ -134,10 +121,7 @@ inline int agg_min_fwd_tuned_go(const CvArgs& a, cudaStream_t st) {
   const int warps = tuned_warps(spw);
   const size_t smem = spw * warps;
   if (smem > 200 * 1024) return -4;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int e = grant_smem(k, smem)) return e;
   const long long items = (long long)a.npb * a.nchunks;
   k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw);
   return (int)cudaGetLastError();
@@ -150,10 +134,7 @@ inline int bwd_tuned_go(const CvArgs& a, cudaStream_t st) {
   const int warps = 4;
   const size_t smem = spw * warps;
   if (smem > 200 * 1024) return -4;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int e = grant_smem(k, smem)) return e;
   const long long items = (long long)a.npb * a.nchunks;
   k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw);
   return (int)cudaGetLastError();
@@ -166,10 +147,7 @@ inline int fwd2_tuned_go(const CvArgs& a, cudaStream_t st) {
   const int warps = tuned_warps(spw);
   const size_t smem = spw * warps;
   if (smem > 200 * 1024) return -4;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int e = grant_smem(k, smem)) return e;
   const long long items = (long long)a.npb * a.nchunks;
   k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw);
   return (int)cudaGetLastError();
@@ -182,10 +160,7 @@ inline int fwd2_min_tuned_go(const CvArgs& a, cudaStream_t st) {
   const int warps = tuned_warps(spw);
   const size_t smem = spw * warps;
   if (smem > 200 * 1024) return -4;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int e = grant_smem(k, smem)) return e;
   const long long items = (long long)a.npb * a.nchunks;
   k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw);
   return (int)cudaGetLastError();
@@ -198,46 +173,40 @@ inline int bwd2_tuned_go(const CvArgs& a, cudaStream_t st) {
   const int warps = 4;
   const size_t smem = spw * warps;
   if (smem > 200 * 1024) return -4;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int e = grant_smem(k, smem)) return e;
   const long long items = (long long)a.npb * a.nchunks;
   k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw);
   return (int)cudaGetLastError();
 }
 
 // ---- packed-pair kernels (cv_packed.cuh) ----------------------------------------------------------------
-// Opt-in to more than 48 KB of dynamic shared memory is a per-(device, kernel) attribute: it is set the
-// first time a launch of that kernel on that device needs it, not on every call.
-struct SmemGrant {
-  std::atomic<int> bytes[64];
-};
-template <typename K>
-inline int grant_smem(K kernel, size_t smem, SmemGrant& gr) {
-  if (smem <= 48 * 1024) return 0;
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return (int)e;
-  if (dev >= 0 && dev < 64 && gr.bytes[dev].load(std::memory_order_acquire) >= (int)smem) return 0;
-  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return (int)e;
-  if (dev >= 0 && dev < 64) {
-    int seen = gr.bytes[dev].load();
-    while (seen < (int)smem && !gr.bytes[dev].compare_exchange_weak(seen, (int)smem)) {}
-  }
-  return 0;
-}
+template <typename T, int C, int NV>
+inline int fwd_pm_go(const CvArgs& a, cudaStream_t st);
 
 template <typename T, int C>
 inline int fwd_packed_go(const CvArgs& a, cudaStream_t st) {
-  static SmemGrant gr;
+#ifndef CHOP_NO_PM
+  if (a.N == 1) return fwd_pm_go<T, C, 1>(a, st);
+  if (a.N == 2) return fwd_pm_go<T, C, 2>(a, st);
+#endif
   auto k = cv_fwd_packed<T, C>;
   const size_t spw = packed_fwd_smem_per_warp(a.N, 32 / (C / 4));
   const int warps = tuned_warps(spw);
   const size_t smem = spw * warps;
   if (smem > 200 * 1024) return -4;
-  if (int e = grant_smem(k, smem, gr)) return e;
+  if (int e = grant_smem(k, smem)) return e;
+  const long long items = (long long)a.npb * a.nchunks;
+  k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw);
+  return (int)cudaGetLastError();
+}
+
+template <typename T, int C, int NV>
+inline int fwd_pm_go(const CvArgs& a, cudaStream_t st) {
+  auto k = cv_fwd_pm<T, C, NV>;
+  const size_t spw = pm_fwd_smem_per_warp(NV);
+  const int warps = 8;
+  const size_t smem = spw * warps;
+  if (int e = grant_smem(k, smem)) return e;
   const long long items = (long long)a.npb * a.nchunks;
   k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw);
   return (int)cudaGetLastError();
@@ -245,14 +214,13 @@ inline int fwd_packed_go(const CvArgs& a, cudaStream_t st) {
 
 template <typename T, int C>
 inline int bwd_packed_go(const CvArgs& a, cudaStream_t st) {
-  static SmemGrant gr;
   auto k = cv_bwd_packed<T, C>;
   const int vpp = a.N < 2 ? a.N : 2;   // views per pass: shared memory per warp independent of N
   const size_t spw = packed_bwd_smem_per_warp<C>(a.N, 32 / (C / 4), vpp);
   const int warps = 4;
   const size_t smem = spw * warps;
   if (smem > 200 * 1024) return -4;
-  if (int e = grant_smem(k, smem, gr)) return e;
+  if (int e = grant_smem(k, smem)) return e;
   const long long items = (long long)a.npb * a.nchunks;
   k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw, vpp);
   return (int)cudaGetLastError();

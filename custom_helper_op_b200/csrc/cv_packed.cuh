@@ -247,6 +247,267 @@ __global__ void __launch_bounds__(256, CHOP_PK_FWD_BLOCKS) cv_fwd_packed(const C
 }
 
 // ---------------------------------------------------------------------------------------------------
+// forward, plane-major nest, for a compile-time number of source views NV <= 2
+//
+// With few views the footprints of ALL views fit in registers (16 per view), so the nest can be
+//     depth block -> plane -> view
+// instead of block -> view -> plane: a plane's cost is finished and stored before the next plane
+// starts (no accumulator array: 28 fewer registers), and a view's footprint survives from one block of
+// planes to the next - it is reloaded only where the texel really changes, not at every block start.
+// What limits these kernels is the SM's load-store data path (every 16 bytes a lane receives from shared
+// or global memory is a quarter of a wavefront, broadcast or not), so the kernel keeps per-lane loads low:
+//   * the row products of the pixel (Coef) stay in registers for the whole work item;
+//   * the division by the view count needs no load: with at most two views it is a multiplication by
+//     one half where both see the voxel (a ballot bit), by one otherwise (zero views give an exact zero);
+//   * the reload is one asm block that updates the eight footprint registers in place; a view that does
+//     not see the plane reads the reference pixel four times instead, which makes all differences zero.
+// ---------------------------------------------------------------------------------------------------
+struct Footprint {
+  pk2 a0a, a0b, ua, ub, va, vb, ta, tb;  // t00 - ref, t10 - t00, t01 - t00, t11 - t01 - (t10 - t00); channel pairs {0,1}, {2,3}
+};
+
+// p: this lane's channels of texel (fh, fw); dx / dy: bytes to the next texel of the row / to the next row.
+template <typename T>
+struct FootprintLoad;
+template <>
+struct FootprintLoad<float> {
+  static __device__ __forceinline__ void go(Footprint& f, const float* p, long long dx, long long dy, pk2 ref0, pk2 ref1) {
+    asm("{\n\t"
+        ".reg .b64 q<8>, px, py, pxy;\n\t"
+        "add.s64 px, %8, %9;\n\t"
+        "add.s64 py, %8, %10;\n\t"
+        "add.s64 pxy, py, %9;\n\t"
+        "ld.global.nc.v2.b64 {q0, q1}, [%8];\n\t"
+        "ld.global.nc.v2.b64 {q2, q3}, [px];\n\t"
+        "ld.global.nc.v2.b64 {q4, q5}, [py];\n\t"
+        "ld.global.nc.v2.b64 {q6, q7}, [pxy];\n\t"
+        "sub.rn.f32x2 %0, q0, %11;\n\t"
+        "sub.rn.f32x2 %1, q1, %12;\n\t"
+        "sub.rn.f32x2 %2, q4, q0;\n\t"
+        "sub.rn.f32x2 %3, q5, q1;\n\t"
+        "sub.rn.f32x2 %4, q2, q0;\n\t"
+        "sub.rn.f32x2 %5, q3, q1;\n\t"
+        "sub.rn.f32x2 %6, q6, q2;\n\t"
+        "sub.rn.f32x2 %7, q7, q3;\n\t"
+        "sub.rn.f32x2 %6, %6, %2;\n\t"
+        "sub.rn.f32x2 %7, %7, %3;\n\t"
+        "}"
+        : "+l"(f.a0a), "+l"(f.a0b), "+l"(f.ua), "+l"(f.ub), "+l"(f.va), "+l"(f.vb), "+l"(f.ta), "+l"(f.tb)
+        : "l"(p), "l"(dx), "l"(dy), "l"(ref0), "l"(ref1));
+  }
+};
+template <>
+struct FootprintLoad<__nv_bfloat16> {
+  static __device__ __forceinline__ void go(Footprint& f, const __nv_bfloat16* p, long long dx, long long dy, pk2 ref0, pk2 ref1) {
+    asm("{\n\t"
+        ".reg .b64 q<8>, px, py, pxy;\n\t"
+        ".reg .b32 w<8>, lo, hi;\n\t"
+        "add.s64 px, %8, %9;\n\t"
+        "add.s64 py, %8, %10;\n\t"
+        "add.s64 pxy, py, %9;\n\t"
+        "ld.global.nc.v2.b32 {w0, w1}, [%8];\n\t"
+        "ld.global.nc.v2.b32 {w2, w3}, [px];\n\t"
+        "ld.global.nc.v2.b32 {w4, w5}, [py];\n\t"
+        "ld.global.nc.v2.b32 {w6, w7}, [pxy];\n\t"
+        "shl.b32 lo, w0, 16;\n\t and.b32 hi, w0, 0xffff0000;\n\t mov.b64 q0, {lo, hi};\n\t"
+        "shl.b32 lo, w1, 16;\n\t and.b32 hi, w1, 0xffff0000;\n\t mov.b64 q1, {lo, hi};\n\t"
+        "shl.b32 lo, w2, 16;\n\t and.b32 hi, w2, 0xffff0000;\n\t mov.b64 q2, {lo, hi};\n\t"
+        "shl.b32 lo, w3, 16;\n\t and.b32 hi, w3, 0xffff0000;\n\t mov.b64 q3, {lo, hi};\n\t"
+        "shl.b32 lo, w4, 16;\n\t and.b32 hi, w4, 0xffff0000;\n\t mov.b64 q4, {lo, hi};\n\t"
+        "shl.b32 lo, w5, 16;\n\t and.b32 hi, w5, 0xffff0000;\n\t mov.b64 q5, {lo, hi};\n\t"
+        "shl.b32 lo, w6, 16;\n\t and.b32 hi, w6, 0xffff0000;\n\t mov.b64 q6, {lo, hi};\n\t"
+        "shl.b32 lo, w7, 16;\n\t and.b32 hi, w7, 0xffff0000;\n\t mov.b64 q7, {lo, hi};\n\t"
+        "sub.rn.f32x2 %0, q0, %11;\n\t"
+        "sub.rn.f32x2 %1, q1, %12;\n\t"
+        "sub.rn.f32x2 %2, q4, q0;\n\t"
+        "sub.rn.f32x2 %3, q5, q1;\n\t"
+        "sub.rn.f32x2 %4, q2, q0;\n\t"
+        "sub.rn.f32x2 %5, q3, q1;\n\t"
+        "sub.rn.f32x2 %6, q6, q2;\n\t"
+        "sub.rn.f32x2 %7, q7, q3;\n\t"
+        "sub.rn.f32x2 %6, %6, %2;\n\t"
+        "sub.rn.f32x2 %7, %7, %3;\n\t"
+        "}"
+        : "+l"(f.a0a), "+l"(f.a0b), "+l"(f.ua), "+l"(f.ub), "+l"(f.va), "+l"(f.vb), "+l"(f.ta), "+l"(f.tb)
+        : "l"(p), "l"(dx), "l"(dy), "l"(ref0), "l"(ref1));
+  }
+};
+
+// Shared memory per warp of the plane-major forward: one 16-byte record and one texel index per (view, lane),
+// three ballot words per view / block.
+__host__ __device__ inline size_t pm_fwd_smem_per_warp(int NV) {
+  return (size_t)NV * 32 * 16 + (size_t)NV * 32 * 4 + 16;
+}
+
+#ifndef CHOP_PM_FWD_BLOCKS
+#define CHOP_PM_FWD_BLOCKS 3
+#endif
+
+template <typename T, int C, int NV>
+__global__ void __launch_bounds__(256, CHOP_PM_FWD_BLOCKS) cv_fwd_pm(const CvArgs a, const int warps, const size_t smem_per_warp) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int LG = C / 4;
+  constexpr int G = 32 / LG;
+  static_assert(LG * 4 == C && (LG & (LG - 1)) == 0 && LG >= 2 && LG <= 8, "C in {8, 16, 32}");
+  static_assert(NV >= 1 && NV <= 2, "the footprints of all views live in registers");
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  const int li = lane & (LG - 1);
+  const int g = lane / LG;
+
+  const long long item = (long long)blockIdx.x * warps + wib;
+  if (item >= (long long)a.npb * a.nchunks) return;
+  const int chunk_id = (int)(item / a.npb);
+  const int pb = (int)(item - (long long)chunk_id * a.npb);
+  const long long pix0 = (long long)pb * G;
+  const bool pvalid = pix0 + g < a.npix;
+  const long long pix = pvalid ? pix0 + g : a.npix - 1;
+  const int dlo = a.d_begin + chunk_id * a.chunk;
+  const int dhi = min(a.d_end, dlo + a.chunk);
+  const int D = a.D;
+
+  unsigned char* mine = smem_raw + (size_t)wib * smem_per_warp;
+  float4* rec = reinterpret_cast<float4*>(mine);               // [NV][32] {dw, dw, dh, dh}
+  int* tex = reinterpret_cast<int*>(rec + NV * 32);            // [NV][32] top-left texel or -1
+  unsigned* flg = reinterpret_cast<unsigned*>(tex + NV * 32);  // [0..NV): footprint changes at plane j; [NV]: every view sees it
+
+  // this lane's pixel: row products of every view (cost_volume_kernels_gpu.cu.cc:65-70,83,88,91), reference pixel
+  Coef<float> cf[NV];
+  {
+    const int w = (int)(pix % a.W);
+    const long long tt = pix / a.W;
+    const int h = (int)(tt % a.H);
+    const int bb = (int)(tt / a.H);
+    float x = (float)w, y = (float)h;
+    if (a.half_centor) {
+      x = xadd(x, 0.5f);
+      y = xadd(y, 0.5f);
+    }
+#pragma unroll
+    for (int n = 0; n < NV; ++n) {
+      const float* Rm = static_cast<const float*>(a.Rs) + (size_t)(bb * NV + n) * 9;
+      const float* tv = static_cast<const float*>(a.Ts) + (size_t)(bb * NV + n) * 3;
+      cf[n].zc = xadd(xadd(xmul(Rm[6], x), xmul(Rm[7], y)), Rm[8]);
+      cf[n].wc = xadd(xadd(xmul(Rm[0], x), xmul(Rm[1], y)), Rm[2]);
+      cf[n].hc = xadd(xadd(xmul(Rm[3], x), xmul(Rm[4], y)), Rm[5]);
+      cf[n].t0 = tv[0];
+      cf[n].t1 = tv[1];
+      cf[n].t2 = tv[2];
+      cf[n].row0 = a.Hs * (n + NV * bb);
+    }
+  }
+  const T* src_lane = static_cast<const T*>(a.src) + li * 4;
+  const T* ref_lane = static_cast<const T*>(a.ref) + pix * C + li * 4;
+  pk2 ref0, ref1;
+  PkLoad<T>::ld(ref_lane, ref0, ref1);
+  const int b = (int)(pix / ((long long)a.H * a.W));
+  const float base = static_cast<const float*>(a.depth)[pix];
+  const float* offs = static_cast<const float*>(a.offsets) + (long long)b * D;
+  const long long dx_bytes = (long long)C * (long long)sizeof(T);
+  const long long dy_bytes = (long long)a.Ws * dx_bytes;
+  float* out = static_cast<float*>(a.cost) + (pix * D + dlo) * C + li * 4;
+  const ulonglong2* rec_mine = reinterpret_cast<const ulonglong2*>(rec) + g * LG;
+  const int* tex_mine = tex + g * LG;
+  const pk2 half2 = pk_make(0.5f, 0.5f);
+
+  Footprint F[NV];
+  int carry[NV];  // texel of the pixel's last plane in the previous block (what the cached footprint holds)
+#pragma unroll
+  for (int n = 0; n < NV; ++n) {
+    F[n].a0a = F[n].a0b = F[n].ua = F[n].ub = F[n].va = F[n].vb = F[n].ta = F[n].tb = 0ull;
+    carry[n] = -1;
+  }
+
+  for (int dblk = dlo; dblk < dhi; dblk += LG, out += LG * C) {
+    // ---- phase A: lane (g, li) projects plane dblk+li of pixel g into every view ---------------------
+#ifdef CHOP_DIAG_NOPHASEA
+    if (dblk == dlo)
+#endif
+    {
+      const int d = dblk + li;
+      const bool dv = pvalid && d < dhi;
+      const float depth = dv ? xadd(base, offs[d]) : 0.0f;
+      int used = 0;
+#pragma unroll
+      for (int n = 0; n < NV; ++n) {
+        int t = -1;
+        float dh = 0.0f, dw = 0.0f;
+        if (dv) {
+          float gh, gw;
+          t = project<float, false>(cf[n], depth, a.half_centor, a.Hs, a.Ws, dh, dw, gh, gw);
+          used += t >= 0;
+        }
+        rec[n * 32 + lane] = make_float4(dw, dw, dh, dh);
+        tex[n * 32 + lane] = t;
+        int prev = __shfl_up_sync(0xffffffffu, t, 1);
+        if (li == 0) prev = carry[n];
+        const unsigned bal = __ballot_sync(0xffffffffu, t != prev);
+        if (lane == 0) flg[n] = bal;
+        carry[n] = __shfl_sync(0xffffffffu, t, g * LG + LG - 1);
+      }
+      if (dv) __stcs(a.mask + pix * D + d, used);
+      if (NV == 2) {
+        const unsigned both = __ballot_sync(0xffffffffu, used == 2);
+        if (lane == 0) flg[NV] = both;
+      }
+    }
+    __syncwarp();
+
+    // ---- phase B ---------------------------------------------------------------------------------------
+    if (pvalid) {
+      unsigned m[NV], many = 0u;
+#pragma unroll
+      for (int n = 0; n < NV; ++n) {
+        m[n] = flg[n] >> (g * LG);
+        many |= m[n];
+      }
+      const unsigned both = NV == 2 ? flg[NV] >> (g * LG) : 0u;
+#ifdef CHOP_DIAG_NORELOAD
+      if (dblk != dlo) many = 0u;
+#endif
+#ifdef CHOP_DIAG_NOSTORE
+      const int left = (F[0].a0a == 0x12345ull) ? dhi - dblk : 0;
+#else
+      const int left = dhi - dblk;
+#endif
+#pragma unroll
+      for (int j = 0; j < LG; ++j) {
+        if ((many >> j) & 1u) {  // some view's footprint moves at this plane (one test per plane on the common path)
+#pragma unroll
+          for (int n = 0; n < NV; ++n) {
+            if ((m[n] >> j) & 1u) {
+              const int t = tex_mine[n * 32 + j];
+              // the empty footprint (the view does not see the plane): four reads of the reference pixel
+              const T* p = t >= 0 ? src_lane + (size_t)t * C : ref_lane;
+              FootprintLoad<T>::go(F[n], p, t >= 0 ? dx_bytes : 0ll, t >= 0 ? dy_bytes : 0ll, ref0, ref1);
+            }
+          }
+        }
+        pk2 acc0, acc1;
+#pragma unroll
+        for (int n = 0; n < NV; ++n) {
+          const ulonglong2 wh = rec_mine[n * 32 + j];  // x = {dw, dw}, y = {dh, dh}
+          const pk2 X0 = pk_fma(F[n].ta, wh.x, F[n].ua);
+          const pk2 X1 = pk_fma(F[n].tb, wh.x, F[n].ub);
+          const pk2 Y0 = pk_fma(wh.x, F[n].va, F[n].a0a);
+          const pk2 Y1 = pk_fma(wh.x, F[n].vb, F[n].a0b);
+          const pk2 d0 = pk_fma(wh.y, X0, Y0);  // sample - ref
+          const pk2 d1 = pk_fma(wh.y, X1, Y1);
+          acc0 = n == 0 ? pk_mul(d0, d0) : pk_fma(d0, d0, acc0);
+          acc1 = n == 0 ? pk_mul(d1, d1) : pk_fma(d1, d1, acc1);
+        }
+        if (NV == 2 && ((both >> j) & 1u)) {  // mean over two views; one view: the sum itself; none: an exact zero
+          acc0 = pk_mul(acc0, half2);
+          acc1 = pk_mul(acc1, half2);
+        }
+        if (j < left) pk_store_stream(out + j * C, acc0, acc1);
+      }
+    }
+    __syncwarp();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
 // gradient
 //
 // Per (plane, view) phase A leaves three 16-byte records

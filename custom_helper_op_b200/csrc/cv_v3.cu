@@ -19,6 +19,7 @@
 // bit-identical to the reference compiled without contraction.
 #include "cv_project.cuh"
 #include "cv_v3_entry.h"
+#include "smem_grant.h"
 
 namespace chop {
 namespace {
@@ -401,10 +402,7 @@ int launch_sub(const CvArgs& a, cudaStream_t st) {
   const long long blocks = (items + warps - 1) / warps;
   if (blocks > 0x7fffffffLL) return -2;     // CHOP_ERR_SHAPE
   auto k = BWD ? cv3_bwd_kernel<T, R, RMIN, SUBT> : cv3_fwd_kernel<T, R, RMIN, SUBT>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int e = grant_smem(k, smem)) return e;
   k<<<(unsigned)blocks, warps * 32, smem, st>>>(a, warps, spw);
   return (int)cudaGetLastError();
 }

@@ -14,6 +14,7 @@
 // them with vector reductions when the footprint changes.
 #include "cv_project.cuh"
 #include "fa_entry.h"
+#include "smem_grant.h"
 
 namespace chop {
 namespace {
@@ -253,10 +254,7 @@ int launch(const CvArgs& a, cudaStream_t st) {
   const long long blocks = (items + warps - 1) / warps;
   if (blocks > 0x7fffffffLL) return -2;     // CHOP_ERR_SHAPE
   auto k = BWD ? fa_bwd_kernel<T, R, CPL> : fa_fwd_kernel<T, R, CPL>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int e = grant_smem(k, smem)) return e;
   k<<<(unsigned)blocks, warps * 32, smem, st>>>(a, warps, spw);
   return (int)cudaGetLastError();
 }

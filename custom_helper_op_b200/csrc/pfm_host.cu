@@ -92,8 +92,10 @@ extern "C" int chop_decode_pfm(const void* contents, size_t size, int64_t* heigh
   *channels = ch;
   off = off + 1;
   if (magic != "Pf") return fail(msg, msg_capacity, "no implement");
+  // sizes from an untrusted header: compare by division, w * h * 4 may not fit 64 bits
+  if (off > input.size() || (h != 0 && (uint64_t)w > (input.size() - off) / 4 / (uint64_t)h))
+    return fail(msg, msg_capacity, "not enough data");
   const size_t n = (size_t)w * (size_t)h;
-  if (off + n * 4 > input.size()) return fail(msg, msg_capacity, "not enough data");
   if (!image) return CHOP_OK;
   if (image_capacity < n) return CHOP_ERR_WORKSPACE;
   const char* data = input.data() + off;

@@ -84,14 +84,14 @@ int fill(const chop_sc_desc* d, ScArgs* a) {
   // the reference indexes these tensors with int32 (fixed_param_op_gpu.cu.cc:171-174); pixel indices here
   // are int32 too, element offsets 64-bit
   if (d->B * d->H * d->W > INT32_MAX) return CHOP_ERR_SHAPE;
-  if ((int64_t)a->fh * a->fw * a->fd * a->Cin > 1024) return CHOP_ERR_UNSUPPORTED;
+  // rows of the filter matrix (taps x channels) are counted in 32 bits
+  if ((int64_t)a->fh * a->fw * a->fd * (a->Cin > a->Cout ? a->Cin : a->Cout) > (1 << 24)) return CHOP_ERR_UNSUPPORTED;
   return 0;
 }
 
 // The transposed op's filter gradient gathers the coarse tensor: taps * Cout accumulator rows.
 int fill_transpose(const chop_sc_desc* d, ScArgs* a) {
   if (int e = fill(d, a)) return e;
-  if ((int64_t)a->fh * a->fw * a->fd * a->Cout > 1024) return CHOP_ERR_UNSUPPORTED;
   a->dynamic_default = 0;
   return 0;
 }

@@ -10,6 +10,7 @@
 //   partials go to a workspace and a second kernel sums them in a fixed order (deterministic, no atomics).
 #include "sc_common.cuh"
 #include "sc_entry.h"
+#include "smem_grant.h"
 
 #include <mutex>
 
@@ -106,7 +107,7 @@ __global__ void __launch_bounds__(256) sc_dgrad_simt(const ScArgs a) {
 constexpr int WG_THREADS = 256;
 constexpr int WG_TM = 32;   // voxels staged per step
 constexpr int WG_NC = 16;   // output channels per sweep
-constexpr int WG_KPT = 4;   // k values per thread -> K <= 1024
+constexpr int WG_KPT = 4;   // k values per thread and sweep
 
 // partial[cta][k][n] (+ partial default gradient at the end of every CTA's slab).
 // TR = false: filter gradient of the convolution; the CTA's voxels are output voxels, k = (tap, input
@@ -137,7 +138,9 @@ __global__ void __launch_bounds__(WG_THREADS) sc_wgrad_partial(const ScArgs a, c
   ACC* part = static_cast<ACC*>(a.workspace) + (size_t)blockIdx.x * ((size_t)K * NC + 1);
   ACC dacc = 0;
 
-  for (int n0 = 0; n0 < NC; n0 += WG_NC) {
+  // K = taps * channels is swept in blocks of WG_THREADS * WG_KPT accumulator rows (one block for K <= 1024)
+  for (int n0 = 0; n0 < NC; n0 += WG_NC)
+  for (int k0 = 0; k0 < K; k0 += WG_THREADS * WG_KPT) {
     const int nn = min(WG_NC, NC - n0);
     ACC acc[WG_KPT][WG_NC];
 #pragma unroll
@@ -169,7 +172,7 @@ __global__ void __launch_bounds__(WG_THREADS) sc_wgrad_partial(const ScArgs a, c
       __syncthreads();
 #pragma unroll
       for (int i = 0; i < WG_KPT; ++i) {
-        const int k = threadIdx.x + i * WG_THREADS;
+        const int k = k0 + threadIdx.x + i * WG_THREADS;
         if (k >= K) break;
         const int t = k / KC, ci = k - t * KC;
         for (int m = 0; m < tm; ++m) {
@@ -188,7 +191,7 @@ __global__ void __launch_bounds__(WG_THREADS) sc_wgrad_partial(const ScArgs a, c
     }
 #pragma unroll
     for (int i = 0; i < WG_KPT; ++i) {
-      const int k = threadIdx.x + i * WG_THREADS;
+      const int k = k0 + threadIdx.x + i * WG_THREADS;
       if (k >= K) break;
 #pragma unroll
       for (int n = 0; n < WG_NC; ++n)
@@ -330,10 +333,7 @@ int wgrad_t(const ScArgs& a, int nparts, cudaStream_t st) {
   const int vox_per_cta = (int)((nvox + nparts - 1) / nparts);
   const size_t smem = (size_t)WG_TM * taps * sizeof(long long) + (size_t)(WG_TM * WG_NC + WG_THREADS) * sizeof(ACC);
   auto k = sc_wgrad_partial<T, ACC, TR>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int e = grant_smem(k, smem)) return e;
   k<<<nparts, WG_THREADS, smem, st>>>(a, vox_per_cta);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;

@@ -11,6 +11,7 @@
 // float64, filters whose weights do not fit in shared memory).
 #include "sc_common.cuh"
 #include "sc_entry.h"
+#include "smem_grant.h"
 
 namespace chop {
 namespace {
@@ -324,10 +325,7 @@ int launch_wgrad(const ScArgs& a, int nparts, cudaStream_t st) {
   const size_t smem = (size_t)WT * taps * sizeof(long long) + ((size_t)WT * NCH + (size_t)taps * NCH + threads) * sizeof(float) +
                       WT * sizeof(int4) + (size_t)taps * sizeof(int3);
   auto k = sc_wgrad_tile_kernel<T, KCH, NCH, TR>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int e = grant_smem(k, smem)) return e;
   k<<<nparts, threads, smem, st>>>(a, vox_per_cta);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
@@ -354,10 +352,7 @@ int launch(const ScArgs& a, cudaStream_t st) {
   const int taps = a.fh * a.fw * a.fd;
   const size_t smem = ((size_t)taps * KCH * NCH + (size_t)taps * NCH) * sizeof(float);
   auto k = sc_tile_kernel<T, KCH, NCH, FORM>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int e = grant_smem(k, smem)) return e;
   const long long nvox = FORM == 0 ? a.nvox_out : a.nvox_in;
   const long long ngroups = (nvox + TileVpt<NCH>::v - 1) / TileVpt<NCH>::v;
   long long blocks = (ngroups + 127) / 128;

@@ -28,6 +28,7 @@
 
 #include "sc_common.cuh"
 #include "sc_entry.h"
+#include "smem_grant.h"
 
 namespace chop {
 namespace {
@@ -1055,10 +1056,7 @@ template <int COUT, bool TG>
 int launch_wgrad_rows(const ScArgs& a, int nparts, cudaStream_t st) {
   auto k = sc_umma_wgrad_rows_kernel<COUT, TG>;
   const size_t smem = (size_t)18 * 132 * 16 + (size_t)16 * 3 * (COUT / 8) * 128 + (size_t)27 * COUT * 4 + 1024;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int e = grant_smem(k, smem)) return e;
   const int PT = 128 / (a.D + 2);
   const long long npix = (long long)a.B * a.H * a.W;
   const long long ntiles = (npix + PT - 1) / PT;
@@ -1086,10 +1084,7 @@ int launch_wgrad(const ScArgs& a, int nparts, cudaStream_t st) {
   auto k = s1 ? sc_umma_wgrad_kernel<CIN, COUT, TG, 1>
               : ((TG && a.ls_r >= 0) ? sc_umma_wgrad_kernel<CIN, COUT, TG, TG ? 2 : 0> : sc_umma_wgrad_kernel<CIN, COUT, TG, 0>);
   const size_t smem = (size_t)16 * 2048 + (size_t)16 * (COUT / 8) * 128 + (size_t)27 * COUT * 4 + 1024;
-  if (smem > 48 * 1024) {  // per device and per kernel: set on every call (a cheap host-side call)
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int e = grant_smem(k, smem)) return e;
   const long long nvox = TG ? a.nvox_in : a.nvox_out;
   const int ntiles = (int)((nvox + 127) / 128);
   if (nparts > ntiles) nparts = ntiles;  // a persistent CTA per slab: more CTAs than tiles would leave slabs unwritten
@@ -1111,10 +1106,7 @@ template <int CIN, int COUT, bool DGRAD>
 int launch_rows(const ScArgs& a, cudaStream_t st) {
   auto k = sc_umma_rows_kernel<CIN, COUT, DGRAD>;
   const size_t smem = (size_t)27 * COUT * CIN * 2 + (size_t)9 * (CIN / 8) * 132 * 16 + 1024;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int e = grant_smem(k, smem)) return e;
   const int PT = 128 / (a.D + 2);
   const long long npix = (long long)a.B * a.H * a.W;
   const long long ntiles = (npix + PT - 1) / PT;
@@ -1136,10 +1128,7 @@ int launch(const ScArgs& a, long long nvox, cudaStream_t st) {
   auto k = s1 ? sc_umma_kernel<CIN, COUT, DGRAD, 1>
               : ((DGRAD && a.ls_r >= 0) ? sc_umma_kernel<CIN, COUT, DGRAD, DGRAD ? 2 : 0> : sc_umma_kernel<CIN, COUT, DGRAD, 0>);
   const size_t smem = (size_t)27 * COUT * CIN * 2 + (size_t)9 * 128 * CIN * 2 + 1024;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-  }
+  if (int e = grant_smem(k, smem)) return e;
   const int ntiles = (int)((nvox + 127) / 128);
   int per_sm = (int)((size_t)220 * 1024 / (smem + 2048));
   if (per_sm > 8) per_sm = 8;

@@ -4,7 +4,14 @@
  * The entry points sit exactly where the reference project's TensorFlow OpKernels call their
  * device functors: the caller (an OpKernel, a torch wrapper, a cgo/ctypes stub ...) validates
  * nothing, owns every buffer, and passes raw DEVICE pointers plus a CUDA stream.  The library
- *   - allocates nothing and keeps no global state (unless an entry point says otherwise),
+ *   - allocates nothing (device or host memory) and keeps no state between calls, with these exceptions,
+ *     all process-wide and none of them visible in results:
+ *       . a table of which kernels have been granted more than 48 KB of dynamic shared memory on which
+ *         device (the opt-in attribute is set the first time a launch needs it, not on every call);
+ *       . chop_umma_timeouts(): a device-side counter of bounded waits that gave up (see below);
+ *       . the 4 MiB device array behind chop_sparse_conv3d_bwd_noalloc and its per-device address;
+ *       . the test / benchmark knobs of chop_set_tuning, inert unless the process sets
+ *         CHOP_ENABLE_TUNING=1 in its environment before the first call,
  *   - enqueues all work on the given stream and never synchronises,
  *   - returns 0 on success, a negative chop_status for an invalid argument detected on the host
  *     before any launch, or a positive cudaError_t value if a launch failed,
@@ -76,6 +83,7 @@ typedef enum chop_reduce { CHOP_REDUCE_MEAN = 0, CHOP_REDUCE_MIN = 1 } chop_redu
 #define CHOP_FLAG_ACCUMULATE 2u /* backward: add into ref_grad/src_grad/base_plane_grad instead of
                                    zero-filling them first (used when a batch item is split by depth
                                    range over several calls). */
+/* Any other bit set in chop_cv_desc.flags is rejected with CHOP_ERR_ATTR. */
 
 /* Describes one cost-volume call.  Replaces the scalar argument list of the reference functors
  * CostVolumeFunctor / CostVolumeGradFunctor (custom_helper_op/cc/kernels/cost_volume.h:37-132) and
@@ -201,8 +209,9 @@ CHOP_API int chop_sparse_pad_bwd(int32_t dtype, int64_t B, int64_t h, int64_t w,
  * feature_aggregate_kernels_gpu.cu.cc:33-121,219-317): the plane-sweep warp without a reduction.
  *   src [B,N,Hs,Ws,C], base_plane [B,H,W,1], offsets [B,D], Rs, Ts ->
  *   mapped_feature [B,H,W,D,N,C] (zeros where a view does not see the voxel), mapped_mask int32 [B,H,W,D,N,1].
- * desc: kind is ignored; (H,W) is the output grid and may differ from (Hs,Ws); reduce/groups unused; the depth
- * range fields and CHOP_FLAG_ACCUMULATE (gradient) are honoured.  Gradient outputs: src_grad like src,
+ * desc: kind and reduce must be 0 and groups 0 or 1 (the op has none of these attributes; anything else is
+ * CHOP_ERR_ATTR); (H,W) is the output grid and may differ from (Hs,Ws); the depth range fields and
+ * CHOP_FLAG_ACCUMULATE (gradient) are honoured, any other flag bit is CHOP_ERR_ATTR.  Gradient outputs: src_grad like src,
  * base_plane_grad like base_plane, zero-filled first as the reference functor does (:337-383). */
 CHOP_API int chop_feature_aggregate_fwd(const chop_cv_desc *desc, const void *src, const void *base_plane,
                                         const void *offsets, const void *Rs, const void *Ts, void *mapped_feature,
@@ -247,8 +256,11 @@ CHOP_API int chop_version(void);
  * kernels where one exists, 0 = always the generic kernels), "umma" (1 = tensor-core manifold convolution
  * where supported, 0 = always the generic kernels), "umma_rows" (1 = the stride-1 tensor-core forward / image
  * gradient stages one copy per neighbour pixel, 0 = one per tap), "tile" (1 = register-tiled float32 manifold
- * convolution kernels where supported, 0 = the one-thread-per-element kernels).  Returns CHOP_ERR_ATTR for an unknown name.
- * Process-wide; not part of the reference surface. */
+ * convolution kernels where supported, 0 = the one-thread-per-element kernels), "packed" (1 = the packed-pair CostVolume
+ * MEAN kernels where one exists, 0 = the previous compile-time-C kernels).  Returns CHOP_ERR_ATTR for an unknown name.
+ * Process-wide, hence a facility for tests and benchmarks only: every call returns CHOP_ERR_UNSUPPORTED unless the
+ * process has CHOP_ENABLE_TUNING=1 in its environment (read once, at the first call); a production host never sets it
+ * and always gets the default kernel selection.  Not part of the reference surface. */
 CHOP_API int chop_set_tuning(const char *name, int value);
 
 #ifdef __cplusplus

@@ -44,6 +44,27 @@ def test_generic_kernels(case, dtype, dynamic_default):
         assert float(dg) == 0.0
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+@pytest.mark.parametrize("chan", [(64, 8), (40, 24)])
+def test_wide_channels(chan, dtype):
+    """3x3x3 with 64 (40) input channels: 1728 (1080) filter rows per output channel - more than one sweep of the
+    generic filter-gradient kernel's accumulator rows.  The reference has no channel limit
+    (sparse_conv3d_fast_op.cc:54-146)."""
+    Cin, Cout = chan
+    B, H, W, D = 1, 6, 7, 5
+    images, filters, defv, bp, _ = make_case(31, B, H, W, D, Cin, Cout, (3, 3, 3), 2 * D + 6, dtype)
+    want = oracle.sparse_conv3d_fwd(images, filters, defv, bp, (1, 1, 1), (1, 1, 1), dtype)
+    og = np.random.default_rng(32).uniform(-1, 1, want.shape).astype(dtype)
+    ig_w, fg_w, dg_w = oracle.sparse_conv3d_bwd(images, filters, defv, bp, og, (1, 1, 1), (1, 1, 1), True, dtype)
+    out, ig, fg, dg = run_gpu(images, filters, defv, bp, og, (1, 1, 1), (1, 1, 1), True,
+                              torch.float32 if dtype == np.float32 else torch.float64)
+    tol = 1e-5 if dtype == np.float32 else 1e-12
+    assert helpers.rel_err(out, want) <= tol
+    assert helpers.rel_err(ig, ig_w) <= tol
+    assert helpers.rel_err(fg, fg_w) <= tol
+    assert abs(float(dg) - float(dg_w)) <= tol * max(1.0, abs(float(dg_w)))
+
+
 @pytest.mark.parametrize("shape", [(1, 12, 14, 9, 16, 16), (2, 9, 11, 9, 16, 16), (1, 8, 8, 5, 32, 16), (1, 7, 9, 9, 16, 32)])
 def test_bfloat16(shape):
     """bf16 storage with float32 accumulation; oracle on the bf16-rounded inputs."""

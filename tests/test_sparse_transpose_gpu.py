@@ -41,6 +41,21 @@ def test_transpose_forward_and_gradient(case, dtype, default):
     assert helpers.rel_err(_np(fg), fg_w) <= tol
 
 
+def test_transpose_wide_channels():
+    """3x3x3 with 48 coarse channels: 1296 accumulator rows in the transposed filter gradient, more than one sweep."""
+    B, H, W, D, Cin, Cout, ks, st, dl = 1, 6, 8, 4, 6, 48, (3, 3, 3), (2, 2, 1), (1, 1, 1)
+    images, filters, defv, bp = make_transpose_case(35, B, H, W, D, Cin, Cout, ks, st, dtype=np.float32, default=None)
+    want = oracle.sparse_conv3d_transpose_fwd(images, filters, defv, bp, (H, W, D), st, dl, np.float32)
+    og = np.random.default_rng(36).uniform(-1, 1, want.shape).astype(np.float32)
+    ig_w, fg_w = oracle.sparse_conv3d_transpose_bwd(images, filters, defv, bp, (H, W, D), og, st, dl, False, np.float32)
+    out = ops.sparse_conv3d_transpose_forward(_t(images), _t(filters), float(defv), _t(bp), (H, W, D), st, dl)
+    ig, fg = ops.sparse_conv3d_transpose_backward(_t(images), _t(filters), float(defv), _t(bp), (H, W, D), _t(og), st, dl)
+    torch.cuda.synchronize()
+    assert helpers.rel_err(_np(out), want) <= 1e-5
+    assert helpers.rel_err(_np(ig), ig_w) <= 1e-5
+    assert helpers.rel_err(_np(fg), fg_w) <= 1e-5
+
+
 @pytest.mark.parametrize("strides", [(1, 1, 1), (2, 2, 2), (2, 2, 1)])
 @pytest.mark.parametrize("chans", [(16, 16), (32, 16), (16, 32), (8, 16), (8, 8)])
 def test_transpose_bfloat16(strides, chans):
