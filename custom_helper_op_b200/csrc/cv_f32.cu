@@ -87,16 +87,6 @@ int cv_bwd_f32(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
     const int r = tuned2_dispatch<float>(true, p.rmin != 0, a, st);
     if (r != -4) return r;
   }
-  if (p.use_tuned && p.use_packed && p.kind == 1 && !p.rmin && p.cpl == 4) {
-    int r = -4;
-    switch (a.C) {
-      case 8: r = bwd_packed_go<float, 8>(a, st); break;
-      case 16: r = bwd_packed_go<float, 16>(a, st); break;
-      case 32: r = bwd_packed_go<float, 32>(a, st); break;
-      default: break;
-    }
-    if (r != -4) return r;
-  }
   if (p.use_tuned && p.kind == 1 && !p.rmin && p.cpl == 4) {
     switch (a.C) {
       case 8: return bwd_tuned_go<float, 8, 4>(a, st);

@@ -212,20 +212,6 @@ inline int fwd_pm_go(const CvArgs& a, cudaStream_t st) {
   return (int)cudaGetLastError();
 }
 
-template <typename T, int C>
-inline int bwd_packed_go(const CvArgs& a, cudaStream_t st) {
-  auto k = cv_bwd_packed<T, C>;
-  const int vpp = a.N < 2 ? a.N : 2;   // views per pass: shared memory per warp independent of N
-  const size_t spw = packed_bwd_smem_per_warp<C>(a.N, 32 / (C / 4), vpp);
-  const int warps = 4;
-  const size_t smem = spw * warps;
-  if (smem > 200 * 1024) return -4;
-  if (int e = grant_smem(k, smem)) return e;
-  const long long items = (long long)a.npb * a.nchunks;
-  k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw, vpp);
-  return (int)cudaGetLastError();
-}
-
 // C in {8,16,32}, channels per group in {1,2,4}; returns -4 if there is no such kernel
 template <typename T>
 inline int tuned2_dispatch(bool backward, bool rmin, const CvArgs& a, cudaStream_t st) {

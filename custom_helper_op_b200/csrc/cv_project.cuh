@@ -95,9 +95,10 @@ __device__ __forceinline__ int project(const Coef<R>& c, R depth, int half_cento
     dw = xsub(sw, (R)fw);
     if (BWD) {
       // :451  ((hc*z - zc*h3d)*h_grad + (wc*z - zc*w3d)*w_grad)/(z*z), factored per term
-      const R zz = z * z;
-      gh = (c.hc * z - c.zc * h3) / zz;
-      gw = (c.wc * z - c.zc * w3) / zz;
+      // one reciprocal serves both factors (gradient tolerance, not the bit-exact part of the projection)
+      const R izz = (R)1 / (z * z);
+      gh = (c.hc * z - c.zc * h3) * izz;
+      gw = (c.wc * z - c.zc * w3) * izz;
     }
     return fw + Ws * (fh + c.row0);
   }

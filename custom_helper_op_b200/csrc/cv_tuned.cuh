@@ -553,6 +553,11 @@ __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const C
   }
   __syncwarp();
 
+  // The lane's validity count / winning view of plane dblk+li streams in from HBM: it is requested one block ahead,
+  // so phase A does not start with an exposed DRAM round trip.
+  const int mk_stride = (RMIN && !AGG) ? C : 1;
+  int m_next = 0;
+  if (pvalid && dlo + li < dhi) m_next = __ldg(a.mask + (pix * D + dlo + li) * mk_stride);
   int buf = 0;
   for (int dblk = dlo; dblk < dhi; dblk += LG, cg_src += LG * C, buf ^= (CG_BUFS - 1)) {
     if (!AGG && CG_BUFS == 2) {
@@ -581,17 +586,16 @@ __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const C
       const bool dv = pvalid && d < dhi;
       float depth = 0.0f, scale = 0.0f;
       bool live = false;
-      int m0 = 0;
+      const int m0 = m_next;
+      if (pvalid && d + LG < dhi) m_next = __ldg(a.mask + (pix * D + d + LG) * mk_stride);
       if (dv) {
         depth = xadd(base, offs[d]);
         if constexpr (RMIN) {
-          m0 = __ldg(a.mask + (pix * D + d) * (AGG ? 1 : C));
           live = m0 >= 0;                    // :484, aggregate :476
           scale = 2.0f;                      // :560
           if (AGG && live)                   // aggregate :500
             scale = 2.0f * __ldg(static_cast<const float*>(a.cost_grad) + pix * D + d) / (float)C;
         } else {
-          m0 = __ldg(a.mask + pix * D + d);
           live = m0 > 0;                       // cost_volume_kernels_gpu.cu.cc:367
           if (live) scale = 2.0f / (float)m0;  // :439
           if (AGG && live)                     // one upstream value per voxel, divided by views*C

@@ -149,3 +149,20 @@ def test_index_initializer_gpu():
     assert torch.equal(ops.IndexInitializer()((3, 4, 3)), ops.index_initializer((3, 4, 3)))
     with pytest.raises(ValueError):
         ops.index_initializer((3, 4, 2))
+
+
+@pytest.mark.parametrize("w,h", [(2 ** 32, 2 ** 32), (2 ** 62, 4), (3, 2 ** 62), (2 ** 31, 2 ** 31)])
+def test_decode_pfm_rejects_a_header_whose_size_product_overflows(w, h):
+    """A crafted header whose width * height * 4 wraps around 64 bits must fail the "not enough data" check in the C
+    ABI itself (a direct caller has no torch allocation in front of it), with or without an image buffer."""
+    import ctypes
+    from custom_helper_op_b200 import _lib
+    contents = ("Pf\n%d %d\n-1.0\n" % (w, h)).encode() + b"\0" * 64
+    hh, ww, cc = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()
+    msg = ctypes.create_string_buffer(256)
+    buf = (ctypes.c_float * 16)()
+    for image, cap in ((None, 0), (ctypes.cast(buf, ctypes.c_void_p), 16)):
+        st = _lib.lib().chop_decode_pfm(contents, len(contents), ctypes.byref(hh), ctypes.byref(ww), ctypes.byref(cc),
+                                        image, cap, msg, 256)
+        assert st == _lib.ERR_FORMAT and b"not enough data" in msg.value
+
