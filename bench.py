@@ -406,7 +406,7 @@ def gpu_main(args):
                 "unit": "GB/s", "frac": ach / peak, "traffic": traffic,
                 "fwd": {"ms": fwd_ms, "algorithmic_bytes": fwd_b, "gbs": fwd_b / (fwd_ms * 1e-3) / 1e9},
                 "bwd": {"ms": bwd_ms, "algorithmic_bytes": bwd_b, "gbs": bwd_b / (bwd_ms * 1e-3) / 1e9,
-                        "note": "includes the three zero-fill memsets of the gradient outputs"},
+                        "note": "includes the zero-fill kernel of the three gradient outputs"},
                 "fwd_plus_bwd_frac": (fwd_b + bwd_b) / (ms_per_step * 1e-3) / 1e9 / peak}
         cpu = None
         if world == 1 and not args.no_cpu_baseline and not args.profile:

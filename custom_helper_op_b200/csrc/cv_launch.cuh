@@ -204,7 +204,7 @@ template <typename T, int C, int NV>
 inline int fwd_pm_go(const CvArgs& a, cudaStream_t st) {
   auto k = cv_fwd_pm<T, C, NV>;
   const size_t spw = pm_fwd_smem_per_warp(NV);
-  const int warps = 8;
+  const int warps = CHOP_PM_FWD_WARPS;
   const size_t smem = spw * warps;
   if (int e = grant_smem(k, smem)) return e;
   const long long items = (long long)a.npb * a.nchunks;

@@ -344,12 +344,16 @@ __host__ __device__ inline size_t pm_fwd_smem_per_warp(int NV) {
   return (size_t)NV * 32 * 16 + (size_t)NV * 32 * 4 + 16;
 }
 
+// six 128-thread CTAs per SM measured fastest at c1 (123 us; three 256-thread CTAs 126 us; more CTAs spill)
+#ifndef CHOP_PM_FWD_WARPS
+#define CHOP_PM_FWD_WARPS 4
+#endif
 #ifndef CHOP_PM_FWD_BLOCKS
-#define CHOP_PM_FWD_BLOCKS 3
+#define CHOP_PM_FWD_BLOCKS 6
 #endif
 
 template <typename T, int C, int NV>
-__global__ void __launch_bounds__(256, CHOP_PM_FWD_BLOCKS) cv_fwd_pm(const CvArgs a, const int warps, const size_t smem_per_warp) {
+__global__ void __launch_bounds__(32 * CHOP_PM_FWD_WARPS, CHOP_PM_FWD_BLOCKS) cv_fwd_pm(const CvArgs a, const int warps, const size_t smem_per_warp) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int LG = C / 4;
   constexpr int G = 32 / LG;
