@@ -785,7 +785,9 @@ def secondary_main(args):
         launches = 12
     elif args.workload == "c3_item":
         # one batch item of the large configuration (what one GPU holds at 8-way batch sharding), bf16 features
-        wl = synth.make("c3_large", with_grad=False, B=1)
+        # --rows H: fewer image rows (same width, planes and views, so the footprints move as in the full item) for
+        # profiler captures of this workload
+        wl = synth.make("c3_large", with_grad=False, B=1, **({"H": args.rows} if args.rows else {}))
         t = {k: torch.from_numpy(v).to(dev) for k, v in wl.items()}
         B, H, W_, C = t["ref"].shape
         D, N = t["offsets"].shape[1], t["src"].shape[1]
@@ -897,6 +899,7 @@ def main():
     ap.add_argument("--shard", default="batch", choices=["batch", "depth"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-chunks", type=int, default=2, help="depth chunks of the host-buffer pipeline")
+    ap.add_argument("--rows", type=int, default=0, help="c3_item only: image rows (default: the configuration's 296)")
     ap.add_argument("--no-extra-legs", action="store_true",
                     help="skip the depth-shard leg (N > 1) and the c3 batch leg that follow the headline measurement")
     ap.add_argument("--profile", action="store_true",

@@ -9,7 +9,8 @@
 //   rec  {dw, dw, dh, dh}   one 16-byte broadcast shared load gives both splatted interpolation weights
 //   chg  one bit per plane  "the footprint differs from the previous plane's" (a ballot of phase A), so
 //                           the texel index is read only where the footprint is reloaded
-// The first source view is peeled: its squared difference starts the accumulators (no zero fill).
+// Accumulators and footprints are updated in place (asm operands tied to their registers), so the compiler has
+// nothing to copy where the control flow of the reload joins.
 // The projection itself stays unfused and in the reference's order (cv_project.cuh), so the validity
 // count is bit-exact; cost meets the float tolerance (same formulas as cv_fwd_tuned).  The gradient stays with
 // cv_bwd_tuned: a packed-pair gradient kernel was measured slower (fewer instructions, but the pair arithmetic
@@ -75,177 +76,12 @@ struct PkLoad<__nv_bfloat16> {
 __device__ __forceinline__ void pk_store_stream(float* p, pk2 a, pk2 b) {
   asm volatile("st.global.cs.v2.b64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
 }
-// Shared-memory bytes per warp: row products, one 16-byte record and one texel index per (view, lane),
-// the splatted 1/views per lane, one change word per view.
-__host__ __device__ inline size_t packed_fwd_smem_per_warp(int N, int G) {
-  return (size_t)N * G * sizeof(Coef<float>) + (size_t)N * 32 * 16 + 32 * 8 + (size_t)N * 32 * 4 +
-         (((size_t)N * 4 + 15) & ~(size_t)15);
-}
+// acc += a * b with the accumulator updated in place (the operand is tied to its register)
+__device__ __forceinline__ void pk_fma_to(pk2& acc, pk2 a, pk2 b) { asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b)); }
 
-#ifndef CHOP_PK_FWD_BLOCKS
-#define CHOP_PK_FWD_BLOCKS 3
-#endif
-
-template <typename T, int C>
-__global__ void __launch_bounds__(256, CHOP_PK_FWD_BLOCKS) cv_fwd_packed(const CvArgs a, const int warps, const size_t smem_per_warp) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  constexpr int LG = C / 4;
-  constexpr int G = 32 / LG;
-  static_assert(LG * 4 == C && (LG & (LG - 1)) == 0 && LG >= 2 && LG <= 8, "C in {8, 16, 32}");
-  const int lane = threadIdx.x & 31;
-  const int wib = threadIdx.x >> 5;
-  const int li = lane & (LG - 1);
-  const int g = lane / LG;
-
-  const long long item = (long long)blockIdx.x * warps + wib;
-  if (item >= (long long)a.npb * a.nchunks) return;
-  const int chunk_id = (int)(item / a.npb);
-  const int pb = (int)(item - (long long)chunk_id * a.npb);
-  const long long pix0 = (long long)pb * G;
-  const bool pvalid = pix0 + g < a.npix;
-  const long long pix = pvalid ? pix0 + g : a.npix - 1;
-  const int dlo = a.d_begin + chunk_id * a.chunk;
-  const int dhi = min(a.d_end, dlo + a.chunk);
-  const int N = a.N;
-  const int D = a.D;
-
-  unsigned char* mine = smem_raw + (size_t)wib * smem_per_warp;
-  Coef<float>* coef = reinterpret_cast<Coef<float>*>(mine);
-  float4* rec = reinterpret_cast<float4*>(coef + N * G);   // [N][32] {dw, dw, dh, dh}
-  float2* inv2 = reinterpret_cast<float2*>(rec + N * 32);  // [32]    {1/views, 1/views}
-  int* tex = reinterpret_cast<int*>(inv2 + 32);            // [N][32] top-left texel or -1
-  unsigned* chg = reinterpret_cast<unsigned*>(tex + N * 32);  // [N] bit (g*LG + j): reload at plane j
-
-  stage_coefs<float>(a, coef, lane, G, pix0);
-  __syncwarp();
-
-  const T* src_lane = static_cast<const T*>(a.src) + li * 4;
-  pk2 ref0, ref1;
-  PkLoad<T>::ld(static_cast<const T*>(a.ref) + pix * C + li * 4, ref0, ref1);
-  const int b = (int)(pix / ((long long)a.H * a.W));
-  const float base = static_cast<const float*>(a.depth)[pix];
-  const float* offs = static_cast<const float*>(a.offsets) + (long long)b * D;
-  const size_t row = (size_t)a.Ws * C;
-  float* out = static_cast<float*>(a.cost) + (pix * D + dlo) * C + li * 4;
-  const ulonglong2* rec_mine = reinterpret_cast<const ulonglong2*>(rec) + g * LG;
-  const int* tex_mine = tex + g * LG;
-  const pk2* inv_mine = reinterpret_cast<const pk2*>(inv2) + g * LG;
-
-  for (int dblk = dlo; dblk < dhi; dblk += LG, out += LG * C) {
-    // ---- phase A: lane (g, li) projects plane dblk+li of pixel g into every view ---------------------
-    {
-      const int d = dblk + li;
-      const bool dv = pvalid && d < dhi;
-      const float depth = dv ? xadd(base, offs[d]) : 0.0f;
-      int used = 0;
-      for (int n = 0; n < N; ++n) {
-        int t = -1;
-        float dh = 0.0f, dw = 0.0f;
-        if (dv) {
-          float gh, gw;
-          t = project<float, false>(coef[n * G + g], depth, a.half_centor, a.Hs, a.Ws, dh, dw, gh, gw);
-          used += t >= 0;
-        }
-        rec[n * 32 + lane] = make_float4(dw, dw, dh, dh);
-        tex[n * 32 + lane] = t;
-        // the footprint registers do not outlive a (block, view): plane 0 always loads
-        const int prev = __shfl_up_sync(0xffffffffu, t, 1);
-        const unsigned bal = __ballot_sync(0xffffffffu, li == 0 || t != prev);
-        if (lane == 0) chg[n] = bal;
-      }
-      if (dv) __stcs(a.mask + pix * D + d, used);
-      const float inv = used > 0 ? 1.0f / (float)used : 0.0f;
-      inv2[lane] = make_float2(inv, inv);
-    }
-    __syncwarp();
-
-    // ---- phase B ---------------------------------------------------------------------------------------
-    if (pvalid) {
-      pk2 acc[LG][2];
-      // One view over the block's planes.  A view that does not see a plane has the "empty footprint"
-      // (all differences zero): the plane then contributes exactly zero without a validity branch.
-      auto view = [&](auto first_tag, const int n) {
-        constexpr bool FIRST = decltype(first_tag)::value;
-        const ulonglong2* r = rec_mine + n * 32;
-        const int* tx = tex_mine + n * 32;
-        const unsigned m = chg[n] >> (g * LG);
-        pk2 a0[2], u[2], v[2], t1[2];
-#pragma unroll
-        for (int j = 0; j < LG; ++j) {
-          if (j == 0 || ((m >> j) & 1u)) {
-            const int t = tx[j];
-            if (t >= 0) {
-              const T* p00 = src_lane + (size_t)t * C;
-              const T* p10 = p00 + row;
-              pk2 t00[2], t01[2], t10[2], t11[2];
-              PkLoad<T>::ld(p00, t00[0], t00[1]);
-              PkLoad<T>::ld(p00 + C, t01[0], t01[1]);
-              PkLoad<T>::ld(p10, t10[0], t10[1]);
-              PkLoad<T>::ld(p10 + C, t11[0], t11[1]);
-              a0[0] = pk_sub(t00[0], ref0);
-              a0[1] = pk_sub(t00[1], ref1);
-#pragma unroll
-              for (int k = 0; k < 2; ++k) {
-                u[k] = pk_sub(t10[k], t00[k]);
-                v[k] = pk_sub(t01[k], t00[k]);
-                t1[k] = pk_sub(pk_sub(t11[k], t01[k]), u[k]);
-              }
-            } else {
-#pragma unroll
-              for (int k = 0; k < 2; ++k) a0[k] = u[k] = v[k] = t1[k] = 0ull;
-            }
-          }
-          const ulonglong2 wh = r[j];  // x = {dw, dw}, y = {dh, dh}
-#pragma unroll
-          for (int k = 0; k < 2; ++k) {
-            const pk2 X = pk_fma(t1[k], wh.x, u[k]);
-            const pk2 Y = pk_fma(wh.x, v[k], a0[k]);
-            const pk2 df = pk_fma(wh.y, X, Y);  // sample - ref
-            acc[j][k] = FIRST ? pk_mul(df, df) : pk_fma(df, df, acc[j][k]);
-          }
-        }
-      };
-      view(std::true_type{}, 0);
-      for (int n = 1; n < N; ++n) view(std::false_type{}, n);
-
-      const int left = dhi - dblk;
-      if (left >= LG) {
-#pragma unroll
-        for (int j = 0; j < LG; ++j) {
-          const pk2 inv = inv_mine[j];
-          pk_store_stream(out + j * C, pk_mul(acc[j][0], inv), pk_mul(acc[j][1], inv));
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < LG; ++j) {
-          if (j < left) {
-            const pk2 inv = inv_mine[j];
-            pk_store_stream(out + j * C, pk_mul(acc[j][0], inv), pk_mul(acc[j][1], inv));
-          }
-        }
-      }
-    }
-    __syncwarp();
-  }
-}
-
-// ---------------------------------------------------------------------------------------------------
-// forward, plane-major nest, for a compile-time number of source views NV <= 2
-//
-// With few views the footprints of ALL views fit in registers (16 per view), so the nest can be
-//     depth block -> plane -> view
-// instead of block -> view -> plane: a plane's cost is finished and stored before the next plane
-// starts (no accumulator array: 28 fewer registers), and a view's footprint survives from one block of
-// planes to the next - it is reloaded only where the texel really changes, not at every block start.
-// The kernel is bound by the time one warp needs for its chain of dependent steps (measured: the same binary
-// runs 2.3x faster with three resident CTAs per SM than with one, while extra arithmetic, shared loads or an
-// L2-resident output change nothing), so it keeps the chain short and the per-lane loads low:
-//   * the row products of the pixel (Coef) stay in registers for the whole work item;
-//   * the division by the view count needs no load: with at most two views it is a multiplication by
-//     one half where both see the voxel (a ballot bit), by one otherwise (zero views give an exact zero);
-//   * the reload is one asm block that updates the eight footprint registers in place; a view that does
-//     not see the plane reads the reference pixel four times instead, which makes all differences zero.
-// ---------------------------------------------------------------------------------------------------
+// The cached 2x2 footprint of one view as differences against the reference pixel.  The reload is one asm block
+// that updates the eight registers in place; a view that does not see the plane reads the reference pixel four
+// times instead (dx = dy = 0), which makes every difference an exact zero: the "empty footprint".
 struct Footprint {
   pk2 a0a, a0b, ua, ub, va, vb, ta, tb;  // t00 - ref, t10 - t00, t01 - t00, t11 - t01 - (t10 - t00); channel pairs {0,1}, {2,3}
 };
@@ -317,6 +153,152 @@ struct FootprintLoad<__nv_bfloat16> {
   }
 };
 
+// Shared-memory bytes per warp: row products, one 16-byte record and one texel index per (view, lane),
+// the splatted 1/views per lane, one change word per view.
+__host__ __device__ inline size_t packed_fwd_smem_per_warp(int N, int G) {
+  return (size_t)N * G * sizeof(Coef<float>) + (size_t)N * 32 * 16 + 32 * 8 + (size_t)N * 32 * 4 +
+         (((size_t)N * 4 + 15) & ~(size_t)15);
+}
+
+#ifndef CHOP_PK_FWD_BLOCKS
+#define CHOP_PK_FWD_BLOCKS 3
+#endif
+
+template <typename T, int C>
+__global__ void __launch_bounds__(256, CHOP_PK_FWD_BLOCKS) cv_fwd_packed(const CvArgs a, const int warps, const size_t smem_per_warp) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int LG = C / 4;
+  constexpr int G = 32 / LG;
+  static_assert(LG * 4 == C && (LG & (LG - 1)) == 0 && LG >= 2 && LG <= 8, "C in {8, 16, 32}");
+  const int lane = threadIdx.x & 31;
+  const int wib = threadIdx.x >> 5;
+  const int li = lane & (LG - 1);
+  const int g = lane / LG;
+
+  const long long item = (long long)blockIdx.x * warps + wib;
+  if (item >= (long long)a.npb * a.nchunks) return;
+  const int chunk_id = (int)(item / a.npb);
+  const int pb = (int)(item - (long long)chunk_id * a.npb);
+  const long long pix0 = (long long)pb * G;
+  const bool pvalid = pix0 + g < a.npix;
+  const long long pix = pvalid ? pix0 + g : a.npix - 1;
+  const int dlo = a.d_begin + chunk_id * a.chunk;
+  const int dhi = min(a.d_end, dlo + a.chunk);
+  const int N = a.N;
+  const int D = a.D;
+
+  unsigned char* mine = smem_raw + (size_t)wib * smem_per_warp;
+  Coef<float>* coef = reinterpret_cast<Coef<float>*>(mine);
+  float4* rec = reinterpret_cast<float4*>(coef + N * G);   // [N][32] {dw, dw, dh, dh}
+  float2* inv2 = reinterpret_cast<float2*>(rec + N * 32);  // [32]    {1/views, 1/views}
+  int* tex = reinterpret_cast<int*>(inv2 + 32);            // [N][32] top-left texel or -1
+  unsigned* chg = reinterpret_cast<unsigned*>(tex + N * 32);  // [N] bit (g*LG + j): reload at plane j
+
+  stage_coefs<float>(a, coef, lane, G, pix0);
+  __syncwarp();
+
+  const T* src_lane = static_cast<const T*>(a.src) + li * 4;
+  const T* ref_lane = static_cast<const T*>(a.ref) + pix * C + li * 4;
+  pk2 ref0, ref1;
+  PkLoad<T>::ld(ref_lane, ref0, ref1);
+  const int b = (int)(pix / ((long long)a.H * a.W));
+  const float base = static_cast<const float*>(a.depth)[pix];
+  const float* offs = static_cast<const float*>(a.offsets) + (long long)b * D;
+  const long long dx_bytes = (long long)C * (long long)sizeof(T);
+  const long long dy_bytes = (long long)a.Ws * dx_bytes;
+  float* out = static_cast<float*>(a.cost) + (pix * D + dlo) * C + li * 4;
+  const ulonglong2* rec_mine = reinterpret_cast<const ulonglong2*>(rec) + g * LG;
+  const int* tex_mine = tex + g * LG;
+  const pk2* inv_mine = reinterpret_cast<const pk2*>(inv2) + g * LG;
+
+  for (int dblk = dlo; dblk < dhi; dblk += LG, out += LG * C) {
+    // ---- phase A: lane (g, li) projects plane dblk+li of pixel g into every view ---------------------
+    {
+      const int d = dblk + li;
+      const bool dv = pvalid && d < dhi;
+      const float depth = dv ? xadd(base, offs[d]) : 0.0f;
+      int used = 0;
+      for (int n = 0; n < N; ++n) {
+        int t = -1;
+        float dh = 0.0f, dw = 0.0f;
+        if (dv) {
+          float gh, gw;
+          t = project<float, false>(coef[n * G + g], depth, a.half_centor, a.Hs, a.Ws, dh, dw, gh, gw);
+          used += t >= 0;
+        }
+        rec[n * 32 + lane] = make_float4(dw, dw, dh, dh);
+        tex[n * 32 + lane] = t;
+        // the footprint registers do not outlive a (block, view): plane 0 always loads
+        const int prev = __shfl_up_sync(0xffffffffu, t, 1);
+        const unsigned bal = __ballot_sync(0xffffffffu, li == 0 || t != prev);
+        if (lane == 0) chg[n] = bal;
+      }
+      if (dv) __stcs(a.mask + pix * D + d, used);
+      const float inv = used > 0 ? 1.0f / (float)used : 0.0f;
+      inv2[lane] = make_float2(inv, inv);
+    }
+    __syncwarp();
+
+    // ---- phase B ---------------------------------------------------------------------------------------
+    if (pvalid) {
+      pk2 acc[LG][2];
+#pragma unroll
+      for (int j = 0; j < LG; ++j) acc[j][0] = acc[j][1] = 0ull;
+      for (int n = 0; n < N; ++n) {
+        const ulonglong2* r = rec_mine + n * 32;
+        const int* tx = tex_mine + n * 32;
+        const unsigned m = chg[n] >> (g * LG);
+        Footprint F;
+        F.a0a = F.a0b = F.ua = F.ub = F.va = F.vb = F.ta = F.tb = 0ull;
+#pragma unroll
+        for (int j = 0; j < LG; ++j) {
+          if (j == 0 || ((m >> j) & 1u)) {   // the footprint registers do not outlive a (block, view): plane 0 always loads
+            const int t = tx[j];
+            const T* p = t >= 0 ? src_lane + (size_t)t * C : ref_lane;
+            FootprintLoad<T>::go(F, p, t >= 0 ? dx_bytes : 0ll, t >= 0 ? dy_bytes : 0ll, ref0, ref1);
+          }
+          const ulonglong2 wh = r[j];  // x = {dw, dw}, y = {dh, dh}
+          const pk2 X0 = pk_fma(F.ta, wh.x, F.ua);
+          const pk2 X1 = pk_fma(F.tb, wh.x, F.ub);
+          const pk2 Y0 = pk_fma(wh.x, F.va, F.a0a);
+          const pk2 Y1 = pk_fma(wh.x, F.vb, F.a0b);
+          const pk2 d0 = pk_fma(wh.y, X0, Y0);  // sample - ref
+          const pk2 d1 = pk_fma(wh.y, X1, Y1);
+          pk_fma_to(acc[j][0], d0, d0);
+          pk_fma_to(acc[j][1], d1, d1);
+        }
+      }
+
+      const int left = dhi - dblk;
+#pragma unroll
+      for (int j = 0; j < LG; ++j) {
+        if (j < left) {
+          const pk2 inv = inv_mine[j];
+          pk_store_stream(out + j * C, pk_mul(acc[j][0], inv), pk_mul(acc[j][1], inv));
+        }
+      }
+    }
+    __syncwarp();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// forward, plane-major nest, for a compile-time number of source views NV <= 2
+//
+// With few views the footprints of ALL views fit in registers (16 per view), so the nest can be
+//     depth block -> plane -> view
+// instead of block -> view -> plane: a plane's cost is finished and stored before the next plane
+// starts (no accumulator array: 28 fewer registers), and a view's footprint survives from one block of
+// planes to the next - it is reloaded only where the texel really changes, not at every block start.
+// The kernel is bound by the time one warp needs for its chain of dependent steps (measured: the same binary
+// runs 2.3x faster with three resident CTAs per SM than with one, while extra arithmetic, shared loads or an
+// L2-resident output change nothing), so it keeps the chain short and the per-lane loads low:
+//   * the row products of the pixel (Coef) stay in registers for the whole work item;
+//   * the division by the view count needs no load: with at most two views it is a multiplication by
+//     one half where both see the voxel (a ballot bit), by one otherwise (zero views give an exact zero);
+//   * the reload is one asm block that updates the eight footprint registers in place; a view that does
+//     not see the plane reads the reference pixel four times instead, which makes all differences zero.
+// ---------------------------------------------------------------------------------------------------
 // project<> without branches: every operation is executed (a non-positive z only produces values that the
 // validity test then discards), so the independent chains of several views can be interleaved by the
 // compiler.  Same unfused operations in the same order as project<float,false>: identical results.
@@ -344,12 +326,13 @@ __host__ __device__ inline size_t pm_fwd_smem_per_warp(int NV) {
   return (size_t)NV * 32 * 16 + (size_t)NV * 32 * 4 + 16;
 }
 
-// six 128-thread CTAs per SM measured fastest at c1 (123 us; three 256-thread CTAs 126 us; more CTAs spill)
+// five 128-thread CTAs per SM (96 registers, nothing spilled) measured fastest at c1: 120 us; six (80 registers,
+// 72 bytes spilled) 124 us; three 256-thread CTAs 126 us; seven and more spill heavily (130 us and up)
 #ifndef CHOP_PM_FWD_WARPS
 #define CHOP_PM_FWD_WARPS 4
 #endif
 #ifndef CHOP_PM_FWD_BLOCKS
-#define CHOP_PM_FWD_BLOCKS 6
+#define CHOP_PM_FWD_BLOCKS 5
 #endif
 
 template <typename T, int C, int NV>
