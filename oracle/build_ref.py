@@ -99,13 +99,14 @@ def extract_kernel(text, name):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("CHOP_REFERENCE_DIR", ""),
+                    help="checkout of zhuimeng999/custom_helper_op (or set CHOP_REFERENCE_DIR)")
     ap.add_argument("--quiet", action="store_true")
     args = ap.parse_args()
-    src_dir = os.path.join(args.reference, KDIR)
-    if not os.path.isdir(src_dir):
+    src_dir = os.path.join(args.reference, KDIR) if args.reference else ""
+    if not src_dir or not os.path.isdir(src_dir):
         if not args.quiet:
-            print("reference checkout not found at %s: keeping any prebuilt oracle/_ref" % args.reference)
+            print("no reference checkout given (--reference DIR or CHOP_REFERENCE_DIR): keeping any prebuilt oracle/_ref")
         return 3
     out_dir = os.path.join(HERE, "_ref")
     os.makedirs(out_dir, exist_ok=True)
