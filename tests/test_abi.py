@@ -59,3 +59,30 @@ def test_invalid_arguments_are_rejected_on_the_host():
     assert _fwd(_desc(d_begin=2, d_end=2)) == 0         # empty depth range: nothing to do
     assert b"NULL" in _lib.lib().chop_status_string(-1)
     assert _lib.lib().chop_set_tuning(b"nope", 1) == -3
+
+
+def test_unknown_flag_bits_and_unused_descriptor_fields_are_rejected():
+    assert _fwd(_desc(flags=4)) == -3                   # a bit this build does not know
+    assert _fwd(_desc(flags=0x80000000)) == -3
+    L = _lib.lib()
+    ptr = ctypes.c_void_p(256)
+
+    def fa(**kw):
+        d = _desc(**dict(dict(kind=0, groups=1), **kw))
+        return L.chop_feature_aggregate_fwd(ctypes.byref(d), ptr, ptr, ptr, ptr, ptr, ptr, ptr, None)
+
+    assert fa(kind=1) == -3 and fa(reduce=1) == -3 and fa(groups=8) == -3 and fa(flags=1) == -3
+    assert fa(d_begin=2, d_end=2) == 0                  # a valid descriptor with an empty depth range: nothing to do
+
+
+def test_tuning_knobs_are_inert_without_the_opt_in():
+    """chop_set_tuning is process-wide, hence refused unless CHOP_ENABLE_TUNING=1 was in the environment when the
+    library first looked (the test session sets it in conftest.py; a fresh process without it must be refused)."""
+    import subprocess
+    import sys
+    assert _lib.lib().chop_set_tuning(b"tuned", 1) == 0
+    code = ("import ctypes; L = ctypes.CDLL(%r); L.chop_set_tuning.argtypes = [ctypes.c_char_p, ctypes.c_int]; "
+            "print(L.chop_set_tuning(b'tuned', 0))" % _lib.LIB_PATH)
+    env = {k: v for k, v in os.environ.items() if k != "CHOP_ENABLE_TUNING"}
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True)
+    assert out.stdout.strip() == "-4", out.stdout + out.stderr
