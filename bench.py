@@ -33,29 +33,36 @@ import numpy as np  # noqa: E402
 
 TRAFFIC_FILE = os.path.join(ROOT, "profiles", "dram_traffic.json")
 KERNEL_SOURCES = ("cv_packed.cuh", "cv_tuned.cuh", "cv_project.cuh", "chop_common.cuh", "cv_launch.cuh")
+CONV_SOURCES = ("sc_umma.cu", "sc_common.cuh", "sc_abi.cu")
 
 
-def kernel_source_digest():
-    """sha1 over the kernel sources the c1 step compiles from: ties a recorded ncu figure to the code it was taken on."""
+def kernel_source_digest(names=KERNEL_SOURCES):
+    """sha1 over the kernel sources a workload compiles from: ties a recorded ncu figure to the code it was taken on."""
     import hashlib
     h = hashlib.sha1()
-    for name in KERNEL_SOURCES:
+    for name in names:
         with open(os.path.join(ROOT, "custom_helper_op_b200", "csrc", name), "rb") as f:
             h.update(f.read())
     return h.hexdigest()
 
 
-def recorded_traffic(workload, which):
-    """dram__bytes_read.sum + dram__bytes_write.sum per launch of the workload's forward / backward kernel, as written
-    into profiles/dram_traffic.json when the ncu capture was summarised.  None if there is no record, or if the kernel
-    sources have changed since (a stale figure is worse than none)."""
+def recorded_counters(workload, which, names=KERNEL_SOURCES):
+    """The ncu figures of one kernel of a workload, as written into profiles/dram_traffic.json when the capture was
+    summarised (dram_bytes = dram__bytes_read.sum + dram__bytes_write.sum per launch; tensor_pipe_util where it
+    applies).  None if there is no record, or if the kernel sources have changed since (a stale figure is worse
+    than none)."""
     try:
         rec = json.load(open(TRAFFIC_FILE))[workload]
-        if rec.get("source_sha1") != kernel_source_digest():
+        if rec.get("source_sha1") != kernel_source_digest(names):
             return None
-        return float(rec[which]["dram_bytes"])
+        return rec[which]
     except Exception:
         return None
+
+
+def recorded_traffic(workload, which):
+    rec = recorded_counters(workload, which)
+    return None if rec is None else float(rec["dram_bytes"])
 
 LAUNCHES_PER_STEP = 3
 METRIC = "cost_volume_fwd_bwd_voxel_views_per_s"
@@ -653,14 +660,20 @@ def sparse_conv_main(args):
     except Exception:
         pass
     ms = fwd_ms + bwd_ms
+    rec_f = recorded_counters("c4_sparse_conv", "fwd", CONV_SOURCES)
+    rec_w = recorded_counters("c4_sparse_conv", "wgrad", CONV_SOURCES)
     out = {"metric": "sparse_conv3d_fwd_bwd_voxels_per_s", "value": nvox / (ms * 1e-3), "unit": "voxels/s", "n_gpus": 1,
            "steps": K, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
            "config": {"workload": "c4_sparse_conv: SparseConv3DFast fwd+bwd, B=%d, %dx%d, band of %d planes, 3x3x3, %d->%d, bf16/fp32-acc"
                                   % (B, H, W, D, Cin, Cout), "l2": "flushed between steps (256 MB write)"},
            "gpu_launches": 4 * K, "umma_timeouts": _lib.lib().chop_umma_timeouts(),
-           "roofline": {"bound": "hbm", "kernel": "sc_umma_kernel (forward)", "achieved": fwd_b / (fwd_ms * 1e-3) / 1e9, "peak": peak,
-                        "peak_source": peak_kind, "unit": "GB/s", "frac": fwd_b / (fwd_ms * 1e-3) / 1e9 / peak, "traffic": None,
+           "roofline": {"bound": "hbm", "kernel": "sc_umma_rows_kernel (forward)", "achieved": fwd_b / (fwd_ms * 1e-3) / 1e9, "peak": peak,
+                        "peak_source": peak_kind, "unit": "GB/s", "frac": fwd_b / (fwd_ms * 1e-3) / 1e9 / peak,
+                        "traffic": (rec_f or {}).get("dram_bytes"),
+                        # sm__pipe_tensor_cycles_active of the recorded ncu captures (null once sc_umma.cu has changed)
+                        "tensor_pipe_util": None if rec_f is None else {"fwd": rec_f.get("tensor_pipe_util"),
+                                                                        "wgrad": (rec_w or {}).get("tensor_pipe_util")},
                         "fwd": {"ms": fwd_ms, "algorithmic_bytes": fwd_b, "tflops": flops_fwd / (fwd_ms * 1e-3) / 1e12,
                                 "tensor_frac_of_measured": flops_fwd / (fwd_ms * 1e-3) / 1e12 / tpeak},
                         "bwd": {"ms": bwd_ms, "algorithmic_bytes": bwd_b, "tflops": 2 * flops_fwd / (bwd_ms * 1e-3) / 1e12,
