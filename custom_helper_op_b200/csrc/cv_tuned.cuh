@@ -821,14 +821,26 @@ __global__ void __launch_bounds__(256, 3) cv2_fwd_tuned(const CvArgs a, const in
             Vec<T, float, CPL>::load(p00 + C, t01);
             Vec<T, float, CPL>::load(p10, t10);
             Vec<T, float, CPL>::load(p10 + C, t11);
+            // The correlation is linear in the sample, so the reference pixel is applied to the four CORNERS first
+            // (one dot product per corner and group) and the bilinear differences are formed on the group sums:
+            // 4 multiply-adds per channel + 4 subtractions per group instead of 8 operations per channel.
+            float d00[NG], d01[NG], d10[NG], d11[NG];
+#pragma unroll
+            for (int q = 0; q < NG; ++q) d00[q] = d01[q] = d10[q] = d11[q] = 0.0f;
 #pragma unroll
             for (int k = 0; k < CPL; ++k) {
               const int q = k / SUB;
-              const float uu = t10[k] - t00[k];
-              a0[q] = fmaf(t00[k], refv[k], a0[q]);
-              u[q] = fmaf(uu, refv[k], u[q]);
-              v[q] = fmaf(t01[k] - t00[k], refv[k], v[q]);
-              t1[q] = fmaf((t11[k] - t01[k]) - uu, refv[k], t1[q]);
+              d00[q] = fmaf(t00[k], refv[k], d00[q]);
+              d01[q] = fmaf(t01[k], refv[k], d01[q]);
+              d10[q] = fmaf(t10[k], refv[k], d10[q]);
+              d11[q] = fmaf(t11[k], refv[k], d11[q]);
+            }
+#pragma unroll
+            for (int q = 0; q < NG; ++q) {
+              a0[q] = d00[q];
+              u[q] = d10[q] - d00[q];
+              v[q] = d01[q] - d00[q];
+              t1[q] = (d11[q] - d01[q]) - u[q];
             }
           }
         }
