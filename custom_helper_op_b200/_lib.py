@@ -86,6 +86,7 @@ def lib():
         L.chop_copy_2d_async.restype = ctypes.c_int
         L.chop_copy_2d_async.argtypes = [vp, ctypes.c_size_t, vp, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, vp]
         L.chop_umma_timeouts.restype = ctypes.c_int
+        L.chop_umma_watch.restype = ctypes.c_int
         L.chop_status_string.restype = ctypes.c_char_p
         L.chop_status_string.argtypes = [ctypes.c_int]
         L.chop_version.restype = ctypes.c_int

@@ -248,5 +248,6 @@ int chop_sparse_pad_bwd(int32_t dtype, int64_t B, int64_t h, int64_t w, int64_t 
 }
 
 int chop_umma_timeouts(void) { return chop::sc_umma_timeouts(); }
+int chop_umma_watch(void) { return chop::sc_umma_watch(); }
 
 }  // extern "C"

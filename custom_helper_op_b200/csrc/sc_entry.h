@@ -27,6 +27,8 @@ int sc_tile_wgrad_launch(int dtype, const ScArgs& a, int nparts, cudaStream_t st
 int sc_tile_twgrad_launch(int dtype, const ScArgs& a, int nparts, cudaStream_t st);
 int sc_tile_gather_launch(int dtype, const ScArgs& a, cudaStream_t st);
 int sc_umma_timeouts();
+int sc_umma_watch();
+int sc_umma_note_timeout_for_test(int on);
 void sc_umma_set_rows(int on);
 size_t sc_wgrad_workspace_bytes(int dtype, int taps, int Cin, int Cout, long long nvox_out);
 }  // namespace chop

@@ -25,6 +25,7 @@
 #include <cuda_bf16.h>
 
 #include <atomic>
+#include <mutex>
 
 #include "sc_common.cuh"
 #include "sc_entry.h"
@@ -34,6 +35,18 @@ namespace chop {
 namespace {
 
 __device__ int g_umma_timeouts = 0;
+// Host-visible mirror of the counter: a mapped, pinned int that sc_umma_watch() publishes to the device on request.
+// A kernel that gives up a wait also bumps it, so a host can notice without synchronising with the device.
+__device__ int* g_umma_host_mirror = nullptr;
+__device__ __forceinline__ void note_timeout() {
+  atomicAdd(&g_umma_timeouts, 1);
+  int* h = g_umma_host_mirror;
+  if (h) {
+    atomicAdd_system(h, 1);
+    __threadfence_system();
+  }
+}
+__global__ void note_timeout_kernel() { note_timeout(); }
 std::atomic<int> g_umma_rows{1};   // tuning knob "umma_rows": 0 = always the per-tap gather
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -294,7 +307,7 @@ __global__ void __launch_bounds__(128) sc_umma_kernel(const ScArgs a, const long
       if (warp == 0) done = mbar_wait(mbar, phase);
       phase ^= 1;
       if (!__syncthreads_and(done)) {
-        if (tid == 0) atomicAdd(&g_umma_timeouts, 1);
+        if (tid == 0) note_timeout();
         alive = false;
         break;
       }
@@ -516,7 +529,7 @@ __global__ void __launch_bounds__(128, CIN <= 16 ? 4 : 2) sc_umma_rows_kernel(co
     if (warp == 0) done = mbar_wait(mbar, phase);
     phase ^= 1;
     if (!__syncthreads_and(done)) {
-      if (tid == 0) atomicAdd(&g_umma_timeouts, 1);
+      if (tid == 0) note_timeout();
       alive = false;
       break;
     }
@@ -700,7 +713,7 @@ __global__ void __launch_bounds__(128) sc_umma_wgrad_kernel(const ScArgs a, cons
       if (warp == 0) done = mbar_wait(mbar, phase);
       phase ^= 1;
       if (!__syncthreads_and(done)) {
-        if (tid == 0) atomicAdd(&g_umma_timeouts, 1);
+        if (tid == 0) note_timeout();
         alive = false;
         break;
       }
@@ -948,7 +961,7 @@ __global__ void __launch_bounds__(128, 4) sc_umma_wgrad_rows_kernel(const ScArgs
     if (warp == 0) done = mbar_wait(mbar, phase);
     phase ^= 1;
     if (!__syncthreads_and(done)) {
-      if (tid == 0) atomicAdd(&g_umma_timeouts, 1);
+      if (tid == 0) note_timeout();
       alive = false;
       break;
     }
@@ -1184,6 +1197,53 @@ int sc_umma_timeouts() {
   int v = -1;
   if (cudaMemcpyFromSymbol(&v, g_umma_timeouts, sizeof(int)) != cudaSuccess) return -1;
   return v;
+}
+
+namespace {
+std::mutex g_watch_mu;
+int* g_watch_host = nullptr;          // mapped pinned int, shared by all devices of the process
+unsigned long long g_watch_devs = 0;  // devices that know its address (bit = device ordinal, < 64)
+}  // namespace
+
+// Number of abandoned waits seen through the host-visible mirror; -1 if it cannot be set up.  The first call per
+// device allocates (once per process) and publishes the mirror - that call synchronises; later calls read host memory.
+int sc_umma_watch() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  std::lock_guard<std::mutex> lk(g_watch_mu);
+  if (!g_watch_host) {
+    int* h = nullptr;
+    if (cudaHostAlloc(reinterpret_cast<void**>(&h), sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+      cudaGetLastError();
+      return -1;
+    }
+    *h = 0;
+    g_watch_host = h;
+  }
+  if (!((g_watch_devs >> dev) & 1ull)) {
+    int* dptr = nullptr;
+    if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&dptr), g_watch_host, 0) != cudaSuccess ||
+        cudaMemcpyToSymbol(g_umma_host_mirror, &dptr, sizeof(dptr)) != cudaSuccess) {
+      cudaGetLastError();
+      return -1;
+    }
+    g_watch_devs |= 1ull << dev;
+  }
+  return *const_cast<volatile int*>(g_watch_host);
+}
+
+// Test facility (behind the tuning opt-in): on != 0 runs the give-up bookkeeping once (default stream), without any wait;
+// on == 0 clears the device counter of the current device and the mirror.
+int sc_umma_note_timeout_for_test(int on) {
+  if (on) {
+    note_timeout_kernel<<<1, 1>>>();
+    return (int)cudaGetLastError();
+  }
+  const int zero = 0;
+  if (cudaMemcpyToSymbol(g_umma_timeouts, &zero, sizeof(int)) != cudaSuccess) return (int)cudaGetLastError();
+  std::lock_guard<std::mutex> lk(g_watch_mu);
+  if (g_watch_host) *const_cast<volatile int*>(g_watch_host) = 0;
+  return 0;
 }
 
 }  // namespace chop

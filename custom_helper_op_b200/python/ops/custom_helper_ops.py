@@ -248,6 +248,19 @@ def _scalar(value, like):
     return torch.full((), float(value), dtype=like.dtype, device=like.device)
 
 
+def _umma_watch(images):
+    """Before a tensor-core (bfloat16) manifold-convolution call: raise if a kernel of an EARLIER call gave up a
+    bounded wait on its MMA barrier - the outputs of the calls since the last check are then incomplete.  Reads one
+    int of pinned host memory (chop_umma_watch); only the first call per device synchronises."""
+    if images.dtype != torch.bfloat16:
+        return
+    with torch.cuda.device(images.device):
+        n = _lib.lib().chop_umma_watch()
+    if n > 0:
+        raise RuntimeError("custom_helper_op: %d tensor-core convolution wait(s) timed out on the device; results of "
+                           "the manifold-convolution calls since the previous check are incomplete" % n)
+
+
 def sparse_conv3d_forward(images, filters, default_value, base_plane, strides=(1, 1, 1), dilations=(1, 1, 1)):
     """Raw op SparseConv3DFast."""
     images = images.contiguous()
@@ -258,6 +271,7 @@ def sparse_conv3d_forward(images, filters, default_value, base_plane, strides=(1
     _require(base_plane.dtype == torch.int32 and tuple(base_plane.shape) == (d.B, d.H, d.W, 1),
              "base_plane must have rank 4, and must compate to ref_image")
     out = torch.empty(out_shape, dtype=images.dtype, device=images.device)
+    _umma_watch(images)
     st = _lib.lib().chop_sparse_conv3d_fwd(ctypes.byref(d), _ptr(images), _ptr(filters), _ptr(default_value),
                                            _ptr(base_plane), _ptr(out), _stream())
     _lib.check(st, "chop_sparse_conv3d_fwd")
@@ -280,6 +294,7 @@ def sparse_conv3d_backward(images, filters, default_value, base_plane, out_grad,
     default_grad = torch.empty((), dtype=wdt, device=images.device)
     nbytes = _lib.lib().chop_sparse_conv3d_bwd_workspace_size(ctypes.byref(d))
     ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=images.device)
+    _umma_watch(images)
     st = _lib.lib().chop_sparse_conv3d_bwd(ctypes.byref(d), _ptr(images), _ptr(filters), _ptr(default_value),
                                            _ptr(base_plane), _ptr(out_grad), _ptr(images_grad), _ptr(filter_grad),
                                            _ptr(default_grad), _ptr(ws), ctypes.c_size_t(ws.numel()), _stream())
@@ -353,6 +368,7 @@ def sparse_conv3d_transpose_forward(images, filters, default_value, base_plane, 
     _require(base_plane.dtype == torch.int32 and tuple(base_plane.shape) == (d.B, d.H, d.W, 1),
              "base_plane must have rank 4, and must compate to ref_image")
     out = torch.empty(out_shape, dtype=images.dtype, device=images.device)
+    _umma_watch(images)
     st = _lib.lib().chop_sparse_conv3d_transpose_fwd(ctypes.byref(d), _ptr(images), _ptr(filters), _ptr(default_value),
                                                      _ptr(base_plane), _ptr(out), _stream())
     _lib.check(st, "chop_sparse_conv3d_transpose_fwd")
@@ -374,6 +390,7 @@ def sparse_conv3d_transpose_backward(images, filters, default_value, base_plane,
     filter_grad = torch.empty(filters.shape, dtype=wdt, device=images.device)
     nbytes = _lib.lib().chop_sparse_conv3d_transpose_bwd_workspace_size(ctypes.byref(d))
     ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=images.device)
+    _umma_watch(images)
     st = _lib.lib().chop_sparse_conv3d_transpose_bwd(ctypes.byref(d), _ptr(images), _ptr(filters), _ptr(default_value),
                                                      _ptr(base_plane), _ptr(out_grad), _ptr(images_grad),
                                                      _ptr(filter_grad), _ptr(ws), ctypes.c_size_t(ws.numel()), _stream())

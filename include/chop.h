@@ -8,7 +8,8 @@
  *     all process-wide and none of them visible in results:
  *       . a table of which kernels have been granted more than 48 KB of dynamic shared memory on which
  *         device (the opt-in attribute is set the first time a launch needs it, not on every call);
- *       . chop_umma_timeouts(): a device-side counter of bounded waits that gave up (see below);
+ *       . chop_umma_timeouts(): a device-side counter of bounded waits that gave up (see below), and - only
+ *         after a call of chop_umma_watch() - one int of pinned host memory that mirrors it;
  *       . the 4 MiB device array behind chop_sparse_conv3d_bwd_noalloc and its per-device address;
  *       . the test / benchmark knobs of chop_set_tuning, inert unless the process sets
  *         CHOP_ENABLE_TUNING=1 in its environment before the first call,
@@ -238,6 +239,15 @@ CHOP_API int chop_decode_pfm(const void *contents, size_t size, int64_t *height,
  * int from the device, so it synchronises with the current device; -1 if that copy fails. */
 CHOP_API int chop_umma_timeouts(void);
 
+/* The same count without touching the device, for hosts that must not synchronise (a framework op, a serving loop):
+ * the kernels also bump a mapped, pinned host int once this function has published it to the current device.  The
+ * first call in a process allocates that int (4 bytes, cudaHostAlloc) and the first call per device copies its address
+ * to the device - those calls synchronise; every later call only reads host memory.  Give-ups on a device before its
+ * first call are not in the count, and a bump becomes visible when the kernel that made it has written it through,
+ * at the latest when that kernel ends: a caller polls before its NEXT call, or after its own synchronisation point.
+ * No compute entry point calls this by itself (they allocate nothing).  -1 if the mirror cannot be set up. */
+CHOP_API int chop_umma_watch(void);
+
 /* Strided host<->device copy of a depth range: `rows` rows of `width_bytes` bytes, row pitches given
  * (cudaMemcpy2DAsync with cudaMemcpyDefault).  A [d0,d1) slice of a [...,D,C] tensor is rows = B*H*W,
  * width = (d1-d0)*C*elem, pitch = D*C*elem.  Used by hosts that stream cost / cost_grad between pinned
@@ -257,7 +267,9 @@ CHOP_API int chop_version(void);
  * where supported, 0 = always the generic kernels), "umma_rows" (1 = the stride-1 tensor-core forward / image
  * gradient stages one copy per neighbour pixel, 0 = one per tap), "tile" (1 = register-tiled float32 manifold
  * convolution kernels where supported, 0 = the one-thread-per-element kernels), "packed" (1 = the packed-pair CostVolume
- * MEAN kernels where one exists, 0 = the previous compile-time-C kernels).  Returns CHOP_ERR_ATTR for an unknown name.
+ * MEAN kernels where one exists, 0 = the previous compile-time-C kernels), "note_timeout" (1 = launch a one-thread
+ * kernel that performs the bookkeeping of an abandoned tensor-core wait, without any wait; 0 = clear the counter of
+ * the current device and its host mirror).  Returns CHOP_ERR_ATTR for an unknown name.
  * Process-wide, hence a facility for tests and benchmarks only: every call returns CHOP_ERR_UNSUPPORTED unless the
  * process has CHOP_ENABLE_TUNING=1 in its environment (read once, at the first call); a production host never sets it
  * and always gets the default kernel selection.  Not part of the reference surface. */

@@ -4,6 +4,8 @@ import ctypes
 import os
 import re
 
+import pytest
+
 from custom_helper_op_b200 import _lib
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -86,3 +88,28 @@ def test_tuning_knobs_are_inert_without_the_opt_in():
     env = {k: v for k, v in os.environ.items() if k != "CHOP_ENABLE_TUNING"}
     out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True)
     assert out.stdout.strip() == "-4", out.stdout + out.stderr
+
+
+def test_wrappers_refuse_to_run_after_a_reported_give_up(monkeypatch):
+    """Host logic of the non-synchronising check: the bf16 manifold-convolution wrappers read chop_umma_watch()
+    before launching and raise when it reports abandoned waits; other dtypes do not look.  (A fake library stands
+    in: without a device the real entry point answers -1, 'no mirror', which the wrappers ignore.)"""
+    import contextlib
+    import types
+    import torch
+    from custom_helper_op_b200.python.ops import custom_helper_ops as ops
+    assert _lib.lib().chop_umma_watch() in (-1, 0)
+    count = {"n": 0}
+    fake = types.SimpleNamespace(chop_umma_watch=lambda: count["n"])
+    monkeypatch.setattr(ops._lib, "lib", lambda: fake)
+    monkeypatch.setattr(torch.cuda, "device", lambda dev: contextlib.nullcontext())
+    bf16 = types.SimpleNamespace(dtype=torch.bfloat16, device=torch.device("cuda", 0))
+    f32 = types.SimpleNamespace(dtype=torch.float32, device=torch.device("cuda", 0))
+    ops._umma_watch(bf16)
+    for n in (-1, 0):
+        count["n"] = n
+        ops._umma_watch(bf16)
+    count["n"] = 2
+    ops._umma_watch(f32)
+    with pytest.raises(RuntimeError, match="2 tensor-core convolution wait"):
+        ops._umma_watch(bf16)

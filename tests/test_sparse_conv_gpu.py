@@ -237,3 +237,29 @@ def test_autograd_wrapper():
     assert abs(float(td.grad) - float(dg_w)) <= 1e-4 * max(1.0, abs(float(dg_w)))
     with pytest.raises(ValueError):
         ops.sparse_conv3d_fast(ti.cpu(), tf.cpu(), 0.0, torch.from_numpy(bp))
+
+
+def test_a_give_up_reaches_the_host_without_a_synchronising_poll():
+    """The bookkeeping a tensor-core kernel performs when a bounded wait runs out, exercised without any wait: a
+    one-thread kernel bumps the device counter and its pinned host mirror (test knob "note_timeout").  The host sees
+    the count through chop_umma_watch() - a plain read of host memory - and the bf16 wrappers refuse to run until
+    the counters are cleared."""
+    from custom_helper_op_b200 import _lib
+    from custom_helper_op_b200.python.ops import custom_helper_ops as ops
+    L = _lib.lib()
+    assert L.chop_umma_watch() == 0 and L.chop_umma_timeouts() == 0
+    images, filters, defv, bp, _ = make_case(31, 1, 6, 7, 9, 16, 16, (3, 3, 3), 24, np.float32)
+    t = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a)).to("cuda:0").to(dt)
+    args = (t(images, torch.bfloat16), t(filters, torch.bfloat16), float(defv), t(bp, torch.int32))
+    ops.sparse_conv3d_forward(*args)
+    try:
+        _lib.set_tuning("note_timeout", 1)
+        torch.cuda.synchronize()
+        assert L.chop_umma_watch() == 1 and L.chop_umma_timeouts() == 1
+        with pytest.raises(RuntimeError, match="timed out"):
+            ops.sparse_conv3d_forward(*args)
+        ops.sparse_conv3d_forward(args[0].float(), args[1].float(), args[2], args[3])   # float32: no tensor-core kernel, no check
+    finally:
+        _lib.set_tuning("note_timeout", 0)
+    assert L.chop_umma_watch() == 0 and L.chop_umma_timeouts() == 0
+    ops.sparse_conv3d_forward(*args)
