@@ -557,7 +557,11 @@ __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const C
   // so phase A does not start with an exposed DRAM round trip.
   const int mk_stride = (RMIN && !AGG) ? C : 1;
   int m_next = 0;
-  if (pvalid && dlo + li < dhi) m_next = __ldg(a.mask + (pix * D + dlo + li) * mk_stride);
+  float ag_next = 0.0f;   // aggregate: the voxel's single upstream value, requested a block ahead as well
+  if (pvalid && dlo + li < dhi) {
+    m_next = __ldg(a.mask + (pix * D + dlo + li) * mk_stride);
+    if (AGG) ag_next = __ldg(static_cast<const float*>(a.cost_grad) + pix * D + dlo + li);
+  }
   int buf = 0;
   for (int dblk = dlo; dblk < dhi; dblk += LG, cg_src += LG * C, buf ^= (CG_BUFS - 1)) {
     if (!AGG && CG_BUFS == 2) {
@@ -587,19 +591,23 @@ __global__ void __launch_bounds__(128, CHOP_BWD_MIN_BLOCKS) cv_bwd_tuned(const C
       float depth = 0.0f, scale = 0.0f;
       bool live = false;
       const int m0 = m_next;
-      if (pvalid && d + LG < dhi) m_next = __ldg(a.mask + (pix * D + d + LG) * mk_stride);
+      const float ag0 = ag_next;
+      if (pvalid && d + LG < dhi) {
+        m_next = __ldg(a.mask + (pix * D + d + LG) * mk_stride);
+        if (AGG) ag_next = __ldg(static_cast<const float*>(a.cost_grad) + pix * D + d + LG);
+      }
       if (dv) {
         depth = xadd(base, offs[d]);
         if constexpr (RMIN) {
           live = m0 >= 0;                    // :484, aggregate :476
           scale = 2.0f;                      // :560
           if (AGG && live)                   // aggregate :500
-            scale = 2.0f * __ldg(static_cast<const float*>(a.cost_grad) + pix * D + d) / (float)C;
+            scale = 2.0f * ag0 / (float)C;
         } else {
           live = m0 > 0;                       // cost_volume_kernels_gpu.cu.cc:367
           if (live) scale = 2.0f / (float)m0;  // :439
           if (AGG && live)                     // one upstream value per voxel, divided by views*C
-            scale = 2.0f * __ldg(static_cast<const float*>(a.cost_grad) + pix * D + d) / (float)(m0 * C);
+            scale = 2.0f * ag0 / (float)(m0 * C);
         }
       }
       for (int n = 0; n < N; ++n) {
@@ -771,12 +779,15 @@ __global__ void __launch_bounds__(256, 3) cv2_fwd_tuned(const CvArgs a, const in
   const ProjF<float>* myrec = proj + g * LG;
   float* out = static_cast<float*>(a.cost) + (pix * D + dlo) * GR + li * NG;
 
+  // the lane's depth hypothesis of plane dblk+li streams in from HBM: requested one block ahead
+  float depth_next = (pvalid && dlo + li < dhi) ? __ldg(dgrid + dlo + li) : 0.0f;
   for (int dblk = dlo; dblk < dhi; dblk += LG, out += LG * GR) {
     float inv_mine;
     {
       const int d = dblk + li;
       const bool dv = pvalid && d < dhi;
-      const float depth = dv ? __ldg(dgrid + d) : 0.0f;
+      const float depth = depth_next;
+      if (pvalid && d + LG < dhi) depth_next = __ldg(dgrid + d + LG);
       int used = 0;
       for (int n = 0; n < N; ++n) {
         ProjF<float> r;
@@ -909,11 +920,14 @@ __global__ void __launch_bounds__(256, 2) cv2_fwd_min_tuned(const CvArgs a, cons
   float* out = static_cast<float*>(a.cost) + (pix * D + dlo) * GR + li * NG;
   int* outm = a.mask + (pix * D + dlo) * GR + li * NG;
 
+  // the lane's depth hypothesis of plane dblk+li streams in from HBM: requested one block ahead
+  float depth_next = (pvalid && dlo + li < dhi) ? __ldg(dgrid + dlo + li) : 0.0f;
   for (int dblk = dlo; dblk < dhi; dblk += LG, out += LG * GR, outm += LG * GR) {
     {
       const int d = dblk + li;
       const bool dv = pvalid && d < dhi;
-      const float depth = dv ? __ldg(dgrid + d) : 0.0f;
+      const float depth = depth_next;
+      if (pvalid && d + LG < dhi) depth_next = __ldg(dgrid + d + LG);
       for (int n = 0; n < N; ++n) {
         ProjF<float> r;
         r.texel = -1;
@@ -1050,21 +1064,55 @@ __global__ void __launch_bounds__(128, CHOP_V2_BWD_MIN_BLOCKS) cv2_bwd_tuned(con
   const float* cg_lane = static_cast<const float*>(a.cost_grad) + (pix * D + dlo) * GR + li * NG;
   const int* mk_lane = a.mask + (pix * D + dlo) * GR + li * NG;  // read for MIN only
 
+  // The lane's depth hypothesis and validity count / winner of plane dblk+li stream in from HBM: they are requested
+  // one block ahead, so phase A does not start with an exposed DRAM round trip.
+  const int mk_stride = RMIN ? GR : 1;
+  float depth_next = 0.0f;
+  int m_next = 0;
+  if (pvalid && dlo + li < dhi) {
+    depth_next = __ldg(dgrid + dlo + li);
+    m_next = __ldg(a.mask + (pix * D + dlo + li) * mk_stride);
+  }
   for (int dblk = dlo; dblk < dhi; dblk += LG, cg_lane += LG * GR, mk_lane += LG * GR) {
     __syncwarp();
+    // the block's upstream gradient (and winners): one request per plane, all in flight together and shared by the
+    // views, instead of a dependent load per (plane, view); requested before phase A, whose projections cover the latency
+    float cgall[LG][NG];
+    int mkall[RMIN ? LG : 1][NG];
+#pragma unroll
+    for (int j = 0; j < LG; ++j) {
+#pragma unroll
+      for (int q = 0; q < NG; ++q) {
+        cgall[j][q] = 0.0f;
+        if (RMIN) mkall[j][q] = -1;
+      }
+      if (dblk + j < dhi) {
+        Vec<float, float, NG>::load(cg_lane + j * GR, cgall[j]);
+        if constexpr (RMIN) {
+          float mk[NG];
+          Vec<float, float, NG>::load(reinterpret_cast<const float*>(mk_lane) + j * GR, mk);
+#pragma unroll
+          for (int q = 0; q < NG; ++q) mkall[j][q] = __float_as_int(mk[q]);
+        }
+      }
+    }
     // ---- phase A -----------------------------------------------------------------------------------------
     const int dA = dblk + li;
     const bool dvA = pvalid && dA < dhi;
     {
       float depth = 0.0f, scale = 0.0f;
       bool live = false;
+      const int m0 = m_next;
+      depth = depth_next;
+      if (pvalid && dA + LG < dhi) {
+        depth_next = __ldg(dgrid + dA + LG);
+        m_next = __ldg(a.mask + (pix * D + dA + LG) * mk_stride);
+      }
       if (dvA) {
-        depth = __ldg(dgrid + dA);
         if constexpr (RMIN) {
-          live = __ldg(a.mask + (pix * D + dA) * GR) >= 0;  // v2:495
-          scale = 1.0f;                                     // v2:583
+          live = m0 >= 0;                      // v2:495
+          scale = 1.0f;                        // v2:583
         } else {
-          const int m0 = __ldg(a.mask + pix * D + dA);
           live = m0 > 0;                       // v2:375
           if (live) scale = 1.0f / (float)m0;  // v2:461
         }
@@ -1087,27 +1135,6 @@ __global__ void __launch_bounds__(128, CHOP_V2_BWD_MIN_BLOCKS) cv2_bwd_tuned(con
     float dv[LG];
 #pragma unroll
     for (int j = 0; j < LG; ++j) dv[j] = 0.0f;
-    // the block's upstream gradient (and winners): one request per plane, all in flight together and shared by the
-    // views, instead of a dependent load per (plane, view)
-    float cgall[LG][NG];
-    int mkall[RMIN ? LG : 1][NG];
-#pragma unroll
-    for (int j = 0; j < LG; ++j) {
-#pragma unroll
-      for (int q = 0; q < NG; ++q) {
-        cgall[j][q] = 0.0f;
-        if (RMIN) mkall[j][q] = -1;
-      }
-      if (dblk + j < dhi) {
-        Vec<float, float, NG>::load(cg_lane + j * GR, cgall[j]);
-        if constexpr (RMIN) {
-          float mk[NG];
-          Vec<float, float, NG>::load(reinterpret_cast<const float*>(mk_lane) + j * GR, mk);
-#pragma unroll
-          for (int q = 0; q < NG; ++q) mkall[j][q] = __float_as_int(mk[q]);
-        }
-      }
-    }
     for (int n = 0; n < N; ++n) {
       const ProjF<float>* rA = recA + n * 32 + g * LG;
       const RecG* rGp = recG + n * 32 + g * LG;

@@ -274,26 +274,44 @@ __global__ void __launch_bounds__(256) cv3_bwd_kernel(const CvArgs a, const int 
   const bool lane_on = li < groups;
   R dsum = (R)0;
 
+  // The lane's mask entry and upstream value of plane dblk+li stream in from HBM: both are requested together and
+  // one block ahead (the upstream value whether or not the voxel turns out to be live), so phase A neither starts
+  // with a DRAM round trip nor chains two of them.
+  int nm0 = -1, nm1 = -1, nm2 = -1;
+  R ncg = (R)0;
+  auto request = [&](int d) {
+    if (pvalid && d < dhi) {
+      const long long vox = pix * D + d;
+      if (RMIN) {
+        nm0 = __ldg(a.mask + vox * 3); nm1 = __ldg(a.mask + vox * 3 + 1); nm2 = __ldg(a.mask + vox * 3 + 2);
+      } else {
+        nm0 = __ldg(a.mask + vox);
+      }
+      ncg = __ldg(static_cast<const R*>(a.cost_grad) + vox);
+    }
+  };
+  request(dlo + li);
   for (int dblk = dlo; dblk < dhi; dblk += LG) {
     __syncwarp();
     {
       const int d = dblk + li;
       const bool dv = pvalid && d < dhi;
       R depth = (R)0, cg = (R)0;
-      int m0 = -1, m1 = -1, m2 = -1;
+      int m0 = nm0, m1 = nm1, m2 = nm2;
+      const R cg_raw = ncg;
+      request(d + LG);
       bool live = false;
       if (dv) {
-        const long long vox = pix * D + d;
         depth = xadd(base, offs[d]);
         if (RMIN) {
-          m0 = __ldg(a.mask + vox * 3); m1 = __ldg(a.mask + vox * 3 + 1); m2 = __ldg(a.mask + vox * 3 + 2);
           live = m0 >= 0 && m0 < N && m1 >= 0 && m1 < groups && m2 >= 0 && m2 < groups;   // :541
-          if (live) cg = static_cast<const R*>(a.cost_grad)[vox];
+          if (live) cg = cg_raw;
         } else {
-          m0 = __ldg(a.mask + vox);
           live = m0 > 0;                                                                  // :393
-          if (live) cg = static_cast<const R*>(a.cost_grad)[vox] / (R)m0;                 // :426
+          if (live) cg = cg_raw / (R)m0;                                                  // :426
         }
+      } else {
+        m0 = m1 = m2 = -1;
       }
       for (int n = 0; n < N; ++n) {
         RecB3<R> r;
