@@ -36,6 +36,14 @@ KERNEL_SOURCES = ("cv_packed.cuh", "cv_tuned.cuh", "cv_project.cuh", "chop_commo
 CONV_SOURCES = ("sc_umma.cu", "sc_common.cuh", "sc_abi.cu")
 
 
+def cost_volume_config(workload, shard, B, N, C, H, W, D):
+    """`config` of a CostVolume line; the CUDA arm and the reference arm print the same dictionary."""
+    return {"workload": "%s: CostVolume fwd+bwd fp32, B=%d per GPU, V=%d, C=%d, %dx%d, D=%d, MEAN" %
+                        (workload, B, N + 1, C, H, W, D),
+            "shard": shard,
+            "l2": "inputs_exceed_l2 (cost and cost_grad are %d MB each, L2 is 126 MB)" % (B * H * W * D * C * 4 // 2**20)}
+
+
 def kernel_source_digest(names=KERNEL_SOURCES):
     """sha1 over the kernel sources a workload compiles from: ties a recorded ncu figure to the code it was taken on."""
     import hashlib
@@ -427,10 +435,7 @@ def gpu_main(args):
                "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
                "scaling": "weak" if args.shard == "batch" else "strong", "vs_baseline": None, "dtype": "f32",
                "data": "synthetic",
-               "config": {"workload": "%s: CostVolume fwd+bwd fp32, B=%d per GPU, V=%d, C=%d, %dx%d, D=%d, MEAN" %
-                                      (args.workload, B, N + 1, C, H, W, D),
-                          "shard": args.shard, "l2": "inputs_exceed_l2 (cost and cost_grad are %d MB each, L2 is 126 MB)" %
-                                                     (B * H * W * D * C * 4 // 2**20)},
+               "config": cost_volume_config(args.workload, args.shard, B, N, C, H, W, D),
                "clocks": sampler.summary(t_wall0, t_wall1), "e2e": e2e,
                # per step: the forward kernel, one zero-fill kernel over the three gradient outputs, the gradient kernel
                "gpu_launches": LAUNCHES_PER_STEP * K,
@@ -891,10 +896,11 @@ def reference_main(args):
     out = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": world, "steps": K,
            "warmup": args.warmup, "ms_per_step": info["ms_per_step"], "higher_is_better": True, "scaling": "weak",
            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-           "config": {"workload": "%s: CostVolume fwd+bwd fp32, V=%d, C=%d, %dx%d, D=%d, MEAN" %
-                                  (args.workload, dims["N"] + 1, dims["C"], dims["H"], dims["W"], dims["D"]),
-                      "note": "the reference registers GPU kernels only; this is its kernel source compiled for the "
-                              "host and swept over all host threads"},
+           # the same dictionary as the CUDA arm prints for this workload: both arms describe one configuration
+           "config": cost_volume_config(args.workload, args.shard, dims.get("B", 1), dims["N"], dims["C"], dims["H"],
+                                        dims["W"], dims["D"]),
+           "note": "the reference registers GPU kernels only; this is its kernel source compiled for the host and "
+                   "swept over all host threads",
            "cpu_baseline": {"value": v, "unit": UNIT, "cores": info["cores"], "kind": info["kind"],
                             "sample": info["sample"]},
            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
