@@ -166,3 +166,25 @@ def test_decode_pfm_rejects_a_header_whose_size_product_overflows(w, h):
                                         image, cap, msg, 256)
         assert st == _lib.ERR_FORMAT and b"not enough data" in msg.value
 
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", [(1, 2, 6, 9, 32, 20, np.float32), (1, 3, 5, 7, 64, 5, np.float64), (2, 1, 6, 5, 8, 9, np.float64),
+                                   (1, 6, 5, 6, 32, 11, np.float32)])
+def test_feature_aggregate_gradient_with_staged_upstream(case):
+    """Channel counts where every lane carries a 16-byte slice: the gradient kernel copies the upstream tensor into
+    shared memory a block of planes ahead (cp.async).  Ragged last blocks, one to six views, float32 and float64
+    (three views of 64 double channels: the staging area starts at a rounded-up offset)."""
+    B, N, H, W, C, D, dt = case
+    c = fa_case(120 + C + N, B, N, H, W, C, D, "random", dt, src_hw=(H + 2, W + 1))
+    want, mask = oracle.feature_aggregate_fwd(c["src"], c["depth"], c["offsets"], c["Rs"], c["Ts"], True, dt)
+    g = np.random.default_rng(121).standard_normal(want.shape).astype(dt)
+    sg_w, bg_w = oracle.feature_aggregate_bwd(c["src"], c["depth"], c["offsets"], c["Rs"], c["Ts"], g, mask, True, dt)
+    a = (_t(c["src"]), _t(c["depth"]), _t(c["offsets"]), _t(c["Rs"]), _t(c["Ts"]))
+    got, m = ops.feature_aggregate_forward(*a)
+    sg, bg = ops.feature_aggregate_backward(*a, _t(g), m)
+    torch.cuda.synchronize()
+    assert helpers.bits_equal(m.cpu().numpy(), mask) and helpers.bits_equal(got.cpu().numpy(), want)
+    tol = 1e-4 if dt == np.float32 else 1e-10
+    assert helpers.rel_err(sg.cpu().numpy(), sg_w) <= tol
+    assert helpers.rel_err(bg.cpu().numpy(), bg_w) <= tol
