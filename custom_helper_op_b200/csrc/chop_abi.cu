@@ -17,6 +17,7 @@ namespace chop {
 extern std::atomic<int> g_use_umma;
 extern std::atomic<int> g_use_tile;
 void sc_umma_set_rows(int on);
+extern std::atomic<int> g_fa_stage;
 int sc_umma_note_timeout_for_test(int on);
 }
 
@@ -515,6 +516,7 @@ int chop_set_tuning(const char* name, int value) {
   if (!std::strcmp(name, "umma")) { chop::g_use_umma = value; return CHOP_OK; }
   if (!std::strcmp(name, "umma_rows")) { chop::sc_umma_set_rows(value); return CHOP_OK; }
   if (!std::strcmp(name, "tile")) { chop::g_use_tile = value; return CHOP_OK; }
+  if (!std::strcmp(name, "fa_stage")) { chop::g_fa_stage = value; return CHOP_OK; }
   if (!std::strcmp(name, "note_timeout")) return chop::sc_umma_note_timeout_for_test(value);
   return CHOP_ERR_ATTR;
 }

@@ -12,11 +12,14 @@
 // with unfused operations in the reference's order, so the forward output is bit-identical to the reference
 // compiled without contraction.  The gradient keeps the corner sums of a footprint as bilinear moments and flushes
 // them with vector reductions when the footprint changes.
+#include <atomic>
+
 #include "cv_project.cuh"
 #include "fa_entry.h"
 #include "smem_grant.h"
 
 namespace chop {
+std::atomic<int> g_fa_stage{1};   // tuning knob "fa_stage": 0 = the gradient reads its upstream tensor plane by plane
 namespace {
 
 template <typename R>
@@ -24,12 +27,12 @@ struct alignas(8) RecGF {
   R gh, gw;
 };
 
-// `stage_planes` > 0 (gradient only): room for the upstream gradient of that many planes of every view, 16 bytes per
-// lane, plane and view.
+// `stage_planes` > 0 (gradient only): two buffers for the upstream gradient of that many planes of ONE view, 16 bytes
+// per lane and plane.
 template <typename R>
 size_t fa_smem_per_warp(int N, int G, bool bwd, int stage_planes = 0) {
   size_t bytes = (size_t)N * G * sizeof(Coef<R>) + (size_t)N * 32 * (sizeof(ProjF<R>) + (bwd ? sizeof(RecGF<R>) : 0));
-  if (stage_planes > 0) bytes = ((bytes + 15) & ~(size_t)15) + (size_t)N * stage_planes * 512;   // 16-byte aligned slices
+  if (stage_planes > 0) bytes = ((bytes + 15) & ~(size_t)15) + (size_t)2 * stage_planes * 512;   // 16-byte aligned slices
   return bytes;
 }
 
@@ -138,10 +141,11 @@ __device__ __forceinline__ void fa_flush(R* gp, size_t row, int C, R (&m)[4][CPL
   red_add<R, CPL>(gp + row + C, m[3]);
 }
 
-// STAGED (16-byte channel slices, every lane carries channels): the upstream gradient of a whole block of planes, all
-// views, is copied into shared memory with cp.async while the previous block is processed - each lane copies exactly
-// the 16-byte slices it will read itself.  The tensor is read once and nothing else hides its latency: with one plane
-// requested ahead per warp the kernel ran at what 24 warps x 512 bytes in flight give (2.1 TB/s at c1 shapes).
+// STAGED (16-byte channel slices, every lane carries channels): the upstream gradient of one view over a whole block
+// of planes is copied into one of two shared-memory buffers with cp.async while the previous (block, view) is
+// processed - each lane copies exactly the 16-byte slices it will read itself, so no barrier is involved.  The tensor is
+// read once and nothing else hides its latency: with one plane requested ahead per warp the kernel ran at what
+// 24 warps x 512 bytes in flight give (2.1 TB/s at c1 shapes).
 template <typename T, typename R, int CPL, bool STAGED>
 __global__ void __launch_bounds__(256) fa_bwd_kernel(const CvArgs a, const int warps, const size_t smem_per_warp) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -163,7 +167,7 @@ __global__ void __launch_bounds__(256) fa_bwd_kernel(const CvArgs a, const int w
   Coef<R>* coef = reinterpret_cast<Coef<R>*>(mine);
   ProjF<R>* rec = reinterpret_cast<ProjF<R>*>(coef + N * G);
   RecGF<R>* recg = reinterpret_cast<RecGF<R>*>(rec + N * 32);
-  // [view][plane of the block][lane] 16-byte slices (STAGED), behind the records at the next 16-byte boundary
+  // [buffer][plane of the block][lane] 16-byte slices (STAGED), behind the records at the next 16-byte boundary
   R* stage = reinterpret_cast<R*>(mine + (((size_t)(reinterpret_cast<unsigned char*>(recg + N * 32) - mine) + 15) & ~(size_t)15));
 
   stage_coefs<R>(a, coef, lane, G, pix0);
@@ -178,16 +182,16 @@ __global__ void __launch_bounds__(256) fa_bwd_kernel(const CvArgs a, const int w
   const size_t row = (size_t)a.Ws * C;
   R dsum = (R)0;
 
-  // the lane's slices of every (view, plane) of the block that starts at plane d0
-  auto request = [&](int d0) {
+  // the lane's slices of view n over the block of planes that starts at d0, into buffer `buf`
+  auto request = [&](int buf, int n, int d0) {
     if constexpr (STAGED) {
-      for (int n = 0; n < N; ++n)
-        for (int j = 0; j < LG && d0 + j < dhi; ++j)
-          fa_cp_async16(stage + ((size_t)(n * LG + j) * 32 + lane) * CPL, mg + ((pix * D + d0 + j) * N + n) * C + li * CPL);
+      for (int j = 0; j < LG && d0 + j < dhi; ++j)
+        fa_cp_async16(stage + ((size_t)(buf * LG + j) * 32 + lane) * CPL, mg + ((pix * D + d0 + j) * N + n) * C + li * CPL);
       asm volatile("cp.async.commit_group;" ::: "memory");
     }
   };
-  if (STAGED && pvalid) request(dlo);
+  int sbuf = 0;   // the buffer of the (block, view) processed next
+  if (STAGED && pvalid) request(0, 0, dlo);
   for (int dblk = dlo; dblk < dhi; dblk += LG) {
     __syncwarp();
     {
@@ -208,7 +212,6 @@ __global__ void __launch_bounds__(256) fa_bwd_kernel(const CvArgs a, const int w
     }
     __syncwarp();
     if (!lane_on || !pvalid) continue;
-    if constexpr (STAGED) asm volatile("cp.async.wait_group 0;" ::: "memory");   // own slices only: no warp barrier needed
 
     for (int n = 0; n < N; ++n) {
       const ProjF<R>* r = rec + n * 32 + g * LG;
@@ -221,11 +224,18 @@ __global__ void __launch_bounds__(256) fa_bwd_kernel(const CvArgs a, const int w
       const R* mgp = mg + ((pix * D + dblk) * N + n) * C + li * CPL;
       const size_t mstep = (size_t)N * C;
       R gnext[CPL];
-      if constexpr (!STAGED) load_stream<R, CPL>(mgp, gnext);
+      if constexpr (STAGED) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");   // this (block, view) has landed: own slices only
+        // the other buffer was read a view ago: fill it with the next view of this block, or the next block's first
+        if (n + 1 < N) request(sbuf ^ 1, n + 1, dblk);
+        else if (dblk + LG < dhi) request(sbuf ^ 1, 0, dblk + LG);
+      } else {
+        load_stream<R, CPL>(mgp, gnext);
+      }
       for (int j = 0; j < jn; ++j) {
         R gv[CPL];
         if constexpr (STAGED) {
-          const uint4 w = *reinterpret_cast<const uint4*>(stage + ((size_t)(n * LG + j) * 32 + lane) * CPL);
+          const uint4 w = *reinterpret_cast<const uint4*>(stage + ((size_t)(sbuf * LG + j) * 32 + lane) * CPL);
           *reinterpret_cast<uint4*>(gv) = w;
         } else {
 #pragma unroll
@@ -267,8 +277,8 @@ __global__ void __launch_bounds__(256) fa_bwd_kernel(const CvArgs a, const int w
         dsum = xfma(q.gh, xfma(rc.dw, P, Q), xfma(q.gw, xfma(rc.dh, P, S), dsum));   // :312
       }
       if (cur >= 0) fa_flush<R, CPL>(sg_lane + (size_t)cur * C, row, C, m);
+      sbuf ^= 1;
     }
-    if (STAGED && dblk + LG < dhi) request(dblk + LG);   // this lane is done with its slots
   }
   if constexpr (STAGED) asm volatile("cp.async.wait_group 0;" ::: "memory");
   for (int o = LG >> 1; o > 0; o >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, o);
@@ -278,13 +288,11 @@ __global__ void __launch_bounds__(256) fa_bwd_kernel(const CvArgs a, const int w
 template <typename T, typename R, int CPL, bool BWD>
 int launch(const CvArgs& a, cudaStream_t st) {
   const int LG = 1 << a.lg_log2, G = 32 / LG;
-  // the gradient stages the upstream tensor when a lane's slice is 16 bytes, every lane carries channels, and at
-  // least four warps of staging buffers fit beside the records
-  bool staged = BWD && CPL * sizeof(R) == 16 && LG * CPL == a.C;
-  if (staged && fa_smem_per_warp<R>(a.N, G, true, LG) * 4 > 200 * 1024) staged = false;
+  // the gradient stages the upstream tensor when a lane's slice is 16 bytes and every lane carries channels
+  const bool staged = BWD && g_fa_stage.load() != 0 && CPL * sizeof(R) == 16 && LG * CPL == a.C;
   const size_t spw = fa_smem_per_warp<R>(a.N, G, BWD, staged ? LG : 0);
   int warps = 8;
-  while (warps > 1 && spw * warps > (staged ? 72 : 200) * 1024) warps >>= 1;   // staged: three CTAs per SM
+  while (warps > 1 && spw * warps > (staged ? 56 : 200) * 1024) warps >>= 1;   // staged: four CTAs per SM
   if (spw * warps > 200 * 1024) return -4;  // CHOP_ERR_UNSUPPORTED
   const size_t smem = spw * warps;
   const long long items = (long long)a.npb * a.nchunks;

@@ -267,7 +267,8 @@ CHOP_API int chop_version(void);
  * where supported, 0 = always the generic kernels), "umma_rows" (1 = the stride-1 tensor-core forward / image
  * gradient stages one copy per neighbour pixel, 0 = one per tap), "tile" (1 = register-tiled float32 manifold
  * convolution kernels where supported, 0 = the one-thread-per-element kernels), "packed" (1 = the packed-pair CostVolume
- * MEAN kernels where one exists, 0 = the previous compile-time-C kernels), "note_timeout" (1 = launch a one-thread
+ * MEAN kernels where one exists, 0 = the previous compile-time-C kernels), "fa_stage" (1 = FeatureAggregateGrad copies
+ * its upstream tensor into shared memory a block of planes ahead where the channel count allows, 0 = never), "note_timeout" (1 = launch a one-thread
  * kernel that performs the bookkeeping of an abandoned tensor-core wait, without any wait; 0 = clear the counter of
  * the current device and its host mirror).  Returns CHOP_ERR_ATTR for an unknown name.
  * Process-wide, hence a facility for tests and benchmarks only: every call returns CHOP_ERR_UNSUPPORTED unless the

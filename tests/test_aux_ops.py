@@ -173,18 +173,24 @@ def test_decode_pfm_rejects_a_header_whose_size_product_overflows(w, h):
                                    (1, 6, 5, 6, 32, 11, np.float32)])
 def test_feature_aggregate_gradient_with_staged_upstream(case):
     """Channel counts where every lane carries a 16-byte slice: the gradient kernel copies the upstream tensor into
-    shared memory a block of planes ahead (cp.async).  Ragged last blocks, one to six views, float32 and float64
-    (three views of 64 double channels: the staging area starts at a rounded-up offset)."""
+    shared memory one (block of planes, view) ahead (cp.async, two buffers).  Ragged last blocks, one to six views,
+    float32 and float64 (three views of 64 double channels: the staging area starts at a rounded-up offset)."""
     B, N, H, W, C, D, dt = case
     c = fa_case(120 + C + N, B, N, H, W, C, D, "random", dt, src_hw=(H + 2, W + 1))
     want, mask = oracle.feature_aggregate_fwd(c["src"], c["depth"], c["offsets"], c["Rs"], c["Ts"], True, dt)
     g = np.random.default_rng(121).standard_normal(want.shape).astype(dt)
     sg_w, bg_w = oracle.feature_aggregate_bwd(c["src"], c["depth"], c["offsets"], c["Rs"], c["Ts"], g, mask, True, dt)
     a = (_t(c["src"]), _t(c["depth"]), _t(c["offsets"]), _t(c["Rs"]), _t(c["Ts"]))
+    from custom_helper_op_b200 import _lib
     got, m = ops.feature_aggregate_forward(*a)
-    sg, bg = ops.feature_aggregate_backward(*a, _t(g), m)
-    torch.cuda.synchronize()
     assert helpers.bits_equal(m.cpu().numpy(), mask) and helpers.bits_equal(got.cpu().numpy(), want)
     tol = 1e-4 if dt == np.float32 else 1e-10
-    assert helpers.rel_err(sg.cpu().numpy(), sg_w) <= tol
-    assert helpers.rel_err(bg.cpu().numpy(), bg_w) <= tol
+    for stage in (1, 0):   # the staged kernel, then the same shapes read plane by plane (knob "fa_stage")
+        try:
+            _lib.set_tuning("fa_stage", stage)
+            sg, bg = ops.feature_aggregate_backward(*a, _t(g), m)
+            torch.cuda.synchronize()
+        finally:
+            _lib.set_tuning("fa_stage", 1)
+        assert helpers.rel_err(sg.cpu().numpy(), sg_w) <= tol
+        assert helpers.rel_err(bg.cpu().numpy(), bg_w) <= tol
