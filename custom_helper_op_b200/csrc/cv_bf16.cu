@@ -5,6 +5,16 @@
 
 namespace chop {
 int cv_fwd_bf16(const CvArgs& a, const CvPlan& p, cudaStream_t st) {
+  if (p.use_tuned && p.use_packed && p.kind == 3 && p.mode == 0 && p.cpl == 4) {
+    int r = -4;
+    switch (a.C) {
+      case 8: r = fwd_agg_packed_go<__nv_bfloat16, 8>(a, st); break;
+      case 16: r = fwd_agg_packed_go<__nv_bfloat16, 16>(a, st); break;
+      case 32: r = fwd_agg_packed_go<__nv_bfloat16, 32>(a, st); break;
+      default: break;
+    }
+    if (r != -4) return r;
+  }
   if (p.use_tuned && p.kind == 3 && p.mode == 0 && p.cpl == 4) {
     switch (a.C) {
       case 8: return fwd_tuned_go<__nv_bfloat16, 8, 4, true>(a, st);

@@ -180,7 +180,7 @@ inline int bwd2_tuned_go(const CvArgs& a, cudaStream_t st) {
 }
 
 // ---- packed-pair kernels (cv_packed.cuh) ----------------------------------------------------------------
-template <typename T, int C, int NV>
+template <typename T, int C, int NV, bool AGG = false>
 inline int fwd_pm_go(const CvArgs& a, cudaStream_t st);
 
 template <typename T, int C>
@@ -200,9 +200,9 @@ inline int fwd_packed_go(const CvArgs& a, cudaStream_t st) {
   return (int)cudaGetLastError();
 }
 
-template <typename T, int C, int NV>
+template <typename T, int C, int NV, bool AGG>
 inline int fwd_pm_go(const CvArgs& a, cudaStream_t st) {
-  auto k = cv_fwd_pm<T, C, NV>;
+  auto k = cv_fwd_pm<T, C, NV, AGG>;
   const size_t spw = pm_fwd_smem_per_warp(NV);
   const int warps = CHOP_PM_FWD_WARPS;
   const size_t smem = spw * warps;
@@ -210,6 +210,16 @@ inline int fwd_pm_go(const CvArgs& a, cudaStream_t st) {
   const long long items = (long long)a.npb * a.nchunks;
   k<<<(unsigned)((items + warps - 1) / warps), warps * 32, smem, st>>>(a, warps, spw);
   return (int)cudaGetLastError();
+}
+
+// CostAggregate MEAN with one or two source views on the plane-major packed kernel; -4: no such kernel
+template <typename T, int C>
+inline int fwd_agg_packed_go(const CvArgs& a, cudaStream_t st) {
+#ifndef CHOP_NO_PM
+  if (a.N == 1) return fwd_pm_go<T, C, 1, true>(a, st);
+  if (a.N == 2) return fwd_pm_go<T, C, 2, true>(a, st);
+#endif
+  return -4;
 }
 
 // C in {8,16,32}, channels per group in {1,2,4}; returns -4 if there is no such kernel

@@ -335,7 +335,11 @@ __host__ __device__ inline size_t pm_fwd_smem_per_warp(int NV) {
 #define CHOP_PM_FWD_BLOCKS 5
 #endif
 
-template <typename T, int C, int NV>
+// AGG = true is CostAggregate MEAN (cost_aggregate_kernels_gpu.cu.cc:34-127): the voxel's cost is the sum of the C
+// squared differences divided by views*C.  A lane keeps the sum over its four channels per plane of the block; after
+// the block the LG lanes of a pixel reduce-scatter those partials (lane li ends up with plane li) and store one float
+// each - LG consecutive floats per pixel.
+template <typename T, int C, int NV, bool AGG = false>
 __global__ void __launch_bounds__(32 * CHOP_PM_FWD_WARPS, CHOP_PM_FWD_BLOCKS) cv_fwd_pm(const CvArgs a, const int warps, const size_t smem_per_warp) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int LG = C / 4;
@@ -397,7 +401,8 @@ __global__ void __launch_bounds__(32 * CHOP_PM_FWD_WARPS, CHOP_PM_FWD_BLOCKS) cv
   const float* offs = static_cast<const float*>(a.offsets) + (long long)b * D;
   const long long dx_bytes = (long long)C * (long long)sizeof(T);
   const long long dy_bytes = (long long)a.Ws * dx_bytes;
-  float* out = static_cast<float*>(a.cost) + (pix * D + dlo) * C + li * 4;
+  float* out = AGG ? static_cast<float*>(a.cost) + pix * D + dlo + li   // one value per voxel, lane li stores plane li
+                   : static_cast<float*>(a.cost) + (pix * D + dlo) * C + li * 4;
   const ulonglong2* rec_mine = reinterpret_cast<const ulonglong2*>(rec) + g * LG;
   const int* tex_mine = tex + g * LG;
   const pk2 half2 = pk_make(0.5f, 0.5f);
@@ -410,7 +415,7 @@ __global__ void __launch_bounds__(32 * CHOP_PM_FWD_WARPS, CHOP_PM_FWD_BLOCKS) cv
     carry[n] = -1;
   }
 
-  for (int dblk = dlo; dblk < dhi; dblk += LG, out += LG * C) {
+  for (int dblk = dlo; dblk < dhi; dblk += LG, out += AGG ? LG : LG * C) {
     // ---- phase A: lane (g, li) projects plane dblk+li of pixel g into every view ---------------------
     {
       const int d = dblk + li;
@@ -443,6 +448,9 @@ __global__ void __launch_bounds__(32 * CHOP_PM_FWD_WARPS, CHOP_PM_FWD_BLOCKS) cv
     __syncwarp();
 
     // ---- phase B ---------------------------------------------------------------------------------------
+    float part[AGG ? LG : 1];   // AGG: the lane's channel sum per plane of the block
+#pragma unroll
+    for (int j = 0; j < (AGG ? LG : 1); ++j) part[j] = 0.0f;
     if (pvalid) {
       unsigned m[NV], many = 0u;
 #pragma unroll
@@ -491,8 +499,28 @@ __global__ void __launch_bounds__(32 * CHOP_PM_FWD_WARPS, CHOP_PM_FWD_BLOCKS) cv
           acc0 = pk_mul(acc0, half2);
           acc1 = pk_mul(acc1, half2);
         }
-        if (j < left) pk_store_stream(out + j * C, acc0, acc1);
+        if constexpr (AGG) {
+          float s0, s1;
+          pk_split(pk_add(acc0, acc1), s0, s1);
+          part[j] = s0 + s1;
+        } else {
+          if (j < left) pk_store_stream(out + j * C, acc0, acc1);
+        }
       }
+    }
+    if constexpr (AGG) {
+      // reduce-scatter over the pixel's LG lanes: lane li keeps plane li
+#pragma unroll
+      for (int sft = LG / 2; sft >= 1; sft >>= 1) {
+#pragma unroll
+        for (int i = 0; i < sft; ++i) {
+          const bool hi = (li & sft) != 0;
+          const float keep = hi ? part[i + sft] : part[i];
+          const float send = hi ? part[i] : part[i + sft];
+          part[i] = keep + __shfl_xor_sync(0xffffffffu, send, sft);
+        }
+      }
+      if (pvalid && dblk + li < dhi) __stcs(out, part[0] * (1.0f / (float)C));
     }
     __syncwarp();
   }

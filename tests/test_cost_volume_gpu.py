@@ -384,3 +384,40 @@ def test_packed_forward_kernels(N, C, bf16):
             _lib.set_tuning("packed", 1)
         assert torch.equal(mask_s, mask)
         assert float((cost_s - cost).abs().max()) <= 1e-5 * float(cost_s.abs().max())
+
+
+@pytest.mark.parametrize("N", [1, 2, 3])
+@pytest.mark.parametrize("C", [8, 16, 32])
+@pytest.mark.parametrize("bf16", [False, True])
+def test_packed_cost_aggregate_forward(N, C, bf16):
+    """CostAggregate MEAN on the plane-major packed kernel (one or two source views; three take the scalar kernel):
+    mask bit-exact, cost within the MEAN tolerances, depth-range calls that cut a block of planes, and the scalar
+    kernel on the same inputs (knob `packed`)."""
+    B, H, W, D = 2, 7, 9, 21
+    dev = "cuda:0"
+    for camera in ("rot_y", "identity", "random"):
+        c = helpers.make_case(1, 400 + 7 * N + C, B, N, H, W, C, D, camera, np.float32)
+        if bf16:
+            for k in ("ref", "src"):
+                c[k] = torch.from_numpy(c[k]).to(torch.bfloat16).float().numpy()
+        want = helpers.oracle_fwd_bwd(3, c, "MEAN", 1, True, np.float32)
+        t = {k: (None if v is None else torch.from_numpy(v).to(dev)) for k, v in c.items()}
+        if bf16:
+            t["ref"], t["src"] = t["ref"].to(torch.bfloat16), t["src"].to(torch.bfloat16)
+        a = (t["ref"], t["src"], t["depth"], t["offsets"], t["Rs"], t["Ts"])
+        cost, mask = ops.cost_forward(3, *a)
+        assert helpers.bits_equal(mask.cpu().numpy(), want["mask"])
+        assert helpers.rel_err(cost.cpu().numpy(), want["cost"]) <= 1e-5
+        assert helpers.elementwise_excess(cost.cpu().numpy(), want["cost"], 1e-5) <= 1.0
+        cost_r = torch.full_like(cost, -1.0)
+        mask_r = torch.full_like(mask, -7)
+        for d0, d1 in ((0, 5), (5, D)):
+            ops.cost_forward(3, *a, d_range=(d0, d1), out=(cost_r, mask_r))
+        assert torch.equal(cost_r, cost) and torch.equal(mask_r, mask)
+        try:
+            _lib.set_tuning("packed", 0)
+            cost_s, mask_s = ops.cost_forward(3, *a)
+        finally:
+            _lib.set_tuning("packed", 1)
+        assert torch.equal(mask_s, mask)
+        assert float((cost_s - cost).abs().max()) <= 1e-5 * float(cost_s.abs().max())
