@@ -130,10 +130,17 @@ void plan_chunks(CvArgs* a, int LG, int wanted_warps, int min_chunk, int forced)
     chunk = forced;
   } else {
     if (min_chunk < LG) min_chunk = LG;
-    int by_depth = (drange + min_chunk - 1) / min_chunk;
-    int by_warps = (wanted_warps + a->npb - 1) / a->npb;
-    int nchunks = by_depth < by_warps ? by_depth : by_warps;
-    if (nchunks < 1) nchunks = 1;
+    const int by_warps = (wanted_warps + a->npb - 1) / a->npb;
+    int nchunks;
+    for (;;) {
+      const int by_depth = (drange + min_chunk - 1) / min_chunk;
+      nchunks = by_depth < by_warps ? by_depth : by_warps;
+      if (nchunks < 1) nchunks = 1;
+      // a small problem (fewer than eight warps per SM): shorter chunks, down to one block of planes, so that the
+      // kernel is not one long serial walk per warp on a mostly idle GPU
+      if ((long long)a->npb * nchunks >= 148 * 8 || min_chunk <= LG) break;
+      min_chunk = min_chunk / 2 > LG ? min_chunk / 2 : LG;
+    }
     chunk = (drange + nchunks - 1) / nchunks;
   }
   chunk = (chunk + LG - 1) / LG * LG;
