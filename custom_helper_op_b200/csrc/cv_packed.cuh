@@ -326,7 +326,7 @@ __host__ __device__ inline size_t pm_fwd_smem_per_warp(int NV) {
   return (size_t)NV * 32 * 16 + (size_t)NV * 32 * 4 + 16;
 }
 
-// five 128-thread CTAs per SM (96 registers, nothing spilled) measured fastest at c1: 120 us; six (80 registers,
+// five 128-thread CTAs per SM (96 registers, 12 bytes of spill) measured fastest at c1: 120 us; six (80 registers,
 // 72 bytes spilled) 124 us; three 256-thread CTAs 126 us; seven and more spill heavily (130 us and up)
 #ifndef CHOP_PM_FWD_WARPS
 #define CHOP_PM_FWD_WARPS 4
