@@ -37,7 +37,13 @@ def _prep(ref_image, src_images, depth, offsets, Rs, Ts, kind):
     _require(ref_image.dtype in _DT, "dtype must be float32, float64 or bfloat16")
     real = torch.float32 if ref_image.dtype == torch.bfloat16 else ref_image.dtype
     dev = ref_image.device
-    cv = lambda t, dt: torch.as_tensor(t, device=dev).to(dt).contiguous()
+
+    def cv(t, dt):
+        # the common case costs no torch dispatch: already a contiguous tensor of the right type on the right device
+        if torch.is_tensor(t) and t.dtype == dt and t.device == dev and t.is_contiguous():
+            return t
+        return torch.as_tensor(t, device=dev).to(dt).contiguous()
+
     ref_image = ref_image.contiguous()
     src_images = cv(src_images, ref_image.dtype)
     depth = cv(depth, real)
