@@ -146,12 +146,15 @@ __device__ __forceinline__ void fa_flush(R* gp, size_t row, int C, R (&m)[4][CPL
 // processed - each lane copies exactly the 16-byte slices it will read itself, so no barrier is involved.  The tensor is
 // read once and nothing else hides its latency: with one plane requested ahead per warp the kernel ran at what
 // 24 warps x 512 bytes in flight give (2.1 TB/s at c1 shapes).
-template <typename T, typename R, int CPL, bool STAGED>
+// LGC > 0 (STAGED only): the lanes per pixel - hence the channel count LGC*CPL and the planes per block - are
+// compile-time constants; the plane loops unroll and the index arithmetic folds (a third of the generic kernel's
+// instructions were integer address and loop work).  LGC = 0 keeps them run-time values.
+template <typename T, typename R, int CPL, bool STAGED, int LGC = 0>
 __global__ void __launch_bounds__(256) fa_bwd_kernel(const CvArgs a, const int warps, const size_t smem_per_warp) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int LG = 1 << a.lg_log2, G = 32 / LG;
+  const int LG = LGC > 0 ? LGC : 1 << a.lg_log2, G = 32 / LG;
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-  const int li = lane & (LG - 1), g = lane >> a.lg_log2;
+  const int li = lane & (LG - 1), g = LGC > 0 ? lane / LGC : lane >> a.lg_log2;
   const long long item = (long long)blockIdx.x * warps + wib;
   if (item >= (long long)a.npb * a.nchunks) return;
   const int chunk_id = (int)(item / a.npb);
@@ -160,7 +163,7 @@ __global__ void __launch_bounds__(256) fa_bwd_kernel(const CvArgs a, const int w
   const bool pvalid = pix0 + g < a.npix;
   const long long pix = pvalid ? pix0 + g : a.npix - 1;
   const int dlo = a.d_begin + chunk_id * a.chunk, dhi = min(a.d_end, dlo + a.chunk);
-  const int N = a.N, D = a.D, C = a.C;
+  const int N = a.N, D = a.D, C = LGC > 0 ? LGC * CPL : a.C;
   const bool lane_on = li * CPL < C;
 
   unsigned char* mine = smem_raw + (size_t)wib * smem_per_warp;
@@ -185,6 +188,12 @@ __global__ void __launch_bounds__(256) fa_bwd_kernel(const CvArgs a, const int w
   // the lane's slices of view n over the block of planes that starts at d0, into buffer `buf`
   auto request = [&](int buf, int n, int d0) {
     if constexpr (STAGED) {
+      if constexpr (LGC > 0) {
+#pragma unroll
+        for (int j = 0; j < LGC; ++j)
+          if (d0 + j < dhi)
+            fa_cp_async16(stage + ((size_t)(buf * LG + j) * 32 + lane) * CPL, mg + ((pix * D + d0 + j) * N + n) * C + li * CPL);
+      } else
       for (int j = 0; j < LG && d0 + j < dhi; ++j)
         fa_cp_async16(stage + ((size_t)(buf * LG + j) * 32 + lane) * CPL, mg + ((pix * D + d0 + j) * N + n) * C + li * CPL);
       asm volatile("cp.async.commit_group;" ::: "memory");
@@ -232,7 +241,9 @@ __global__ void __launch_bounds__(256) fa_bwd_kernel(const CvArgs a, const int w
       } else {
         load_stream<R, CPL>(mgp, gnext);
       }
-      for (int j = 0; j < jn; ++j) {
+#pragma unroll
+      for (int j = 0; j < (LGC > 0 ? LGC : jn); ++j) {
+        if (LGC > 0 && j >= jn) break;
         R gv[CPL];
         if constexpr (STAGED) {
           const uint4 w = *reinterpret_cast<const uint4*>(stage + ((size_t)(sbuf * LG + j) * 32 + lane) * CPL);
@@ -302,7 +313,15 @@ int launch(const CvArgs& a, cudaStream_t st) {
   if constexpr (!BWD) {
     k = fa_fwd_kernel<T, R, CPL>;
   } else if constexpr (CPL * sizeof(R) == 16) {
-    k = staged ? fa_bwd_kernel<T, R, CPL, true> : fa_bwd_kernel<T, R, CPL, false>;
+    k = fa_bwd_kernel<T, R, CPL, false>;
+    if (staged) {
+      switch (LG) {   // 8 / 16 / 32 float channels (4 / 8 / 16 doubles): compile-time loops; 16 lanes and more ran faster without
+        case 2: k = fa_bwd_kernel<T, R, CPL, true, 2>; break;
+        case 4: k = fa_bwd_kernel<T, R, CPL, true, 4>; break;
+        case 8: k = fa_bwd_kernel<T, R, CPL, true, 8>; break;
+        default: k = fa_bwd_kernel<T, R, CPL, true>; break;
+      }
+    }
   } else {
     k = fa_bwd_kernel<T, R, CPL, false>;
   }
