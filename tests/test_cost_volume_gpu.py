@@ -421,3 +421,29 @@ def test_packed_cost_aggregate_forward(N, C, bf16):
             _lib.set_tuning("packed", 1)
         assert torch.equal(mask_s, mask)
         assert float((cost_s - cost).abs().max()) <= 1e-5 * float(cost_s.abs().max())
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_small_configurations(seed):
+    """Seeded random draws over the dispatch boundaries: channel counts with and without a compile-time kernel, one
+    to five source views (plane-major / view-major packed forward, generic kernels), depth counts around the planes
+    per block and the chunk lengths the host picks for small problems, odd image sizes, every kind and reduction,
+    default and strict arithmetic."""
+    rng = np.random.default_rng(9000 + seed)
+    kind = int(rng.choice([1, 1, 2, 3]))
+    C = int(rng.choice([3, 4, 6, 8, 8, 12, 16, 16, 20, 32, 32, 40, 64]))
+    groups = 1
+    if kind == 2:
+        divs = [g for g in (1, 2, 4, 8, 16, 32) if C % g == 0]
+        groups = int(rng.choice(divs))
+    N = int(rng.integers(1, 6))
+    B = int(rng.integers(1, 3))
+    H, W = int(rng.integers(3, 14)), int(rng.integers(3, 20))
+    D = int(rng.choice([1, 2, 3, 5, 8, 9, 16, 17, 31, 32, 33, 48, 50]))
+    reduce = str(rng.choice(["MEAN", "MIN"]))
+    camera = str(rng.choice(["identity", "shift", "rot_z", "rot_y", "random"]))
+    c = helpers.make_case(kind, 9100 + seed, B, N, H, W, C, D, camera, np.float32)
+    want = helpers.oracle_fwd_bwd(kind, c, reduce, groups, True, np.float32)
+    for strict in (False, True):
+        got = run_gpu(kind, c, reduce, groups, True, want["cost_grad"], strict=strict)
+        check(got, want, np.float32, exact_cost=strict or reduce == "MIN")
